@@ -1,0 +1,150 @@
+/*
+ * llaisys C ABI -- paged KV cache and the attention kernels that read it.
+ *
+ * NEW SURFACE. The reference has no KV cache: its self-attention operator takes whole
+ * contiguous K/V tensors (reference: src/ops/self_attention/op.hpp:6, README.md:244-266) and
+ * names a KV cache / KV-cache pool only as future work (reference: README.md:316, :412, :424).
+ * These entry points are what the reference's FFI would bind for that work. They follow the
+ * reference's conventions where it has any (C linkage, llaisys prefix, enums from llaisys.h,
+ * async on the calling thread's runtime stream, caller-allocated outputs) and differ in one:
+ * every function returns a status code and never throws across the ABI.
+ *
+ * Arithmetic contract of the attention calls is the reference's definition of self-attention
+ * (reference: test/ops/self_attention.py:11-28) applied to the K/V rows a sequence holds in the
+ * cache: gathering a sequence's pages to contiguous [len, nkvh, d] tensors and calling
+ * llaisysSelfAttention must give the same result within rounding.
+ *
+ * Memory layout of the pool (one allocation, made once at create):
+ *     pool[layer][page][2 (K=0, V=1)][nkvh][page_size][head_dim]      row-major, `dtype` elements
+ * so a (page, K-or-V, kv-head) tile is page_size*head_dim contiguous elements (4 KiB for bf16,
+ * page 16, d 128) and token `pos` of a sequence lives in slot  table[seq][pos / page_size] * page_size
+ * + pos % page_size.
+ *
+ * Pointer conventions: `*_dev` arguments and all bulk tensors (q, out, k_rows, ...) are addresses
+ * in the cache's device memory (host memory for a CPU cache); small index arrays WITHOUT the
+ * suffix are host arrays that the call validates and stages itself.
+ */
+#ifndef LLAISYS_PAGED_KV_H
+#define LLAISYS_PAGED_KV_H
+
+#include "../llaisys.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes -------------------------------------------------------------------- */
+#define LLAISYS_OK 0
+#define LLAISYS_E_INVALID 1     /* bad argument, shape, dtype or sequence state            */
+#define LLAISYS_E_NO_PAGES 2    /* the free list cannot cover the request (nothing changed) */
+#define LLAISYS_E_NO_SEQ 3      /* unknown / freed sequence id, or max_seqs reached         */
+#define LLAISYS_E_DEVICE 4      /* the device runtime reported an error                     */
+#define LLAISYS_E_UNSUPPORTED 5 /* no kernel for this dtype / shape on this device          */
+#define LLAISYS_E_KERNEL 6      /* a kernel flagged bad metadata instead of faulting        */
+
+/* Text of the calling thread's most recent non-OK status ("" if none). */
+LLAISYS_API const char *llaisysGetLastError(void);
+
+typedef struct LlaisysPagedKV *llaisysPagedKV_t;
+
+/* ---- lifetime ------------------------------------------------------------------------ */
+
+/* Allocates the page pool, block tables and split-KV scratch on (device_type, device_id).
+ * max_seqs bounds live sequences; max_pages_per_seq bounds one sequence's block table.
+ * dtype is F32, F16 or BF16. */
+LLAISYS_API int llaisysPagedKVCreate(llaisysPagedKV_t *kv_out, llaisysDeviceType_t device_type, int device_id,
+                                     llaisysDataType_t dtype, size_t nlayer, size_t num_pages, size_t page_size,
+                                     size_t nkvh, size_t head_dim, size_t max_seqs, size_t max_pages_per_seq);
+LLAISYS_API int llaisysPagedKVDestroy(llaisysPagedKV_t kv);
+
+/* ---- block manager (host only; no device work) ---------------------------------------- */
+
+/* New empty sequence; its id (0 <= id < max_seqs) is written to *seq_out. */
+LLAISYS_API int llaisysPagedKVSeqAdd(llaisysPagedKV_t kv, int32_t *seq_out);
+/* Grows the sequence's capacity to at least n_tokens by popping pages off the free list.
+ * All-or-nothing: on LLAISYS_E_NO_PAGES the sequence and the free list are unchanged. */
+LLAISYS_API int llaisysPagedKVSeqReserve(llaisysPagedKV_t kv, int32_t seq, size_t n_tokens);
+/* Appends the given physical pages (each must be free) to the sequence's block table. */
+LLAISYS_API int llaisysPagedKVSeqAssignPages(llaisysPagedKV_t kv, int32_t seq, const int32_t *pages, size_t n_pages);
+/* Returns every page of the sequence to the free list and retires the id. */
+LLAISYS_API int llaisysPagedKVSeqFree(llaisysPagedKV_t kv, int32_t seq);
+
+LLAISYS_API size_t llaisysPagedKVNumFreePages(llaisysPagedKV_t kv);
+LLAISYS_API size_t llaisysPagedKVNumSeqs(llaisysPagedKV_t kv);
+/* Pages held by a sequence, or -1 for an unknown id. */
+LLAISYS_API int64_t llaisysPagedKVSeqNumPages(llaisysPagedKV_t kv, int32_t seq);
+/* Copies up to `cap` block-table entries of the sequence into pages_out. */
+LLAISYS_API int llaisysPagedKVSeqPages(llaisysPagedKV_t kv, int32_t seq, int32_t *pages_out, size_t cap);
+
+/* ---- device-side views ----------------------------------------------------------------- */
+
+LLAISYS_API void *llaisysPagedKVPoolData(llaisysPagedKV_t kv, size_t layer); /* pool[layer]          */
+LLAISYS_API size_t llaisysPagedKVLayerBytes(llaisysPagedKV_t kv);
+/* int32 table[max_seqs][max_pages_per_seq] in device memory. Rows changed by the block manager
+ * reach the device at the next data-path call, or at llaisysPagedKVFlush. */
+LLAISYS_API const int32_t *llaisysPagedKVBlockTableData(llaisysPagedKV_t kv);
+LLAISYS_API int llaisysPagedKVFlush(llaisysPagedKV_t kv);
+/* Synchronises the cache's stream and reports LLAISYS_E_KERNEL if any kernel since the last
+ * check met an out-of-range page or position (the kernel skips such an access). */
+LLAISYS_API int llaisysPagedKVCheck(llaisysPagedKV_t kv);
+
+/* ---- data path, host index arrays ------------------------------------------------------ */
+
+/* Scatters n_rows new K/V rows into the pages: row i goes to token `positions[i]` of sequence
+ * `seq_ids[i]`. k_rows / v_rows are [n_rows, nkvh, head_dim]. Bit-exact copy. */
+LLAISYS_API int llaisysPagedKVAppend(llaisysPagedKV_t kv, size_t layer, const void *k_rows, const void *v_rows,
+                                     const int32_t *seq_ids, const int32_t *positions, size_t n_rows);
+/* Inverse of append for one sequence: tokens [0, n_tokens) -> k_out, v_out [n_tokens, nkvh, head_dim]. */
+LLAISYS_API int llaisysPagedKVGather(llaisysPagedKV_t kv, size_t layer, int32_t seq, size_t n_tokens, void *k_out,
+                                     void *v_out);
+
+/* One query token per sequence: out, q are [n_seqs, nh, head_dim]; sequence i attends to its first
+ * kv_lens[i] tokens (all visible: the single query is the newest token). */
+LLAISYS_API int llaisysPagedAttentionDecode(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
+                                            const int32_t *seq_ids, const int32_t *kv_lens, size_t n_seqs, size_t nh,
+                                            float scale);
+/* Ragged chunks: q, out are [sum(q_lens), nh, head_dim], sequences back to back. Query t of sequence i
+ * (0 <= t < q_lens[i]) sees keys j <= t + (kv_lens[i] - q_lens[i]); kv_lens counts the chunk itself,
+ * which the caller has already appended. */
+LLAISYS_API int llaisysPagedAttentionPrefill(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
+                                             const int32_t *seq_ids, const int32_t *q_lens, const int32_t *kv_lens,
+                                             size_t n_seqs, size_t nh, float scale);
+/* Decode that stops before normalising across devices: part is float [n_seqs, nh, head_dim + 2] holding,
+ * per (sequence, head), the locally normalised output o[0..d), then m = max scaled score and
+ * l = sum exp(score - m) over this cache's tokens (m = -inf, l = 0, o = 0 for kv_len 0). */
+LLAISYS_API int llaisysPagedAttentionDecodePartial(llaisysPagedKV_t kv, size_t layer, float *part, const void *q,
+                                                   const int32_t *seq_ids, const int32_t *kv_lens, size_t n_seqs,
+                                                   size_t nh, float scale);
+
+/* Log-sum-exp merge of n_parts partial results (each float [n_rows, head_dim + 2], packed back to back as
+ * an all-gather leaves them) into out [n_rows, head_dim] of `dtype`, on the calling thread's current
+ * runtime of `device_type`. */
+LLAISYS_API int llaisysLseMerge(llaisysDeviceType_t device_type, int device_id, void *out, llaisysDataType_t dtype,
+                                const float *parts, size_t n_parts, size_t n_rows, size_t head_dim);
+
+/* ---- data path, device-resident index arrays, explicit stream --------------------------- */
+/* No host validation, no staging copy, no synchronisation: safe to capture in a CUDA graph. The block
+ * table must be current (llaisysPagedKVFlush). Out-of-range metadata is skipped and flagged
+ * (llaisysPagedKVCheck). max_kv_len / max_q_len are upper bounds used to size the launch. */
+LLAISYS_API int llaisysPagedKVAppendDev(llaisysPagedKV_t kv, size_t layer, const void *k_rows, const void *v_rows,
+                                        const int32_t *seq_ids_dev, const int32_t *positions_dev, size_t n_rows,
+                                        llaisysStream_t stream);
+LLAISYS_API int llaisysPagedAttentionDecodeDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
+                                               const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
+                                               size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream);
+LLAISYS_API int llaisysPagedAttentionDecodePartialDev(llaisysPagedKV_t kv, size_t layer, float *part, const void *q,
+                                                      const int32_t *seq_ids_dev, const int32_t *kv_lens_dev,
+                                                      size_t n_seqs, size_t max_kv_len, size_t nh, float scale,
+                                                      llaisysStream_t stream);
+/* q_starts_dev is int32 [n_seqs + 1]: row offset of each sequence's chunk in q / out. */
+LLAISYS_API int llaisysPagedAttentionPrefillDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
+                                                const int32_t *seq_ids_dev, const int32_t *q_starts_dev,
+                                                const int32_t *kv_lens_dev, size_t n_seqs, size_t total_q,
+                                                size_t max_q_len, size_t max_kv_len, size_t nh, float scale,
+                                                llaisysStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* LLAISYS_PAGED_KV_H */

@@ -1,0 +1,18 @@
+"""llaisys_b200 -- B200-native implementation of the LLAISYS KV-cache / self-attention path.
+
+The public names are the reference frontend's (python/llaisys/__init__.py:1-20): RuntimeAPI, DeviceType,
+DataType, MemcpyKind, Stream, Tensor, Ops. `PagedKVCache`, `lse_merge` and `LlaisysError` are new: the
+reference has no KV cache. A program written against the reference package can switch with
+`import llaisys_b200 as llaisys`.
+"""
+from .libllaisys import DataType, DeviceType, MemcpyKind, Status
+from .libllaisys import llaisysStream_t as Stream
+from .runtime import RuntimeAPI, context_stream, set_context_runtime
+from .tensor import Tensor
+from .ops import Ops
+from .paged_kv import LlaisysError, PagedKVCache, lse_merge
+
+__all__ = [
+    "RuntimeAPI", "DeviceType", "DataType", "MemcpyKind", "Stream", "Tensor", "Ops",
+    "PagedKVCache", "lse_merge", "LlaisysError", "Status", "context_stream", "set_context_runtime",
+]

@@ -1,0 +1,228 @@
+// extern "C" thunks of the paged-KV API. Unlike the legacy ABI these never let an exception out: every
+// failure becomes a status code plus a thread-local message (llaisysGetLastError).
+#include "llaisys/paged_kv.h"
+
+#include "../cpu/cpu_kernels.hpp"
+#include "../kv/paged_kv.hpp"
+#ifdef ENABLE_NVIDIA_API
+#include "../kernels/kernels.hpp"
+#endif
+
+#include <string>
+
+struct LlaisysPagedKV {
+    llaisys::kv::PagedKV impl;
+    explicit LlaisysPagedKV(const llaisys::kv::PagedKVConfig &cfg) : impl(cfg) {}
+};
+
+namespace {
+
+thread_local std::string g_last_error;
+
+template <typename F>
+int guarded(F &&body) {
+    try {
+        body();
+        return LLAISYS_OK;
+    } catch (const llaisys::kv::StatusError &e) {
+        g_last_error = e.what();
+        return e.code;
+    } catch (const std::invalid_argument &e) {
+        g_last_error = e.what();
+        return LLAISYS_E_INVALID;
+    } catch (const std::bad_alloc &) {
+        g_last_error = "out of host memory";
+        return LLAISYS_E_DEVICE;
+    } catch (const std::exception &e) {
+        g_last_error = e.what();
+        return LLAISYS_E_DEVICE;
+    } catch (...) {
+        g_last_error = "unknown error";
+        return LLAISYS_E_DEVICE;
+    }
+}
+
+int null_handle() {
+    g_last_error = "paged KV: null cache handle";
+    return LLAISYS_E_INVALID;
+}
+
+} // namespace
+
+#define KV_OR_FAIL(kv)        \
+    if ((kv) == nullptr) {    \
+        return null_handle(); \
+    }
+
+extern "C" {
+
+const char *llaisysGetLastError(void) { return g_last_error.c_str(); }
+
+int llaisysPagedKVCreate(llaisysPagedKV_t *kv_out, llaisysDeviceType_t device_type, int device_id,
+                         llaisysDataType_t dtype, size_t nlayer, size_t num_pages, size_t page_size, size_t nkvh,
+                         size_t head_dim, size_t max_seqs, size_t max_pages_per_seq) {
+    return guarded([&] {
+        if (kv_out == nullptr) {
+            throw llaisys::kv::StatusError(LLAISYS_E_INVALID, "paged KV: kv_out is null");
+        }
+        *kv_out = nullptr;
+        llaisys::kv::PagedKVConfig cfg;
+        cfg.device_type = device_type;
+        cfg.device_id = device_id;
+        cfg.dtype = dtype;
+        cfg.nlayer = nlayer;
+        cfg.num_pages = num_pages;
+        cfg.page_size = page_size;
+        cfg.nkvh = nkvh;
+        cfg.head_dim = head_dim;
+        cfg.max_seqs = max_seqs;
+        cfg.max_pages_per_seq = max_pages_per_seq;
+        *kv_out = new LlaisysPagedKV(cfg);
+    });
+}
+
+int llaisysPagedKVDestroy(llaisysPagedKV_t kv) {
+    return guarded([&] { delete kv; });
+}
+
+int llaisysPagedKVSeqAdd(llaisysPagedKV_t kv, int32_t *seq_out) {
+    KV_OR_FAIL(kv);
+    return guarded([&] {
+        if (seq_out == nullptr) {
+            throw llaisys::kv::StatusError(LLAISYS_E_INVALID, "paged KV: seq_out is null");
+        }
+        *seq_out = kv->impl.seqAdd();
+    });
+}
+int llaisysPagedKVSeqReserve(llaisysPagedKV_t kv, int32_t seq, size_t n_tokens) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.seqReserve(seq, n_tokens); });
+}
+int llaisysPagedKVSeqAssignPages(llaisysPagedKV_t kv, int32_t seq, const int32_t *pages, size_t n_pages) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.seqAssignPages(seq, pages, n_pages); });
+}
+int llaisysPagedKVSeqFree(llaisysPagedKV_t kv, int32_t seq) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.seqFree(seq); });
+}
+size_t llaisysPagedKVNumFreePages(llaisysPagedKV_t kv) { return kv ? kv->impl.numFreePages() : 0; }
+size_t llaisysPagedKVNumSeqs(llaisysPagedKV_t kv) { return kv ? kv->impl.numSeqs() : 0; }
+int64_t llaisysPagedKVSeqNumPages(llaisysPagedKV_t kv, int32_t seq) { return kv ? kv->impl.seqNumPages(seq) : -1; }
+int llaisysPagedKVSeqPages(llaisysPagedKV_t kv, int32_t seq, int32_t *pages_out, size_t cap) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.seqPages(seq, pages_out, cap); });
+}
+
+void *llaisysPagedKVPoolData(llaisysPagedKV_t kv, size_t layer) {
+    void *p = nullptr;
+    if (kv != nullptr) {
+        guarded([&] { p = kv->impl.poolData(layer); });
+    }
+    return p;
+}
+size_t llaisysPagedKVLayerBytes(llaisysPagedKV_t kv) { return kv ? kv->impl.layerBytes() : 0; }
+const int32_t *llaisysPagedKVBlockTableData(llaisysPagedKV_t kv) { return kv ? kv->impl.blockTableData() : nullptr; }
+int llaisysPagedKVFlush(llaisysPagedKV_t kv) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.flush(); });
+}
+int llaisysPagedKVCheck(llaisysPagedKV_t kv) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.check(); });
+}
+
+int llaisysPagedKVAppend(llaisysPagedKV_t kv, size_t layer, const void *k_rows, const void *v_rows,
+                         const int32_t *seq_ids, const int32_t *positions, size_t n_rows) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.append(layer, k_rows, v_rows, seq_ids, positions, n_rows); });
+}
+int llaisysPagedKVGather(llaisysPagedKV_t kv, size_t layer, int32_t seq, size_t n_tokens, void *k_out, void *v_out) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.gather(layer, seq, n_tokens, k_out, v_out); });
+}
+int llaisysPagedAttentionDecode(llaisysPagedKV_t kv, size_t layer, void *out, const void *q, const int32_t *seq_ids,
+                                const int32_t *kv_lens, size_t n_seqs, size_t nh, float scale) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.decode(layer, out, nullptr, q, seq_ids, kv_lens, n_seqs, nh, scale); });
+}
+int llaisysPagedAttentionPrefill(llaisysPagedKV_t kv, size_t layer, void *out, const void *q, const int32_t *seq_ids,
+                                 const int32_t *q_lens, const int32_t *kv_lens, size_t n_seqs, size_t nh,
+                                 float scale) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.prefill(layer, out, q, seq_ids, q_lens, kv_lens, n_seqs, nh, scale); });
+}
+int llaisysPagedAttentionDecodePartial(llaisysPagedKV_t kv, size_t layer, float *part, const void *q,
+                                       const int32_t *seq_ids, const int32_t *kv_lens, size_t n_seqs, size_t nh,
+                                       float scale) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.decode(layer, nullptr, part, q, seq_ids, kv_lens, n_seqs, nh, scale); });
+}
+
+int llaisysLseMerge(llaisysDeviceType_t device_type, int device_id, void *out, llaisysDataType_t dtype,
+                    const float *parts, size_t n_parts, size_t n_rows, size_t head_dim) {
+    return guarded([&] {
+        using llaisys::kv::StatusError;
+        if (n_rows == 0 || head_dim == 0) {
+            return;
+        }
+        if (out == nullptr || parts == nullptr || n_parts == 0) {
+            throw StatusError(LLAISYS_E_INVALID, "lse merge: null argument or no parts");
+        }
+        if (n_parts > 65535 || n_rows > (size_t(1) << 30) || head_dim > 65535) {
+            throw StatusError(LLAISYS_E_INVALID, "lse merge: sizes out of range");
+        }
+        if (dtype != LLAISYS_DTYPE_F32 && dtype != LLAISYS_DTYPE_F16 && dtype != LLAISYS_DTYPE_BF16) {
+            throw StatusError(LLAISYS_E_INVALID, "lse merge: dtype must be F32, F16 or BF16");
+        }
+        if (device_type == LLAISYS_DEVICE_CPU) {
+            llaisys::cpu::lse_merge(dtype, out, parts, int32_t(n_parts), int32_t(n_rows), int32_t(head_dim));
+            return;
+        }
+#ifdef ENABLE_NVIDIA_API
+        if (device_type == LLAISYS_DEVICE_NVIDIA) {
+            auto &ctx = llaisys::core::context();
+            ctx.setDevice(device_type, device_id);
+            llaisys::kernels::lse_merge(ctx.runtime().stream(), dtype, out, parts, int32_t(n_parts), int32_t(n_rows),
+                                        int32_t(head_dim));
+            return;
+        }
+#endif
+        throw StatusError(LLAISYS_E_UNSUPPORTED, "lse merge: unsupported device");
+    });
+}
+
+int llaisysPagedKVAppendDev(llaisysPagedKV_t kv, size_t layer, const void *k_rows, const void *v_rows,
+                            const int32_t *seq_ids_dev, const int32_t *positions_dev, size_t n_rows,
+                            llaisysStream_t stream) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.appendDev(layer, k_rows, v_rows, seq_ids_dev, positions_dev, n_rows, stream); });
+}
+int llaisysPagedAttentionDecodeDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
+                                   const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
+                                   size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream) {
+    KV_OR_FAIL(kv);
+    return guarded([&] {
+        kv->impl.decodeDev(layer, out, nullptr, q, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale, stream);
+    });
+}
+int llaisysPagedAttentionDecodePartialDev(llaisysPagedKV_t kv, size_t layer, float *part, const void *q,
+                                          const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
+                                          size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream) {
+    KV_OR_FAIL(kv);
+    return guarded([&] {
+        kv->impl.decodeDev(layer, nullptr, part, q, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale, stream);
+    });
+}
+int llaisysPagedAttentionPrefillDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
+                                    const int32_t *seq_ids_dev, const int32_t *q_starts_dev,
+                                    const int32_t *kv_lens_dev, size_t n_seqs, size_t total_q, size_t max_q_len,
+                                    size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream) {
+    KV_OR_FAIL(kv);
+    return guarded([&] {
+        kv->impl.prefillDev(layer, out, q, seq_ids_dev, q_starts_dev, kv_lens_dev, n_seqs, total_q, max_q_len,
+                            max_kv_len, nh, scale, stream);
+    });
+}
+
+} // extern "C"

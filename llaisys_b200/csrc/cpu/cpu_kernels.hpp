@@ -1,0 +1,29 @@
+// Host implementations of the same operations, for tensors and caches that live on LLAISYS_DEVICE_CPU.
+// They are the library's CPU device backend (the reference keeps one beside every operator:
+// src/ops/add/op.cpp:16-19, src/ops/add/cpu/add_cpu.cpp:7-32), selected only by the device type of the
+// arguments -- never as a substitute for a missing or failing CUDA kernel.
+#pragma once
+
+#include "../kernels/args.hpp"
+
+namespace llaisys::cpu {
+
+void add(llaisysDataType_t dtype, void *c, const void *a, const void *b, size_t n);
+
+void rearrange(size_t elem_size, size_t ndim, const size_t *shape, const ptrdiff_t *dst_strides,
+               const ptrdiff_t *src_strides, void *dst, const void *src);
+
+// Returns the OR of the kErr* bits (kernels/device_utils.cuh uses the same values) for rows it had to skip.
+int paged_append(size_t elem_size, const kernels::KVView &kv, const void *k_rows, const void *v_rows,
+                 const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t max_blocks);
+int paged_gather(size_t elem_size, const kernels::KVView &kv, int32_t seq_row, int32_t n_tokens, void *k_out,
+                 void *v_out);
+
+// f32 accumulation, result rounded once to the tensor dtype ("compute in f32, store in T", the convention of
+// the reference's only CPU kernel). Parallel over (query row, head) with OpenMP when built with it.
+int attention(llaisysDataType_t dtype, const kernels::KVView &kv, const kernels::AttnBatch &batch, const void *q,
+              float scale, const kernels::AttnOut &out);
+
+void lse_merge(llaisysDataType_t dtype, void *out, const float *parts, int32_t n_parts, int32_t n_rows, int32_t d);
+
+} // namespace llaisys::cpu

@@ -1,0 +1,50 @@
+// Host-callable launchers of every CUDA kernel in the library. Each launcher queues work on `stream` and
+// returns; none allocates, synchronises or touches host copies of the data. Launchers that return int give
+// 0 when work was queued and a negative value when they have no kernel for the shape (the caller then picks
+// another launcher); launch failures throw.
+#pragma once
+
+#include "args.hpp"
+
+namespace llaisys::kernels {
+
+// Queues a memset of `bytes` zero bytes.
+void fill_zero(stream_t stream, void *ptr, size_t bytes);
+
+// c = a + b over n contiguous elements of F32 / F16 / BF16 (arithmetic in f32).
+void add(stream_t stream, llaisysDataType_t dtype, void *c, const void *a, const void *b, size_t n);
+
+// Strided copy dst[idx] = src[idx] for every index of `shape` (ndim <= 8), elements of elem_size bytes.
+void rearrange(stream_t stream, size_t elem_size, size_t ndim, const size_t *shape, const ptrdiff_t *dst_strides,
+               const ptrdiff_t *src_strides, void *dst, const void *src);
+
+// K1: row i of k_rows / v_rows [n_rows, nkvh, d] -> token positions[i] of the sequence in table row seq_ids[i].
+// 16-byte vector copies; a row whose block or page is out of range is skipped and flagged.
+void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const void *k_rows, const void *v_rows,
+                  const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t max_blocks,
+                  int32_t *error_flag);
+
+// K5: tokens [0, n_tokens) of table row seq_row -> k_out, v_out [n_tokens, nkvh, d].
+void paged_gather(stream_t stream, size_t elem_size, const KVView &kv, int32_t seq_row, int32_t n_tokens,
+                  void *k_out, void *v_out, int32_t *error_flag);
+
+// Any dtype, head_dim <= 256, any GQA ratio, any page size: one CTA per (query row, query head), online
+// softmax in f32. The correctness baseline for the specialised kernels and the kernel behind the legacy
+// operator for shapes they do not cover.
+void attention_generic(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
+                       const void *q, float scale, const AttnOut &out, int32_t *error_flag);
+
+// K2 (+ fused K3): split-KV flash decoding for 16-bit K/V, head_dim 128, page size 16, GQA group <= 8,
+// one query per sequence. Returns -1 if the shape is not covered.
+int attention_decode_split(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
+                           const void *q, float scale, const AttnOut &out, const AttnScratch &scratch);
+// Scratch the split-KV decode needs for a batch of n_seqs sequences of at most max_kv_len tokens.
+void attention_decode_split_scratch(int32_t n_seqs, int32_t nh, int32_t nkvh, int32_t d, int32_t max_kv_len,
+                                    size_t *partials_floats, size_t *counters_len);
+
+// K3: out[r, :] = sum_p w_p o_p[r, :] / sum_p w_p, w_p = l_p exp(m_p - max_p m_p), over n_parts partials laid out
+// float [n_parts][n_rows][d + 2].
+void lse_merge(stream_t stream, llaisysDataType_t dtype, void *out, const float *parts, int32_t n_parts,
+               int32_t n_rows, int32_t d);
+
+} // namespace llaisys::kernels

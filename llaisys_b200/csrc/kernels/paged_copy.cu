@@ -1,0 +1,148 @@
+// K1 paged append and K5 paged gather: bit-exact row movement between [rows, nkvh, d] tensors and the page
+// pool, 16 bytes per thread.
+//
+// Work decomposition: one thread per 16-byte piece of one (row, K-or-V, kv-head) head-row. A head-row is
+// d*elem_size bytes (256 B for bf16, d 128) and is contiguous on both sides, so a quarter-warp moves a full
+// head-row with coalesced 128-bit loads and stores. The slot lookup (two int32 loads per row, then one table
+// entry) hits in L1 for the other threads of the row.
+//
+// Roofline: HBM. Algorithmic bytes per row = 2 * (2 * nkvh * d * elem_size) (read the new K and V row, write
+// them) + 8 (sequence id and position) + 4 (table entry).
+#include "device_utils.cuh"
+#include "kernels.hpp"
+
+namespace llaisys::kernels {
+
+namespace {
+
+struct CopyGeom {
+    int64_t page_stride_b, head_stride_b, token_stride_b; // in bytes
+    int32_t vecs_per_head_row;                            // d * elem_size / 16
+    int32_t nkvh, page_size, num_pages, table_stride;
+};
+
+// Resolves (table row, position) to a physical page and slot; returns false (and flags) if out of range.
+__device__ __forceinline__ bool resolve_slot(const int32_t *__restrict__ table, const CopyGeom &g, int32_t seq_row,
+                                             int32_t pos, int32_t max_blocks, int32_t *error_flag, int32_t &page,
+                                             int32_t &slot) {
+    const int32_t blk = pos / g.page_size;
+    if (pos < 0 || blk >= max_blocks || seq_row < 0) {
+        atomicOr(error_flag, kErrBadPosition);
+        return false;
+    }
+    page = table ? table[int64_t(seq_row) * g.table_stride + blk] : blk;
+    slot = pos - blk * g.page_size;
+    if (page < 0 || page >= g.num_pages) {
+        atomicOr(error_flag, kErrBadPage);
+        return false;
+    }
+    return true;
+}
+
+__global__ void paged_append_kernel(uint4 *__restrict__ k_pool, uint4 *__restrict__ v_pool,
+                                    const uint4 *__restrict__ k_rows, const uint4 *__restrict__ v_rows,
+                                    const int32_t *__restrict__ table, const int32_t *__restrict__ seq_ids,
+                                    const int32_t *__restrict__ positions, CopyGeom g, int32_t n_rows,
+                                    int32_t max_blocks, int32_t *error_flag) {
+    const int32_t vecs_per_row = g.vecs_per_head_row * g.nkvh; // per K (or V) row
+    const int64_t total = int64_t(n_rows) * 2 * vecs_per_row;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int32_t row = int32_t(i / (2 * vecs_per_row));
+        const int32_t r = int32_t(i - int64_t(row) * 2 * vecs_per_row);
+        const int32_t is_v = r / vecs_per_row;
+        const int32_t in_row = r - is_v * vecs_per_row;
+        const int32_t kvh = in_row / g.vecs_per_head_row;
+        const int32_t vec = in_row - kvh * g.vecs_per_head_row;
+        int32_t page, slot;
+        if (!resolve_slot(table, g, seq_ids[row], positions[row], max_blocks, error_flag, page, slot)) {
+            continue;
+        }
+        const uint4 val = (is_v ? v_rows : k_rows)[int64_t(row) * vecs_per_row + in_row];
+        const int64_t off_b = int64_t(page) * g.page_stride_b + int64_t(kvh) * g.head_stride_b +
+                              int64_t(slot) * g.token_stride_b;
+        (is_v ? v_pool : k_pool)[off_b / 16 + vec] = val;
+    }
+}
+
+__global__ void paged_gather_kernel(const uint4 *__restrict__ k_pool, const uint4 *__restrict__ v_pool,
+                                    uint4 *__restrict__ k_out, uint4 *__restrict__ v_out,
+                                    const int32_t *__restrict__ table, CopyGeom g, int32_t seq_row, int32_t n_tokens,
+                                    int32_t max_blocks, int32_t *error_flag) {
+    const int32_t vecs_per_row = g.vecs_per_head_row * g.nkvh;
+    const int64_t total = int64_t(n_tokens) * 2 * vecs_per_row;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int32_t tok = int32_t(i / (2 * vecs_per_row));
+        const int32_t r = int32_t(i - int64_t(tok) * 2 * vecs_per_row);
+        const int32_t is_v = r / vecs_per_row;
+        const int32_t in_row = r - is_v * vecs_per_row;
+        const int32_t kvh = in_row / g.vecs_per_head_row;
+        const int32_t vec = in_row - kvh * g.vecs_per_head_row;
+        int32_t page, slot;
+        if (!resolve_slot(table, g, seq_row, tok, max_blocks, error_flag, page, slot)) {
+            continue;
+        }
+        const int64_t off_b = int64_t(page) * g.page_stride_b + int64_t(kvh) * g.head_stride_b +
+                              int64_t(slot) * g.token_stride_b;
+        const uint4 val = (is_v ? v_pool : k_pool)[off_b / 16 + vec];
+        (is_v ? v_out : k_out)[int64_t(tok) * vecs_per_row + in_row] = val;
+    }
+}
+
+CopyGeom make_geom(const KVView &kv, size_t elem_size) {
+    CHECK_ARGUMENT((size_t(kv.d) * elem_size) % 16 == 0, "paged copy: head rows must be a multiple of 16 bytes");
+    CHECK_ARGUMENT((size_t(kv.token_stride) * elem_size) % 16 == 0 && (size_t(kv.head_stride) * elem_size) % 16 == 0 &&
+                       (size_t(kv.page_stride) * elem_size) % 16 == 0,
+                   "paged copy: strides must be multiples of 16 bytes");
+    CopyGeom g;
+    g.page_stride_b = kv.page_stride * int64_t(elem_size);
+    g.head_stride_b = kv.head_stride * int64_t(elem_size);
+    g.token_stride_b = kv.token_stride * int64_t(elem_size);
+    g.vecs_per_head_row = int32_t(size_t(kv.d) * elem_size / 16);
+    g.nkvh = kv.nkvh;
+    g.page_size = kv.page_size;
+    g.num_pages = kv.num_pages;
+    g.table_stride = kv.table_stride;
+    return g;
+}
+
+int grid_for(int64_t threads, int block) {
+    const int64_t want = (threads + block - 1) / block;
+    const int64_t cap = 148 * 8;
+    return int(want < cap ? (want ? want : 1) : cap);
+}
+
+} // namespace
+
+void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const void *k_rows, const void *v_rows,
+                  const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t max_blocks,
+                  int32_t *error_flag) {
+    if (n_rows <= 0) {
+        return;
+    }
+    const CopyGeom g = make_geom(kv, elem_size);
+    const int block = 256;
+    const int grid = grid_for(int64_t(n_rows) * 2 * g.vecs_per_head_row * g.nkvh, block);
+    paged_append_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint4 *>(kv.k_base), static_cast<uint4 *>(kv.v_base), static_cast<const uint4 *>(k_rows),
+        static_cast<const uint4 *>(v_rows), kv.block_table, seq_ids, positions, g, n_rows, max_blocks, error_flag);
+    check_launch("paged_append");
+}
+
+void paged_gather(stream_t stream, size_t elem_size, const KVView &kv, int32_t seq_row, int32_t n_tokens,
+                  void *k_out, void *v_out, int32_t *error_flag) {
+    if (n_tokens <= 0) {
+        return;
+    }
+    const CopyGeom g = make_geom(kv, elem_size);
+    const int block = 256;
+    const int grid = grid_for(int64_t(n_tokens) * 2 * g.vecs_per_head_row * g.nkvh, block);
+    paged_gather_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint4 *>(kv.k_base), static_cast<const uint4 *>(kv.v_base), static_cast<uint4 *>(k_out),
+        static_cast<uint4 *>(v_out), kv.block_table, g, seq_row, n_tokens,
+        kv.block_table ? kv.table_stride : INT32_MAX, error_flag);
+    check_launch("paged_gather");
+}
+
+} // namespace llaisys::kernels

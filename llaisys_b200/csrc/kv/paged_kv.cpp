@@ -1,0 +1,572 @@
+#include "paged_kv.hpp"
+
+#include "../common/check.hpp"
+#include "../common/dtypes.hpp"
+#include "../cpu/cpu_kernels.hpp"
+#include "llaisys/paged_kv.h"
+#ifdef ENABLE_NVIDIA_API
+#include "../kernels/kernels.hpp"
+#endif
+
+#include <algorithm>
+#include <cstring>
+#include <limits>
+#include <sstream>
+
+namespace llaisys::kv {
+
+namespace {
+
+template <typename... Args>
+[[noreturn]] void fail(int code, Args &&...args) {
+    std::ostringstream os;
+    (os << ... << args);
+    throw StatusError(code, os.str());
+}
+
+#define KV_REQUIRE(cond, code, ...) \
+    do {                            \
+        if (!(cond)) {              \
+            fail(code, __VA_ARGS__); \
+        }                           \
+    } while (0)
+
+constexpr size_t kMaxInt32 = size_t(std::numeric_limits<int32_t>::max());
+
+} // namespace
+
+// ---- construction ---------------------------------------------------------------------------------
+
+PagedKV::PagedKV(const PagedKVConfig &cfg) : _cfg(cfg) {
+    KV_REQUIRE(cfg.dtype == LLAISYS_DTYPE_F32 || cfg.dtype == LLAISYS_DTYPE_F16 || cfg.dtype == LLAISYS_DTYPE_BF16,
+               LLAISYS_E_INVALID, "paged KV: dtype must be F32, F16 or BF16");
+    KV_REQUIRE(cfg.nlayer > 0 && cfg.num_pages > 0 && cfg.page_size > 0 && cfg.nkvh > 0 && cfg.head_dim > 0 &&
+                   cfg.max_seqs > 0 && cfg.max_pages_per_seq > 0,
+               LLAISYS_E_INVALID, "paged KV: every size must be positive");
+    KV_REQUIRE(cfg.num_pages <= kMaxInt32 && cfg.max_seqs <= kMaxInt32 && cfg.max_pages_per_seq <= kMaxInt32 &&
+                   cfg.page_size * cfg.max_pages_per_seq <= kMaxInt32,
+               LLAISYS_E_INVALID, "paged KV: sizes must fit 32-bit indices");
+    _elem = utils::dsize(cfg.dtype);
+    KV_REQUIRE((cfg.head_dim * _elem) % 16 == 0, LLAISYS_E_INVALID,
+               "paged KV: a head row (head_dim * element size) must be a multiple of 16 bytes");
+    _page_elems = 2 * cfg.nkvh * cfg.page_size * cfg.head_dim;
+    _layer_bytes = cfg.num_pages * _page_elems * _elem;
+
+    auto &ctx = core::context();
+    KV_REQUIRE(cfg.device_type == LLAISYS_DEVICE_CPU || cfg.device_type == LLAISYS_DEVICE_NVIDIA, LLAISYS_E_INVALID,
+               "paged KV: unknown device type");
+    const int n_dev = llaisysGetRuntimeAPI(cfg.device_type)->get_device_count();
+    KV_REQUIRE(cfg.device_id >= 0 && cfg.device_id < n_dev, LLAISYS_E_DEVICE, "paged KV: device ", cfg.device_id,
+               " does not exist (", n_dev, " device(s) of this type)");
+    ctx.setDevice(cfg.device_type, cfg.device_id);
+    auto &rt = ctx.runtime();
+
+    _pool = rt.allocateDeviceStorage(cfg.nlayer * _layer_bytes);
+    _table_dev = rt.allocateDeviceStorage(cfg.max_seqs * cfg.max_pages_per_seq * sizeof(int32_t));
+    _error_dev = rt.allocateDeviceStorage(sizeof(int32_t));
+    // Pages start zeroed: tokens past a sequence's length are never read as data, but a tile load may touch
+    // them, and zero keeps such lanes finite.
+    if (onDevice()) {
+#ifdef ENABLE_NVIDIA_API
+        kernels::fill_zero(rt.stream(), _pool->memory(), _pool->size());
+        kernels::fill_zero(rt.stream(), _table_dev->memory(), _table_dev->size());
+        kernels::fill_zero(rt.stream(), _error_dev->memory(), _error_dev->size());
+        rt.synchronize();
+#endif
+    } else {
+        std::memset(_pool->memory(), 0, _pool->size());
+        std::memset(_table_dev->memory(), 0, _table_dev->size());
+        std::memset(_error_dev->memory(), 0, _error_dev->size());
+    }
+
+    _page_owner.assign(cfg.num_pages, -1);
+    _free_pages.resize(cfg.num_pages);
+    for (size_t i = 0; i < cfg.num_pages; ++i) {
+        _free_pages[i] = int32_t(cfg.num_pages - 1 - i); // page 0 is handed out first
+    }
+    _seqs.resize(cfg.max_seqs);
+    _free_seq_ids.resize(cfg.max_seqs);
+    for (size_t i = 0; i < cfg.max_seqs; ++i) {
+        _free_seq_ids[i] = int32_t(cfg.max_seqs - 1 - i);
+    }
+    _table_host.assign(cfg.max_seqs * cfg.max_pages_per_seq, 0);
+}
+
+// ---- block manager ----------------------------------------------------------------------------------
+
+PagedKV::Seq &PagedKV::liveSeq(int32_t seq) {
+    KV_REQUIRE(seq >= 0 && size_t(seq) < _seqs.size() && _seqs[seq].live, LLAISYS_E_NO_SEQ, "paged KV: sequence ",
+               seq, " does not exist");
+    return _seqs[seq];
+}
+const PagedKV::Seq &PagedKV::liveSeq(int32_t seq) const { return const_cast<PagedKV *>(this)->liveSeq(seq); }
+
+void PagedKV::markDirty(int32_t seq, int32_t lo, int32_t hi) {
+    Seq &s = _seqs[seq];
+    if (!s.queued_dirty) {
+        s.queued_dirty = true;
+        s.dirty_lo = lo;
+        s.dirty_hi = hi;
+        _dirty_seqs.push_back(seq);
+    } else {
+        s.dirty_lo = std::min(s.dirty_lo, lo);
+        s.dirty_hi = std::max(s.dirty_hi, hi);
+    }
+}
+
+int32_t PagedKV::seqAdd() {
+    KV_REQUIRE(!_free_seq_ids.empty(), LLAISYS_E_NO_SEQ, "paged KV: all ", _cfg.max_seqs, " sequence slots are in use");
+    const int32_t id = _free_seq_ids.back();
+    _free_seq_ids.pop_back();
+    Seq &s = _seqs[id];
+    s.live = true;
+    s.n_pages = 0;
+    ++_n_live;
+    return id;
+}
+
+void PagedKV::seqReserve(int32_t seq, size_t n_tokens) {
+    Seq &s = liveSeq(seq);
+    const size_t want_pages = (n_tokens + _cfg.page_size - 1) / _cfg.page_size;
+    if (want_pages <= size_t(s.n_pages)) {
+        return;
+    }
+    KV_REQUIRE(want_pages <= _cfg.max_pages_per_seq, LLAISYS_E_INVALID, "paged KV: ", n_tokens,
+               " tokens need more than max_pages_per_seq = ", _cfg.max_pages_per_seq, " pages");
+    const size_t extra = want_pages - size_t(s.n_pages);
+    KV_REQUIRE(extra <= _free_pages.size(), LLAISYS_E_NO_PAGES, "paged KV: need ", extra, " more pages, ",
+               _free_pages.size(), " free");
+    int32_t *row = _table_host.data() + size_t(seq) * _cfg.max_pages_per_seq;
+    const int32_t first = s.n_pages;
+    for (size_t i = 0; i < extra; ++i) {
+        const int32_t page = _free_pages.back();
+        _free_pages.pop_back();
+        _page_owner[page] = seq;
+        row[s.n_pages++] = page;
+    }
+    markDirty(seq, first, s.n_pages);
+}
+
+void PagedKV::seqAssignPages(int32_t seq, const int32_t *pages, size_t n_pages) {
+    Seq &s = liveSeq(seq);
+    if (n_pages == 0) {
+        return;
+    }
+    KV_REQUIRE(pages != nullptr, LLAISYS_E_INVALID, "paged KV: pages is null");
+    KV_REQUIRE(size_t(s.n_pages) + n_pages <= _cfg.max_pages_per_seq, LLAISYS_E_INVALID,
+               "paged KV: sequence would exceed max_pages_per_seq = ", _cfg.max_pages_per_seq);
+    // Validate everything before changing anything (all-or-nothing). A provisional owner mark catches a page
+    // named twice in the same request; marks are rolled back if a later entry fails.
+    for (size_t i = 0; i < n_pages; ++i) {
+        const int32_t p = pages[i];
+        const bool in_range = p >= 0 && size_t(p) < _cfg.num_pages;
+        if (!in_range || _page_owner[p] != -1) {
+            for (size_t k = 0; k < i; ++k) {
+                _page_owner[pages[k]] = -1;
+            }
+            KV_REQUIRE(in_range, LLAISYS_E_INVALID, "paged KV: page ", p, " is out of range");
+            fail(LLAISYS_E_NO_PAGES, "paged KV: page ", p, " is not free");
+        }
+        _page_owner[p] = -2;
+    }
+    for (size_t i = 0; i < n_pages; ++i) {
+        _page_owner[pages[i]] = seq;
+    }
+    // remove the claimed pages from the free stack in one pass
+    _free_pages.erase(std::remove_if(_free_pages.begin(), _free_pages.end(),
+                                     [&](int32_t p) { return _page_owner[p] != -1; }),
+                      _free_pages.end());
+    int32_t *row = _table_host.data() + size_t(seq) * _cfg.max_pages_per_seq;
+    const int32_t first = s.n_pages;
+    for (size_t i = 0; i < n_pages; ++i) {
+        row[s.n_pages++] = pages[i];
+    }
+    markDirty(seq, first, s.n_pages);
+}
+
+void PagedKV::seqFree(int32_t seq) {
+    Seq &s = liveSeq(seq);
+    const int32_t *row = _table_host.data() + size_t(seq) * _cfg.max_pages_per_seq;
+    for (int32_t i = s.n_pages; i-- > 0;) { // reverse, so a re-reserve pops them in the original order
+        _page_owner[row[i]] = -1;
+        _free_pages.push_back(row[i]);
+    }
+    s.live = false;
+    s.n_pages = 0;
+    --_n_live;
+    _free_seq_ids.push_back(seq);
+}
+
+int64_t PagedKV::seqNumPages(int32_t seq) const {
+    if (seq < 0 || size_t(seq) >= _seqs.size() || !_seqs[seq].live) {
+        return -1;
+    }
+    return _seqs[seq].n_pages;
+}
+
+void PagedKV::seqPages(int32_t seq, int32_t *pages_out, size_t cap) const {
+    const Seq &s = liveSeq(seq);
+    const size_t n = std::min(cap, size_t(s.n_pages));
+    if (n > 0) {
+        KV_REQUIRE(pages_out != nullptr, LLAISYS_E_INVALID, "paged KV: pages_out is null");
+        std::memcpy(pages_out, _table_host.data() + size_t(seq) * _cfg.max_pages_per_seq, n * sizeof(int32_t));
+    }
+}
+
+// ---- device views -----------------------------------------------------------------------------------
+
+void PagedKV::checkLayer(size_t layer) const {
+    KV_REQUIRE(layer < _cfg.nlayer, LLAISYS_E_INVALID, "paged KV: layer ", layer, " out of range (", _cfg.nlayer, ")");
+}
+
+std::byte *PagedKV::poolData(size_t layer) const {
+    checkLayer(layer);
+    return _pool->memory() + layer * _layer_bytes;
+}
+
+kernels::KVView PagedKV::view(size_t layer) const {
+    kernels::KVView v;
+    v.k_base = poolData(layer);
+    v.v_base = poolData(layer) + _cfg.nkvh * _cfg.page_size * _cfg.head_dim * _elem;
+    v.page_stride = int64_t(_page_elems);
+    v.head_stride = int64_t(_cfg.page_size * _cfg.head_dim);
+    v.token_stride = int64_t(_cfg.head_dim);
+    v.block_table = blockTableData();
+    v.table_stride = int32_t(_cfg.max_pages_per_seq);
+    v.page_size = int32_t(_cfg.page_size);
+    v.num_pages = int32_t(_cfg.num_pages);
+    v.nkvh = int32_t(_cfg.nkvh);
+    v.d = int32_t(_cfg.head_dim);
+    return v;
+}
+
+core::Runtime &PagedKV::enter() const {
+    auto &ctx = core::context();
+    ctx.setDevice(_cfg.device_type, _cfg.device_id);
+    return ctx.runtime();
+}
+
+void PagedKV::flush() {
+    if (_dirty_seqs.empty()) {
+        return;
+    }
+    auto &rt = enter();
+    auto *dev = reinterpret_cast<int32_t *>(_table_dev->memory());
+    for (int32_t seq : _dirty_seqs) {
+        Seq &s = _seqs[seq];
+        s.queued_dirty = false;
+        if (!s.live || s.dirty_hi <= s.dirty_lo) {
+            continue;
+        }
+        const size_t off = size_t(seq) * _cfg.max_pages_per_seq + size_t(s.dirty_lo);
+        const size_t bytes = size_t(s.dirty_hi - s.dirty_lo) * sizeof(int32_t);
+        // The source is ordinary pageable memory: the runtime stages it before the call returns, so the host
+        // table may change again straight away.
+        rt.api()->memcpy_async(dev + off, _table_host.data() + off, bytes, LLAISYS_MEMCPY_H2D, rt.stream());
+    }
+    _dirty_seqs.clear();
+}
+
+void PagedKV::check() {
+    auto &rt = enter();
+    rt.synchronize();
+    int32_t word = 0;
+    rt.api()->memcpy_sync(&word, _error_dev->memory(), sizeof(word), LLAISYS_MEMCPY_D2H);
+    if (word != 0) {
+        const int32_t zero = 0;
+        rt.api()->memcpy_sync(_error_dev->memory(), &zero, sizeof(zero), LLAISYS_MEMCPY_H2D);
+        fail(LLAISYS_E_KERNEL, "paged KV: a kernel skipped out-of-range metadata (flags 0x", std::hex, word,
+             std::dec, ": 1 = page, 2 = position, 4 = sequence)");
+    }
+}
+
+// Copies several small host arrays, back to back, into the cache's device-side metadata buffer and returns its
+// base; array i starts at the sum of the lengths before it. One copy per call.
+int32_t *PagedKV::stage(const int32_t *const *arrays, const size_t *lens, size_t n_arrays) {
+    size_t total = 0;
+    for (size_t i = 0; i < n_arrays; ++i) {
+        total += lens[i];
+    }
+    auto &rt = enter();
+    if (total > _meta_cap) {
+        _meta_cap = std::max<size_t>(total * 2, 1024);
+        _meta_dev = rt.allocateDeviceStorage(_meta_cap * sizeof(int32_t));
+    }
+    _stage_buf.resize(total);
+    size_t at = 0;
+    for (size_t i = 0; i < n_arrays; ++i) {
+        std::memcpy(_stage_buf.data() + at, arrays[i], lens[i] * sizeof(int32_t));
+        at += lens[i];
+    }
+    auto *dev = reinterpret_cast<int32_t *>(_meta_dev->memory());
+    if (total > 0) {
+        rt.api()->memcpy_async(dev, _stage_buf.data(), total * sizeof(int32_t), LLAISYS_MEMCPY_H2D, rt.stream());
+    }
+    return dev;
+}
+
+kernels::AttnScratch PagedKV::scratchFor(size_t n_seqs, size_t nh, size_t max_kv_len) {
+    kernels::AttnScratch sc;
+    sc.error_flag = reinterpret_cast<int32_t *>(_error_dev->memory());
+#ifdef ENABLE_NVIDIA_API
+    if (onDevice()) {
+        size_t floats = 0, counters = 0;
+        kernels::attention_decode_split_scratch(int32_t(n_seqs), int32_t(nh), int32_t(_cfg.nkvh),
+                                                int32_t(_cfg.head_dim), int32_t(max_kv_len), &floats, &counters);
+        auto &rt = enter();
+        if (floats > _partials_floats) {
+            _partials_floats = floats;
+            _partials = rt.allocateDeviceStorage(floats * sizeof(float));
+        }
+        if (counters > _counters_len) {
+            _counters_len = counters;
+            _counters = rt.allocateDeviceStorage(counters * sizeof(int32_t));
+            kernels::fill_zero(rt.stream(), _counters->memory(), _counters->size());
+            rt.synchronize(); // the next launch may be on a caller's stream
+        }
+        sc.partials = _partials ? reinterpret_cast<float *>(_partials->memory()) : nullptr;
+        sc.partials_floats = _partials_floats;
+        sc.counters = _counters ? reinterpret_cast<int32_t *>(_counters->memory()) : nullptr;
+        sc.counters_len = _counters_len;
+    }
+#else
+    (void)n_seqs;
+    (void)nh;
+    (void)max_kv_len;
+#endif
+    return sc;
+}
+
+// ---- data path, device index arrays -----------------------------------------------------------------
+
+void PagedKV::appendDev(size_t layer, const void *k_rows, const void *v_rows, const int32_t *seq_ids_dev,
+                        const int32_t *positions_dev, size_t n_rows, llaisysStream_t stream) {
+    checkLayer(layer);
+    KV_REQUIRE(n_rows <= kMaxInt32, LLAISYS_E_INVALID, "paged KV: too many rows");
+    if (n_rows == 0) {
+        return;
+    }
+    KV_REQUIRE(k_rows && v_rows && seq_ids_dev && positions_dev, LLAISYS_E_INVALID, "paged KV append: null argument");
+    const kernels::KVView v = view(layer);
+    if (!onDevice()) {
+        const int err = cpu::paged_append(_elem, v, k_rows, v_rows, seq_ids_dev, positions_dev, int32_t(n_rows),
+                                          int32_t(_cfg.max_pages_per_seq));
+        *reinterpret_cast<int32_t *>(_error_dev->memory()) |= err;
+        return;
+    }
+#ifdef ENABLE_NVIDIA_API
+    enter();
+    kernels::paged_append(stream, _elem, v, k_rows, v_rows, seq_ids_dev, positions_dev, int32_t(n_rows),
+                          int32_t(_cfg.max_pages_per_seq), reinterpret_cast<int32_t *>(_error_dev->memory()));
+#else
+    (void)stream;
+    fail(LLAISYS_E_UNSUPPORTED, "this build has no NVIDIA backend");
+#endif
+}
+
+void PagedKV::decodeDev(size_t layer, void *out, float *part, const void *q, const int32_t *seq_ids_dev,
+                        const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len, size_t nh, float scale,
+                        llaisysStream_t stream) {
+    checkLayer(layer);
+    KV_REQUIRE(nh > 0 && nh % _cfg.nkvh == 0, LLAISYS_E_INVALID, "paged attention: nh = ", nh,
+               " is not a multiple of nkvh = ", _cfg.nkvh);
+    KV_REQUIRE(n_seqs <= kMaxInt32 && max_kv_len <= _cfg.page_size * _cfg.max_pages_per_seq, LLAISYS_E_INVALID,
+               "paged attention: batch or context too large for this cache");
+    if (n_seqs == 0) {
+        return;
+    }
+    KV_REQUIRE((out != nullptr) != (part != nullptr), LLAISYS_E_INVALID, "paged attention: exactly one output");
+    KV_REQUIRE(q && seq_ids_dev && kv_lens_dev, LLAISYS_E_INVALID, "paged attention: null argument");
+    const kernels::KVView v = view(layer);
+    kernels::AttnBatch b;
+    b.seq_ids = seq_ids_dev;
+    b.kv_lens = kv_lens_dev;
+    b.const_q_len = 1;
+    b.n_seqs = int32_t(n_seqs);
+    b.total_q = int32_t(n_seqs);
+    b.max_q_len = 1;
+    b.max_kv_len = int32_t(max_kv_len);
+    b.nh = int32_t(nh);
+    kernels::AttnOut o;
+    o.out = out;
+    o.part = part;
+    if (!onDevice()) {
+        const int err = cpu::attention(_cfg.dtype, v, b, q, scale, o);
+        *reinterpret_cast<int32_t *>(_error_dev->memory()) |= err;
+        return;
+    }
+#ifdef ENABLE_NVIDIA_API
+    const kernels::AttnScratch sc = scratchFor(n_seqs, nh, max_kv_len);
+    run_attention_nvidia(stream, _cfg.dtype, v, b, q, scale, o, sc);
+#else
+    (void)stream;
+    fail(LLAISYS_E_UNSUPPORTED, "this build has no NVIDIA backend");
+#endif
+}
+
+void PagedKV::prefillDev(size_t layer, void *out, const void *q, const int32_t *seq_ids_dev,
+                         const int32_t *q_starts_dev, const int32_t *kv_lens_dev, size_t n_seqs, size_t total_q,
+                         size_t max_q_len, size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream) {
+    checkLayer(layer);
+    KV_REQUIRE(nh > 0 && nh % _cfg.nkvh == 0, LLAISYS_E_INVALID, "paged attention: nh = ", nh,
+               " is not a multiple of nkvh = ", _cfg.nkvh);
+    KV_REQUIRE(n_seqs <= kMaxInt32 && total_q <= kMaxInt32 && max_kv_len <= _cfg.page_size * _cfg.max_pages_per_seq,
+               LLAISYS_E_INVALID, "paged attention: batch or context too large for this cache");
+    if (n_seqs == 0 || total_q == 0) {
+        return;
+    }
+    KV_REQUIRE(out && q && seq_ids_dev && q_starts_dev && kv_lens_dev, LLAISYS_E_INVALID,
+               "paged attention: null argument");
+    const kernels::KVView v = view(layer);
+    kernels::AttnBatch b;
+    b.seq_ids = seq_ids_dev;
+    b.kv_lens = kv_lens_dev;
+    b.q_starts = q_starts_dev;
+    b.n_seqs = int32_t(n_seqs);
+    b.total_q = int32_t(total_q);
+    b.max_q_len = int32_t(max_q_len);
+    b.max_kv_len = int32_t(max_kv_len);
+    b.nh = int32_t(nh);
+    kernels::AttnOut o;
+    o.out = out;
+    if (!onDevice()) {
+        const int err = cpu::attention(_cfg.dtype, v, b, q, scale, o);
+        *reinterpret_cast<int32_t *>(_error_dev->memory()) |= err;
+        return;
+    }
+#ifdef ENABLE_NVIDIA_API
+    kernels::AttnScratch sc;
+    sc.error_flag = reinterpret_cast<int32_t *>(_error_dev->memory());
+    enter();
+    run_attention_nvidia(stream, _cfg.dtype, v, b, q, scale, o, sc);
+#else
+    (void)stream;
+    fail(LLAISYS_E_UNSUPPORTED, "this build has no NVIDIA backend");
+#endif
+}
+
+// ---- data path, host index arrays -------------------------------------------------------------------
+
+void PagedKV::append(size_t layer, const void *k_rows, const void *v_rows, const int32_t *seq_ids,
+                     const int32_t *positions, size_t n_rows) {
+    checkLayer(layer);
+    if (n_rows == 0) {
+        return;
+    }
+    KV_REQUIRE(k_rows && v_rows && seq_ids && positions, LLAISYS_E_INVALID, "paged KV append: null argument");
+    for (size_t i = 0; i < n_rows; ++i) {
+        const Seq &s = liveSeq(seq_ids[i]);
+        KV_REQUIRE(positions[i] >= 0 && size_t(positions[i]) < size_t(s.n_pages) * _cfg.page_size, LLAISYS_E_INVALID,
+                   "paged KV append: row ", i, " position ", positions[i], " is beyond the ", s.n_pages,
+                   " page(s) reserved for sequence ", seq_ids[i]);
+    }
+    flush();
+    if (!onDevice()) {
+        return appendDev(layer, k_rows, v_rows, seq_ids, positions, n_rows, nullptr);
+    }
+    const int32_t *arrays[2] = {seq_ids, positions};
+    const size_t lens[2] = {n_rows, n_rows};
+    int32_t *dev = stage(arrays, lens, 2);
+    appendDev(layer, k_rows, v_rows, dev, dev + n_rows, n_rows, enter().stream());
+}
+
+void PagedKV::gather(size_t layer, int32_t seq, size_t n_tokens, void *k_out, void *v_out) {
+    checkLayer(layer);
+    const Seq &s = liveSeq(seq);
+    KV_REQUIRE(n_tokens <= size_t(s.n_pages) * _cfg.page_size, LLAISYS_E_INVALID, "paged KV gather: ", n_tokens,
+               " tokens exceed the sequence's capacity");
+    if (n_tokens == 0) {
+        return;
+    }
+    KV_REQUIRE(k_out && v_out, LLAISYS_E_INVALID, "paged KV gather: null output");
+    flush();
+    const kernels::KVView v = view(layer);
+    if (!onDevice()) {
+        const int err = cpu::paged_gather(_elem, v, seq, int32_t(n_tokens), k_out, v_out);
+        *reinterpret_cast<int32_t *>(_error_dev->memory()) |= err;
+        return;
+    }
+#ifdef ENABLE_NVIDIA_API
+    auto &rt = enter();
+    kernels::paged_gather(rt.stream(), _elem, v, seq, int32_t(n_tokens), k_out, v_out,
+                          reinterpret_cast<int32_t *>(_error_dev->memory()));
+#else
+    fail(LLAISYS_E_UNSUPPORTED, "this build has no NVIDIA backend");
+#endif
+}
+
+void PagedKV::decode(size_t layer, void *out, float *part, const void *q, const int32_t *seq_ids,
+                     const int32_t *kv_lens, size_t n_seqs, size_t nh, float scale) {
+    checkLayer(layer);
+    if (n_seqs == 0) {
+        return;
+    }
+    KV_REQUIRE(seq_ids && kv_lens, LLAISYS_E_INVALID, "paged attention: null index array");
+    size_t max_kv = 0;
+    for (size_t i = 0; i < n_seqs; ++i) {
+        const Seq &s = liveSeq(seq_ids[i]);
+        KV_REQUIRE(kv_lens[i] >= 0 && size_t(kv_lens[i]) <= size_t(s.n_pages) * _cfg.page_size, LLAISYS_E_INVALID,
+                   "paged attention: kv_len ", kv_lens[i], " exceeds the ", s.n_pages,
+                   " page(s) reserved for sequence ", seq_ids[i]);
+        max_kv = std::max(max_kv, size_t(kv_lens[i]));
+    }
+    flush();
+    if (!onDevice()) {
+        return decodeDev(layer, out, part, q, seq_ids, kv_lens, n_seqs, max_kv, nh, scale, nullptr);
+    }
+    const int32_t *arrays[2] = {seq_ids, kv_lens};
+    const size_t lens[2] = {n_seqs, n_seqs};
+    int32_t *dev = stage(arrays, lens, 2);
+    decodeDev(layer, out, part, q, dev, dev + n_seqs, n_seqs, max_kv, nh, scale, enter().stream());
+}
+
+void PagedKV::prefill(size_t layer, void *out, const void *q, const int32_t *seq_ids, const int32_t *q_lens,
+                      const int32_t *kv_lens, size_t n_seqs, size_t nh, float scale) {
+    checkLayer(layer);
+    if (n_seqs == 0) {
+        return;
+    }
+    KV_REQUIRE(seq_ids && q_lens && kv_lens, LLAISYS_E_INVALID, "paged attention: null index array");
+    std::vector<int32_t> starts(n_seqs + 1, 0);
+    size_t max_kv = 0, max_q = 0;
+    for (size_t i = 0; i < n_seqs; ++i) {
+        const Seq &s = liveSeq(seq_ids[i]);
+        KV_REQUIRE(q_lens[i] >= 0 && kv_lens[i] >= q_lens[i], LLAISYS_E_INVALID,
+                   "paged attention: sequence ", i, " has q_len ", q_lens[i], " > kv_len ", kv_lens[i]);
+        KV_REQUIRE(size_t(kv_lens[i]) <= size_t(s.n_pages) * _cfg.page_size, LLAISYS_E_INVALID,
+                   "paged attention: kv_len ", kv_lens[i], " exceeds the ", s.n_pages,
+                   " page(s) reserved for sequence ", seq_ids[i]);
+        KV_REQUIRE(size_t(starts[i]) + size_t(q_lens[i]) <= kMaxInt32, LLAISYS_E_INVALID, "paged attention: too many rows");
+        starts[i + 1] = starts[i] + q_lens[i];
+        max_kv = std::max(max_kv, size_t(kv_lens[i]));
+        max_q = std::max(max_q, size_t(q_lens[i]));
+    }
+    const size_t total_q = size_t(starts[n_seqs]);
+    flush();
+    if (!onDevice()) {
+        return prefillDev(layer, out, q, seq_ids, starts.data(), kv_lens, n_seqs, total_q, max_q, max_kv, nh, scale,
+                          nullptr);
+    }
+    const int32_t *arrays[3] = {seq_ids, kv_lens, starts.data()};
+    const size_t lens[3] = {n_seqs, n_seqs, n_seqs + 1};
+    int32_t *dev = stage(arrays, lens, 3);
+    prefillDev(layer, out, q, dev, dev + 2 * n_seqs, dev + n_seqs, n_seqs, total_q, max_q, max_kv, nh, scale,
+               enter().stream());
+}
+
+// ---- kernel choice on NVIDIA ------------------------------------------------------------------------
+
+#ifdef ENABLE_NVIDIA_API
+void run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const kernels::KVView &view,
+                          const kernels::AttnBatch &batch, const void *q, float scale, const kernels::AttnOut &out,
+                          const kernels::AttnScratch &scratch) {
+    const bool one_query_each = batch.q_starts == nullptr && batch.const_q_len == 1;
+    if (one_query_each && scratch.counters != nullptr &&
+        kernels::attention_decode_split(stream, dtype, view, batch, q, scale, out, scratch) == 0) {
+        return;
+    }
+    kernels::attention_generic(stream, dtype, view, batch, q, scale, out, scratch.error_flag);
+}
+#endif
+
+} // namespace llaisys::kv

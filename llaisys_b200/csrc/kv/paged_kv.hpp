@@ -1,0 +1,119 @@
+// Paged KV cache: a fixed pool of pages, a free list, per-sequence block tables, and the data-path calls that
+// read and write pages through them. New code -- the reference names a KV cache only as future work
+// (README.md:316, :412, :424).
+//
+// Host state (block manager) is plain C++ and identical for CPU and NVIDIA caches; the device copy of the
+// block table is refreshed lazily (only rows that changed) when a data-path call needs it.
+#pragma once
+
+#include "../kernels/args.hpp"
+#include "../tensor/tensor.hpp"
+
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace llaisys::kv {
+
+// Thrown inside the library for every failure of the status-returning API; the C thunks turn it into a code.
+struct StatusError : std::runtime_error {
+    int code;
+    StatusError(int code_, const std::string &what) : std::runtime_error(what), code(code_) {}
+};
+
+struct PagedKVConfig {
+    llaisysDeviceType_t device_type = LLAISYS_DEVICE_CPU;
+    int device_id = 0;
+    llaisysDataType_t dtype = LLAISYS_DTYPE_BF16;
+    size_t nlayer = 1, num_pages = 0, page_size = 16, nkvh = 0, head_dim = 0;
+    size_t max_seqs = 0, max_pages_per_seq = 0;
+};
+
+class PagedKV {
+public:
+    explicit PagedKV(const PagedKVConfig &cfg);
+    ~PagedKV() = default;
+    PagedKV(const PagedKV &) = delete;
+    PagedKV &operator=(const PagedKV &) = delete;
+
+    const PagedKVConfig &config() const { return _cfg; }
+
+    // ---- block manager (host only) ----
+    int32_t seqAdd();
+    void seqReserve(int32_t seq, size_t n_tokens);
+    void seqAssignPages(int32_t seq, const int32_t *pages, size_t n_pages);
+    void seqFree(int32_t seq);
+    size_t numFreePages() const { return _free_pages.size(); }
+    size_t numSeqs() const { return _n_live; }
+    int64_t seqNumPages(int32_t seq) const;
+    void seqPages(int32_t seq, int32_t *pages_out, size_t cap) const;
+
+    // ---- device-side views ----
+    std::byte *poolData(size_t layer) const;
+    size_t layerBytes() const { return _layer_bytes; }
+    const int32_t *blockTableData() const { return reinterpret_cast<const int32_t *>(_table_dev->memory()); }
+    void flush(); // queue uploads of the table rows that changed since the last flush
+    void check(); // synchronise, throw LLAISYS_E_KERNEL if a kernel flagged bad metadata
+
+    // ---- data path: host index arrays (validated, staged, queued on the calling thread's stream) ----
+    void append(size_t layer, const void *k_rows, const void *v_rows, const int32_t *seq_ids, const int32_t *positions,
+                size_t n_rows);
+    void gather(size_t layer, int32_t seq, size_t n_tokens, void *k_out, void *v_out);
+    void decode(size_t layer, void *out, float *part, const void *q, const int32_t *seq_ids, const int32_t *kv_lens,
+                size_t n_seqs, size_t nh, float scale);
+    void prefill(size_t layer, void *out, const void *q, const int32_t *seq_ids, const int32_t *q_lens,
+                 const int32_t *kv_lens, size_t n_seqs, size_t nh, float scale);
+
+    // ---- data path: device index arrays, explicit stream (no validation, no staging) ----
+    void appendDev(size_t layer, const void *k_rows, const void *v_rows, const int32_t *seq_ids_dev,
+                   const int32_t *positions_dev, size_t n_rows, llaisysStream_t stream);
+    void decodeDev(size_t layer, void *out, float *part, const void *q, const int32_t *seq_ids_dev,
+                   const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len, size_t nh, float scale,
+                   llaisysStream_t stream);
+    void prefillDev(size_t layer, void *out, const void *q, const int32_t *seq_ids_dev, const int32_t *q_starts_dev,
+                    const int32_t *kv_lens_dev, size_t n_seqs, size_t total_q, size_t max_q_len, size_t max_kv_len,
+                    size_t nh, float scale, llaisysStream_t stream);
+
+private:
+    struct Seq {
+        bool live = false;
+        int32_t n_pages = 0;
+        int32_t dirty_lo = 0, dirty_hi = 0; // table entries [lo, hi) not yet on the device
+        bool queued_dirty = false;
+    };
+
+    Seq &liveSeq(int32_t seq);
+    const Seq &liveSeq(int32_t seq) const;
+    void markDirty(int32_t seq, int32_t lo, int32_t hi);
+    void checkLayer(size_t layer) const;
+    kernels::KVView view(size_t layer) const;
+    core::Runtime &enter() const;                   // make the cache's device current on this thread
+    int32_t *stage(const int32_t *const *arrays, const size_t *lens, size_t n_arrays); // host arrays -> device
+    kernels::AttnScratch scratchFor(size_t n_seqs, size_t nh, size_t max_kv_len);
+    bool onDevice() const { return _cfg.device_type != LLAISYS_DEVICE_CPU; }
+
+    PagedKVConfig _cfg;
+    size_t _elem = 0, _page_elems = 0, _layer_bytes = 0;
+
+    // block manager
+    std::vector<int32_t> _free_pages; // stack; back() is handed out next
+    std::vector<int32_t> _page_owner; // sequence id, or -1 when free
+    std::vector<Seq> _seqs;
+    std::vector<int32_t> _free_seq_ids;
+    std::vector<int32_t> _table_host; // [max_seqs][max_pages_per_seq]
+    std::vector<int32_t> _dirty_seqs;
+    size_t _n_live = 0;
+
+    // device memory (host memory for a CPU cache)
+    core::storage_t _pool, _table_dev, _error_dev, _meta_dev, _partials, _counters;
+    size_t _meta_cap = 0, _partials_floats = 0, _counters_len = 0;
+    std::vector<int32_t> _stage_buf;
+};
+
+// Picks the kernel for a batch on an NVIDIA device and queues it: split-KV decode or tensor-core prefill where
+// the shape allows, the generic kernel otherwise. `scratch` may be empty when the shape cannot use it.
+void run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const kernels::KVView &view,
+                          const kernels::AttnBatch &batch, const void *q, float scale, const kernels::AttnOut &out,
+                          const kernels::AttnScratch &scratch);
+
+} // namespace llaisys::kv

@@ -1,0 +1,180 @@
+"""Paged KV cache: block manager plus append / gather / attention over pages.
+
+Thin wrapper over the status-returning entry points of include/llaisys/paged_kv.h; a non-zero status
+becomes a LlaisysError carrying the code and the library's message. Bulk arguments (q, out, k_rows, ...)
+may be llaisys Tensors, torch tensors, or raw addresses -- anything with data_ptr() -- in the cache's device
+memory; index arguments are Python sequences or numpy int32 arrays on the host.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import byref, c_int32
+from typing import Sequence
+
+import numpy as np
+
+from .libllaisys import LIB_LLAISYS, DataType, DeviceType, Status, llaisysPagedKV_t
+from .runtime import _addr
+
+_I32P = ctypes.POINTER(c_int32)
+
+
+class LlaisysError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        self.status = Status(status)
+        super().__init__(f"{self.status.name}: {message}")
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise LlaisysError(status, LIB_LLAISYS.llaisysGetLastError().decode())
+
+
+def _i32(values) -> tuple[np.ndarray, ctypes.Array]:
+    arr = np.ascontiguousarray(values, dtype=np.int32)
+    return arr, arr.ctypes.data_as(_I32P)
+
+
+class PagedKVCache:
+    """Fixed pool of pages with a free list and per-sequence block tables.
+
+    Pool layout: pool[layer][page][K|V][nkvh][page_size][head_dim]. Token `pos` of a sequence lives in page
+    table[seq][pos // page_size], slot pos % page_size.
+    """
+
+    def __init__(self, num_pages: int, nkvh: int, head_dim: int, *, page_size: int = 16, nlayer: int = 1,
+                 dtype: DataType = DataType.BF16, device: DeviceType = DeviceType.CPU, device_id: int = 0,
+                 max_seqs: int = 256, max_pages_per_seq: int | None = None):
+        self.num_pages, self.nkvh, self.head_dim = num_pages, nkvh, head_dim
+        self.page_size, self.nlayer, self.dtype = page_size, nlayer, DataType(dtype)
+        self.device, self.device_id = DeviceType(device), device_id
+        self.max_seqs = max_seqs
+        self.max_pages_per_seq = max_pages_per_seq if max_pages_per_seq is not None else num_pages
+        handle = llaisysPagedKV_t()
+        self._kv = None
+        _check(LIB_LLAISYS.llaisysPagedKVCreate(byref(handle), int(device), device_id, int(dtype), nlayer, num_pages,
+                                                page_size, nkvh, head_dim, max_seqs, self.max_pages_per_seq))
+        self._kv = handle
+
+    def close(self) -> None:
+        if self._kv is not None:
+            LIB_LLAISYS.llaisysPagedKVDestroy(self._kv)
+            self._kv = None
+
+    def __del__(self):
+        self.close()
+
+    # ---- block manager ----
+    def add_seq(self) -> int:
+        seq = c_int32(-1)
+        _check(LIB_LLAISYS.llaisysPagedKVSeqAdd(self._kv, byref(seq)))
+        return seq.value
+
+    def reserve(self, seq: int, n_tokens: int) -> None:
+        _check(LIB_LLAISYS.llaisysPagedKVSeqReserve(self._kv, seq, n_tokens))
+
+    def assign_pages(self, seq: int, pages: Sequence[int]) -> None:
+        arr, ptr = _i32(pages)
+        _check(LIB_LLAISYS.llaisysPagedKVSeqAssignPages(self._kv, seq, ptr, arr.size))
+
+    def free_seq(self, seq: int) -> None:
+        _check(LIB_LLAISYS.llaisysPagedKVSeqFree(self._kv, seq))
+
+    def num_free_pages(self) -> int:
+        return int(LIB_LLAISYS.llaisysPagedKVNumFreePages(self._kv))
+
+    def num_seqs(self) -> int:
+        return int(LIB_LLAISYS.llaisysPagedKVNumSeqs(self._kv))
+
+    def seq_num_pages(self, seq: int) -> int:
+        return int(LIB_LLAISYS.llaisysPagedKVSeqNumPages(self._kv, seq))
+
+    def seq_pages(self, seq: int) -> list[int]:
+        n = self.seq_num_pages(seq)
+        if n < 0:
+            raise LlaisysError(Status.NO_SEQ, f"sequence {seq} does not exist")
+        buf = (c_int32 * max(n, 1))()
+        _check(LIB_LLAISYS.llaisysPagedKVSeqPages(self._kv, seq, buf, n))
+        return list(buf[:n])
+
+    # ---- device views ----
+    def pool_ptr(self, layer: int = 0) -> int:
+        return LIB_LLAISYS.llaisysPagedKVPoolData(self._kv, layer)
+
+    def layer_bytes(self) -> int:
+        return int(LIB_LLAISYS.llaisysPagedKVLayerBytes(self._kv))
+
+    def block_table_ptr(self) -> int:
+        return LIB_LLAISYS.llaisysPagedKVBlockTableData(self._kv)
+
+    def flush(self) -> None:
+        _check(LIB_LLAISYS.llaisysPagedKVFlush(self._kv))
+
+    def check(self) -> None:
+        """Synchronises and raises LlaisysError(KERNEL) if a kernel skipped out-of-range metadata."""
+        _check(LIB_LLAISYS.llaisysPagedKVCheck(self._kv))
+
+    # ---- data path: host index arrays ----
+    def append(self, layer: int, k_rows, v_rows, seq_ids, positions) -> None:
+        s, sp = _i32(seq_ids)
+        p, pp = _i32(positions)
+        if s.size != p.size:
+            raise ValueError("seq_ids and positions must have the same length")
+        _check(LIB_LLAISYS.llaisysPagedKVAppend(self._kv, layer, _addr(k_rows), _addr(v_rows), sp, pp, s.size))
+
+    def gather(self, layer: int, seq: int, n_tokens: int, k_out, v_out) -> None:
+        _check(LIB_LLAISYS.llaisysPagedKVGather(self._kv, layer, seq, n_tokens, _addr(k_out), _addr(v_out)))
+
+    def decode(self, layer: int, out, q, seq_ids, kv_lens, nh: int, scale: float) -> None:
+        s, sp = _i32(seq_ids)
+        l, lp = _i32(kv_lens)
+        if s.size != l.size:
+            raise ValueError("seq_ids and kv_lens must have the same length")
+        _check(LIB_LLAISYS.llaisysPagedAttentionDecode(self._kv, layer, _addr(out), _addr(q), sp, lp, s.size, nh,
+                                                       scale))
+
+    def decode_partial(self, layer: int, part, q, seq_ids, kv_lens, nh: int, scale: float) -> None:
+        s, sp = _i32(seq_ids)
+        l, lp = _i32(kv_lens)
+        if s.size != l.size:
+            raise ValueError("seq_ids and kv_lens must have the same length")
+        _check(LIB_LLAISYS.llaisysPagedAttentionDecodePartial(self._kv, layer, _addr(part), _addr(q), sp, lp, s.size,
+                                                              nh, scale))
+
+    def prefill(self, layer: int, out, q, seq_ids, q_lens, kv_lens, nh: int, scale: float) -> None:
+        s, sp = _i32(seq_ids)
+        ql, qlp = _i32(q_lens)
+        l, lp = _i32(kv_lens)
+        if not (s.size == ql.size == l.size):
+            raise ValueError("seq_ids, q_lens and kv_lens must have the same length")
+        _check(LIB_LLAISYS.llaisysPagedAttentionPrefill(self._kv, layer, _addr(out), _addr(q), sp, qlp, lp, s.size,
+                                                        nh, scale))
+
+    # ---- data path: device index arrays, explicit stream ----
+    def append_dev(self, layer: int, k_rows, v_rows, seq_ids_dev, positions_dev, n_rows: int, stream) -> None:
+        _check(LIB_LLAISYS.llaisysPagedKVAppendDev(self._kv, layer, _addr(k_rows), _addr(v_rows), _addr(seq_ids_dev),
+                                                   _addr(positions_dev), n_rows, stream))
+
+    def decode_dev(self, layer: int, out, q, seq_ids_dev, kv_lens_dev, n_seqs: int, max_kv_len: int, nh: int,
+                   scale: float, stream) -> None:
+        _check(LIB_LLAISYS.llaisysPagedAttentionDecodeDev(self._kv, layer, _addr(out), _addr(q), _addr(seq_ids_dev),
+                                                          _addr(kv_lens_dev), n_seqs, max_kv_len, nh, scale, stream))
+
+    def decode_partial_dev(self, layer: int, part, q, seq_ids_dev, kv_lens_dev, n_seqs: int, max_kv_len: int,
+                           nh: int, scale: float, stream) -> None:
+        _check(LIB_LLAISYS.llaisysPagedAttentionDecodePartialDev(self._kv, layer, _addr(part), _addr(q),
+                                                                 _addr(seq_ids_dev), _addr(kv_lens_dev), n_seqs,
+                                                                 max_kv_len, nh, scale, stream))
+
+    def prefill_dev(self, layer: int, out, q, seq_ids_dev, q_starts_dev, kv_lens_dev, n_seqs: int, total_q: int,
+                    max_q_len: int, max_kv_len: int, nh: int, scale: float, stream) -> None:
+        _check(LIB_LLAISYS.llaisysPagedAttentionPrefillDev(self._kv, layer, _addr(out), _addr(q), _addr(seq_ids_dev),
+                                                           _addr(q_starts_dev), _addr(kv_lens_dev), n_seqs, total_q,
+                                                           max_q_len, max_kv_len, nh, scale, stream))
+
+
+def lse_merge(out, parts, n_parts: int, n_rows: int, head_dim: int, *, dtype: DataType,
+              device: DeviceType = DeviceType.CPU, device_id: int = 0) -> None:
+    """Merges n_parts partial results float [n_parts, n_rows, head_dim + 2] into out [n_rows, head_dim]."""
+    _check(LIB_LLAISYS.llaisysLseMerge(int(device), device_id, _addr(out), int(dtype), _addr(parts), n_parts, n_rows,
+                                       head_dim))
