@@ -1,0 +1,268 @@
+"""Paged append / gather / attention through the C ABI against the oracle, on a CPU cache here and -- marked
+gpu -- on a B200. Append and gather must be bit-exact; attention within the bound of the dtype."""
+import numpy as np
+import pytest
+import torch
+
+import llaisys_b200 as llaisys
+from llaisys_b200 import LlaisysError, Status
+from oracle import attention, workloads
+from oracle.paged import PagedCacheModel
+from tests import helpers
+
+CPU, NVIDIA = llaisys.DeviceType.CPU, llaisys.DeviceType.NVIDIA
+
+
+def words(t: torch.Tensor) -> np.ndarray:
+    w = helpers.tensor_words(t).numpy()
+    return w.view(np.uint32 if w.itemsize == 4 else np.uint16)
+
+
+def check_append_gather_bit_exact(device, dname, batch: workloads.DecodeBatch, pool_pages, nlayer=2):
+    dev = helpers.torch_device(device)
+    nkvh, d = batch.k[0].shape[1], batch.k[0].shape[2]
+    cache, seqs = helpers.build_cache(device, dname, batch.pages, num_pages=pool_pages, nkvh=nkvh, d=d, nlayer=nlayer)
+    model = PagedCacheModel(pool_pages, 16, nkvh, d, word_dtype=np.uint32 if dname == "f32" else np.uint16,
+                            max_seqs=len(seqs))
+    for pages in batch.pages:
+        model.assign_pages(model.add_seq(), pages)
+    layer = nlayer - 1
+    # two appends: all but the last row of every sequence (a "prefill"), then the last rows (a "decode step")
+    last = [c - 1 for c in batch.ctx]
+    helpers.append_all(cache, layer, seqs, batch.k, batch.v, device, hi=last)
+    helpers.append_all(cache, layer, seqs, batch.k, batch.v, device, lo=last)
+    for i, s in enumerate(seqs):
+        model.append(words(batch.k[i]), words(batch.v[i]), [i] * batch.ctx[i], range(batch.ctx[i]))
+    for i, s in enumerate(seqs):
+        k_out = torch.empty_like(batch.k[i], device=dev)
+        v_out = torch.empty_like(batch.v[i], device=dev)
+        cache.gather(layer, s, batch.ctx[i], k_out, v_out)
+        cache.check()
+        mk, mv = model.gather(i, batch.ctx[i])
+        assert np.array_equal(words(k_out.cpu()), mk) and np.array_equal(words(v_out.cpu()), mv)
+        assert torch.equal(helpers.tensor_words(k_out.cpu()), helpers.tensor_words(batch.k[i]))
+        assert torch.equal(helpers.tensor_words(v_out.cpu()), helpers.tensor_words(batch.v[i]))
+    # the whole pool, byte for byte, equals the model's (untouched slots stay zero), and layer 0 is untouched
+    pool = torch.empty(cache.layer_bytes(), dtype=torch.uint8)
+    api = llaisys.RuntimeAPI(device)
+    kind = llaisys.MemcpyKind.H2H if device == CPU else llaisys.MemcpyKind.D2H
+    api.memcpy_sync(pool.data_ptr(), cache.pool_ptr(layer), pool.numel(), kind)
+    assert np.array_equal(pool.numpy(), model.pool.reshape(-1).view(np.uint8))
+    api.memcpy_sync(pool.data_ptr(), cache.pool_ptr(0), pool.numel(), kind)
+    assert not pool.any()
+    return cache, seqs
+
+
+def check_decode(device, dname, batch: workloads.DecodeBatch, pool_pages, tol=None):
+    dev = helpers.torch_device(device)
+    nh, d = batch.q.shape[1], batch.q.shape[2]
+    cache, seqs = helpers.build_cache(device, dname, batch.pages, num_pages=pool_pages, nkvh=batch.k[0].shape[1], d=d)
+    helpers.append_all(cache, 0, seqs, batch.k, batch.v, device)
+    out = torch.empty_like(batch.q, device=dev)
+    cache.decode(0, out, batch.q.to(dev), seqs, batch.ctx, nh, batch.scale)
+    cache.check()
+    out = out.cpu()
+    bound = tol or helpers.MAX_ABS[dname]
+    ulp = {"f32": 1e-6, "f16": 1e-3, "bf16": 8e-3}[dname]
+    for i in range(len(seqs)):
+        q = batch.q[i:i + 1]
+        expect = attention.self_attention(q, batch.k[i], batch.v[i], batch.scale)
+        assert helpers.max_abs(out[i:i + 1], expect) <= bound, (i, batch.ctx[i])
+        f64 = attention.self_attention_f64(q, batch.k[i], batch.v[i], batch.scale)
+        assert helpers.max_abs(out[i:i + 1], f64) <= ulp * max(1.0, f64.abs().max().item()), (i, batch.ctx[i])
+    # partial variant + merge over one part reproduces the same result
+    part = torch.empty((len(seqs), nh, d + 2), dtype=torch.float32, device=dev)
+    cache.decode_partial(0, part, batch.q.to(dev), seqs, batch.ctx, nh, batch.scale)
+    merged = torch.empty_like(batch.q, device=dev)
+    llaisys.lse_merge(merged, part, 1, len(seqs) * nh, d, dtype=helpers.LL_DTYPE[dname], device=device)
+    cache.check()
+    assert helpers.max_abs(merged.cpu(), out) <= ulp
+    return cache, seqs
+
+
+def check_prefill(device, dname, batch: workloads.PrefillBatch, pool_pages):
+    dev = helpers.torch_device(device)
+    nh, d = batch.q[0].shape[1], batch.q[0].shape[2]
+    cache, seqs = helpers.build_cache(device, dname, batch.pages, num_pages=pool_pages, nkvh=batch.k[0].shape[1], d=d)
+    # existing context first, then the chunk (appended, then attended causally)
+    helpers.append_all(cache, 0, seqs, batch.k, batch.v, device, hi=batch.context)
+    helpers.append_all(cache, 0, seqs, batch.k, batch.v, device, lo=batch.context)
+    q = torch.cat(batch.q).contiguous()
+    out = torch.empty_like(q, device=dev)
+    q_lens = [batch.chunk] * len(seqs)
+    kv_lens = [c + batch.chunk for c in batch.context]
+    cache.prefill(0, out, q.to(dev), seqs, q_lens, kv_lens, nh, batch.scale)
+    cache.check()
+    out = out.cpu()
+    ulp = {"f32": 1e-6, "f16": 1e-3, "bf16": 8e-3}[dname]
+    for i in range(len(seqs)):
+        got = out[i * batch.chunk:(i + 1) * batch.chunk]
+        expect = attention.self_attention(batch.q[i], batch.k[i], batch.v[i], batch.scale)
+        assert helpers.max_abs(got, expect) <= helpers.MAX_ABS[dname], (i, batch.context[i])
+        f64 = attention.self_attention_f64(batch.q[i], batch.k[i], batch.v[i], batch.scale)
+        assert helpers.max_abs(got, f64) <= ulp * max(1.0, f64.abs().max().item()), (i, batch.context[i])
+
+
+# ---- CPU cache --------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dname", ["bf16", "f16", "f32"])
+def test_append_gather_bit_exact_cpu(dname):
+    batch = workloads.decode_batch(6, 1, 70, seed=11, dtype=helpers.TORCH_DTYPE[dname], pool_pages=64)
+    check_append_gather_bit_exact(CPU, dname, batch, 64)
+
+
+@pytest.mark.parametrize("dname", ["bf16", "f16", "f32"])
+def test_decode_cpu(dname):
+    batch = workloads.decode_batch(5, 1, 90, seed=12, dtype=helpers.TORCH_DTYPE[dname], pool_pages=64)
+    check_decode(CPU, dname, batch, 64)
+
+
+def test_decode_gqa_and_head_dim_variants_cpu():
+    for nh, nkvh, d in ((8, 8, 64), (4, 1, 32), (6, 2, 8)):
+        batch = workloads.decode_batch(3, 1, 40, seed=13, dtype=torch.float32, pool_pages=32, nh=nh, nkvh=nkvh, d=d)
+        check_decode(CPU, "f32", batch, 32)
+
+
+@pytest.mark.parametrize("dname", ["bf16", "f32"])
+def test_prefill_cpu(dname):
+    batch = workloads.prefill_batch(3, 40, 9, seed=14, dtype=helpers.TORCH_DTYPE[dname], pool_pages=32)
+    check_prefill(CPU, dname, batch, 32)
+
+
+def test_prefill_with_empty_context_and_ragged_chunks_cpu():
+    g = torch.Generator().manual_seed(3)
+    cache = llaisys.PagedKVCache(16, 2, 128, dtype=llaisys.DataType.F32, max_seqs=3)
+    seqs, ks, vs, qs, q_lens, kv_lens = [], [], [], [], [1, 5, 0], [33, 5, 0]
+    for ql, kl in zip(q_lens, kv_lens):
+        s = cache.add_seq()
+        cache.reserve(s, kl)
+        seqs.append(s)
+        ks.append(workloads.randn((kl, 2, 128), torch.float32, g))
+        vs.append(workloads.randn((kl, 2, 128), torch.float32, g))
+        qs.append(workloads.randn((ql, 12, 128), torch.float32, g))
+    helpers.append_all(cache, 0, seqs, ks, vs, CPU)
+    q = torch.cat(qs)
+    out = torch.full_like(q, 7.0)
+    cache.prefill(0, out, q, seqs, q_lens, kv_lens, 12, 0.1)
+    at = 0
+    for i, ql in enumerate(q_lens):
+        if ql:
+            assert helpers.max_abs(out[at:at + ql], attention.self_attention(qs[i], ks[i], vs[i], 0.1)) <= 1e-5
+        at += ql
+
+
+def test_data_path_argument_errors_cpu():
+    cache = llaisys.PagedKVCache(8, 2, 128, dtype=llaisys.DataType.BF16, max_seqs=2)
+    s = cache.add_seq()
+    cache.reserve(s, 16)
+    rows = torch.zeros((1, 2, 128), dtype=torch.bfloat16)
+    q = torch.zeros((1, 12, 128), dtype=torch.bfloat16)
+    cases = [
+        (lambda: cache.append(0, rows, rows, [s], [16]), Status.INVALID),        # position beyond reserved pages
+        (lambda: cache.append(0, rows, rows, [s], [-1]), Status.INVALID),
+        (lambda: cache.append(0, rows, rows, [s + 1], [0]), Status.NO_SEQ),      # unknown sequence
+        (lambda: cache.append(1, rows, rows, [s], [0]), Status.INVALID),         # layer out of range
+        (lambda: cache.decode(0, q, q, [s], [17], 12, 1.0), Status.INVALID),     # kv_len beyond capacity
+        (lambda: cache.decode(0, q, q, [s], [1], 11, 1.0), Status.INVALID),      # nh not a multiple of nkvh
+        (lambda: cache.prefill(0, q, q, [s], [2], [1], 12, 1.0), Status.INVALID),  # q_len > kv_len
+        (lambda: cache.gather(0, s, 17, rows, rows), Status.INVALID),
+    ]
+    for call, status in cases:
+        with pytest.raises(LlaisysError) as e:
+            call()
+        assert e.value.status == status
+    cache.append(0, rows, rows, [s], [15])  # still usable after the errors
+    cache.decode(0, q, q, [s], [0], 12, 1.0)  # zero-length context: output is zero, not NaN
+    assert not q.float().abs().any()
+    cache.check()
+
+
+def test_lse_merge_cpu():
+    g = torch.Generator().manual_seed(9)
+    q = workloads.randn((1, 12, 128), torch.float32, g)
+    k = workloads.randn((200, 2, 128), torch.float32, g)
+    v = workloads.randn((200, 2, 128), torch.float32, g)
+    cuts = [0, 0, 50, 127, 200]
+    parts = []
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        o, m, l = attention.partial_attention_f64(q, k[a:b], v[a:b], 0.09)
+        parts.append(torch.cat([o, m[:, None], l[:, None]], dim=1).float())
+    parts = torch.stack(parts).contiguous()  # [P, 12, 130]
+    out = torch.empty((12, 128), dtype=torch.float32)
+    llaisys.lse_merge(out, parts, len(cuts) - 1, 12, 128, dtype=llaisys.DataType.F32)
+    assert helpers.max_abs(out, attention.self_attention_f64(q, k, v, 0.09)[0]) <= 1e-6
+
+
+# ---- NVIDIA cache -----------------------------------------------------------------------------------
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dname", ["bf16", "f16", "f32"])
+def test_append_gather_bit_exact_nvidia(cuda_device, dname):
+    batch = workloads.decode_batch(8, 1, 300, seed=21, dtype=helpers.TORCH_DTYPE[dname], pool_pages=256)
+    check_append_gather_bit_exact(NVIDIA, dname, batch, 256)
+
+
+@pytest.mark.gpu
+def test_append_gather_config2_full_size_nvidia(cuda_device):
+    """Configuration 2 at full size: 32 sequences, ctx ~ U{128..4096}, 16384-page pool, random page permutation."""
+    batch = workloads.config2()
+    check_append_gather_bit_exact(NVIDIA, "bf16", batch, workloads.POOL_PAGES, nlayer=2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dname", ["bf16", "f16", "f32"])
+def test_decode_small_nvidia(cuda_device, dname):
+    batch = workloads.decode_batch(7, 1, 700, seed=22, dtype=helpers.TORCH_DTYPE[dname], pool_pages=512)
+    check_decode(NVIDIA, dname, batch, 512)
+
+
+@pytest.mark.gpu
+def test_decode_config2_full_size_nvidia(cuda_device):
+    check_decode(NVIDIA, "bf16", workloads.config2(), workloads.POOL_PAGES)
+
+
+@pytest.mark.gpu
+def test_decode_gqa_and_head_dim_variants_nvidia(cuda_device):
+    for nh, nkvh, d, dt, dname in ((8, 8, 64, torch.float32, "f32"), (4, 1, 32, torch.float16, "f16"),
+                                   (16, 2, 128, torch.bfloat16, "bf16"), (2, 2, 128, torch.bfloat16, "bf16"),
+                                   (14, 2, 128, torch.float16, "f16")):
+        batch = workloads.decode_batch(4, 1, 600, seed=23, dtype=dt, pool_pages=256, nh=nh, nkvh=nkvh, d=d)
+        check_decode(NVIDIA, dname, batch, 256)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dname", ["bf16", "f32"])
+def test_prefill_small_nvidia(cuda_device, dname):
+    batch = workloads.prefill_batch(4, 300, 37, seed=24, dtype=helpers.TORCH_DTYPE[dname], pool_pages=256)
+    check_prefill(NVIDIA, dname, batch, 256)
+
+
+@pytest.mark.gpu
+def test_prefill_config3_reduced_nvidia(cuda_device):
+    """Configuration 3's shape with a shorter context bound so the CPU oracle finishes in seconds:
+    8 sequences, context ~ U{0..1024}, 512-token chunk."""
+    check_prefill(NVIDIA, "bf16", workloads.prefill_batch(8, 1024, 512, seed=3, pool_pages=2048), 2048)
+
+
+@pytest.mark.gpu
+def test_kernel_flags_bad_metadata_instead_of_faulting_nvidia(cuda_device):
+    """Device-array entry points do no host validation; a position past the block table is skipped and reported
+    by check(), and the cache stays usable."""
+    cache = llaisys.PagedKVCache(8, 2, 128, dtype=llaisys.DataType.BF16, device=NVIDIA, max_seqs=2,
+                                 max_pages_per_seq=2)
+    s = cache.add_seq()
+    cache.reserve(s, 32)
+    cache.flush()
+    rows = torch.ones((2, 2, 128), dtype=torch.bfloat16, device="cuda")
+    ids = torch.tensor([s, s], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([3, 9999], dtype=torch.int32, device="cuda")
+    cache.append_dev(0, rows, rows, ids, pos, 2, llaisys.context_stream())
+    with pytest.raises(LlaisysError) as e:
+        cache.check()
+    assert e.value.status == Status.KERNEL
+    cache.check()  # flag was cleared
+    k_out = torch.empty((4, 2, 128), dtype=torch.bfloat16, device="cuda")
+    v_out = torch.empty_like(k_out)
+    cache.gather(0, s, 4, k_out, v_out)
+    cache.check()
+    assert k_out[3].float().eq(1).all() and not k_out[:3].float().abs().any()
