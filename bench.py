@@ -1,0 +1,385 @@
+"""Benchmark of the paged KV-cache decode path: one step = append one new K/V row per sequence, then
+flash-decoding attention of one query per sequence over its whole paged context (one layer).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload north_star|config2]
+
+Prints ONE JSON line (rank 0). With N > 1 it is launched under torch.distributed.run, one rank per GPU; whole
+sequences are sharded across ranks, each rank owns its page pool, and there is no data-path collective
+(weak scaling: per-GPU work is fixed).
+
+Workloads (synthetic, seeded, N(0,1) bf16; 12 query / 2 kv heads, head_dim 128, 16-token pages, physical pages a
+random permutation of a 16384-page pool):
+  north_star  64 sequences x 4096-token context -- the shape the target "paged decode attention sustaining
+              >= 70 % of HBM peak" is quoted on; uses the whole pool (256 MiB per layer)
+  config2     32 sequences, context ~ U{128..4096}
+
+Numbers:
+  value      tokens/s of the step with inputs resident in HBM, device-timed (CUDA events on the launch stream),
+             max over ranks
+  roofline   achieved HBM GB/s of the decode kernel = algorithmic bytes / its mean event-timed duration
+  e2e        same step through the host-array C-ABI calls with host<->device copies of q, k, v, out in the
+             timed region, wall clock bracketed by device synchronisation
+  cpu_baseline / --impl reference   the reference's CPU definition of the path (oracle port of its PyTorch
+             torch_self_attention) on a bounded sample of the same workload, all host threads
+Between timed steps the layer rotates over pools that together exceed L2 several times, so K/V always comes
+from HBM.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+NH, NKVH, D, PAGE, POOL_PAGES = 12, 2, 128, 16, 16384
+METRIC = "decode tokens/s (paged KV append + flash-decoding attention, one layer)"
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch on the north_star workload, from the ncu
+# capture summarised in profiles/; None until a capture exists.
+NCU_TRAFFIC_BYTES = {"north_star": None, "config2": None}
+
+
+def workload_lengths(name: str, seed: int):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    if name == "north_star":
+        return [4096] * 64
+    if name == "config2":
+        return torch.randint(128, 4097, (32,), generator=g).tolist()
+    raise SystemExit(f"unknown workload {name}")
+
+
+def algorithmic_bytes(ctx: list[int]) -> int:
+    """Bytes one decode launch must move: K and V read once, q read, out written, block-table entries."""
+    b = len(ctx)
+    return sum(ctx) * (2 * NKVH * D * 2) + 2 * b * NH * D * 2 + 4 * sum(-(-c // PAGE) for c in ctx)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            time.sleep(0.06)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(names, r[2:6]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no nvidia-smi samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_cpu_rate(ctx: list[int], seed: int, min_seconds: float, max_seqs: int):
+    """Times the oracle port of the reference's torch_self_attention (reference: test/ops/self_attention.py:11-28),
+    one call per sequence on contiguous bf16 K/V, on a bounded sample of the workload. -> tokens/s, description"""
+    import torch
+
+    from oracle import attention, workloads
+
+    g = torch.Generator().manual_seed(seed)
+    sample = ctx[:max_seqs]
+    qs = [workloads.randn((1, NH, D), torch.bfloat16, g) for _ in sample]
+    ks = [workloads.randn((c, NKVH, D), torch.bfloat16, g) for c in sample]
+    vs = [workloads.randn((c, NKVH, D), torch.bfloat16, g) for c in sample]
+    scale = 1.0 / D ** 0.5
+    attention.self_attention(qs[0], ks[0], vs[0], scale)  # warm-up
+    done, t0 = 0, time.perf_counter()
+    while True:
+        for q, k, v in zip(qs, ks, vs):
+            attention.self_attention(q, k, v, scale)
+        done += len(sample)
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds:
+            break
+    desc = (f"{len(sample)} of {len(ctx)} sequences (ctx {sample[0]}..), {done // len(sample)} passes, "
+            f"{dt:.1f} s, torch {torch.__version__}")
+    return done / dt, dt, desc, torch.get_num_threads()
+
+
+def run_reference_arm(args) -> None:
+    """--impl reference: the reference's own CPU definition of the path on the host cores, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ctx = workload_lengths(args.workload, seed=2)
+    per_step = max(1, min(4, len(ctx)))
+    times, threads, desc = [], 1, ""
+    import torch
+
+    from oracle import attention, workloads
+
+    g = torch.Generator().manual_seed(2)
+    sample = ctx[:per_step]
+    qs = [workloads.randn((1, NH, D), torch.bfloat16, g) for _ in sample]
+    ks = [workloads.randn((c, NKVH, D), torch.bfloat16, g) for c in sample]
+    vs = [workloads.randn((c, NKVH, D), torch.bfloat16, g) for c in sample]
+    scale = 1.0 / D ** 0.5
+    threads = torch.get_num_threads()
+    for step in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        for q, k, v in zip(qs, ks, vs):
+            attention.self_attention(q, k, v, scale)
+        if step >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = per_step * len(times) / total
+    desc = f"each step = {per_step} of the workload's {len(ctx)} sequences (ctx {sample}), bf16, contiguous K/V"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "batch": len(ctx), "heads": "12q/2kv", "head_dim": D},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="north_star", choices=["north_star", "config2"])
+    ap.add_argument("--layers", type=int, default=4, help="pools to rotate over between steps (L2 flush)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+
+    import llaisys_b200 as llaisys
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU stand-in")
+    torch.cuda.set_device(local_rank)
+    dev = llaisys.DeviceType.NVIDIA
+    llaisys.set_context_runtime(dev, local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    # ---- build the workload on this rank's GPU -----------------------------------------------------------
+    ctx = workload_lengths(args.workload, seed=2 + rank)
+    B, layers = len(ctx), args.layers
+    max_pages = max(-(-c // PAGE) for c in ctx)
+    cache = llaisys.PagedKVCache(POOL_PAGES, NKVH, D, nlayer=layers, dtype=llaisys.DataType.BF16, device=dev,
+                                 device_id=local_rank, max_seqs=B, max_pages_per_seq=max_pages)
+    g = torch.Generator().manual_seed(100 + rank)
+    perm = torch.randperm(POOL_PAGES, generator=g).tolist()
+    seqs, at = [], 0
+    for c in ctx:
+        s = cache.add_seq()
+        n = -(-c // PAGE)
+        cache.assign_pages(s, perm[at:at + n])
+        at += n
+        seqs.append(s)
+    cache.flush()
+    stream = torch.cuda.Stream()
+    cg = torch.Generator(device="cuda").manual_seed(200 + rank)
+    seq_ids_dev = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    kv_lens_dev = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+    last_pos_dev = kv_lens_dev - 1
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        # fill every layer's pages: all rows but the last of each sequence (the timed step appends the last)
+        row_seq = torch.repeat_interleave(seq_ids_dev, (kv_lens_dev - 1).long())
+        starts = torch.cumsum(kv_lens_dev - 1, 0) - (kv_lens_dev - 1)
+        row_pos = (torch.arange(row_seq.numel(), device="cuda", dtype=torch.int32)
+                   - torch.repeat_interleave(starts, (kv_lens_dev - 1).long()).int())
+        n_rows = row_seq.numel()
+        for layer in range(layers):
+            k_rows = torch.randn((n_rows, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+            v_rows = torch.randn((n_rows, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+            cache.append_dev(layer, k_rows, v_rows, row_seq, row_pos, n_rows, stream.cuda_stream)
+            stream.synchronize()
+            del k_rows, v_rows
+        q = torch.randn((B, NH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+        k_new = torch.randn((B, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+        v_new = torch.randn((B, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+        out = torch.empty_like(q)
+    stream.synchronize()
+    cache.check()
+    scale = 1.0 / D ** 0.5
+    max_kv = max(ctx)
+
+    def step_device(i: int, ev=None):
+        layer = i % layers
+        if ev is not None:
+            ev[0].record(stream)
+        cache.append_dev(layer, k_new, v_new, seq_ids_dev, last_pos_dev, B, stream.cuda_stream)
+        if ev is not None:
+            ev[1].record(stream)
+        cache.decode_dev(layer, out, q, seq_ids_dev, kv_lens_dev, B, max_kv, NH, scale, stream.cuda_stream)
+        if ev is not None:
+            ev[2].record(stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed region ----------------------------------------------------------------------------------
+    for i in range(args.warmup):
+        step_device(i)
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        t_begin.record(stream)
+        for i in range(args.steps):
+            step_device(args.warmup + i, events[i])
+        t_end.record(stream)
+        stream.synchronize()
+        barrier()
+    cache.check()
+    elapsed_ms = t_begin.elapsed_time(t_end)
+    append_ms = statistics.fmean(e[0].elapsed_time(e[1]) for e in events)
+    decode_ms = statistics.fmean(e[1].elapsed_time(e[2]) for e in events)
+    decode_ms_median = statistics.median(e[1].elapsed_time(e[2]) for e in events)
+
+    # ---- end to end through the host-array API, host buffers, copies inside the timed region ---------------------
+    api = llaisys.RuntimeAPI(dev)
+    ctx_stream = llaisys.context_stream()
+    q_h, k_h, v_h = (t.cpu().pin_memory() for t in (q, k_new, v_new))
+    out_h = torch.empty_like(q_h).pin_memory()
+    q_d, k_d, v_d, out_d = (torch.empty_like(t) for t in (q, k_new, v_new, out))
+    last_pos = [c - 1 for c in ctx]
+    H2D, D2H = llaisys.MemcpyKind.H2D, llaisys.MemcpyKind.D2H
+
+    def step_e2e(i: int):
+        layer = i % layers
+        api.memcpy_async(q_d, q_h, q_h.numel() * 2, H2D, ctx_stream)
+        api.memcpy_async(k_d, k_h, k_h.numel() * 2, H2D, ctx_stream)
+        api.memcpy_async(v_d, v_h, v_h.numel() * 2, H2D, ctx_stream)
+        cache.append(layer, k_d, v_d, seqs, last_pos)
+        cache.decode(layer, out_d, q_d, seqs, ctx, NH, scale)
+        api.memcpy_async(out_h, out_d, out_h.numel() * 2, D2H, ctx_stream)
+        api.stream_synchronize(ctx_stream)  # the step's result is read on the host every step
+
+    e2e_steps = max(10, args.steps // 2)
+    for i in range(3):
+        step_e2e(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        step_e2e(i)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    cache.check()
+    same = torch.equal(out_h.view(torch.int16), out.cpu().view(torch.int16))
+
+    # ---- reduce over ranks ------------------------------------------------------------------------------
+    stats = torch.tensor([elapsed_ms, e2e_s, decode_ms, append_ms, float(sum(ctx))], device="cuda",
+                         dtype=torch.float64)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        elapsed_ms, e2e_s, decode_ms, append_ms = (float(x) for x in mx[:4])
+    total_tokens = B * world
+
+    if rank == 0:
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        if peaks_file.exists():
+            peak, peak_kind = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
+        else:
+            peak, peak_kind = 6650.0, "fallback"
+        bytes_per_launch = algorithmic_bytes(ctx)
+        achieved = bytes_per_launch / (decode_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC,
+            "value": total_tokens * args.steps / (elapsed_ms * 1e-3),
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": B, "context": f"{min(ctx)}..{max(ctx)}",
+                       "heads": "12q/2kv", "head_dim": D, "page_size": PAGE, "pool_pages": POOL_PAGES,
+                       "parallelism": f"sequences sharded over {world} GPU(s), no collective",
+                       "l2": f"inputs larger than L2: layer pool rotates over {layers} x "
+                             f"{cache.layer_bytes() >> 20} MiB between steps"},
+            "roofline": {"bound": "hbm", "kernel": "paged_decode_split_kernel", "achieved": achieved, "peak": peak,
+                         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                         "frac_of_nominal_8000": achieved / 8000.0, "traffic": NCU_TRAFFIC_BYTES[args.workload],
+                         "algorithmic_bytes_per_launch": bytes_per_launch, "kernel_ms_mean": decode_ms,
+                         "kernel_ms_median": decode_ms_median, "append_kernel_ms_mean": append_ms},
+            "e2e": {"value": total_tokens * e2e_steps / e2e_s, "unit": "tokens/s",
+                    "h2d_bytes_per_step": (q_h.numel() + k_h.numel() + v_h.numel()) * 2,
+                    "d2h_bytes_per_step": out_h.numel() * 2, "steps": e2e_steps,
+                    "matches_device_path": bool(same)},
+            "gpu_launches": 2 * args.steps,
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            rate, dt, desc, threads = reference_cpu_rate(ctx, seed=2, min_seconds=10.0, max_seqs=4)
+            line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                    "sample": desc}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
