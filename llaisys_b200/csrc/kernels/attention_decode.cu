@@ -584,9 +584,15 @@ void launch(cudaStream_t s, const DecodeParams &p, int grid, size_t smem) {
     static std::once_flag once[64];
     int dev = 0;
     LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
-    std::call_once(once[dev & 63], [] {
+    std::call_once(once[dev & 63], [dev] {
+        // opt in to the device's full per-block shared memory, less what the kernel holds statically
+        int optin = 0;
+        LLAISYS_CUDA_CHECK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        cudaFuncAttributes attr{};
+        LLAISYS_CUDA_CHECK(cudaFuncGetAttributes(&attr, paged_decode_split_kernel<kBf16>));
         LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_split_kernel<kBf16>,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                optin - int(attr.sharedSizeBytes)));
     });
     paged_decode_split_kernel<kBf16><<<grid, kThreads, smem, s>>>(p);
 }

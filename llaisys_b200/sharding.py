@@ -1,0 +1,71 @@
+"""Multi-GPU partitioning of the KV-cache path, one process per GPU over torch.distributed.
+
+Two modes, matching how the path shards:
+  * a batch of sequences: whole sequences go to ranks (longest-first bin packing); every rank owns its page
+    pool and block tables and there is NO data-path collective;
+  * one very long sequence: the KV range is cut into page-aligned slices, one per rank; each rank runs the
+    partial decode over its slice and the (o, m, l) partials are merged after ONE all-gather
+    (NCCL over NVLink on GPUs, gloo on CPU ranks). Peer data always lands in local memory first; no kernel
+    reads another GPU's memory.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+from .libllaisys import DataType, DeviceType
+from .paged_kv import PagedKVCache, lse_merge
+
+_TORCH_DTYPE = {DataType.F32: torch.float32, DataType.F16: torch.float16, DataType.BF16: torch.bfloat16}
+
+
+def shard_sequences(ctx_lens: Sequence[int], world: int) -> list[list[int]]:
+    """Assigns sequence indices to ranks, longest first onto the least loaded rank (ties: lowest rank)."""
+    loads = [0] * world
+    shards: list[list[int]] = [[] for _ in range(world)]
+    for i in sorted(range(len(ctx_lens)), key=lambda i: (-ctx_lens[i], i)):
+        r = min(range(world), key=lambda r: (loads[r], r))
+        shards[r].append(i)
+        loads[r] += ctx_lens[i]
+    return [sorted(s) for s in shards]
+
+
+def kv_range(total_tokens: int, world: int, rank: int, page_size: int = 16) -> tuple[int, int]:
+    """Token range [lo, hi) of `rank`: page-aligned cuts, pages spread as evenly as possible."""
+    pages = -(-total_tokens // page_size)
+    base, extra = divmod(pages, world)
+    lo_page = rank * base + min(rank, extra)
+    hi_page = lo_page + base + (1 if rank < extra else 0)
+    return min(lo_page * page_size, total_tokens), min(hi_page * page_size, total_tokens)
+
+
+def split_decode(cache: PagedKVCache, layer: int, out: torch.Tensor, q: torch.Tensor, seq_ids: Sequence[int],
+                 local_kv_lens: Sequence[int], nh: int, scale: float, group=None) -> None:
+    """Decode over a KV range split across the ranks of `group`.
+
+    Every rank passes the same q [n_seqs, nh, d] and its LOCAL sequences / lengths (the slice of each sequence
+    its cache holds; 0 is allowed). Each rank computes partials, all ranks gather them, and every rank merges
+    into `out` [n_seqs, nh, d].
+    """
+    n_seqs, d = q.shape[0], q.shape[-1]
+    world = dist.get_world_size(group)
+    part = torch.empty((n_seqs, nh, d + 2), dtype=torch.float32, device=q.device)
+    cache.decode_partial(layer, part, q, seq_ids, local_kv_lens, nh, scale)
+    if cache.device == DeviceType.NVIDIA:
+        # the partial was queued on the library's stream; the collective runs on torch's
+        torch.cuda.current_stream().wait_stream(torch.cuda.ExternalStream(_context_stream()))
+    # [world * n_seqs, nh, d + 2]: rank r's partial occupies rows [r * n_seqs, (r + 1) * n_seqs)
+    gathered = torch.empty((world * n_seqs, nh, d + 2), dtype=torch.float32, device=q.device)
+    dist.all_gather_into_tensor(gathered, part, group=group)
+    if cache.device == DeviceType.NVIDIA:
+        torch.cuda.ExternalStream(_context_stream()).wait_stream(torch.cuda.current_stream())
+    lse_merge(out, gathered, world, n_seqs * nh, d, dtype=cache.dtype, device=cache.device,
+              device_id=cache.device_id)
+
+
+def _context_stream() -> int:
+    from .runtime import context_stream
+
+    return int(context_stream() or 0)
