@@ -30,8 +30,9 @@
 //
 // Rows past a sequence's length inside its last page are zero-filled by the copy (src-size 0), never read
 // from the pool; out-of-range block-table entries are skipped and flagged in the error word.
-#include "device_utils.cuh"
 #include "kernels.hpp"
+#include "decode_epilogue.cuh"
+#include "mma_utils.cuh"
 
 #include <mutex>
 
@@ -72,76 +73,6 @@ struct DecodeParams {
     int32_t *counters; // [n_pairs], zero on entry and on exit
     int32_t *error_flag;
 };
-
-// ---- PTX wrappers ---------------------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, int src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
-    uint32_t d;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
-    return d;
-}
-
-template <bool kBf16>
-__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    if constexpr (kBf16) {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-                     "{%0,%1,%2,%3};\n"
-                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    } else {
-        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-                     "{%0,%1,%2,%3};\n"
-                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-    }
-}
-
-template <bool kBf16>
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    if constexpr (kBf16) {
-        __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-        return *reinterpret_cast<uint32_t *>(&v);
-    } else {
-        __half2 v = __floats2half2_rn(lo, hi);
-        return *reinterpret_cast<uint32_t *>(&v);
-    }
-}
-
-template <bool kBf16>
-__device__ __forceinline__ void store_out(void *out, long long idx, float v) {
-    if constexpr (kBf16) {
-        static_cast<__nv_bfloat16 *>(out)[idx] = __float2bfloat16_rn(v);
-    } else {
-        static_cast<__half *>(out)[idx] = __float2half_rn(v);
-    }
-}
-
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y; // ex2(-inf) = +0
-}
 
 // ---- walking a span of the flattened page list -----------------------------------------------------
 
@@ -503,41 +434,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) paged_decode_split_kerne
         }
 
         if (expected > 1) {
-            __threadfence(); // partial visible device-wide before the arrival is counted
-            __syncthreads();
+            __syncthreads(); // every thread's partial is written
             if (tid == 0) {
+                __threadfence(); // cumulative: publishes the CTA's partial device-wide before the arrival counts
                 const int before = atomicAdd(&p.counters[pair], 1);
                 s_last = (before == expected - 1) ? 1 : 0;
+                __threadfence(); // the other CTAs' partials are visible to this CTA's reads below
             }
             __syncthreads();
             if (s_last) {
-                __threadfence();
                 const float *first = p.partials + (long long)(c_first + pair) * p.group * (kD + 2);
-                for (int h = 0; h < p.group; ++h) {
-                    float m_all = -INFINITY;
-                    for (int i = 0; i < expected; ++i) {
-                        m_all = fmaxf(m_all, __ldcg(first + ((long long)i * p.group + h) * (kD + 2) + kD));
-                    }
-                    float l_all = 0.f, o = 0.f;
-                    for (int i = 0; i < expected; ++i) {
-                        const float *pp = first + ((long long)i * p.group + h) * (kD + 2);
-                        const float mi = __ldcg(pp + kD);
-                        const float wgt = mi == -INFINITY ? 0.f : fast_exp2(mi - m_all);
-                        l_all += __ldcg(pp + kD + 1) * wgt;
-                        o += __ldcg(pp + tid) * wgt;
-                    }
-                    const long long row = (long long)st.s * p.nh + st.kvh * p.group + h;
-                    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-                    if (p.part != nullptr) {
-                        p.part[row * (kD + 2) + tid] = o * inv;
-                        if (tid == 0) {
-                            p.part[row * (kD + 2) + kD] = m_all * 0.6931471805599453f;
-                            p.part[row * (kD + 2) + kD + 1] = l_all;
-                        }
-                    } else {
-                        store_out<kBf16>(p.out, row * kD + tid, o * inv);
-                    }
-                }
+                combine_partials<kBf16>(first, expected, p.group, tid, red_o, [] { __syncthreads(); }, p.out, p.part,
+                                        (long long)st.s * p.nh + st.kvh * p.group);
                 if (tid == 0) {
                     p.counters[pair] = 0; // ready for the next launch
                 }
@@ -551,28 +459,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) paged_decode_split_kerne
 }
 
 // ---- host side --------------------------------------------------------------------------------------
-
-int sm_count() {
-    static int cached[64] = {0};
-    int dev = 0;
-    LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64) {
-        int n = 0;
-        LLAISYS_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
-        return n;
-    }
-    if (cached[dev] == 0) {
-        LLAISYS_CUDA_CHECK(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
-    }
-    return cached[dev];
-}
-
-int decode_grid(int32_t n_seqs, int32_t nkvh, int32_t max_kv_len) {
-    const long long pages_bound = (long long)n_seqs * nkvh * ((max_kv_len + kPage - 1) / kPage);
-    const long long by_work = (pages_bound + kPagesPerStage - 1) / kPagesPerStage; // at least one stage per CTA
-    const long long cap = (long long)kCtasPerSm * sm_count();
-    return int(by_work < 1 ? 1 : (by_work < cap ? by_work : cap));
-}
 
 size_t smem_bytes(int group, int n_seqs) {
     return size_t(kRingBytes) + size_t(kWarps) * group * kD * sizeof(float) + size_t(kWarps) * kMaxGroup * 2 * sizeof(float) +
@@ -599,6 +485,32 @@ void launch(cudaStream_t s, const DecodeParams &p, int grid, size_t smem) {
 
 } // namespace
 
+namespace {
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        int n = 0;
+        LLAISYS_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+        return n;
+    }
+    if (cached[dev] == 0) {
+        LLAISYS_CUDA_CHECK(cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev));
+    }
+    return cached[dev];
+}
+
+} // namespace
+
+int decode_grid_size(int32_t n_seqs, int32_t nkvh, int32_t max_kv_len) {
+    const long long pages_bound = (long long)n_seqs * nkvh * ((max_kv_len + kPage - 1) / kPage);
+    const long long by_work = (pages_bound + kPagesPerStage - 1) / kPagesPerStage; // at least one stage per CTA
+    const long long cap = (long long)kCtasPerSm * sm_count();
+    return int(by_work < 1 ? 1 : (by_work < cap ? by_work : cap));
+}
+
+
 void attention_decode_split_scratch(int32_t n_seqs, int32_t nh, int32_t nkvh, int32_t d, int32_t max_kv_len,
                                     size_t *partials_floats, size_t *counters_len) {
     *partials_floats = 0;
@@ -606,7 +518,7 @@ void attention_decode_split_scratch(int32_t n_seqs, int32_t nh, int32_t nkvh, in
     if (n_seqs <= 0 || nkvh <= 0 || nh <= 0 || d != kD || nh % nkvh != 0) {
         return;
     }
-    const int grid = decode_grid(n_seqs, nkvh, max_kv_len);
+    const int grid = decode_grid_size(n_seqs, nkvh, max_kv_len);
     const size_t n_pairs = size_t(n_seqs) * nkvh;
     *partials_floats = (size_t(grid) + n_pairs) * size_t(nh / nkvh) * (kD + 2);
     *counters_len = n_pairs;
@@ -621,7 +533,7 @@ int attention_decode_split(stream_t stream, llaisysDataType_t dtype, const KVVie
         return -1;
     }
     const int group = batch.nh / kv.nkvh;
-    const int grid = decode_grid(batch.n_seqs, kv.nkvh, batch.max_kv_len);
+    const int grid = decode_grid_size(batch.n_seqs, kv.nkvh, batch.max_kv_len);
     const size_t n_pairs = size_t(batch.n_seqs) * kv.nkvh;
     if (scratch.partials == nullptr || scratch.counters == nullptr || scratch.error_flag == nullptr ||
         scratch.partials_floats < (size_t(grid) + n_pairs) * group * (kD + 2) || scratch.counters_len < n_pairs) {

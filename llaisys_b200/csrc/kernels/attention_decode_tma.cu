@@ -1,0 +1,623 @@
+// K2 + K3 for the page pool, TMA edition: split-KV flash decoding with a warp-specialised copy pipeline.
+//
+// Same mathematics, work decomposition ("even page split" over persistent CTAs, two per SM) and fused
+// log-sum-exp combine as attention_decode.cu; what changes is how K/V reach shared memory and who moves them:
+//   * one PRODUCER warp per CTA walks the CTA's span of pages, reads the block table 32 entries at a time, and
+//     an elected lane issues the copies: each (page, kv-head) is four 2 KiB TMA tiles (K low/high 64 dims, V
+//     low/high 64 dims; cp.async.bulk.tensor.2d over one tensor map that views the whole pool as rows of 128
+//     elements), landing in one 8 KiB slot of a 12-slot ring with the hardware 128-byte swizzle, completion
+//     counted on the slot's "full" mbarrier;
+//   * four CONSUMER warps take pages round-robin: wait on "full", 8 + 8 mma.sync m16n8k16 with conflict-free
+//     ldmatrix reads (the swizzle XORs the 16-byte chunk index with token % 8), then hand the slot back through
+//     its "empty" mbarrier. They execute ~100 instructions per page and never compute an address in global
+//     memory, so the copy engine runs up to 96 KiB ahead of them per CTA (192 KiB per SM in flight).
+// Measured motivation: the cp.async version spent its issue slots on address arithmetic and its time in
+// long-scoreboard stalls behind block-table loads, reaching 45 % of DRAM throughput with 8 warps per SM.
+//
+// Every mbarrier wait is bounded; a wait that runs out sets bit 8 of the error word, the CTA stops touching the
+// ring (its warps still meet at their named barriers) and the launch ends with wrong output and a flagged error
+// instead of a hang. No cluster multicast is used anywhere.
+#include "kernels.hpp"
+#include "decode_epilogue.cuh"
+#include "mma_utils.cuh"
+
+#include <cuda.h>
+
+#include <cstring>
+#include <mutex>
+
+namespace llaisys::kernels {
+
+namespace {
+
+constexpr int kConsumerWarps = 4;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32; // + the producer warp
+constexpr int kSlots = 12;
+constexpr int kPage = 16;
+constexpr int kD = 128;
+constexpr int kHalfTileBytes = kPage * 64 * 2;  // 2 KiB: 16 tokens x 64 dims
+constexpr int kTileBytes = 2 * kHalfTileBytes;  // K (or V) of one page and kv-head
+constexpr int kSlotBytes = 2 * kTileBytes;      // 8 KiB
+constexpr int kRingBytes = kSlots * kSlotBytes; // 96 KiB
+constexpr int kMaxGroup = 8;
+constexpr int kMaxSeqs = 1024;
+constexpr int kCtasPerSm = 2;
+constexpr uint32_t kWaitLimit = 1u << 22; // polls before a wait gives up (well under a second)
+constexpr int kErrTimeout = 8;
+static_assert(kConsumerThreads == kD, "the pair epilogue maps one consumer thread to one output dimension");
+
+struct TmaDecodeParams {
+    long long row0;             // first tensor-map row of this layer
+    const int32_t *block_table; // [rows][table_stride]
+    int32_t table_stride, num_pages, max_tokens;
+    const int32_t *seq_ids;
+    const int32_t *kv_lens;
+    int32_t n_seqs, nkvh, group, nh;
+    const void *q;
+    void *out;
+    float *part;
+    float scale_log2;
+    float *partials;
+    int32_t *counters;
+    int32_t *error_flag;
+};
+
+struct Cursor {
+    int s, kvh, j, np, kv_len, remaining;
+};
+
+struct Segment {
+    int s, kvh, j0, n, kv_len; // pages [j0, j0 + n) of pair (s, kvh): the piece of the pair inside this span
+};
+
+__device__ __forceinline__ int seq_kv_len(const TmaDecodeParams &p, int s) {
+    return min(max(p.kv_lens[s], 0), p.max_tokens);
+}
+
+__device__ __forceinline__ Segment next_segment(Cursor &c, const int *cum, const TmaDecodeParams &p) {
+    Segment sg;
+    sg.s = c.s;
+    sg.kvh = c.kvh;
+    sg.j0 = c.j;
+    sg.kv_len = c.kv_len;
+    sg.n = min(c.np - c.j, c.remaining);
+    c.j += sg.n;
+    c.remaining -= sg.n;
+    if (c.j == c.np && c.remaining > 0) {
+        c.j = 0;
+        if (++c.kvh == p.nkvh) {
+            c.kvh = 0;
+            do { // remaining > 0 guarantees a later sequence with pages; the bound only guards the walk
+                ++c.s;
+                c.np = cum[c.s + 1] - cum[c.s];
+            } while (c.np == 0 && c.s + 1 < p.n_seqs);
+            c.kv_len = seq_kv_len(p, c.s);
+        }
+    }
+    return sg;
+}
+
+// Polls a barrier phase; gives up after kWaitLimit polls or when another warp of the CTA already gave up.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+        if ((i & 1023u) == 1023u && *abort_flag != 0) {
+            return false;
+        }
+    }
+    return false;
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+    paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, TmaDecodeParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    // the 128-byte swizzle is a function of the shared-memory address: slots must start on 1 KiB boundaries
+    const uint32_t raw_u32 = smem_u32(smem_raw);
+    const uint32_t ring_u32 = (raw_u32 + 1023u) & ~1023u;
+    unsigned char *aligned = smem_raw + (ring_u32 - raw_u32);
+    float *red_o = reinterpret_cast<float *>(aligned + kRingBytes);                       // [warps][group][kD]
+    float *red_ml = red_o + kConsumerWarps * p.group * kD;                                // [warps][kMaxGroup][2]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(red_ml + kConsumerWarps * kMaxGroup * 2); // full[kSlots], empty[kSlots]
+    int *cum = reinterpret_cast<int *>(bars + 2 * kSlots);                                // [n_seqs + 1]
+    __shared__ int s_last;
+    __shared__ int s_abort;
+    const uint32_t bars_u32 = smem_u32(bars);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        for (int i = 0; i < 2 * kSlots; ++i) {
+            mbar_init(bars_u32 + i * 8, 1);
+        }
+        s_abort = 0;
+        mbar_init_fence();
+    }
+    // -- prefix sums of page counts (warp 0) -------------------------------------------------------------
+    if (warp == 0) {
+        int running = 0;
+        if (lane == 0) {
+            cum[0] = 0;
+        }
+        for (int base = 0; base < p.n_seqs; base += 32) {
+            const int s = base + lane;
+            int np = 0;
+            if (s < p.n_seqs) {
+                np = (seq_kv_len(p, s) + kPage - 1) / kPage;
+            }
+            int incl = np;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) {
+                    incl += up;
+                }
+            }
+            if (s < p.n_seqs) {
+                cum[s + 1] = running + incl;
+            }
+            running += __shfl_sync(0xffffffffu, incl, 31);
+        }
+    }
+    __syncthreads();
+
+    const int n_pairs = p.n_seqs * p.nkvh;
+    const long long total = (long long)cum[p.n_seqs] * p.nkvh;
+    const int span = int((total + gridDim.x - 1) / gridDim.x);
+    const long long x0 = (long long)blockIdx.x * span;
+    const long long x1 = min(total, x0 + span);
+
+    // -- sequences without any token: the output row is zero (partial: o = 0, m = -inf, l = 0) ----------
+    if (tid < kD) {
+        for (int pair = blockIdx.x; pair < n_pairs; pair += gridDim.x) {
+            const int s = pair / p.nkvh, kvh = pair - s * p.nkvh;
+            if (cum[s + 1] - cum[s] != 0) {
+                continue;
+            }
+            for (int h = 0; h < p.group; ++h) {
+                const long long row = (long long)s * p.nh + kvh * p.group + h;
+                if (p.part != nullptr) {
+                    p.part[row * (kD + 2) + tid] = 0.f;
+                    if (tid == 0) {
+                        p.part[row * (kD + 2) + kD] = -INFINITY;
+                        p.part[row * (kD + 2) + kD + 1] = 0.f;
+                    }
+                } else {
+                    store_out<kBf16>(p.out, row * kD + tid, 0.f);
+                }
+            }
+        }
+    }
+    if (x0 >= x1) {
+        return;
+    }
+
+    // -- first page of the span ----------------------------------------------------------------------------
+    Cursor cur;
+    {
+        int lo = 0, hi = p.n_seqs - 1;
+        while (lo < hi) { // last s with cum[s] * nkvh <= x0; it owns page x0 and is never an empty sequence
+            const int mid = (lo + hi + 1) >> 1;
+            if ((long long)cum[mid] * p.nkvh <= x0) {
+                lo = mid;
+            } else {
+                hi = mid - 1;
+            }
+        }
+        cur.s = lo;
+        cur.np = cum[lo + 1] - cum[lo];
+        const int r = int(x0 - (long long)cum[lo] * p.nkvh);
+        cur.kvh = r / cur.np;
+        cur.j = r - cur.kvh * cur.np;
+        cur.kv_len = seq_kv_len(p, lo);
+        cur.remaining = int(x1 - x0);
+    }
+
+    // ======================================= producer warp ================================================
+    if (warp == kConsumerWarps) {
+        int n = 0; // pages issued so far; page n uses slot n % kSlots for the (n / kSlots)-th time
+        bool dead = false;
+        while (cur.remaining > 0 && !dead) {
+            const Segment sg = next_segment(cur, cum, p);
+            if (sg.n <= 0) {
+                break; // inconsistent lengths: the consumers flag it
+            }
+            const int seq_row = p.seq_ids ? p.seq_ids[sg.s] : sg.s;
+            const long long tbase = (long long)seq_row * p.table_stride + sg.j0;
+            for (int base = 0; base < sg.n && !dead; base += 32) {
+                int page = 0;
+                if (base + lane < sg.n) {
+                    page = p.block_table[tbase + base + lane];
+                    if (page < 0 || page >= p.num_pages) {
+                        atomicOr(p.error_flag, kErrBadPage);
+                        page = 0;
+                    }
+                }
+                const int cnt = min(32, sg.n - base);
+                for (int l = 0; l < cnt; ++l) {
+                    const int pg = __shfl_sync(0xffffffffu, page, l);
+                    int ok = 1;
+                    if (lane == 0) {
+                        const int slot = n % kSlots, use = n / kSlots;
+                        const uint32_t full_bar = bars_u32 + slot * 8, empty_bar = bars_u32 + (kSlots + slot) * 8;
+                        if (use > 0 && !wait_or_abort(empty_bar, uint32_t(use - 1) & 1u, &s_abort)) {
+                            ok = 0;
+                        } else {
+                            mbar_arrive_expect_tx(full_bar, kSlotBytes);
+                            const int row_k = int(p.row0 + ((long long)pg * 2 * p.nkvh + sg.kvh) * kPage);
+                            const int row_v = row_k + p.nkvh * kPage;
+                            const uint32_t dst = ring_u32 + slot * kSlotBytes;
+                            tma_load_2d(dst, &tmap, 0, row_k, full_bar);
+                            tma_load_2d(dst + kHalfTileBytes, &tmap, 64, row_k, full_bar);
+                            tma_load_2d(dst + kTileBytes, &tmap, 0, row_v, full_bar);
+                            tma_load_2d(dst + kTileBytes + kHalfTileBytes, &tmap, 64, row_v, full_bar);
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) {
+                        dead = true;
+                        break;
+                    }
+                    ++n;
+                }
+            }
+        }
+        if (dead && lane == 0) {
+            s_abort = 1;
+            atomicOr(p.error_flag, kErrTimeout);
+            // wait (bounded) for the copies this warp still has in flight before the CTA may exit
+            for (int back = 1; back <= kSlots && back <= n; ++back) {
+                const int m = n - back;
+                mbar_wait_bounded(bars_u32 + (m % kSlots) * 8, uint32_t(m / kSlots) & 1u, kWaitLimit);
+            }
+        }
+        return;
+    }
+
+    // ======================================= consumer warps ===============================================
+    const int g = lane >> 2, q4 = lane & 3; // MMA fragment coordinates: row group, column pair
+    // ldmatrix row addresses. A tile is [half (64 dims)][16 tokens][128 B] with chunk' = chunk ^ (token % 8):
+    //   K (not transposed): lane supplies token lm_r + 8 * (mi & 1), chunk 2 * ks + (mi >> 1)
+    //   V (transposed):     lane supplies token lm_r + 8 * (mi >> 1), chunk 2 * mt + (mi & 1)
+    const int lm_r = lane & 7, lm_mi = lane >> 3;
+    const int k_tok = lm_r + 8 * (lm_mi & 1), k_cc0 = lm_mi >> 1;
+    const int v_tok = lm_r + 8 * (lm_mi >> 1), v_cc0 = lm_mi & 1;
+
+    float m2[2], l[2], o_acc[8][4];
+    uint32_t qf[8][2];
+    auto reset_state = [&]() {
+        m2[0] = m2[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+            o_acc[mt][0] = o_acc[mt][1] = o_acc[mt][2] = o_acc[mt][3] = 0.f;
+        }
+    };
+    reset_state();
+
+    int n_base = 0;
+    bool dead = false;
+    while (cur.remaining > 0) {
+        const Segment sg = next_segment(cur, cum, p);
+        if (sg.n <= 0) { // cannot happen with consistent lengths; leave rather than spin (uniform over the CTA)
+            if (tid == 0) {
+                atomicOr(p.error_flag, kErrBadSeq);
+            }
+            break;
+        }
+        {
+            // query fragments of this pair: B operand [k = dim][n = head], head g of the group (zero beyond it)
+            const uint32_t *q_row = reinterpret_cast<const uint32_t *>(
+                static_cast<const char *>(p.q) + ((long long)sg.s * p.nh + sg.kvh * p.group + g) * (kD * 2));
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                qf[ks][0] = g < p.group ? q_row[ks * 8 + q4] : 0u;
+                qf[ks][1] = g < p.group ? q_row[ks * 8 + 4 + q4] : 0u;
+            }
+        }
+
+        for (int i = warp; i < sg.n && !dead; i += kConsumerWarps) {
+            const int n = n_base + i;
+            const int slot = n % kSlots, use = n / kSlots;
+            const uint32_t full_bar = bars_u32 + slot * 8, empty_bar = bars_u32 + (kSlots + slot) * 8;
+            if (!wait_or_abort(full_bar, uint32_t(use) & 1u, &s_abort)) {
+                dead = true;
+                if (lane == 0) {
+                    s_abort = 1;
+                    atomicOr(p.error_flag, kErrTimeout);
+                }
+                break;
+            }
+            const uint32_t tile = ring_u32 + slot * kSlotBytes;
+            const int n_valid = min(kPage, sg.kv_len - (sg.j0 + i) * kPage);
+            if (n_valid < kPage) {
+                // Rows past the sequence's end hold whatever the page held before. K rows are neutralised by the
+                // score mask; V rows are cleared here so that 0 * garbage cannot make a NaN.
+                const int chunks = (kPage - n_valid) * 16;
+                for (int c = lane; c < chunks; c += 32) {
+                    const int r = n_valid + (c >> 4), cc = c & 15;
+                    const uint32_t a = tile + kTileBytes + (cc >> 3) * kHalfTileBytes + r * 128 + ((cc & 7) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(a), "r"(0u) : "memory");
+                }
+                __syncwarp();
+            }
+            // S^T = K . Q^T
+            float sc[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t k_row = tile + k_tok * 128;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a[4];
+                ldmatrix_x4(a, k_row + (ks >> 2) * kHalfTileBytes + ((((2 * ks + k_cc0) & 7) ^ lm_r) << 4));
+                mma_16816<kBf16>(sc, a, qf[ks][0], qf[ks][1]);
+            }
+            // online softmax in the log2 domain; this thread holds tokens g, g + 8 for heads 2*q4, 2*q4 + 1
+            const bool ok_lo = g < n_valid, ok_hi = g + 8 < n_valid;
+            const float t0 = ok_lo ? sc[0] * p.scale_log2 : -INFINITY;
+            const float t1 = ok_lo ? sc[1] * p.scale_log2 : -INFINITY;
+            const float t2 = ok_hi ? sc[2] * p.scale_log2 : -INFINITY;
+            const float t3 = ok_hi ? sc[3] * p.scale_log2 : -INFINITY;
+            float mx0 = fmaxf(t0, t2), mx1 = fmaxf(t1, t3);
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+            }
+            const float mn0 = fmaxf(m2[0], mx0), mn1 = fmaxf(m2[1], mx1);
+            const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float a0 = fast_exp2(m2[0] - ref0), a1 = fast_exp2(m2[1] - ref1);
+            const float p0 = fast_exp2(t0 - ref0), p1 = fast_exp2(t1 - ref1);
+            const float p2 = fast_exp2(t2 - ref0), p3 = fast_exp2(t3 - ref1);
+            l[0] = l[0] * a0 + p0 + p2;
+            l[1] = l[1] * a1 + p1 + p3;
+            m2[0] = mn0;
+            m2[1] = mn1;
+            if (__any_sync(0xffffffffu, a0 != 1.f || a1 != 1.f)) {
+#pragma unroll
+                for (int mt = 0; mt < 8; ++mt) {
+                    o_acc[mt][0] *= a0;
+                    o_acc[mt][1] *= a1;
+                    o_acc[mt][2] *= a0;
+                    o_acc[mt][3] *= a1;
+                }
+            }
+            // P as the B operand [k = token][n = head]: transpose the C-fragment pairs across the warp
+            const uint32_t b0 = movmatrix_trans(pack2<kBf16>(p0, p1));
+            const uint32_t b1 = movmatrix_trans(pack2<kBf16>(p2, p3));
+            // O^T += V^T . P
+            const uint32_t v_row = tile + kTileBytes + v_tok * 128;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, v_row + (mt >> 2) * kHalfTileBytes + ((((2 * mt + v_cc0) & 7) ^ lm_r) << 4));
+                mma_16816<kBf16>(o_acc[mt], a, b0, b1);
+            }
+            // hand the slot back: every lane's reads are done once the warp has converged here
+            if (n_valid < kPage) {
+                fence_proxy_async_smem(); // the cleared rows were ordinary stores; the next writer is the TMA unit
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(empty_bar);
+            }
+        }
+        n_base += sg.n;
+
+        // -- the pair (or this span's piece of it) is done: merge the consumer warps, then publish --------------
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            l[0] += __shfl_xor_sync(0xffffffffu, l[0], o);
+            l[1] += __shfl_xor_sync(0xffffffffu, l[1], o);
+        }
+        if (g == 0) {
+            red_ml[(warp * kMaxGroup + 2 * q4) * 2 + 0] = m2[0];
+            red_ml[(warp * kMaxGroup + 2 * q4) * 2 + 1] = l[0];
+            red_ml[(warp * kMaxGroup + 2 * q4 + 1) * 2 + 0] = m2[1];
+            red_ml[(warp * kMaxGroup + 2 * q4 + 1) * 2 + 1] = l[1];
+        }
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int head = 2 * q4 + (e & 1);
+                if (head < p.group) {
+                    red_o[(warp * p.group + head) * kD + mt * 16 + g + 8 * (e >> 1)] = o_acc[mt][e];
+                }
+            }
+        }
+        named_barrier_sync(1, kConsumerThreads);
+
+        const int pair = sg.s * p.nkvh + sg.kvh;
+        const int pair_np = cum[sg.s + 1] - cum[sg.s];
+        const long long pair_off = (long long)cum[sg.s] * p.nkvh + (long long)sg.kvh * pair_np;
+        const int c_first = int(pair_off / span), c_last = int((pair_off + pair_np - 1) / span);
+        const int expected = c_last - c_first + 1;
+        float *slot_out = p.partials + (long long)(blockIdx.x + pair) * p.group * (kD + 2);
+
+        // consumer thread `tid` owns output dimension `tid` of every head of the group
+        for (int h = 0; h < p.group; ++h) {
+            float m_all = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                m_all = fmaxf(m_all, red_ml[(w * kMaxGroup + h) * 2]);
+            }
+            float l_all = 0.f, o = 0.f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                const float mw = red_ml[(w * kMaxGroup + h) * 2];
+                const float wgt = mw == -INFINITY ? 0.f : fast_exp2(mw - m_all);
+                l_all += red_ml[(w * kMaxGroup + h) * 2 + 1] * wgt;
+                o += red_o[(w * p.group + h) * kD + tid] * wgt;
+            }
+            if (expected == 1) {
+                const long long row = (long long)sg.s * p.nh + sg.kvh * p.group + h;
+                const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+                if (p.part != nullptr) {
+                    p.part[row * (kD + 2) + tid] = o * inv;
+                    if (tid == 0) {
+                        p.part[row * (kD + 2) + kD] = m_all * 0.6931471805599453f; // log2 units -> natural log
+                        p.part[row * (kD + 2) + kD + 1] = l_all;
+                    }
+                } else {
+                    store_out<kBf16>(p.out, row * kD + tid, o * inv);
+                }
+            } else {
+                slot_out[h * (kD + 2) + tid] = o; // un-normalised, relative to m_all
+                if (tid == 0) {
+                    slot_out[h * (kD + 2) + kD] = m_all;
+                    slot_out[h * (kD + 2) + kD + 1] = l_all;
+                }
+            }
+        }
+
+        if (expected > 1) {
+            named_barrier_sync(1, kConsumerThreads); // every thread's partial is written
+            if (tid == 0) {
+                __threadfence(); // cumulative: publishes the CTA's partial device-wide before the arrival counts
+                const int before = atomicAdd(&p.counters[pair], 1);
+                s_last = (before == expected - 1) ? 1 : 0;
+                __threadfence(); // the other CTAs' partials are visible to this CTA's reads below
+            }
+            named_barrier_sync(1, kConsumerThreads);
+            if (s_last) {
+                const float *first = p.partials + (long long)(c_first + pair) * p.group * (kD + 2);
+                combine_partials<kBf16>(first, expected, p.group, tid, red_o, [] { named_barrier_sync(1, kConsumerThreads); }, p.out, p.part,
+                                        (long long)sg.s * p.nh + sg.kvh * p.group);
+                if (tid == 0) {
+                    p.counters[pair] = 0; // ready for the next launch
+                }
+            }
+        }
+        reset_state();
+        // red_o / red_ml are next written after this pair's readers have passed the barrier below
+        named_barrier_sync(1, kConsumerThreads);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) != cudaSuccess ||
+            res != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            return EncodeTiledFn(nullptr);
+        }
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+size_t smem_bytes(int group, int n_seqs) {
+    return 1024 + size_t(kRingBytes) + size_t(kConsumerWarps) * group * kD * sizeof(float) +
+           size_t(kConsumerWarps) * kMaxGroup * 2 * sizeof(float) + 2 * kSlots * sizeof(uint64_t) +
+           size_t(n_seqs + 1) * sizeof(int);
+}
+
+template <bool kBf16>
+void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, int grid, size_t smem) {
+    static std::once_flag once[64];
+    int dev = 0;
+    LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
+    std::call_once(once[dev & 63], [dev] {
+        int optin = 0;
+        LLAISYS_CUDA_CHECK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        cudaFuncAttributes attr{};
+        LLAISYS_CUDA_CHECK(cudaFuncGetAttributes(&attr, paged_decode_tma_kernel<kBf16>));
+        LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tma_kernel<kBf16>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                optin - int(attr.sharedSizeBytes)));
+    });
+    paged_decode_tma_kernel<kBf16><<<grid, kThreads, smem, s>>>(tmap, p);
+}
+
+} // namespace
+
+int make_kv_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, llaisysDataType_t dtype) {
+    if (dtype != LLAISYS_DTYPE_BF16 && dtype != LLAISYS_DTYPE_F16) {
+        return -1;
+    }
+    // rows are addressed with 32-bit coordinates; the base must satisfy the TMA's 16-byte rule
+    if (total_rows == 0 || total_rows >= (uint64_t(1) << 31) || reinterpret_cast<uintptr_t>(pool_base) % 16 != 0) {
+        return -1;
+    }
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (encode == nullptr) {
+        return -1;
+    }
+    // The pool seen as rows of 128 elements (256 B): one row per (layer, page, K|V, kv-head, slot). A box is
+    // 64 elements x 16 rows = one half of a tile; the 128-byte swizzle permutes 16-byte chunks by row % 8.
+    const cuuint64_t dims[2] = {cuuint64_t(kD), cuuint64_t(total_rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(kD * 2)};
+    const cuuint32_t box[2] = {64, cuuint32_t(kPage)};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    CUtensorMap map;
+    const CUresult rc =
+        encode(&map, dtype == LLAISYS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+               pool_base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        return -1;
+    }
+    static_assert(sizeof(CUtensorMap) == 128, "tensor map blob size");
+    memcpy(out_128_bytes, &map, sizeof(map));
+    return 0;
+}
+
+int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
+                         const void *q, float scale, const AttnOut &out, const AttnScratch &scratch) {
+    const bool bf16 = dtype == LLAISYS_DTYPE_BF16;
+    if (kv.tma_desc == nullptr || !(bf16 || dtype == LLAISYS_DTYPE_F16) || kv.d != kD || kv.page_size != kPage ||
+        kv.nkvh <= 0 || kv.block_table == nullptr || batch.kv_lens == nullptr || batch.nh % kv.nkvh != 0 ||
+        batch.nh / kv.nkvh > kMaxGroup || batch.q_starts != nullptr || batch.const_q_len != 1 || batch.n_seqs <= 0 ||
+        batch.n_seqs > kMaxSeqs || reinterpret_cast<uintptr_t>(q) % 4 != 0) {
+        return -1;
+    }
+    const int group = batch.nh / kv.nkvh;
+    const int grid = decode_grid_size(batch.n_seqs, kv.nkvh, batch.max_kv_len);
+    const size_t n_pairs = size_t(batch.n_seqs) * kv.nkvh;
+    if (scratch.partials == nullptr || scratch.counters == nullptr || scratch.error_flag == nullptr ||
+        scratch.partials_floats < (size_t(grid) + n_pairs) * group * (kD + 2) || scratch.counters_len < n_pairs) {
+        return -1;
+    }
+    TmaDecodeParams p;
+    p.row0 = kv.tma_row0;
+    p.block_table = kv.block_table;
+    p.table_stride = kv.table_stride;
+    p.num_pages = kv.num_pages;
+    p.max_tokens = kv.table_stride * kPage;
+    p.seq_ids = batch.seq_ids;
+    p.kv_lens = batch.kv_lens;
+    p.n_seqs = batch.n_seqs;
+    p.nkvh = kv.nkvh;
+    p.group = group;
+    p.nh = batch.nh;
+    p.q = q;
+    p.out = out.out;
+    p.part = out.part;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.partials = scratch.partials;
+    p.counters = scratch.counters;
+    p.error_flag = scratch.error_flag;
+    CUtensorMap tmap;
+    memcpy(&tmap, kv.tma_desc, sizeof(tmap));
+    const size_t smem = smem_bytes(group, batch.n_seqs);
+    auto s = static_cast<cudaStream_t>(stream);
+    if (bf16) {
+        launch<true>(s, tmap, p, grid, smem);
+    } else {
+        launch<false>(s, tmap, p, grid, smem);
+    }
+    check_launch("paged_decode_tma");
+    return 0;
+}
+
+} // namespace llaisys::kernels

@@ -1,0 +1,102 @@
+// Last-arriver side of the split-KV combine, shared by the decode kernels.
+//
+// A (sequence, kv-head) pair that was cut across E CTAs leaves E partial results, slot i holding for every head
+// h of the group the un-normalised output o_i,h[128] relative to its own max m_i,h (log2 units) and sum l_i,h:
+//     float [E][group][130]   (o[128], m, l)
+// The CTA whose arrival completes the pair merges them:  M = max_i m_i,  w_i = 2^(m_i - M),
+//     out = sum_i w_i o_i / sum_i w_i l_i.
+// Latency matters more than arithmetic here (each dependent L2 read costs ~0.5 us and the merge sits on the
+// kernel's critical path), so the loads are batched: all (m, l) of up to 256 parts are staged in shared memory
+// in one round trip, then every thread (one output dimension each) accumulates o with 4 parts x `group` heads of
+// independent loads in flight. More than 256 parts are folded in chunks with a running (M, L, O).
+#pragma once
+
+#include "mma_utils.cuh"
+
+namespace llaisys::kernels {
+
+constexpr int kCombineChunk = 256; // parts staged per round; needs 2 * kCombineChunk * group floats of staging
+
+// All `n_threads` (== 128 == head_dim) threads of the merging group call this; `sync` is their barrier.
+// stage: shared memory, at least 2 * kCombineChunk * group floats. out_row0: index of head 0's output row.
+template <bool kBf16, typename Sync>
+__device__ __forceinline__ void combine_partials(const float *first, int expected, int group, int tid, float *stage,
+                                                 Sync sync, void *out, float *part, long long out_row0) {
+    constexpr int kD = 128, kMaxGroup = 8, kStride = kD + 2;
+    float m_run[kMaxGroup], l_run[kMaxGroup], o_run[kMaxGroup];
+#pragma unroll
+    for (int h = 0; h < kMaxGroup; ++h) {
+        m_run[h] = -INFINITY;
+        l_run[h] = 0.f;
+        o_run[h] = 0.f;
+    }
+    float *m_s = stage, *l_s = stage + kCombineChunk * group;
+    for (int c0 = 0; c0 < expected; c0 += kCombineChunk) {
+        const int ce = min(kCombineChunk, expected - c0);
+        sync(); // staging area free (previous chunk, or the caller's last use)
+        for (int idx = tid; idx < ce * group; idx += kD) {
+            const float *pp = first + (long long)(c0 * group + idx) * kStride;
+            m_s[idx] = __ldcg(pp + kD);
+            l_s[idx] = __ldcg(pp + kD + 1);
+        }
+        sync();
+        // fold this chunk's maxima into the running ones
+#pragma unroll
+        for (int h = 0; h < kMaxGroup; ++h) {
+            if (h < group) {
+                float cm = -INFINITY;
+                for (int i = 0; i < ce; ++i) {
+                    cm = fmaxf(cm, m_s[i * group + h]);
+                }
+                const float nm = fmaxf(m_run[h], cm);
+                const float sc = (m_run[h] == -INFINITY) ? 0.f : fast_exp2(m_run[h] - nm);
+                l_run[h] *= sc;
+                o_run[h] *= sc;
+                m_run[h] = nm;
+            }
+        }
+        // accumulate: 4 parts x group heads of independent loads per round
+        for (int i0 = 0; i0 < ce; i0 += 4) {
+            float v[4][kMaxGroup];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int h = 0; h < kMaxGroup; ++h) {
+                    v[u][h] = (i0 + u < ce && h < group)
+                                  ? __ldcg(first + (long long)((c0 + i0 + u) * group + h) * kStride + tid)
+                                  : 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int h = 0; h < kMaxGroup; ++h) {
+                    if (i0 + u < ce && h < group) {
+                        const float mi = m_s[(i0 + u) * group + h];
+                        const float w = (mi == -INFINITY) ? 0.f : fast_exp2(mi - m_run[h]);
+                        l_run[h] = fmaf(l_s[(i0 + u) * group + h], w, l_run[h]);
+                        o_run[h] = fmaf(v[u][h], w, o_run[h]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < kMaxGroup; ++h) {
+        if (h < group) {
+            const long long row = out_row0 + h;
+            const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+            if (part != nullptr) {
+                part[row * kStride + tid] = o_run[h] * inv;
+                if (tid == 0) {
+                    part[row * kStride + kD] = m_run[h] * 0.6931471805599453f; // log2 units -> natural log
+                    part[row * kStride + kD + 1] = l_run[h];
+                }
+            } else {
+                store_out<kBf16>(out, row * kD + tid, o_run[h] * inv);
+            }
+        }
+    }
+}
+
+} // namespace llaisys::kernels

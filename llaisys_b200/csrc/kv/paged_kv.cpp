@@ -9,6 +9,7 @@
 #endif
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <sstream>
@@ -72,6 +73,11 @@ PagedKV::PagedKV(const PagedKVConfig &cfg) : _cfg(cfg) {
         kernels::fill_zero(rt.stream(), _table_dev->memory(), _table_dev->size());
         kernels::fill_zero(rt.stream(), _error_dev->memory(), _error_dev->size());
         rt.synchronize();
+        if (_elem == 2 && cfg.head_dim == 128 && cfg.page_size == 16) {
+            // one row of 128 elements per (layer, page, K|V, kv-head, slot)
+            const uint64_t rows = uint64_t(cfg.nlayer) * cfg.num_pages * 2 * cfg.nkvh * cfg.page_size;
+            _has_tma = kernels::make_kv_tensor_map(_tma_desc, _pool->memory(), rows, cfg.dtype) == 0;
+        }
 #endif
     } else {
         std::memset(_pool->memory(), 0, _pool->size());
@@ -237,6 +243,10 @@ kernels::KVView PagedKV::view(size_t layer) const {
     v.num_pages = int32_t(_cfg.num_pages);
     v.nkvh = int32_t(_cfg.nkvh);
     v.d = int32_t(_cfg.head_dim);
+    if (_has_tma) {
+        v.tma_desc = _tma_desc;
+        v.tma_row0 = int64_t(layer) * int64_t(_cfg.num_pages * 2 * _cfg.nkvh * _cfg.page_size);
+    }
     return v;
 }
 
@@ -561,9 +571,18 @@ void run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const
                           const kernels::AttnBatch &batch, const void *q, float scale, const kernels::AttnOut &out,
                           const kernels::AttnScratch &scratch) {
     const bool one_query_each = batch.q_starts == nullptr && batch.const_q_len == 1;
-    if (one_query_each && scratch.counters != nullptr &&
-        kernels::attention_decode_split(stream, dtype, view, batch, q, scale, out, scratch) == 0) {
-        return;
+    if (one_query_each && scratch.counters != nullptr) {
+        // LLAISYS_DECODE_PATH=cp_async keeps page pools on the cp.async kernel (for A/B measurements)
+        static const bool allow_tma = [] {
+            const char *e = std::getenv("LLAISYS_DECODE_PATH");
+            return !(e != nullptr && std::string(e) == "cp_async");
+        }();
+        if (allow_tma && kernels::attention_decode_tma(stream, dtype, view, batch, q, scale, out, scratch) == 0) {
+            return;
+        }
+        if (kernels::attention_decode_split(stream, dtype, view, batch, q, scale, out, scratch) == 0) {
+            return;
+        }
     }
     kernels::attention_generic(stream, dtype, view, batch, q, scale, out, scratch.error_flag);
 }

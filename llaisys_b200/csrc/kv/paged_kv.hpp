@@ -108,6 +108,10 @@ private:
     core::storage_t _pool, _table_dev, _error_dev, _meta_dev, _partials, _counters;
     size_t _meta_cap = 0, _partials_floats = 0, _counters_len = 0;
     std::vector<int32_t> _stage_buf;
+
+    // TMA view of the pool (NVIDIA, 16-bit, head_dim 128, page 16 only); _has_tma is false otherwise
+    alignas(64) unsigned char _tma_desc[128] = {};
+    bool _has_tma = false;
 };
 
 // Picks the kernel for a batch on an NVIDIA device and queues it: split-KV decode or tensor-core prefill where
