@@ -520,7 +520,7 @@ void attention_decode_split_scratch(int32_t n_seqs, int32_t nh, int32_t nkvh, in
     }
     const int grid = decode_grid_size(n_seqs, nkvh, max_kv_len);
     const size_t n_pairs = size_t(n_seqs) * nkvh;
-    *partials_floats = (size_t(grid) + n_pairs) * size_t(nh / nkvh) * (kD + 2);
+    *partials_floats = (size_t(grid) + n_pairs) * size_t(nh / nkvh) * (kD + 4); // the TMA kernel pads rows to 132
     *counters_len = n_pairs;
 }
 

@@ -32,10 +32,13 @@ namespace {
 
 constexpr int kConsumerWarps = 4;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32; // + the producer warp
+constexpr int kProducerWarp = kConsumerWarps;      // warp 4 issues the copies
+constexpr int kEpilogueWarp = kConsumerWarps + 1;  // warp 5 counts arrivals and merges cut pairs
+constexpr int kThreads = kConsumerThreads + 64;
 constexpr int kSlots = 12;
 constexpr int kPage = 16;
 constexpr int kD = 128;
+constexpr int kPartStride = kD + 4; // floats per (part, head): o[128], m, l, 2 pad (16-byte rows)
 constexpr int kHalfTileBytes = kPage * 64 * 2;  // 2 KiB: 16 tokens x 64 dims
 constexpr int kTileBytes = 2 * kHalfTileBytes;  // K (or V) of one page and kv-head
 constexpr int kSlotBytes = 2 * kTileBytes;      // 8 KiB
@@ -121,9 +124,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     unsigned char *aligned = smem_raw + (ring_u32 - raw_u32);
     float *red_o = reinterpret_cast<float *>(aligned + kRingBytes);                       // [warps][group][kD]
     float *red_ml = red_o + kConsumerWarps * p.group * kD;                                // [warps][kMaxGroup][2]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(red_ml + kConsumerWarps * kMaxGroup * 2); // full[kSlots], empty[kSlots]
-    int *cum = reinterpret_cast<int *>(bars + 2 * kSlots);                                // [n_seqs + 1]
-    __shared__ int s_last;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(red_ml + kConsumerWarps * kMaxGroup * 2); // full[], empty[], epi_ready, epi_done
+    int *cum = reinterpret_cast<int *>(bars + 2 * kSlots + 2);                                // [n_seqs + 1]
     __shared__ int s_abort;
     const uint32_t bars_u32 = smem_u32(bars);
 
@@ -133,6 +135,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         for (int i = 0; i < 2 * kSlots; ++i) {
             mbar_init(bars_u32 + i * 8, 1);
         }
+        mbar_init(bars_u32 + 2 * kSlots * 8, kConsumerThreads); // epi_ready: every consumer thread arrives
+        mbar_init(bars_u32 + (2 * kSlots + 1) * 8, 1);          // epi_done: the epilogue warp's lane 0
         s_abort = 0;
         mbar_init_fence();
     }
@@ -217,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     }
 
     // ======================================= producer warp ================================================
-    if (warp == kConsumerWarps) {
+    if (warp == kProducerWarp) {
         int n = 0; // pages issued so far; page n uses slot n % kSlots for the (n / kSlots)-th time
         bool dead = false;
         while (cur.remaining > 0 && !dead) {
@@ -277,6 +281,57 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         return;
     }
 
+    // ======================================= epilogue warp ================================================
+    // Walks the same segments as everyone else. For a pair that is cut across CTAs it waits until the consumers
+    // have written this CTA's partial, publishes it (fence + arrival count) and, if this was the last arrival,
+    // merges all partials of the pair -- off the consumers' critical path, so the ring keeps draining meanwhile.
+    const uint32_t epi_ready = bars_u32 + 2 * kSlots * 8, epi_done = bars_u32 + (2 * kSlots + 1) * 8;
+    if (warp == kEpilogueWarp) {
+        int k = 0; // cut segments handled so far
+        while (cur.remaining > 0) {
+            const Segment sg = next_segment(cur, cum, p);
+            if (sg.n <= 0) {
+                break;
+            }
+            const int pair = sg.s * p.nkvh + sg.kvh;
+            const int pair_np = cum[sg.s + 1] - cum[sg.s];
+            const long long pair_off = (long long)cum[sg.s] * p.nkvh + (long long)sg.kvh * pair_np;
+            const int c_first = int(pair_off / span), c_last = int((pair_off + pair_np - 1) / span);
+            const int expected = c_last - c_first + 1;
+            if (expected == 1) {
+                continue; // the consumers wrote the final output themselves
+            }
+            if (!wait_or_abort(epi_ready, uint32_t(k) & 1u, &s_abort)) {
+                if (lane == 0) {
+                    s_abort = 1;
+                    atomicOr(p.error_flag, kErrTimeout);
+                }
+                break;
+            }
+            int last = 0;
+            if (lane == 0) {
+                __threadfence(); // cumulative: the consumers' partial, ordered before by the mbarrier, goes device-wide
+                last = (atomicAdd(&p.counters[pair], 1) == expected - 1) ? 1 : 0;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence(); // the other CTAs' partials are visible to the reads below
+                const float *first = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
+                warp_combine_partials<kBf16>(first, expected, p.group, lane, p.out, p.part,
+                                             (long long)sg.s * p.nh + sg.kvh * p.group);
+                if (lane == 0) {
+                    p.counters[pair] = 0; // ready for the next launch
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(epi_done);
+            }
+            ++k;
+        }
+        return;
+    }
+
     // ======================================= consumer warps ===============================================
     const int g = lane >> 2, q4 = lane & 3; // MMA fragment coordinates: row group, column pair
     // ldmatrix row addresses. A tile is [half (64 dims)][16 tokens][128 B] with chunk' = chunk ^ (token % 8):
@@ -298,7 +353,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     };
     reset_state();
 
-    int n_base = 0;
+    int n_base = 0, n_cut = 0; // pages consumed so far; cut segments handed to the epilogue warp so far
     bool dead = false;
     while (cur.remaining > 0) {
         const Segment sg = next_segment(cur, cum, p);
@@ -434,7 +489,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         const long long pair_off = (long long)cum[sg.s] * p.nkvh + (long long)sg.kvh * pair_np;
         const int c_first = int(pair_off / span), c_last = int((pair_off + pair_np - 1) / span);
         const int expected = c_last - c_first + 1;
-        float *slot_out = p.partials + (long long)(blockIdx.x + pair) * p.group * (kD + 2);
+        float *slot_out = p.partials + (long long)(blockIdx.x + pair) * p.group * kPartStride;
 
         // consumer thread `tid` owns output dimension `tid` of every head of the group
         for (int h = 0; h < p.group; ++h) {
@@ -464,31 +519,27 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                     store_out<kBf16>(p.out, row * kD + tid, o * inv);
                 }
             } else {
-                slot_out[h * (kD + 2) + tid] = o; // un-normalised, relative to m_all
+                slot_out[h * kPartStride + tid] = o; // un-normalised, relative to m_all
                 if (tid == 0) {
-                    slot_out[h * (kD + 2) + kD] = m_all;
-                    slot_out[h * (kD + 2) + kD + 1] = l_all;
+                    slot_out[h * kPartStride + kD] = m_all;
+                    slot_out[h * kPartStride + kD + 1] = l_all;
                 }
             }
         }
 
         if (expected > 1) {
-            named_barrier_sync(1, kConsumerThreads); // every thread's partial is written
-            if (tid == 0) {
-                __threadfence(); // cumulative: publishes the CTA's partial device-wide before the arrival counts
-                const int before = atomicAdd(&p.counters[pair], 1);
-                s_last = (before == expected - 1) ? 1 : 0;
-                __threadfence(); // the other CTAs' partials are visible to this CTA's reads below
-            }
-            named_barrier_sync(1, kConsumerThreads);
-            if (s_last) {
-                const float *first = p.partials + (long long)(c_first + pair) * p.group * (kD + 2);
-                combine_partials<kBf16>(first, expected, p.group, tid, red_o, [] { named_barrier_sync(1, kConsumerThreads); }, p.out, p.part,
-                                        (long long)sg.s * p.nh + sg.kvh * p.group);
-                if (tid == 0) {
-                    p.counters[pair] = 0; // ready for the next launch
+            // Hand the pair to the epilogue warp and carry on with the next pages. It must have finished the
+            // previous cut pair first (the two barriers advance one phase per pair); that wait is normally over
+            // long before, since a merge takes microseconds and a segment tens of them.
+            if (n_cut > 0 && !dead && !wait_or_abort(epi_done, uint32_t(n_cut - 1) & 1u, &s_abort)) {
+                dead = true;
+                if (lane == 0) {
+                    s_abort = 1;
+                    atomicOr(p.error_flag, kErrTimeout);
                 }
             }
+            mbar_arrive(epi_ready); // release: this thread's partial stores are ordered before the epilogue's fence
+            ++n_cut;
         }
         reset_state();
         // red_o / red_ml are next written after this pair's readers have passed the barrier below
@@ -518,7 +569,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 size_t smem_bytes(int group, int n_seqs) {
     return 1024 + size_t(kRingBytes) + size_t(kConsumerWarps) * group * kD * sizeof(float) +
-           size_t(kConsumerWarps) * kMaxGroup * 2 * sizeof(float) + 2 * kSlots * sizeof(uint64_t) +
+           size_t(kConsumerWarps) * kMaxGroup * 2 * sizeof(float) + (2 * kSlots + 2) * sizeof(uint64_t) +
            size_t(n_seqs + 1) * sizeof(int);
 }
 
@@ -585,7 +636,7 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
     const int grid = decode_grid_size(batch.n_seqs, kv.nkvh, batch.max_kv_len);
     const size_t n_pairs = size_t(batch.n_seqs) * kv.nkvh;
     if (scratch.partials == nullptr || scratch.counters == nullptr || scratch.error_flag == nullptr ||
-        scratch.partials_floats < (size_t(grid) + n_pairs) * group * (kD + 2) || scratch.counters_len < n_pairs) {
+        scratch.partials_floats < (size_t(grid) + n_pairs) * group * kPartStride || scratch.counters_len < n_pairs) {
         return -1;
     }
     TmaDecodeParams p;

@@ -99,4 +99,77 @@ __device__ __forceinline__ void combine_partials(const float *first, int expecte
     }
 }
 
+
+// Warp edition for partials laid out float [E][group][132] (o[128], m, l, 2 pad: 16-byte aligned rows): lane j owns
+// output dimensions 4j .. 4j+3 of every head. Two parts x `group` heads of 16-byte loads are in flight per round.
+template <bool kBf16>
+__device__ __forceinline__ void warp_combine_partials(const float *first, int expected, int group, int lane, void *out,
+                                                      float *part, long long out_row0) {
+    constexpr int kD = 128, kMaxGroup = 8, kStride = kD + 4, kOutStride = kD + 2;
+    float m_run[kMaxGroup], l_run[kMaxGroup];
+    float4 o_run[kMaxGroup];
+#pragma unroll
+    for (int h = 0; h < kMaxGroup; ++h) {
+        m_run[h] = -INFINITY;
+        l_run[h] = 0.f;
+        o_run[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int i0 = 0; i0 < expected; i0 += 2) {
+        float4 v[2][kMaxGroup];
+        float2 ml[2][kMaxGroup];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+            for (int h = 0; h < kMaxGroup; ++h) {
+                if (i0 + u < expected && h < group) {
+                    const float *pp = first + (long long)((i0 + u) * group + h) * kStride;
+                    v[u][h] = __ldcg(reinterpret_cast<const float4 *>(pp) + lane);
+                    ml[u][h] = __ldcg(reinterpret_cast<const float2 *>(pp + kD));
+                } else {
+                    v[u][h] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    ml[u][h] = make_float2(-INFINITY, 0.f);
+                }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < kMaxGroup; ++h) {
+            if (h < group) {
+                const float nm = fmaxf(m_run[h], fmaxf(ml[0][h].x, ml[1][h].x));
+                const float ref = nm == -INFINITY ? 0.f : nm;
+                const float sc = fast_exp2(m_run[h] - ref); // 2^(-inf) = 0 on the first round
+                const float w0 = fast_exp2(ml[0][h].x - ref), w1 = fast_exp2(ml[1][h].x - ref);
+                l_run[h] = l_run[h] * sc + ml[0][h].y * w0 + ml[1][h].y * w1;
+                o_run[h].x = o_run[h].x * sc + v[0][h].x * w0 + v[1][h].x * w1;
+                o_run[h].y = o_run[h].y * sc + v[0][h].y * w0 + v[1][h].y * w1;
+                o_run[h].z = o_run[h].z * sc + v[0][h].z * w0 + v[1][h].z * w1;
+                o_run[h].w = o_run[h].w * sc + v[0][h].w * w0 + v[1][h].w * w1;
+                m_run[h] = nm;
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < kMaxGroup; ++h) {
+        if (h < group) {
+            const long long row = out_row0 + h;
+            const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+            const float r[4] = {o_run[h].x * inv, o_run[h].y * inv, o_run[h].z * inv, o_run[h].w * inv};
+            if (part != nullptr) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    part[row * kOutStride + lane * 4 + e] = r[e];
+                }
+                if (lane == 0) {
+                    part[row * kOutStride + kD] = m_run[h] * 0.6931471805599453f; // log2 units -> natural log
+                    part[row * kOutStride + kD + 1] = l_run[h];
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    store_out<kBf16>(out, row * kD + lane * 4 + e, r[e]);
+                }
+            }
+        }
+    }
+}
+
 } // namespace llaisys::kernels
