@@ -101,54 +101,73 @@ __device__ __forceinline__ void combine_partials(const float *first, int expecte
 
 
 // Warp edition for partials laid out float [E][group][132] (o[128], m, l, 2 pad: 16-byte aligned rows): lane j owns
-// output dimensions 4j .. 4j+3 of every head. Two parts x `group` heads of 16-byte loads are in flight per round.
-template <bool kBf16>
-__device__ __forceinline__ void warp_combine_partials(const float *first, int expected, int group, int lane, void *out,
-                                                      float *part, long long out_row0) {
-    constexpr int kD = 128, kMaxGroup = 8, kStride = kD + 4, kOutStride = kD + 2;
-    float m_run[kMaxGroup], l_run[kMaxGroup];
-    float4 o_run[kMaxGroup];
+// output dimensions 4j .. 4j+3 of every head. A dependent read of another SM's freshly written partial costs about
+// a microsecond, so a round keeps kParts parts x kHeads heads of 16-byte loads in flight per lane (the common cut,
+// 2-4 pieces per pair, merges in ONE round trip); the (m, l) scalars of a round are loaded one per lane and
+// broadcast with shuffles instead of occupying kParts * kHeads more registers.
+template <bool kBf16, int kHeads, int kParts>
+__device__ __forceinline__ void warp_combine_impl(const float *first, int expected, int group, int lane, void *out,
+                                                  float *part, long long out_row0) {
+    constexpr int kD = 128, kStride = kD + 4, kOutStride = kD + 2;
+    static_assert(kHeads * kParts <= 32, "one (m, l) pair per lane per round");
+    float m_run[kHeads], l_run[kHeads];
+    float4 o_run[kHeads];
 #pragma unroll
-    for (int h = 0; h < kMaxGroup; ++h) {
+    for (int h = 0; h < kHeads; ++h) {
         m_run[h] = -INFINITY;
         l_run[h] = 0.f;
         o_run[h] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (int i0 = 0; i0 < expected; i0 += 2) {
-        float4 v[2][kMaxGroup];
-        float2 ml[2][kMaxGroup];
+    for (int i0 = 0; i0 < expected; i0 += kParts) {
+        float4 v[kParts][kHeads];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < kParts; ++u) {
 #pragma unroll
-            for (int h = 0; h < kMaxGroup; ++h) {
-                if (i0 + u < expected && h < group) {
-                    const float *pp = first + (long long)((i0 + u) * group + h) * kStride;
-                    v[u][h] = __ldcg(reinterpret_cast<const float4 *>(pp) + lane);
-                    ml[u][h] = __ldcg(reinterpret_cast<const float2 *>(pp + kD));
-                } else {
-                    v[u][h] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    ml[u][h] = make_float2(-INFINITY, 0.f);
-                }
+            for (int h = 0; h < kHeads; ++h) {
+                v[u][h] = (i0 + u < expected && h < group)
+                              ? __ldcg(reinterpret_cast<const float4 *>(first + (long long)((i0 + u) * group + h) * kStride) + lane)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        // lane u * kHeads + h fetches (m, l) of part i0 + u, head h
+        float2 ml = make_float2(-INFINITY, 0.f);
+        {
+            const int u = lane / kHeads, h = lane - u * kHeads;
+            if (u < kParts && i0 + u < expected && h < group) {
+                ml = __ldcg(reinterpret_cast<const float2 *>(first + (long long)((i0 + u) * group + h) * kStride + kD));
             }
         }
 #pragma unroll
-        for (int h = 0; h < kMaxGroup; ++h) {
-            if (h < group) {
-                const float nm = fmaxf(m_run[h], fmaxf(ml[0][h].x, ml[1][h].x));
-                const float ref = nm == -INFINITY ? 0.f : nm;
-                const float sc = fast_exp2(m_run[h] - ref); // 2^(-inf) = 0 on the first round
-                const float w0 = fast_exp2(ml[0][h].x - ref), w1 = fast_exp2(ml[1][h].x - ref);
-                l_run[h] = l_run[h] * sc + ml[0][h].y * w0 + ml[1][h].y * w1;
-                o_run[h].x = o_run[h].x * sc + v[0][h].x * w0 + v[1][h].x * w1;
-                o_run[h].y = o_run[h].y * sc + v[0][h].y * w0 + v[1][h].y * w1;
-                o_run[h].z = o_run[h].z * sc + v[0][h].z * w0 + v[1][h].z * w1;
-                o_run[h].w = o_run[h].w * sc + v[0][h].w * w0 + v[1][h].w * w1;
-                m_run[h] = nm;
+        for (int h = 0; h < kHeads; ++h) {
+            float mi[kParts], li[kParts];
+            float nm = m_run[h];
+#pragma unroll
+            for (int u = 0; u < kParts; ++u) {
+                mi[u] = __shfl_sync(0xffffffffu, ml.x, u * kHeads + h);
+                li[u] = __shfl_sync(0xffffffffu, ml.y, u * kHeads + h);
+                nm = fmaxf(nm, mi[u]);
             }
+            const float ref = nm == -INFINITY ? 0.f : nm;
+            const float sc = fast_exp2(m_run[h] - ref); // 2^(-inf) = 0 on the first round
+            l_run[h] *= sc;
+            o_run[h].x *= sc;
+            o_run[h].y *= sc;
+            o_run[h].z *= sc;
+            o_run[h].w *= sc;
+#pragma unroll
+            for (int u = 0; u < kParts; ++u) {
+                const float w = fast_exp2(mi[u] - ref);
+                l_run[h] = fmaf(li[u], w, l_run[h]);
+                o_run[h].x = fmaf(v[u][h].x, w, o_run[h].x);
+                o_run[h].y = fmaf(v[u][h].y, w, o_run[h].y);
+                o_run[h].z = fmaf(v[u][h].z, w, o_run[h].z);
+                o_run[h].w = fmaf(v[u][h].w, w, o_run[h].w);
+            }
+            m_run[h] = nm;
         }
     }
 #pragma unroll
-    for (int h = 0; h < kMaxGroup; ++h) {
+    for (int h = 0; h < kHeads; ++h) {
         if (h < group) {
             const long long row = out_row0 + h;
             const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
@@ -169,6 +188,18 @@ __device__ __forceinline__ void warp_combine_partials(const float *first, int ex
                 }
             }
         }
+    }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ void warp_combine_partials(const float *first, int expected, int group, int lane, void *out,
+                                                      float *part, long long out_row0) {
+    if (group <= 4) {
+        warp_combine_impl<kBf16, 4, 4>(first, expected, group, lane, out, part, out_row0);
+    } else if (group <= 6) {
+        warp_combine_impl<kBf16, 6, 4>(first, expected, group, lane, out, part, out_row0);
+    } else {
+        warp_combine_impl<kBf16, 8, 2>(first, expected, group, lane, out, part, out_row0);
     }
 }
 
