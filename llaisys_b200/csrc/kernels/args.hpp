@@ -27,10 +27,10 @@ struct KVView {
     int32_t num_pages = 0; // physical pages addressable through this view (bounds check)
     int32_t nkvh = 0;
     int32_t d = 0;
-    // Optional TMA view of the same memory (page pools only): a 128-byte tensor-map blob in HOST memory that sees
-    // the pool as rows of 128 elements, and the row index of this layer's (page 0, K, kv-head 0, slot 0).
+    // Optional TMA view of the same memory (page pools only): a 128-byte tensor-map blob in HOST memory over the
+    // whole multi-layer pool, and the index of this layer's page 0 in it (layer * num_pages).
     const void *tma_desc = nullptr;
-    int64_t tma_row0 = 0;
+    int64_t tma_page0 = 0;
 };
 
 // Which queries attend to which sequences. Arrays live on the executing device; a null array selects the

@@ -30,28 +30,34 @@ namespace llaisys::kernels {
 
 namespace {
 
-constexpr int kConsumerWarps = 4;
+#ifndef LLAISYS_DECODE_CONSUMER_WARPS
+#define LLAISYS_DECODE_CONSUMER_WARPS 4
+#endif
+constexpr int kConsumerWarps = LLAISYS_DECODE_CONSUMER_WARPS; // 4 (two CTAs per SM) or 8 (one CTA per SM)
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kProducerWarp = kConsumerWarps;      // warp 4 issues the copies
 constexpr int kEpilogueWarp = kConsumerWarps + 1;  // warp 5 counts arrivals and merges cut pairs
 constexpr int kThreads = kConsumerThreads + 64;
-constexpr int kSlots = 12;
+constexpr int kSlots = 3 * kConsumerWarps;
+constexpr int kIssueLanes = kSlots < 32 ? kSlots : 32; // producer lanes that issue copies in one round
 constexpr int kPage = 16;
 constexpr int kD = 128;
 constexpr int kPartStride = kD + 4; // floats per (part, head): o[128], m, l, 2 pad (16-byte rows)
-constexpr int kHalfTileBytes = kPage * 64 * 2;  // 2 KiB: 16 tokens x 64 dims
-constexpr int kTileBytes = 2 * kHalfTileBytes;  // K (or V) of one page and kv-head
-constexpr int kSlotBytes = 2 * kTileBytes;      // 8 KiB
+// A ring slot holds one page of one kv-head as the two TMA boxes leave it: [dims 0-63 | dims 64-127][K | V][16 tokens][128 B]
+constexpr int kQuarterBytes = kPage * 64 * 2;   // 2 KiB: 16 tokens x 64 dims of K (or V)
+constexpr int kHalfBytes = 2 * kQuarterBytes;   // 4 KiB: one box = K and V, 64 dims
+constexpr int kSlotBytes = 2 * kHalfBytes;      // 8 KiB
 constexpr int kRingBytes = kSlots * kSlotBytes; // 96 KiB
 constexpr int kMaxGroup = 8;
 constexpr int kMaxSeqs = 1024;
-constexpr int kCtasPerSm = 2;
+constexpr int kCtasPerSm = 8 / kConsumerWarps;
 constexpr uint32_t kWaitLimit = 1u << 22; // polls before a wait gives up (well under a second)
 constexpr int kErrTimeout = 8;
-static_assert(kConsumerThreads == kD, "the pair epilogue maps one consumer thread to one output dimension");
+constexpr int kDimGroups = kConsumerThreads / kD; // the pair epilogue maps a consumer thread to one output
+static_assert(kConsumerThreads % kD == 0, "dimension and to every kDimGroups-th head of the group");
 
 struct TmaDecodeParams {
-    long long row0;             // first tensor-map row of this layer
+    long long page0;            // layer * num_pages: first page of this layer in the tensor map
     const int32_t *block_table; // [rows][table_stride]
     int32_t table_stride, num_pages, max_tokens;
     const int32_t *seq_ids;
@@ -231,42 +237,40 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             }
             const int seq_row = p.seq_ids ? p.seq_ids[sg.s] : sg.s;
             const long long tbase = (long long)seq_row * p.table_stride + sg.j0;
-            for (int base = 0; base < sg.n && !dead; base += 32) {
-                int page = 0;
-                if (base + lane < sg.n) {
-                    page = p.block_table[tbase + base + lane];
+            for (int base = 0; base < sg.n && !dead; base += kIssueLanes) {
+                // One page per lane: kIssueLanes lanes fetch their table entries in one coalesced read and each lane
+                // issues the copies of its own page, so the per-instruction latency of TMA issue is paid once
+                // per 32 pages instead of once per page. A lane whose slot is still in use spins on that slot's
+                // "empty" barrier; the lanes ahead of it have already issued, and the consumers free slots in
+                // page order, so every wait ends. No more lanes than ring slots take part in a round: two lanes
+                // on one slot would wait for consecutive phases of the same barrier, and a parity wait cannot tell
+                // phase k + 1 from phase k - 1.
+                const bool active = lane < kIssueLanes && base + lane < sg.n;
+                int ok = 1;
+                if (active) {
+                    int page = p.block_table[tbase + base + lane];
                     if (page < 0 || page >= p.num_pages) {
                         atomicOr(p.error_flag, kErrBadPage);
                         page = 0;
                     }
-                }
-                const int cnt = min(32, sg.n - base);
-                for (int l = 0; l < cnt; ++l) {
-                    const int pg = __shfl_sync(0xffffffffu, page, l);
-                    int ok = 1;
-                    if (lane == 0) {
-                        const int slot = n % kSlots, use = n / kSlots;
-                        const uint32_t full_bar = bars_u32 + slot * 8, empty_bar = bars_u32 + (kSlots + slot) * 8;
-                        if (use > 0 && !wait_or_abort(empty_bar, uint32_t(use - 1) & 1u, &s_abort)) {
-                            ok = 0;
-                        } else {
-                            mbar_arrive_expect_tx(full_bar, kSlotBytes);
-                            const int row_k = int(p.row0 + ((long long)pg * 2 * p.nkvh + sg.kvh) * kPage);
-                            const int row_v = row_k + p.nkvh * kPage;
-                            const uint32_t dst = ring_u32 + slot * kSlotBytes;
-                            tma_load_2d(dst, &tmap, 0, row_k, full_bar);
-                            tma_load_2d(dst + kHalfTileBytes, &tmap, 64, row_k, full_bar);
-                            tma_load_2d(dst + kTileBytes, &tmap, 0, row_v, full_bar);
-                            tma_load_2d(dst + kTileBytes + kHalfTileBytes, &tmap, 64, row_v, full_bar);
-                        }
+                    const int mine = n + lane;
+                    const int slot = mine % kSlots, use = mine / kSlots;
+                    const uint32_t full_bar = bars_u32 + slot * 8, empty_bar = bars_u32 + (kSlots + slot) * 8;
+                    if (use > 0 && !wait_or_abort(empty_bar, uint32_t(use - 1) & 1u, &s_abort)) {
+                        ok = 0;
+                    } else {
+                        mbar_arrive_expect_tx(full_bar, kSlotBytes);
+                        const int c3 = int((p.page0 + page) * 2); // (page, K) ; the box also takes (page, V)
+                        const uint32_t dst = ring_u32 + slot * kSlotBytes;
+                        tma_load_4d(dst, &tmap, 0, 0, sg.kvh, c3, full_bar);
+                        tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, sg.kvh, c3, full_bar);
                     }
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) {
-                        dead = true;
-                        break;
-                    }
-                    ++n;
                 }
+                if (__any_sync(0xffffffffu, ok == 0)) {
+                    dead = true;
+                    break;
+                }
+                n += min(kIssueLanes, sg.n - base);
             }
         }
         if (dead && lane == 0) {
@@ -394,7 +398,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 const int chunks = (kPage - n_valid) * 16;
                 for (int c = lane; c < chunks; c += 32) {
                     const int r = n_valid + (c >> 4), cc = c & 15;
-                    const uint32_t a = tile + kTileBytes + (cc >> 3) * kHalfTileBytes + r * 128 + ((cc & 7) << 4);
+                    const uint32_t a = tile + kQuarterBytes + (cc >> 3) * kHalfBytes + r * 128 + ((cc & 7) << 4);
                     asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(a), "r"(0u) : "memory");
                 }
                 __syncwarp();
@@ -405,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 uint32_t a[4];
-                ldmatrix_x4(a, k_row + (ks >> 2) * kHalfTileBytes + ((((2 * ks + k_cc0) & 7) ^ lm_r) << 4));
+                ldmatrix_x4(a, k_row + (ks >> 2) * kHalfBytes + ((((2 * ks + k_cc0) & 7) ^ lm_r) << 4));
                 mma_16816<kBf16>(sc, a, qf[ks][0], qf[ks][1]);
             }
             // online softmax in the log2 domain; this thread holds tokens g, g + 8 for heads 2*q4, 2*q4 + 1
@@ -442,11 +446,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             const uint32_t b0 = movmatrix_trans(pack2<kBf16>(p0, p1));
             const uint32_t b1 = movmatrix_trans(pack2<kBf16>(p2, p3));
             // O^T += V^T . P
-            const uint32_t v_row = tile + kTileBytes + v_tok * 128;
+            const uint32_t v_row = tile + kQuarterBytes + v_tok * 128;
 #pragma unroll
             for (int mt = 0; mt < 8; ++mt) {
                 uint32_t a[4];
-                ldmatrix_x4_trans(a, v_row + (mt >> 2) * kHalfTileBytes + ((((2 * mt + v_cc0) & 7) ^ lm_r) << 4));
+                ldmatrix_x4_trans(a, v_row + (mt >> 2) * kHalfBytes + ((((2 * mt + v_cc0) & 7) ^ lm_r) << 4));
                 mma_16816<kBf16>(o_acc[mt], a, b0, b1);
             }
             // hand the slot back: every lane's reads are done once the warp has converged here
@@ -491,36 +495,44 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         const int expected = c_last - c_first + 1;
         float *slot_out = p.partials + (long long)(blockIdx.x + pair) * p.group * kPartStride;
 
-        // consumer thread `tid` owns output dimension `tid` of every head of the group
-        for (int h = 0; h < p.group; ++h) {
-            float m_all = -INFINITY;
+        // consumer thread `tid` owns output dimension tid % 128 of the heads h = tid / 128 (mod kDimGroups); the
+        // heads are independent chains of shared-memory reads, unrolled so that they overlap
+        const int dim = tid & (kD - 1);
+        const long long row0 = (long long)sg.s * p.nh + sg.kvh * p.group;
+#pragma unroll
+        for (int hh = 0; hh < kMaxGroup / kDimGroups; ++hh) {
+            const int h = hh * kDimGroups + tid / kD;
+            if (h >= p.group) {
+                continue;
+            }
+            float mw[kConsumerWarps], m_all = -INFINITY;
 #pragma unroll
             for (int w = 0; w < kConsumerWarps; ++w) {
-                m_all = fmaxf(m_all, red_ml[(w * kMaxGroup + h) * 2]);
+                mw[w] = red_ml[(w * kMaxGroup + h) * 2];
+                m_all = fmaxf(m_all, mw[w]);
             }
             float l_all = 0.f, o = 0.f;
 #pragma unroll
             for (int w = 0; w < kConsumerWarps; ++w) {
-                const float mw = red_ml[(w * kMaxGroup + h) * 2];
-                const float wgt = mw == -INFINITY ? 0.f : fast_exp2(mw - m_all);
-                l_all += red_ml[(w * kMaxGroup + h) * 2 + 1] * wgt;
-                o += red_o[(w * p.group + h) * kD + tid] * wgt;
+                const float wgt = mw[w] == -INFINITY ? 0.f : fast_exp2(mw[w] - m_all);
+                l_all = fmaf(red_ml[(w * kMaxGroup + h) * 2 + 1], wgt, l_all);
+                o = fmaf(red_o[(w * p.group + h) * kD + dim], wgt, o);
             }
             if (expected == 1) {
-                const long long row = (long long)sg.s * p.nh + sg.kvh * p.group + h;
+                const long long row = row0 + h;
                 const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
                 if (p.part != nullptr) {
-                    p.part[row * (kD + 2) + tid] = o * inv;
-                    if (tid == 0) {
+                    p.part[row * (kD + 2) + dim] = o * inv;
+                    if (dim == 0) {
                         p.part[row * (kD + 2) + kD] = m_all * 0.6931471805599453f; // log2 units -> natural log
                         p.part[row * (kD + 2) + kD + 1] = l_all;
                     }
                 } else {
-                    store_out<kBf16>(p.out, row * kD + tid, o * inv);
+                    store_out<kBf16>(p.out, row * kD + dim, o * inv);
                 }
             } else {
-                slot_out[h * kPartStride + tid] = o; // un-normalised, relative to m_all
-                if (tid == 0) {
+                slot_out[h * kPartStride + dim] = o; // un-normalised, relative to m_all
+                if (dim == 0) {
                     slot_out[h * kPartStride + kD] = m_all;
                     slot_out[h * kPartStride + kD + 1] = l_all;
                 }
@@ -592,27 +604,31 @@ void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, i
 
 } // namespace
 
-int make_kv_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, llaisysDataType_t dtype) {
+int make_kv_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, uint32_t total_rows_per_head_block,
+                       llaisysDataType_t dtype) {
     if (dtype != LLAISYS_DTYPE_BF16 && dtype != LLAISYS_DTYPE_F16) {
         return -1;
     }
     // rows are addressed with 32-bit coordinates; the base must satisfy the TMA's 16-byte rule
-    if (total_rows == 0 || total_rows >= (uint64_t(1) << 31) || reinterpret_cast<uintptr_t>(pool_base) % 16 != 0) {
+    if (total_rows == 0 || total_rows_per_head_block == 0 || total_rows % (uint64_t(kPage) * total_rows_per_head_block) != 0 ||
+        total_rows >= (uint64_t(1) << 31) || reinterpret_cast<uintptr_t>(pool_base) % 16 != 0) {
         return -1;
     }
     EncodeTiledFn encode = encode_tiled_fn();
     if (encode == nullptr) {
         return -1;
     }
-    // The pool seen as rows of 128 elements (256 B): one row per (layer, page, K|V, kv-head, slot). A box is
-    // 64 elements x 16 rows = one half of a tile; the 128-byte swizzle permutes 16-byte chunks by row % 8.
-    const cuuint64_t dims[2] = {cuuint64_t(kD), cuuint64_t(total_rows)};
-    const cuuint64_t strides[1] = {cuuint64_t(kD * 2)};
-    const cuuint32_t box[2] = {64, cuuint32_t(kPage)};
-    const cuuint32_t elem_strides[2] = {1, 1};
+    // The pool as a 4-D tensor: [page-and-K|V][kv-head][slot 0..15][128 elements]. One box = 64 elements x 16
+    // slots x 1 head x 2 (K and V of the page): two 2 KiB blocks in shared memory, each with the 128-byte swizzle
+    // (16-byte chunks permuted by slot % 8).
+    const cuuint64_t n_heads = total_rows_per_head_block;
+    const cuuint64_t dims[4] = {cuuint64_t(kD), cuuint64_t(kPage), n_heads, cuuint64_t(total_rows / (kPage * n_heads))};
+    const cuuint64_t strides[3] = {cuuint64_t(kD * 2), cuuint64_t(kPage * kD * 2), cuuint64_t(kPage * kD * 2) * n_heads};
+    const cuuint32_t box[4] = {64, cuuint32_t(kPage), 1, 2};
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
     CUtensorMap map;
     const CUresult rc =
-        encode(&map, dtype == LLAISYS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+        encode(&map, dtype == LLAISYS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                pool_base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (rc != CUDA_SUCCESS) {
@@ -633,14 +649,16 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
         return -1;
     }
     const int group = batch.nh / kv.nkvh;
-    const int grid = decode_grid_size(batch.n_seqs, kv.nkvh, batch.max_kv_len);
+    // decode_grid_size caps at two CTAs per SM; this kernel may be built with one
+    const int two_per_sm = decode_grid_size(1 << 20, 1, 1 << 20);
+    const int grid = min(decode_grid_size(batch.n_seqs, kv.nkvh, batch.max_kv_len), two_per_sm / 2 * kCtasPerSm);
     const size_t n_pairs = size_t(batch.n_seqs) * kv.nkvh;
     if (scratch.partials == nullptr || scratch.counters == nullptr || scratch.error_flag == nullptr ||
         scratch.partials_floats < (size_t(grid) + n_pairs) * group * kPartStride || scratch.counters_len < n_pairs) {
         return -1;
     }
     TmaDecodeParams p;
-    p.row0 = kv.tma_row0;
+    p.page0 = kv.tma_page0;
     p.block_table = kv.block_table;
     p.table_stride = kv.table_stride;
     p.num_pages = kv.num_pages;

@@ -49,9 +49,10 @@ int decode_grid_size(int32_t n_seqs, int32_t nkvh, int32_t max_kv_len);
 // as attention_decode_split; returns -1 if the view or shape is not covered.
 int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
                          const void *q, float scale, const AttnOut &out, const AttnScratch &scratch);
-// Encodes the tensor map over a 16-bit page pool of `total_rows` rows of 128 elements starting at pool_base into
-// out_128_bytes (host memory). Returns -1 when the driver cannot provide one (the cp.async kernel is used then).
-int make_kv_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, llaisysDataType_t dtype);
+// Encodes the tensor map over a 16-bit page pool (head_dim 128, page 16) starting at pool_base into out_128_bytes
+// (host memory): total_rows rows of 128 elements, nkvh of them per (page, K|V) block of 16 slots each. Returns -1
+// when the driver cannot provide one (the cp.async kernel is used then).
+int make_kv_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, uint32_t nkvh, llaisysDataType_t dtype);
 
 // K3: out[r, :] = sum_p w_p o_p[r, :] / sum_p w_p, w_p = l_p exp(m_p - max_p m_p), over n_parts partials laid out
 // float [n_parts][n_rows][d + 2].

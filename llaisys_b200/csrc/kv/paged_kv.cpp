@@ -76,7 +76,7 @@ PagedKV::PagedKV(const PagedKVConfig &cfg) : _cfg(cfg) {
         if (_elem == 2 && cfg.head_dim == 128 && cfg.page_size == 16) {
             // one row of 128 elements per (layer, page, K|V, kv-head, slot)
             const uint64_t rows = uint64_t(cfg.nlayer) * cfg.num_pages * 2 * cfg.nkvh * cfg.page_size;
-            _has_tma = kernels::make_kv_tensor_map(_tma_desc, _pool->memory(), rows, cfg.dtype) == 0;
+            _has_tma = kernels::make_kv_tensor_map(_tma_desc, _pool->memory(), rows, uint32_t(cfg.nkvh), cfg.dtype) == 0;
         }
 #endif
     } else {
@@ -245,7 +245,7 @@ kernels::KVView PagedKV::view(size_t layer) const {
     v.d = int32_t(_cfg.head_dim);
     if (_has_tma) {
         v.tma_desc = _tma_desc;
-        v.tma_row0 = int64_t(layer) * int64_t(_cfg.num_pages * 2 * _cfg.nkvh * _cfg.page_size);
+        v.tma_page0 = int64_t(layer) * int64_t(_cfg.num_pages);
     }
     return v;
 }
