@@ -1,6 +1,8 @@
 """Builds libllaisys.so (C ABI + sm_100a CUDA kernels) in-tree with g++ and nvcc.
 
-    python -m llaisys_b200.build [--force] [--verbose] [--no-cuda]
+    python llaisys_b200/build.py [--force] [--verbose] [--no-cuda]
+
+(run it as a script: importing the package loads the library, which may not exist yet)
 
 The result is written to llaisys_b200/libllaisys/libllaisys.so, the place the ctypes loader looks
 (the reference installs its library the same way: xmake.lua:112-121 copies lib/*.so into
