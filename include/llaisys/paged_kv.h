@@ -143,6 +143,29 @@ LLAISYS_API int llaisysPagedAttentionPrefillDev(llaisysPagedKV_t kv, size_t laye
                                                 size_t max_q_len, size_t max_kv_len, size_t nh, float scale,
                                                 llaisysStream_t stream);
 
+/* ---- decode without any allocation ------------------------------------------------------------- */
+/* No counterpart in the reference. For callers that cannot let a library allocate device memory: a server that
+ * has already given all free HBM to its own page pool (a library cudaMalloc would fail or fragment it), or a
+ * decode loop that cannot afford the device-wide stall of an allocation or release. The caller passes its own
+ * page pool of one layer (layout as above: [page][K|V][nkvh][16][128], BF16 or F16), its block table, the
+ * per-sequence table rows (seq_ids_dev, or NULL for row i = sequence i) and lengths, q and out -- all device
+ * memory -- and the split-KV scratch comes from a fixed array inside the library's device image instead of an
+ * allocation.
+ *   Limits: n_seqs * nkvh <= 512, nh / nkvh <= 8, head_dim 128, page size 16, GPUs of up to 160 SMs; larger
+ *           requests return LLAISYS_E_INVALID and queue nothing. The array costs about 3.5 MiB on every GPU
+ *           that loads the library, for the life of the process.
+ *   Sharing: every call on a device uses the same array. What has to start at zero is cleared at the start of
+ *           each call; calls that overlap on the GPU (unordered streams) race on it -- keep them ordered.
+ *   First call on a device looks up the array's device address; make that call before any stream capture.
+ * error_flag_dev (optional, device int32, caller-zeroed): receives the kErr bits if the kernel had to skip an
+ * out-of-range page; NULL keeps the word inside the library. */
+LLAISYS_API int llaisysPagedAttentionDecodeNoAlloc(int device_id, void *out, const void *q, void *pool_layer,
+                                                   const int32_t *block_table_dev, size_t table_stride,
+                                                   size_t num_pages, const int32_t *seq_ids_dev,
+                                                   const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len,
+                                                   size_t nh, size_t nkvh, llaisysDataType_t dtype, float scale,
+                                                   int32_t *error_flag_dev, llaisysStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

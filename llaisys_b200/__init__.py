@@ -10,9 +10,9 @@ from .libllaisys import llaisysStream_t as Stream
 from .runtime import RuntimeAPI, context_stream, set_context_runtime
 from .tensor import Tensor
 from .ops import Ops
-from .paged_kv import LlaisysError, PagedKVCache, lse_merge
+from .paged_kv import LlaisysError, PagedKVCache, decode_no_alloc, lse_merge
 
 __all__ = [
     "RuntimeAPI", "DeviceType", "DataType", "MemcpyKind", "Stream", "Tensor", "Ops",
-    "PagedKVCache", "lse_merge", "LlaisysError", "Status", "context_stream", "set_context_runtime",
+    "PagedKVCache", "lse_merge", "decode_no_alloc", "LlaisysError", "Status", "context_stream", "set_context_runtime",
 ]

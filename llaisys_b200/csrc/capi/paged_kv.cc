@@ -42,6 +42,15 @@ int guarded(F &&body) {
     }
 }
 
+} // namespace
+
+namespace llaisys::kernels {
+// Entry points that live beside their kernels (attention_decode_static.cu) record their message here.
+void set_last_error(const std::string &msg) { g_last_error = msg; }
+} // namespace llaisys::kernels
+
+namespace {
+
 int null_handle() {
     g_last_error = "paged KV: null cache handle";
     return LLAISYS_E_INVALID;

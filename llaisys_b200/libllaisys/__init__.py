@@ -161,6 +161,9 @@ PROTOTYPES: dict[str, tuple] = {
     "llaisysPagedAttentionPrefillDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, c_float,
                                                 llaisysStream_t]),
+    "llaisysPagedAttentionDecodeNoAlloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t,
+                                                   c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t,
+                                                   llaisysDataType_t, c_float, c_void_p, llaisysStream_t]),
 }
 
 
@@ -180,7 +183,7 @@ def load_shared_library() -> ctypes.CDLL:
     path = library_path()
     if not path.is_file():
         raise FileNotFoundError(
-            f"Shared library not found: {path}. Build it with `python -m llaisys_b200.build`; "
+            f"Shared library not found: {path}. Build it with `python llaisys_b200/build.py`; "
             "there is no Python fallback for the compiled kernels.")
     lib = ctypes.CDLL(str(path))
     for name, (restype, argtypes) in PROTOTYPES.items():

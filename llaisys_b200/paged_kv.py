@@ -178,3 +178,19 @@ def lse_merge(out, parts, n_parts: int, n_rows: int, head_dim: int, *, dtype: Da
     """Merges n_parts partial results float [n_parts, n_rows, head_dim + 2] into out [n_rows, head_dim]."""
     _check(LIB_LLAISYS.llaisysLseMerge(int(device), device_id, _addr(out), int(dtype), _addr(parts), n_parts, n_rows,
                                        head_dim))
+
+
+def decode_no_alloc(out, q, pool_layer, block_table_dev, table_stride: int, num_pages: int, seq_ids_dev, kv_lens_dev,
+                    n_seqs: int, max_kv_len: int, nh: int, nkvh: int, scale: float, *, dtype: DataType = DataType.BF16,
+                    device_id: int = 0, error_flag_dev=None, stream=None) -> None:
+    """Split-KV decode over a caller-owned page pool with no device allocation inside the library.
+
+    For servers that have committed all free HBM to their own pool, or decode loops that cannot take the
+    device-wide stall of an allocation: the kernel's scratch is a fixed array in the library image. Limits:
+    n_seqs * nkvh <= 512, head_dim 128, 16-token pages, BF16/F16. All calls on a device share that array, so
+    calls must be ordered on the GPU; the first call on a device should come before any stream capture.
+    """
+    _check(LIB_LLAISYS.llaisysPagedAttentionDecodeNoAlloc(
+        device_id, _addr(out), _addr(q), _addr(pool_layer), _addr(block_table_dev), table_stride, num_pages,
+        _addr(seq_ids_dev), _addr(kv_lens_dev), n_seqs, max_kv_len, nh, nkvh, int(dtype), scale,
+        _addr(error_flag_dev), stream))
