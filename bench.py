@@ -42,8 +42,8 @@ sys.path.insert(0, str(ROOT))
 NH, NKVH, D, PAGE, POOL_PAGES = 12, 2, 128, 16, 16384
 METRIC = "decode tokens/s (paged KV append + flash-decoding attention, one layer)"
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode launch on the north_star workload, from the ncu
-# capture summarised in profiles/; None until a capture exists.
-NCU_TRAFFIC_BYTES = {"north_star": None, "config2": None}
+# capture summarised in profiles/decode_tma_north_star.md; None where no capture exists.
+NCU_TRAFFIC_BYTES = {"north_star": 273_930_000, "config2": None}
 
 
 def workload_lengths(name: str, seed: int):
