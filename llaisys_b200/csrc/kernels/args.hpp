@@ -29,7 +29,8 @@ struct KVView {
     int32_t d = 0;
     // Optional TMA view of the same memory (page pools only): a 128-byte tensor-map blob in HOST memory over the
     // whole multi-layer pool, and the index of this layer's page 0 in it (layer * num_pages).
-    const void *tma_desc = nullptr;
+    const void *tma_desc = nullptr;      // box = K and V of a page, 64 dims (decode)
+    const void *tma_tile_desc = nullptr; // box = one half-tile: 16 slots x 64 dims (prefill)
     int64_t tma_page0 = 0;
 };
 

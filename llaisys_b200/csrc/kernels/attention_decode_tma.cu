@@ -51,7 +51,7 @@ constexpr int kRingBytes = kSlots * kSlotBytes; // 96 KiB
 constexpr int kMaxGroup = 8;
 constexpr int kMaxSeqs = 1024;
 constexpr int kCtasPerSm = 8 / kConsumerWarps;
-constexpr uint32_t kWaitLimit = 1u << 22; // polls before a wait gives up (well under a second)
+constexpr uint32_t kWaitLimit = 1u << 20; // polls before a wait gives up (about a second at worst)
 constexpr int kErrTimeout = 8;
 constexpr int kDimGroups = kConsumerThreads / kD; // the pair epilogue maps a consumer thread to one output
 static_assert(kConsumerThreads % kD == 0, "dimension and to every kDimGroups-th head of the group");

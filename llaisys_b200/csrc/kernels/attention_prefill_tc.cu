@@ -1,0 +1,583 @@
+// K4: chunked-prefill attention over the page pool on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// Roofline: tensor. Algorithmic flops per sequence = 4 * nh * d * sum over chunk rows of visible keys
+//                                                  = 4 * nh * 128 * (L * C + L * (L + 1) / 2)
+// for a chunk of L queries after C cached tokens (QK^T and PV, 2 flops per multiply-add; masked work not counted).
+//
+// One CTA per (sequence, query head, block of 128 chunk rows). Its 128 query rows stay in shared memory for the
+// whole tile; K/V arrive 128 tokens (8 pages) at a time:
+//   warp 4 (producer)  reads the block table and issues TMA tiles (16 tokens x 64 dims, 128-byte swizzle) into a
+//                      two-stage K/V ring -- K as [2 dim-halves][128 tokens][128 B], V the same;
+//   warp 5 (MMA)       one thread issues tcgen05.mma (M 128, N 128, K 16, bf16/f16 -> f32):
+//                        S = Q . K^T      8 instructions, both operands K-major, accumulator S[buf] in TMEM
+//                        O += P . V       8 instructions, P K-major from shared memory, V MN-major (the page layout
+//                                         keeps head_dim contiguous), accumulator O in TMEM
+//                      QK^T of block i+1 is issued before PV of block i, so the tensor pipe works under the softmax;
+//   warps 0-3          the 128 softmax threads, one query row each (TMEM lane = row): tcgen05.ld S in 32-column
+//                      pieces, causal mask, running max / sum in the log2 domain, P = 2^(s - m) written to shared
+//                      memory as bf16 in the swizzled K-major layout, O rescaled in TMEM only when a row's max grew by
+//                      more than 2^8 since the last rescale (the stale max is used consistently for P and the sum).
+// TMEM: 512 columns allocated: S double-buffered (2 x 128) + O (128). Shared memory: Q 32 KiB + P 32 KiB + K/V
+// 2 x 64 KiB = 192 KiB, so one CTA per SM and the TMEM allocation never contends.
+//
+// Synchronisation is mbarriers only; tcgen05.commit arrives on them when the tensor pipe has finished. Every wait is
+// bounded: a wait that runs out sets bit 8 of the error word and the CTA winds down (TMEM is freed) instead of hanging.
+// No cluster launch, no multicast.
+#include "kernels.hpp"
+#include "mma_utils.cuh"
+
+#include <cuda.h>
+
+#include <cstring>
+#include <mutex>
+
+namespace llaisys::kernels {
+
+namespace {
+
+constexpr int kD = 128;
+constexpr int kPage = 16;
+constexpr int kBlockM = 128;                 // query rows per CTA
+constexpr int kBlockN = 128;                 // keys per K/V block (8 pages)
+constexpr int kPagesPerBlock = kBlockN / kPage;
+constexpr int kStages = 2;
+constexpr int kSoftmaxThreads = 128;
+constexpr int kProducerWarp = 4, kMmaWarp = 5;
+constexpr int kThreads = 192;
+constexpr int kHalfBytes = kBlockM * 128;    // [128 rows][128 B]: one 64-element half of a 128-row operand, 16 KiB
+constexpr int kOperandBytes = 2 * kHalfBytes; // 32 KiB: Q, P, one K block, one V block
+constexpr int kStageBytes = 2 * kOperandBytes; // K block + V block
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0, kColO = 256;        // S buffers at columns 0 and 128, O at 256
+constexpr uint32_t kWaitLimit = 1u << 20; // polls before a wait gives up (about a second at worst)
+constexpr int kErrTimeout = 8;
+constexpr float kRescaleThreshold = 8.f;     // log2 units
+
+// barrier indices
+enum : int {
+    kBarKvFull = 0,                   // [kStages] producer -> MMA: K/V block landed (transaction bytes)
+    kBarKvEmpty = kBarKvFull + kStages, // [kStages] MMA (commit) -> producer: PV of the block finished
+    kBarSFull = kBarKvEmpty + kStages,  // [2] MMA (commit) -> softmax: S[buf] written
+    kBarSFree = kBarSFull + 2,          // [2] softmax (128) -> MMA: S[buf] read
+    kBarPFull = kBarSFree + 2,          // softmax (128) -> MMA: P in shared memory, O rescaled
+    kBarPFree = kBarPFull + 1,          // MMA (commit) -> softmax: PV finished: P reusable, O stable
+    kNumBars = kBarPFree + 1
+};
+
+struct PrefillParams {
+    long long page0;
+    const int32_t *block_table;
+    int32_t table_stride, num_pages;
+    const int32_t *seq_ids;
+    const int32_t *kv_lens;
+    const int32_t *q_starts; // [n_seqs + 1]
+    int32_t n_seqs, nkvh, group, nh, q_blocks; // q_blocks = ceil(max_q_len / 128)
+    const void *q;
+    void *out;
+    float scale_log2;
+    int32_t *error_flag;
+};
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] . B[smem]; accumulate = 0 overwrites D.
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+                 "}\n" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// The mbarrier gets one arrival when every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+// 32 consecutive f32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        v[i] = __uint_as_float(r[i]);
+    }
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+                 "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+                 "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
+                 "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
+                 "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                 "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+                 "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
+                 "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
+                 "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                 "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+                 "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
+                 "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle. Fields (bit positions): start address >> 4 [0,14),
+// leading byte offset >> 4 [16,30), stride byte offset >> 4 [32,46), descriptor version 1 [46,48),
+// layout type 2 = SWIZZLE_128B [61,64).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= uint64_t((addr & 0x3FFFFu) >> 4);
+    d |= uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= uint64_t(1) << 46;
+    d |= uint64_t(2) << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: D f32 [4,6) = 1; A/B format [7,10) / [10,13): 0 = f16, 1 = bf16;
+// A major bit 15, B major bit 16 (0 = K-major, 1 = MN-major); N >> 3 at [17,23); M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool b_mn_major, int m, int n) {
+    return (1u << 4) | (uint32_t(bf16 ? 1 : 0) << 7) | (uint32_t(bf16 ? 1 : 0) << 10) | (uint32_t(b_mn_major ? 1 : 0) << 16) |
+           (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+        if ((i & 1023u) == 1023u && *abort_flag != 0) {
+            return false;
+        }
+    }
+    return false;
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1)
+    paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, PrefillParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw_u32 = smem_u32(smem_raw);
+    const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u; // swizzled operands need 1 KiB alignment
+    unsigned char *base = smem_raw + (base_u32 - raw_u32);
+    const uint32_t q_u32 = base_u32, p_u32 = base_u32 + kOperandBytes, kv_u32 = base_u32 + 2 * kOperandBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + 2 * kOperandBytes + kStages * kStageBytes);
+    const uint32_t bars_u32 = smem_u32(bars);
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // ---- which tile ----------------------------------------------------------------------------------------
+    const int linear = blockIdx.x;
+    const int qb = p.q_blocks - 1 - (linear % p.q_blocks); // late query blocks see the most keys: schedule them first
+    const int h = (linear / p.q_blocks) % p.nh;
+    const int s = linear / (p.q_blocks * p.nh);
+    const int q_start = p.q_starts[s];
+    const int q_len = p.q_starts[s + 1] - q_start;
+    if (qb * kBlockM >= q_len) {
+        return; // uniform over the CTA, before any barrier or allocation
+    }
+    const int kv_len = min(max(p.kv_lens[s], q_len), p.table_stride * kPage);
+    const int off = kv_len - q_len;                                   // query t sees keys j <= t + off
+    const int kv_hi = min(kv_len, qb * kBlockM + kBlockM + off);      // keys any row of this tile can see
+    const int nblk = (kv_hi + kBlockN - 1) / kBlockN;
+    const int n_pages = (kv_hi + kPage - 1) / kPage;
+    const int kvh = h / p.group;
+    const int seq_row = p.seq_ids ? p.seq_ids[s] : s;
+
+    // ---- set-up: barriers, TMEM, Q tile, cleared K/V ring ---------------------------------------------------
+    if (tid == 0) {
+        for (int i = 0; i < kNumBars; ++i) {
+            const bool many = (i >= kBarSFree && i < kBarSFree + 2) || i == kBarPFull;
+            mbar_init(bars_u32 + i * 8, many ? kSoftmaxThreads : 1);
+        }
+        s_abort = 0;
+        mbar_init_fence();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(&s_tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    {
+        // Q rows of this tile, 16 bytes per store, into the K-major 128-byte-swizzled layout
+        // [dims 0-63 | dims 64-127][128 rows][128 B]; rows past the chunk are zero.
+        const char *q_base = static_cast<const char *>(p.q);
+        for (int idx = tid; idx < kBlockM * 16; idx += kThreads) {
+            const int r = idx >> 4, cc = idx & 15;
+            const int t = qb * kBlockM + r;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (t < q_len) {
+                val = *reinterpret_cast<const uint4 *>(q_base + ((long long)(q_start + t) * p.nh + h) * (kD * 2) + cc * 16);
+            }
+            const uint32_t dst = q_u32 + (cc >> 3) * kHalfBytes + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
+        }
+        // A block shorter than 128 keys leaves ring rows unwritten; they are masked out of S, but V rows enter the
+        // PV product with weight 0, so they must at least be finite: start from zeros.
+        for (int idx = tid; idx < kStages * kStageBytes / 16; idx += kThreads) {
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(kv_u32 + idx * 16), "r"(0u) : "memory");
+        }
+        fence_proxy_async_smem(); // generic-proxy stores above are read (Q) or overwritten (ring) by the async proxy
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+
+    auto bar = [&](int which) { return bars_u32 + uint32_t(which) * 8; };
+    auto give_up = [&]() {
+        s_abort = 1;
+        atomicOr(p.error_flag, kErrTimeout);
+    };
+
+    if (warp == kProducerWarp) {
+        // ================================ producer: TMA tiles of K and V =====================================
+        const long long tbase = (long long)seq_row * p.table_stride;
+        for (int i = 0; i < nblk; ++i) {
+            const int st = i & 1;
+            if (i >= kStages && !wait_or_abort(bar(kBarKvEmpty + st), uint32_t((i >> 1) - 1) & 1u, &s_abort)) {
+                if (lane == 0) {
+                    give_up();
+                }
+                break;
+            }
+            const int first = i * kPagesPerBlock;
+            const int n_pg = min(kPagesPerBlock, n_pages - first);
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar(kBarKvFull + st), uint32_t(n_pg) * 4 * 2048);
+            }
+            __syncwarp();
+            if (lane < n_pg) {
+                int page = p.block_table[tbase + first + lane];
+                if (page < 0 || page >= p.num_pages) {
+                    atomicOr(p.error_flag, kErrBadPage);
+                    page = 0;
+                }
+                const int c3 = int((p.page0 + page) * 2);
+                const uint32_t dst = kv_u32 + st * kStageBytes + lane * 2048;
+                tma_load_4d(dst, &tmap, 0, 0, kvh, c3, bar(kBarKvFull + st));                                   // K, dims 0-63
+                tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, kvh, c3, bar(kBarKvFull + st));                     // K, dims 64-127
+                tma_load_4d(dst + kOperandBytes, &tmap, 0, 0, kvh, c3 + 1, bar(kBarKvFull + st));               // V, dims 0-63
+                tma_load_4d(dst + kOperandBytes + kHalfBytes, &tmap, 64, 0, kvh, c3 + 1, bar(kBarKvFull + st)); // V, dims 64-127
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ================================ MMA issuer (one thread) =============================================
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = make_idesc(kBf16, false, kBlockM, kBlockN);
+            constexpr uint32_t idesc_pv = make_idesc(kBf16, true, kBlockM, kD);
+            const uint32_t tmem_o = tmem_base + kColO;
+            bool ok = true;
+            auto issue_pv = [&](int j) { // O (+)= P . V of block j
+                if (!wait_or_abort(bar(kBarPFull), uint32_t(j) & 1u, &s_abort)) {
+                    return false;
+                }
+                tc_fence_after();
+                const uint32_t v_u32 = kv_u32 + (j & 1) * kStageBytes + kOperandBytes;
+#pragma unroll
+                for (int kk = 0; kk < kBlockN / 16; ++kk) {
+                    // A = P rows x 16 keys (K-major: 32 bytes into the 128-byte row per step, next half after 4 steps)
+                    const uint64_t a = smem_desc_sw128(p_u32 + (kk >> 2) * kHalfBytes + (kk & 3) * 32, 0, 1024);
+                    // B = 16 keys x 128 dims of V, MN-major: 8-key groups 1 KiB apart, the two 64-dim halves 16 KiB apart
+                    const uint64_t b = smem_desc_sw128(v_u32 + kk * 2048, kHalfBytes, 1024);
+                    umma_f16(tmem_o, a, b, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(bar(kBarPFree));
+                umma_commit(bar(kBarKvEmpty + (j & 1)));
+                return true;
+            };
+            for (int i = 0; i < nblk && ok; ++i) {
+                const int st = i & 1, buf = i & 1;
+                ok = wait_or_abort(bar(kBarKvFull + st), uint32_t(i >> 1) & 1u, &s_abort);
+                if (ok && i >= 2) {
+                    ok = wait_or_abort(bar(kBarSFree + buf), uint32_t((i >> 1) - 1) & 1u, &s_abort);
+                }
+                if (!ok) {
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t k_u32 = kv_u32 + st * kStageBytes;
+#pragma unroll
+                for (int ks = 0; ks < kD / 16; ++ks) {
+                    const uint64_t a = smem_desc_sw128(q_u32 + (ks >> 2) * kHalfBytes + (ks & 3) * 32, 0, 1024);
+                    const uint64_t b = smem_desc_sw128(k_u32 + (ks >> 2) * kHalfBytes + (ks & 3) * 32, 0, 1024);
+                    umma_f16(tmem_base + kColS + buf * kBlockN, a, b, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(bar(kBarSFull + buf));
+                if (i >= 1) {
+                    ok = issue_pv(i - 1);
+                }
+            }
+            if (ok) {
+                ok = issue_pv(nblk - 1);
+            }
+            if (!ok) {
+                give_up();
+            }
+        }
+    } else {
+        // ================================ softmax: one query row per thread =====================================
+        const int row = tid;                       // TMEM lane
+        const int t = qb * kBlockM + row;          // query index inside the chunk
+        const int last_visible = t + off;          // keys j <= last_visible (and < kv_len) take part
+        const uint32_t lane_base = uint32_t(warp * 32) << 16;
+        const uint32_t tmem_o = tmem_base + lane_base + kColO;
+        float m_used = -INFINITY, l = 0.f;
+        bool dead = false;
+        for (int i = 0; i < nblk && !dead; ++i) {
+            const int buf = i & 1;
+            if (!wait_or_abort(bar(kBarSFull + buf), uint32_t(i >> 1) & 1u, &s_abort)) {
+                dead = true;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t tmem_s = tmem_base + lane_base + kColS + buf * kBlockN;
+            const int j0 = i * kBlockN;
+            const int n_ok = min(min(last_visible, kv_len - 1) - j0 + 1, kBlockN); // visible columns are [0, n_ok)
+            // pass 1: row maximum of the visible scores (log2 domain)
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+                float v[32];
+                tmem_ld32(tmem_s + c4 * 32, v);
+#pragma unroll
+                for (int k = 0; k < 32; ++k) {
+                    if (c4 * 32 + k < n_ok) {
+                        mx = fmaxf(mx, v[k] * p.scale_log2);
+                    }
+                }
+            }
+            // The running max only moves when it grew by more than 2^8: P and the row sum both use m_used, so the
+            // result is exact either way, and O is rescaled rarely.
+            float alpha = 1.f;
+            const bool grow = mx > m_used + kRescaleThreshold;
+            if (grow) {
+                alpha = fast_exp2(m_used - mx); // 0 on the first block
+                m_used = mx;
+            }
+            if (i >= 1) {
+                // PV of the previous block must be finished before P is overwritten or O is rescaled
+                if (!wait_or_abort(bar(kBarPFree), uint32_t(i - 1) & 1u, &s_abort)) {
+                    dead = true;
+                    break;
+                }
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        float v[32];
+                        tmem_ld32(tmem_o + c4 * 32, v);
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) {
+                            v[k] *= alpha;
+                        }
+                        tmem_st32(tmem_o + c4 * 32, v);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            l *= alpha;
+            // pass 2: P = 2^(s - m) as 16-bit, into the swizzled K-major operand layout
+            const float m_ref = m_used == -INFINITY ? 0.f : m_used;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+                float v[32];
+                tmem_ld32(tmem_s + c4 * 32, v);
+                uint32_t packed[16];
+#pragma unroll
+                for (int k = 0; k < 32; k += 2) {
+                    const float p0 = (c4 * 32 + k < n_ok) ? fast_exp2(v[k] * p.scale_log2 - m_ref) : 0.f;
+                    const float p1 = (c4 * 32 + k + 1 < n_ok) ? fast_exp2(v[k + 1] * p.scale_log2 - m_ref) : 0.f;
+                    l += p0 + p1;
+                    packed[k >> 1] = pack2<kBf16>(p0, p1);
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int cc = c4 * 4 + q4; // 16-byte chunk (8 keys) of this row
+                    const uint32_t dst = p_u32 + (cc >> 3) * kHalfBytes + row * 128 + (((cc & 7) ^ (row & 7)) << 4);
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(packed[q4 * 4]),
+                                 "r"(packed[q4 * 4 + 1]), "r"(packed[q4 * 4 + 2]), "r"(packed[q4 * 4 + 3])
+                                 : "memory");
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(kBarSFree + buf)); // S[buf] may be overwritten by QK^T of block i + 2
+            fence_proxy_async_smem();          // P stores -> visible to the tensor pipe's reads
+            mbar_arrive(bar(kBarPFull));
+        }
+        // ---- epilogue: O / l -> out ------------------------------------------------------------------------------
+        if (!dead && !wait_or_abort(bar(kBarPFree), uint32_t(nblk - 1) & 1u, &s_abort)) {
+            dead = true;
+        }
+        if (dead) {
+            if (lane == 0) {
+                give_up();
+            }
+        } else {
+            tc_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            char *out_row = static_cast<char *>(p.out) + ((long long)(q_start + t) * p.nh + h) * (kD * 2);
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+                float v[32];
+                tmem_ld32(tmem_o + c4 * 32, v);
+                if (t < q_len) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 w;
+                        w.x = pack2<kBf16>(v[q4 * 8 + 0] * inv, v[q4 * 8 + 1] * inv);
+                        w.y = pack2<kBf16>(v[q4 * 8 + 2] * inv, v[q4 * 8 + 3] * inv);
+                        w.z = pack2<kBf16>(v[q4 * 8 + 4] * inv, v[q4 * 8 + 5] * inv);
+                        w.w = pack2<kBf16>(v[q4 * 8 + 6] * inv, v[q4 * 8 + 7] * inv);
+                        *reinterpret_cast<uint4 *>(out_row + c4 * 64 + q4 * 16) = w;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown: everyone is done with TMEM before the allocating warp frees it ----------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+} // namespace
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn prefill_encode_fn() {
+    static EncodeTiledFn fn = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) != cudaSuccess ||
+            res != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            return EncodeTiledFn(nullptr);
+        }
+        return reinterpret_cast<EncodeTiledFn>(sym);
+    }();
+    return fn;
+}
+
+constexpr size_t kSmemBytes = 1024 + 2 * kOperandBytes + kStages * kStageBytes + kNumBars * sizeof(uint64_t);
+
+template <bool kBf16>
+void launch(cudaStream_t s, const CUtensorMap &tmap, const PrefillParams &p, int grid) {
+    static std::once_flag once[64];
+    int dev = 0;
+    LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
+    std::call_once(once[dev & 63], [] {
+        LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_tc_kernel<kBf16>,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
+    });
+    paged_prefill_tc_kernel<kBf16><<<grid, kThreads, kSmemBytes, s>>>(tmap, p);
+}
+
+} // namespace
+
+int make_kv_tile_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, uint32_t nkvh,
+                            llaisysDataType_t dtype) {
+    if (dtype != LLAISYS_DTYPE_BF16 && dtype != LLAISYS_DTYPE_F16) {
+        return -1;
+    }
+    if (total_rows == 0 || nkvh == 0 || total_rows % (uint64_t(kPage) * nkvh) != 0 || total_rows >= (uint64_t(1) << 31) ||
+        reinterpret_cast<uintptr_t>(pool_base) % 16 != 0) {
+        return -1;
+    }
+    EncodeTiledFn encode = prefill_encode_fn();
+    if (encode == nullptr) {
+        return -1;
+    }
+    // Same 4-D view of the pool as the decode kernel's map -- [page-and-K|V][kv-head][slot][128 elements] -- with a
+    // box of one half-tile: 64 elements x 16 slots (2 KiB, 128-byte swizzle).
+    const cuuint64_t dims[4] = {cuuint64_t(kD), cuuint64_t(kPage), cuuint64_t(nkvh), cuuint64_t(total_rows / (kPage * nkvh))};
+    const cuuint64_t strides[3] = {cuuint64_t(kD * 2), cuuint64_t(kPage * kD * 2), cuuint64_t(kPage * kD * 2) * nkvh};
+    const cuuint32_t box[4] = {64, cuuint32_t(kPage), 1, 1};
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    CUtensorMap map;
+    const CUresult rc =
+        encode(&map, dtype == LLAISYS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+               pool_base, dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        return -1;
+    }
+    memcpy(out_128_bytes, &map, sizeof(map));
+    return 0;
+}
+
+int attention_prefill_tc(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
+                         const void *q, float scale, const AttnOut &out, int32_t *error_flag) {
+    const bool bf16 = dtype == LLAISYS_DTYPE_BF16;
+    if (kv.tma_tile_desc == nullptr || !(bf16 || dtype == LLAISYS_DTYPE_F16) || kv.d != kD || kv.page_size != kPage ||
+        kv.nkvh <= 0 || kv.block_table == nullptr || batch.kv_lens == nullptr || batch.q_starts == nullptr ||
+        out.out == nullptr || out.part != nullptr || batch.nh % kv.nkvh != 0 || batch.n_seqs <= 0 ||
+        batch.max_q_len <= 0 || error_flag == nullptr || reinterpret_cast<uintptr_t>(q) % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(out.out) % 16 != 0) {
+        return -1;
+    }
+    PrefillParams p;
+    p.page0 = kv.tma_page0;
+    p.block_table = kv.block_table;
+    p.table_stride = kv.table_stride;
+    p.num_pages = kv.num_pages;
+    p.seq_ids = batch.seq_ids;
+    p.kv_lens = batch.kv_lens;
+    p.q_starts = batch.q_starts;
+    p.n_seqs = batch.n_seqs;
+    p.nkvh = kv.nkvh;
+    p.group = batch.nh / kv.nkvh;
+    p.nh = batch.nh;
+    p.q_blocks = (batch.max_q_len + kBlockM - 1) / kBlockM;
+    p.q = q;
+    p.out = out.out;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.error_flag = error_flag;
+    const long long grid = (long long)batch.n_seqs * batch.nh * p.q_blocks;
+    if (grid > 0x7fffffffLL) {
+        return -1;
+    }
+    CUtensorMap tmap;
+    memcpy(&tmap, kv.tma_tile_desc, sizeof(tmap));
+    auto s = static_cast<cudaStream_t>(stream);
+    if (bf16) {
+        launch<true>(s, tmap, p, int(grid));
+    } else {
+        launch<false>(s, tmap, p, int(grid));
+    }
+    check_launch("paged_prefill_tc");
+    return 0;
+}
+
+} // namespace llaisys::kernels

@@ -54,6 +54,14 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
 // when the driver cannot provide one (the cp.async kernel is used then).
 int make_kv_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, uint32_t nkvh, llaisysDataType_t dtype);
 
+// K4: chunked-prefill attention on tcgen05 for page pools that carry the half-tile tensor map
+// (KVView::tma_tile_desc): 16-bit K/V, head_dim 128, page 16, ragged causal chunks (batch.q_starts). Returns -1 if
+// the view or shape is not covered.
+int attention_prefill_tc(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
+                         const void *q, float scale, const AttnOut &out, int32_t *error_flag);
+int make_kv_tile_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, uint32_t nkvh,
+                            llaisysDataType_t dtype);
+
 // K3: out[r, :] = sum_p w_p o_p[r, :] / sum_p w_p, w_p = l_p exp(m_p - max_p m_p), over n_parts partials laid out
 // float [n_parts][n_rows][d + 2].
 void lse_merge(stream_t stream, llaisysDataType_t dtype, void *out, const float *parts, int32_t n_parts,

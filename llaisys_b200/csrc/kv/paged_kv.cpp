@@ -77,6 +77,8 @@ PagedKV::PagedKV(const PagedKVConfig &cfg) : _cfg(cfg) {
             // one row of 128 elements per (layer, page, K|V, kv-head, slot)
             const uint64_t rows = uint64_t(cfg.nlayer) * cfg.num_pages * 2 * cfg.nkvh * cfg.page_size;
             _has_tma = kernels::make_kv_tensor_map(_tma_desc, _pool->memory(), rows, uint32_t(cfg.nkvh), cfg.dtype) == 0;
+            _has_tma_tile =
+                kernels::make_kv_tile_tensor_map(_tma_tile_desc, _pool->memory(), rows, uint32_t(cfg.nkvh), cfg.dtype) == 0;
         }
 #endif
     } else {
@@ -243,6 +245,10 @@ kernels::KVView PagedKV::view(size_t layer) const {
     v.num_pages = int32_t(_cfg.num_pages);
     v.nkvh = int32_t(_cfg.nkvh);
     v.d = int32_t(_cfg.head_dim);
+    if (_has_tma_tile) {
+        v.tma_tile_desc = _tma_tile_desc;
+        v.tma_page0 = int64_t(layer) * int64_t(_cfg.num_pages);
+    }
     if (_has_tma) {
         v.tma_desc = _tma_desc;
         v.tma_page0 = int64_t(layer) * int64_t(_cfg.num_pages);
@@ -581,6 +587,16 @@ void run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const
             return;
         }
         if (kernels::attention_decode_split(stream, dtype, view, batch, q, scale, out, scratch) == 0) {
+            return;
+        }
+    }
+    if (batch.q_starts != nullptr) {
+        // LLAISYS_PREFILL_PATH=generic keeps chunks on the generic kernel (for A/B measurements)
+        static const bool allow_tc = [] {
+            const char *e = std::getenv("LLAISYS_PREFILL_PATH");
+            return !(e != nullptr && std::string(e) == "generic");
+        }();
+        if (allow_tc && kernels::attention_prefill_tc(stream, dtype, view, batch, q, scale, out, scratch.error_flag) == 0) {
             return;
         }
     }

@@ -110,8 +110,9 @@ private:
     std::vector<int32_t> _stage_buf;
 
     // TMA view of the pool (NVIDIA, 16-bit, head_dim 128, page 16 only); _has_tma is false otherwise
-    alignas(64) unsigned char _tma_desc[128] = {};
-    bool _has_tma = false;
+    alignas(64) unsigned char _tma_desc[128] = {};      // decode: box = K and V of a page
+    alignas(64) unsigned char _tma_tile_desc[128] = {}; // prefill: box = one half-tile
+    bool _has_tma = false, _has_tma_tile = false;
 };
 
 // Picks the kernel for a batch on an NVIDIA device and queues it: split-KV decode or tensor-core prefill where
