@@ -5,20 +5,21 @@
 // for a chunk of L queries after C cached tokens (QK^T and PV, 2 flops per multiply-add; masked work not counted).
 //
 // One CTA per (sequence, query head, block of 128 chunk rows). Its 128 query rows stay in shared memory for the
-// whole tile; K/V arrive 128 tokens (8 pages) at a time:
+// whole tile; K/V arrive 64 tokens (4 pages) at a time:
 //   warp 4 (producer)  reads the block table and issues TMA tiles (16 tokens x 64 dims, 128-byte swizzle) into a
-//                      two-stage K/V ring -- K as [2 dim-halves][128 tokens][128 B], V the same;
-//   warp 5 (MMA)       one thread issues tcgen05.mma (M 128, N 128, K 16, bf16/f16 -> f32):
-//                        S = Q . K^T      8 instructions, both operands K-major, accumulator S[buf] in TMEM
-//                        O += P . V       8 instructions, P K-major from shared memory, V MN-major (the page layout
+//                      two-stage K/V ring -- K as [2 dim-halves][64 tokens][128 B], V the same;
+//   warp 5 (MMA)       one thread issues tcgen05.mma (M 128, K 16, bf16/f16 -> f32):
+//                        S = Q . K^T      N 64, 8 instructions, both operands K-major, accumulator S[buf] in TMEM
+//                        O += P . V       N 128, 4 instructions, P K-major from shared memory, V MN-major (the page layout
 //                                         keeps head_dim contiguous), accumulator O in TMEM
 //                      QK^T of block i+1 is issued before PV of block i, so the tensor pipe works under the softmax;
 //   warps 0-3          the 128 softmax threads, one query row each (TMEM lane = row): tcgen05.ld S in 32-column
 //                      pieces, causal mask, running max / sum in the log2 domain, P = 2^(s - m) written to shared
 //                      memory as bf16 in the swizzled K-major layout, O rescaled in TMEM only when a row's max grew by
 //                      more than 2^8 since the last rescale (the stale max is used consistently for P and the sum).
-// TMEM: 512 columns allocated: S double-buffered (2 x 128) + O (128). Shared memory: Q 32 KiB + P 32 KiB + K/V
-// 2 x 64 KiB = 192 KiB, so one CTA per SM and the TMEM allocation never contends.
+// TMEM: 256 columns per CTA: S double-buffered (2 x 64) + O (128). Shared memory: Q 32 KiB + P 16 KiB + K/V
+// 2 x 32 KiB = 112 KiB, so TWO CTAs share an SM (and its 512 TMEM columns): while one CTA's 128 softmax threads work
+// on a block, the other CTA's MMAs keep the tensor pipe busy. Tiles are handed out longest sequence first.
 //
 // Synchronisation is mbarriers only; tcgen05.commit arrives on them when the tensor pipe has finished. Every wait is
 // bounded: a wait that runs out sets bit 8 of the error word and the CTA winds down (TMEM is freed) instead of hanging.
@@ -38,26 +39,36 @@ namespace {
 constexpr int kD = 128;
 constexpr int kPage = 16;
 constexpr int kBlockM = 128;                 // query rows per CTA
-constexpr int kBlockN = 128;                 // keys per K/V block (8 pages)
+constexpr int kBlockN = 64;                  // keys per K/V block (4 pages)
 constexpr int kPagesPerBlock = kBlockN / kPage;
 constexpr int kStages = 2;
 constexpr int kSoftmaxThreads = 128;
 constexpr int kProducerWarp = 4, kMmaWarp = 5;
 constexpr int kThreads = 192;
-constexpr int kHalfBytes = kBlockM * 128;    // [128 rows][128 B]: one 64-element half of a 128-row operand, 16 KiB
-constexpr int kOperandBytes = 2 * kHalfBytes; // 32 KiB: Q, P, one K block, one V block
-constexpr int kStageBytes = 2 * kOperandBytes; // K block + V block
-constexpr int kTmemCols = 512;
-constexpr int kColS = 0, kColO = 256;        // S buffers at columns 0 and 128, O at 256
+// Every operand is stored as 64-element (128-byte) column halves of [rows][128 B], 128-byte swizzled.
+constexpr int kQHalfBytes = kBlockM * 128;       // Q: 128 rows x 64 dims, 16 KiB; two of them
+constexpr int kQBytes = 2 * kQHalfBytes;
+constexpr int kPHalfBytes = kBlockM * 128;       // P: 128 rows x 64 keys
+constexpr int kPBytes = (kBlockN / 64) * kPHalfBytes;
+constexpr int kKvHalfBytes = kBlockN * 128;      // K (or V): kBlockN keys x 64 dims; two of them per operand
+constexpr int kKvOperandBytes = 2 * kKvHalfBytes;
+constexpr int kStageBytes = 2 * kKvOperandBytes; // K block + V block
+constexpr int kTmemCols = 256;                   // per CTA; two CTAs share the SM's 512 columns
+constexpr int kColS = 0, kColO = 2 * kBlockN;    // S buffers at columns 0 and kBlockN, O (128 columns) after them
+constexpr int kAlignSlack = 256;                 // spare bytes in front of the operands (two CTAs must fit one SM)
+constexpr int kMaxSortedSeqs = 256;              // batches up to this size are scheduled longest sequence first
+static_assert(kBlockN % 64 == 0 && kColO + kD <= kTmemCols, "TMEM budget");
 constexpr uint32_t kWaitLimit = 1u << 20; // polls before a wait gives up (about a second at worst)
 constexpr int kErrTimeout = 8;
 constexpr float kRescaleThreshold = 8.f;     // log2 units
 
 // barrier indices
 enum : int {
-    kBarKvFull = 0,                   // [kStages] producer -> MMA: K/V block landed (transaction bytes)
-    kBarKvEmpty = kBarKvFull + kStages, // [kStages] MMA (commit) -> producer: PV of the block finished
-    kBarSFull = kBarKvEmpty + kStages,  // [2] MMA (commit) -> softmax: S[buf] written
+    kBarKFull = 0,                    // [kStages] producer -> MMA: K block landed (transaction bytes)
+    kBarKEmpty = kBarKFull + kStages, // [kStages] MMA (commit) -> producer: QK^T of the block finished
+    kBarVFull = kBarKEmpty + kStages, // [kStages] producer -> MMA: V block landed
+    kBarVEmpty = kBarVFull + kStages, // [kStages] MMA (commit) -> producer: PV of the block finished
+    kBarSFull = kBarVEmpty + kStages, // [2] MMA (commit) -> softmax: S[buf] written
     kBarSFree = kBarSFull + 2,          // [2] softmax (128) -> MMA: S[buf] read
     kBarPFull = kBarSFree + 2,          // softmax (128) -> MMA: P in shared memory, O rescaled
     kBarPFree = kBarPFull + 1,          // MMA (commit) -> softmax: PV finished: P reusable, O stable
@@ -176,29 +187,51 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 }
 
 template <bool kBf16>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
     paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, PrefillParams p) {
-    extern __shared__ unsigned char smem_raw[];
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t raw_u32 = smem_u32(smem_raw);
     const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u; // swizzled operands need 1 KiB alignment
     unsigned char *base = smem_raw + (base_u32 - raw_u32);
-    const uint32_t q_u32 = base_u32, p_u32 = base_u32 + kOperandBytes, kv_u32 = base_u32 + 2 * kOperandBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(base + 2 * kOperandBytes + kStages * kStageBytes);
+    const uint32_t q_u32 = base_u32, p_u32 = base_u32 + kQBytes, kv_u32 = base_u32 + kQBytes + kPBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(base + kQBytes + kPBytes + kStages * kStageBytes);
     const uint32_t bars_u32 = smem_u32(bars);
-    __shared__ uint32_t s_tmem_base;
-    __shared__ int s_abort;
+    uint32_t *s_tmem_base = reinterpret_cast<uint32_t *>(bars + kNumBars);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(s_tmem_base + 1);
+    int16_t *s_order = reinterpret_cast<int16_t *>(s_tmem_base + 2); // [min(n_seqs, kMaxSortedSeqs)]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (base_u32 - raw_u32 > uint32_t(kAlignSlack)) { // cannot place the swizzled operands: report, do not run
+        if (tid == 0) {
+            atomicOr(p.error_flag, kErrTimeout);
+        }
+        return;
+    }
 
-    // ---- which tile ----------------------------------------------------------------------------------------
+    // ---- which tile: sequences by decreasing length (the order CTAs are handed out is the order they start) ------
+    const bool sorted = p.n_seqs <= kMaxSortedSeqs;
+    if (sorted) {
+        for (int a = tid; a < p.n_seqs; a += kThreads) {
+            const int len_a = p.kv_lens[a];
+            int rank = 0;
+            for (int b = 0; b < p.n_seqs; ++b) {
+                const int len_b = p.kv_lens[b];
+                rank += (len_b > len_a || (len_b == len_a && b < a)) ? 1 : 0;
+            }
+            s_order[rank] = int16_t(a);
+        }
+    }
+    __syncthreads();
     const int linear = blockIdx.x;
-    const int qb = p.q_blocks - 1 - (linear % p.q_blocks); // late query blocks see the most keys: schedule them first
-    const int h = (linear / p.q_blocks) % p.nh;
-    const int s = linear / (p.q_blocks * p.nh);
+    const int per_seq = p.q_blocks * p.nh;
+    const int s = sorted ? int(s_order[linear / per_seq]) : linear / per_seq;
+    const int within = linear % per_seq;
+    const int qb = p.q_blocks - 1 - within / p.nh; // late query blocks see the most keys: first
+    const int h = within % p.nh;
     const int q_start = p.q_starts[s];
     const int q_len = p.q_starts[s + 1] - q_start;
     if (qb * kBlockM >= q_len) {
-        return; // uniform over the CTA, before any barrier or allocation
+        return; // uniform over the CTA, before any mbarrier or TMEM allocation
     }
     const int kv_len = min(max(p.kv_lens[s], q_len), p.table_stride * kPage);
     const int off = kv_len - q_len;                                   // query t sees keys j <= t + off
@@ -214,11 +247,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             const bool many = (i >= kBarSFree && i < kBarSFree + 2) || i == kBarPFull;
             mbar_init(bars_u32 + i * 8, many ? kSoftmaxThreads : 1);
         }
-        s_abort = 0;
+        *s_abort = 0;
         mbar_init_fence();
     }
     if (warp == kMmaWarp) {
-        tmem_alloc(smem_u32(&s_tmem_base), kTmemCols);
+        tmem_alloc(smem_u32(s_tmem_base), kTmemCols);
         tmem_relinquish();
     }
     {
@@ -232,11 +265,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (t < q_len) {
                 val = *reinterpret_cast<const uint4 *>(q_base + ((long long)(q_start + t) * p.nh + h) * (kD * 2) + cc * 16);
             }
-            const uint32_t dst = q_u32 + (cc >> 3) * kHalfBytes + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+            const uint32_t dst = q_u32 + (cc >> 3) * kQHalfBytes + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
             asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
         }
-        // A block shorter than 128 keys leaves ring rows unwritten; they are masked out of S, but V rows enter the
-        // PV product with weight 0, so they must at least be finite: start from zeros.
+        // A block shorter than kBlockN keys leaves ring rows unwritten; they are masked out of S, but V rows enter
+        // the PV product with weight 0, so they must at least be finite: start from zeros.
         for (int idx = tid; idx < kStages * kStageBytes / 16; idx += kThreads) {
             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(kv_u32 + idx * 16), "r"(0u) : "memory");
         }
@@ -245,43 +278,53 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = s_tmem_base;
+    const uint32_t tmem_base = *s_tmem_base;
 
     auto bar = [&](int which) { return bars_u32 + uint32_t(which) * 8; };
     auto give_up = [&]() {
-        s_abort = 1;
+        *s_abort = 1;
         atomicOr(p.error_flag, kErrTimeout);
     };
 
     if (warp == kProducerWarp) {
         // ================================ producer: TMA tiles of K and V =====================================
         const long long tbase = (long long)seq_row * p.table_stride;
-        for (int i = 0; i < nblk; ++i) {
+        // K and V of a block have separate barriers: the K slot is free again as soon as QK^T of its block is done,
+        // one whole block earlier than the V slot (PV runs after the softmax), so K of block i + 2 is in flight early
+        // enough to hide the copy latency with only two stages.
+        bool alive = true;
+        for (int i = 0; i < nblk && alive; ++i) {
             const int st = i & 1;
-            if (i >= kStages && !wait_or_abort(bar(kBarKvEmpty + st), uint32_t((i >> 1) - 1) & 1u, &s_abort)) {
-                if (lane == 0) {
-                    give_up();
-                }
-                break;
-            }
             const int first = i * kPagesPerBlock;
             const int n_pg = min(kPagesPerBlock, n_pages - first);
-            if (lane == 0) {
-                mbar_arrive_expect_tx(bar(kBarKvFull + st), uint32_t(n_pg) * 4 * 2048);
-            }
-            __syncwarp();
+            int page = 0;
             if (lane < n_pg) {
-                int page = p.block_table[tbase + first + lane];
+                page = p.block_table[tbase + first + lane];
                 if (page < 0 || page >= p.num_pages) {
                     atomicOr(p.error_flag, kErrBadPage);
                     page = 0;
                 }
-                const int c3 = int((p.page0 + page) * 2);
-                const uint32_t dst = kv_u32 + st * kStageBytes + lane * 2048;
-                tma_load_4d(dst, &tmap, 0, 0, kvh, c3, bar(kBarKvFull + st));                                   // K, dims 0-63
-                tma_load_4d(dst + kHalfBytes, &tmap, 64, 0, kvh, c3, bar(kBarKvFull + st));                     // K, dims 64-127
-                tma_load_4d(dst + kOperandBytes, &tmap, 0, 0, kvh, c3 + 1, bar(kBarKvFull + st));               // V, dims 0-63
-                tma_load_4d(dst + kOperandBytes + kHalfBytes, &tmap, 64, 0, kvh, c3 + 1, bar(kBarKvFull + st)); // V, dims 64-127
+            }
+            const int c3 = int((p.page0 + page) * 2);
+            const uint32_t dst = kv_u32 + st * kStageBytes + lane * 2048;
+#pragma unroll
+            for (int is_v = 0; is_v < 2; ++is_v) {
+                const int full = (is_v ? kBarVFull : kBarKFull) + st, empty = (is_v ? kBarVEmpty : kBarKEmpty) + st;
+                if (i >= kStages && !wait_or_abort(bar(empty), uint32_t((i >> 1) - 1) & 1u, s_abort)) {
+                    if (lane == 0) {
+                        give_up();
+                    }
+                    alive = false;
+                    break;
+                }
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar(full), uint32_t(n_pg) * 2 * 2048);
+                }
+                __syncwarp();
+                if (lane < n_pg) {
+                    tma_load_4d(dst + is_v * kKvOperandBytes, &tmap, 0, 0, kvh, c3 + is_v, bar(full));                  // dims 0-63
+                    tma_load_4d(dst + is_v * kKvOperandBytes + kKvHalfBytes, &tmap, 64, 0, kvh, c3 + is_v, bar(full)); // dims 64-127
+                }
             }
         }
     } else if (warp == kMmaWarp) {
@@ -292,28 +335,30 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t tmem_o = tmem_base + kColO;
             bool ok = true;
             auto issue_pv = [&](int j) { // O (+)= P . V of block j
-                if (!wait_or_abort(bar(kBarPFull), uint32_t(j) & 1u, &s_abort)) {
+                if (!wait_or_abort(bar(kBarPFull), uint32_t(j) & 1u, s_abort) ||
+                    !wait_or_abort(bar(kBarVFull + (j & 1)), uint32_t(j >> 1) & 1u, s_abort)) {
                     return false;
                 }
                 tc_fence_after();
-                const uint32_t v_u32 = kv_u32 + (j & 1) * kStageBytes + kOperandBytes;
+                const uint32_t v_u32 = kv_u32 + (j & 1) * kStageBytes + kKvOperandBytes;
 #pragma unroll
                 for (int kk = 0; kk < kBlockN / 16; ++kk) {
                     // A = P rows x 16 keys (K-major: 32 bytes into the 128-byte row per step, next half after 4 steps)
-                    const uint64_t a = smem_desc_sw128(p_u32 + (kk >> 2) * kHalfBytes + (kk & 3) * 32, 0, 1024);
-                    // B = 16 keys x 128 dims of V, MN-major: 8-key groups 1 KiB apart, the two 64-dim halves 16 KiB apart
-                    const uint64_t b = smem_desc_sw128(v_u32 + kk * 2048, kHalfBytes, 1024);
+                    const uint64_t a = smem_desc_sw128(p_u32 + (kk >> 2) * kPHalfBytes + (kk & 3) * 32, 0, 1024);
+                    // B = 16 keys x 128 dims of V, MN-major: 8-key groups 1 KiB apart, the two 64-dim halves one
+                    // half-operand apart
+                    const uint64_t b = smem_desc_sw128(v_u32 + kk * 2048, kKvHalfBytes, 1024);
                     umma_f16(tmem_o, a, b, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(bar(kBarPFree));
-                umma_commit(bar(kBarKvEmpty + (j & 1)));
+                umma_commit(bar(kBarVEmpty + (j & 1)));
                 return true;
             };
             for (int i = 0; i < nblk && ok; ++i) {
                 const int st = i & 1, buf = i & 1;
-                ok = wait_or_abort(bar(kBarKvFull + st), uint32_t(i >> 1) & 1u, &s_abort);
+                ok = wait_or_abort(bar(kBarKFull + st), uint32_t(i >> 1) & 1u, s_abort);
                 if (ok && i >= 2) {
-                    ok = wait_or_abort(bar(kBarSFree + buf), uint32_t((i >> 1) - 1) & 1u, &s_abort);
+                    ok = wait_or_abort(bar(kBarSFree + buf), uint32_t((i >> 1) - 1) & 1u, s_abort);
                 }
                 if (!ok) {
                     break;
@@ -322,11 +367,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const uint32_t k_u32 = kv_u32 + st * kStageBytes;
 #pragma unroll
                 for (int ks = 0; ks < kD / 16; ++ks) {
-                    const uint64_t a = smem_desc_sw128(q_u32 + (ks >> 2) * kHalfBytes + (ks & 3) * 32, 0, 1024);
-                    const uint64_t b = smem_desc_sw128(k_u32 + (ks >> 2) * kHalfBytes + (ks & 3) * 32, 0, 1024);
+                    const uint64_t a = smem_desc_sw128(q_u32 + (ks >> 2) * kQHalfBytes + (ks & 3) * 32, 0, 1024);
+                    const uint64_t b = smem_desc_sw128(k_u32 + (ks >> 2) * kKvHalfBytes + (ks & 3) * 32, 0, 1024);
                     umma_f16(tmem_base + kColS + buf * kBlockN, a, b, idesc_qk, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(kBarSFull + buf));
+                umma_commit(bar(kBarKEmpty + st));
                 if (i >= 1) {
                     ok = issue_pv(i - 1);
                 }
@@ -349,7 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         bool dead = false;
         for (int i = 0; i < nblk && !dead; ++i) {
             const int buf = i & 1;
-            if (!wait_or_abort(bar(kBarSFull + buf), uint32_t(i >> 1) & 1u, &s_abort)) {
+            if (!wait_or_abort(bar(kBarSFull + buf), uint32_t(i >> 1) & 1u, s_abort)) {
                 dead = true;
                 break;
             }
@@ -357,18 +403,31 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint32_t tmem_s = tmem_base + lane_base + kColS + buf * kBlockN;
             const int j0 = i * kBlockN;
             const int n_ok = min(min(last_visible, kv_len - 1) - j0 + 1, kBlockN); // visible columns are [0, n_ok)
+            // Most blocks lie wholly below the diagonal: the whole warp then skips the mask (warp-uniform choice, so
+            // the collective TMEM loads stay convergent).
+            const bool plain = __all_sync(0xffffffffu, n_ok >= kBlockN) && p.scale_log2 > 0.f;
             // pass 1: row maximum of the visible scores (log2 domain)
             float mx = -INFINITY;
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
+            for (int c = 0; c < kBlockN / 32; ++c) {
                 float v[32];
-                tmem_ld32(tmem_s + c4 * 32, v);
+                tmem_ld32(tmem_s + c * 32, v);
+                if (plain) {
 #pragma unroll
-                for (int k = 0; k < 32; ++k) {
-                    if (c4 * 32 + k < n_ok) {
-                        mx = fmaxf(mx, v[k] * p.scale_log2);
+                    for (int k = 0; k < 32; ++k) {
+                        mx = fmaxf(mx, v[k]);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) {
+                        if (c * 32 + k < n_ok) {
+                            mx = fmaxf(mx, v[k] * p.scale_log2);
+                        }
                     }
                 }
+            }
+            if (plain) {
+                mx *= p.scale_log2;
             }
             // The running max only moves when it grew by more than 2^8: P and the row sum both use m_used, so the
             // result is exact either way, and O is rescaled rarely.
@@ -380,21 +439,21 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             if (i >= 1) {
                 // PV of the previous block must be finished before P is overwritten or O is rescaled
-                if (!wait_or_abort(bar(kBarPFree), uint32_t(i - 1) & 1u, &s_abort)) {
+                if (!wait_or_abort(bar(kBarPFree), uint32_t(i - 1) & 1u, s_abort)) {
                     dead = true;
                     break;
                 }
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll
-                    for (int c4 = 0; c4 < 4; ++c4) {
+                    for (int c = 0; c < kD / 32; ++c) {
                         float v[32];
-                        tmem_ld32(tmem_o + c4 * 32, v);
+                        tmem_ld32(tmem_o + c * 32, v);
 #pragma unroll
                         for (int k = 0; k < 32; ++k) {
                             v[k] *= alpha;
                         }
-                        tmem_st32(tmem_o + c4 * 32, v);
+                        tmem_st32(tmem_o + c * 32, v);
                     }
                     tmem_wait_st();
                 }
@@ -402,22 +461,27 @@ __global__ void __launch_bounds__(kThreads, 1)
             l *= alpha;
             // pass 2: P = 2^(s - m) as 16-bit, into the swizzled K-major operand layout
             const float m_ref = m_used == -INFINITY ? 0.f : m_used;
+            const float neg_m = -m_ref;
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
+            for (int c = 0; c < kBlockN / 32; ++c) {
                 float v[32];
-                tmem_ld32(tmem_s + c4 * 32, v);
+                tmem_ld32(tmem_s + c * 32, v);
                 uint32_t packed[16];
 #pragma unroll
                 for (int k = 0; k < 32; k += 2) {
-                    const float p0 = (c4 * 32 + k < n_ok) ? fast_exp2(v[k] * p.scale_log2 - m_ref) : 0.f;
-                    const float p1 = (c4 * 32 + k + 1 < n_ok) ? fast_exp2(v[k + 1] * p.scale_log2 - m_ref) : 0.f;
+                    float p0 = fast_exp2(fmaf(v[k], p.scale_log2, neg_m));
+                    float p1 = fast_exp2(fmaf(v[k + 1], p.scale_log2, neg_m));
+                    if (!plain) {
+                        p0 = (c * 32 + k < n_ok) ? p0 : 0.f;
+                        p1 = (c * 32 + k + 1 < n_ok) ? p1 : 0.f;
+                    }
                     l += p0 + p1;
                     packed[k >> 1] = pack2<kBf16>(p0, p1);
                 }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
-                    const int cc = c4 * 4 + q4; // 16-byte chunk (8 keys) of this row
-                    const uint32_t dst = p_u32 + (cc >> 3) * kHalfBytes + row * 128 + (((cc & 7) ^ (row & 7)) << 4);
+                    const int cc = c * 4 + q4; // 16-byte chunk (8 keys) of this row
+                    const uint32_t dst = p_u32 + (cc >> 3) * kPHalfBytes + row * 128 + (((cc & 7) ^ (row & 7)) << 4);
                     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(packed[q4 * 4]),
                                  "r"(packed[q4 * 4 + 1]), "r"(packed[q4 * 4 + 2]), "r"(packed[q4 * 4 + 3])
                                  : "memory");
@@ -429,7 +493,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_arrive(bar(kBarPFull));
         }
         // ---- epilogue: O / l -> out ------------------------------------------------------------------------------
-        if (!dead && !wait_or_abort(bar(kBarPFree), uint32_t(nblk - 1) & 1u, &s_abort)) {
+        if (!dead && !wait_or_abort(bar(kBarPFree), uint32_t(nblk - 1) & 1u, s_abort)) {
             dead = true;
         }
         if (dead) {
@@ -490,7 +554,10 @@ EncodeTiledFn prefill_encode_fn() {
     return fn;
 }
 
-constexpr size_t kSmemBytes = 1024 + 2 * kOperandBytes + kStages * kStageBytes + kNumBars * sizeof(uint64_t);
+// operands + barriers + TMEM-address / abort words + sequence order; kAlignSlack bytes for the 1 KiB alignment of the
+// operand area (the dynamic window itself starts aligned when the kernel has no static shared memory)
+constexpr size_t kSmemBytes = kAlignSlack + kQBytes + kPBytes + kStages * kStageBytes + kNumBars * sizeof(uint64_t) + 8 +
+                              kMaxSortedSeqs * sizeof(int16_t);
 
 template <bool kBf16>
 void launch(cudaStream_t s, const CUtensorMap &tmap, const PrefillParams &p, int grid) {
