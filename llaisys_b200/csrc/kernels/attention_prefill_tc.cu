@@ -118,7 +118,20 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 
-// 32 consecutive f32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// 32 consecutive f32 columns of this thread's TMEM lane. The _nowait form only issues the load: the registers are
+// valid after tmem_wait_ld().
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     uint32_t r[32];
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -403,31 +416,37 @@ __global__ void __launch_bounds__(kThreads, 2)
             const uint32_t tmem_s = tmem_base + lane_base + kColS + buf * kBlockN;
             const int j0 = i * kBlockN;
             const int n_ok = min(min(last_visible, kv_len - 1) - j0 + 1, kBlockN); // visible columns are [0, n_ok)
-            // Most blocks lie wholly below the diagonal: the whole warp then skips the mask (warp-uniform choice, so
-            // the collective TMEM loads stay convergent).
-            const bool plain = __all_sync(0xffffffffu, n_ok >= kBlockN) && p.scale_log2 > 0.f;
-            // pass 1: row maximum of the visible scores (log2 domain)
-            float mx = -INFINITY;
+            // One TMEM read of the row's kBlockN scores; S[buf] is handed back to the tensor pipe straight away.
+            uint32_t sr[kBlockN / 32][32];
 #pragma unroll
             for (int c = 0; c < kBlockN / 32; ++c) {
-                float v[32];
-                tmem_ld32(tmem_s + c * 32, v);
-                if (plain) {
+                tmem_ld32_nowait(tmem_s + c * 32, sr[c]);
+            }
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(kBarSFree + buf)); // S[buf] may be overwritten by QK^T of block i + 2
+            // Most blocks lie wholly below the diagonal: the whole warp then skips the mask (warp-uniform choice).
+            const bool plain = __all_sync(0xffffffffu, n_ok >= kBlockN) && p.scale_log2 > 0.f;
+            float mx = -INFINITY;
+            if (plain) {
+#pragma unroll
+                for (int c = 0; c < kBlockN / 32; ++c) {
 #pragma unroll
                     for (int k = 0; k < 32; ++k) {
-                        mx = fmaxf(mx, v[k]);
+                        mx = fmaxf(mx, __uint_as_float(sr[c][k]));
                     }
-                } else {
+                }
+                mx *= p.scale_log2;
+            } else {
+#pragma unroll
+                for (int c = 0; c < kBlockN / 32; ++c) {
 #pragma unroll
                     for (int k = 0; k < 32; ++k) {
                         if (c * 32 + k < n_ok) {
-                            mx = fmaxf(mx, v[k] * p.scale_log2);
+                            mx = fmaxf(mx, __uint_as_float(sr[c][k]) * p.scale_log2);
                         }
                     }
                 }
-            }
-            if (plain) {
-                mx *= p.scale_log2;
             }
             // The running max only moves when it grew by more than 2^8: P and the row sum both use m_used, so the
             // result is exact either way, and O is rescaled rarely.
@@ -436,6 +455,25 @@ __global__ void __launch_bounds__(kThreads, 2)
             if (grow) {
                 alpha = fast_exp2(m_used - mx); // 0 on the first block
                 m_used = mx;
+            }
+            l *= alpha;
+            // P = 2^(s - m) as 16-bit, computed into registers BEFORE waiting for the previous PV: only the stores of
+            // P sit on the block-to-block dependency chain.
+            const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+            uint32_t packed[kBlockN / 2];
+#pragma unroll
+            for (int c = 0; c < kBlockN / 32; ++c) {
+#pragma unroll
+                for (int k = 0; k < 32; k += 2) {
+                    float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][k]), p.scale_log2, neg_m));
+                    float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][k + 1]), p.scale_log2, neg_m));
+                    if (!plain) {
+                        p0 = (c * 32 + k < n_ok) ? p0 : 0.f;
+                        p1 = (c * 32 + k + 1 < n_ok) ? p1 : 0.f;
+                    }
+                    l += p0 + p1;
+                    packed[c * 16 + (k >> 1)] = pack2<kBf16>(p0, p1);
+                }
             }
             if (i >= 1) {
                 // PV of the previous block must be finished before P is overwritten or O is rescaled
@@ -456,40 +494,17 @@ __global__ void __launch_bounds__(kThreads, 2)
                         tmem_st32(tmem_o + c * 32, v);
                     }
                     tmem_wait_st();
+                    tc_fence_before();
                 }
             }
-            l *= alpha;
-            // pass 2: P = 2^(s - m) as 16-bit, into the swizzled K-major operand layout
-            const float m_ref = m_used == -INFINITY ? 0.f : m_used;
-            const float neg_m = -m_ref;
 #pragma unroll
-            for (int c = 0; c < kBlockN / 32; ++c) {
-                float v[32];
-                tmem_ld32(tmem_s + c * 32, v);
-                uint32_t packed[16];
-#pragma unroll
-                for (int k = 0; k < 32; k += 2) {
-                    float p0 = fast_exp2(fmaf(v[k], p.scale_log2, neg_m));
-                    float p1 = fast_exp2(fmaf(v[k + 1], p.scale_log2, neg_m));
-                    if (!plain) {
-                        p0 = (c * 32 + k < n_ok) ? p0 : 0.f;
-                        p1 = (c * 32 + k + 1 < n_ok) ? p1 : 0.f;
-                    }
-                    l += p0 + p1;
-                    packed[k >> 1] = pack2<kBf16>(p0, p1);
-                }
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int cc = c * 4 + q4; // 16-byte chunk (8 keys) of this row
-                    const uint32_t dst = p_u32 + (cc >> 3) * kPHalfBytes + row * 128 + (((cc & 7) ^ (row & 7)) << 4);
-                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(packed[q4 * 4]),
-                                 "r"(packed[q4 * 4 + 1]), "r"(packed[q4 * 4 + 2]), "r"(packed[q4 * 4 + 3])
-                                 : "memory");
-                }
+            for (int cc = 0; cc < kBlockN / 8; ++cc) { // 16-byte chunk (8 keys) of this row, swizzled K-major layout
+                const uint32_t dst = p_u32 + (cc >> 3) * kPHalfBytes + row * 128 + (((cc & 7) ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(packed[cc * 4]),
+                             "r"(packed[cc * 4 + 1]), "r"(packed[cc * 4 + 2]), "r"(packed[cc * 4 + 3])
+                             : "memory");
             }
-            tc_fence_before();
-            mbar_arrive(bar(kBarSFree + buf)); // S[buf] may be overwritten by QK^T of block i + 2
-            fence_proxy_async_smem();          // P stores -> visible to the tensor pipe's reads
+            fence_proxy_async_smem(); // P stores -> visible to the tensor pipe's reads
             mbar_arrive(bar(kBarPFull));
         }
         // ---- epilogue: O / l -> out ------------------------------------------------------------------------------
