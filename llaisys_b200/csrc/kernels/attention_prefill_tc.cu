@@ -461,20 +461,34 @@ __global__ void __launch_bounds__(kThreads, 2)
             // P sit on the block-to-block dependency chain.
             const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
             uint32_t packed[kBlockN / 2];
+            float l0 = 0.f, l1 = 0.f; // two independent sums: shorter dependency chains
+            if (plain) {
 #pragma unroll
-            for (int c = 0; c < kBlockN / 32; ++c) {
+                for (int c = 0; c < kBlockN / 32; ++c) {
 #pragma unroll
-                for (int k = 0; k < 32; k += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][k]), p.scale_log2, neg_m));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][k + 1]), p.scale_log2, neg_m));
-                    if (!plain) {
-                        p0 = (c * 32 + k < n_ok) ? p0 : 0.f;
-                        p1 = (c * 32 + k + 1 < n_ok) ? p1 : 0.f;
+                    for (int k = 0; k < 32; k += 2) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][k]), p.scale_log2, neg_m));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][k + 1]), p.scale_log2, neg_m));
+                        l0 += p0;
+                        l1 += p1;
+                        packed[c * 16 + (k >> 1)] = pack2<kBf16>(p0, p1);
                     }
-                    l += p0 + p1;
-                    packed[c * 16 + (k >> 1)] = pack2<kBf16>(p0, p1);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < kBlockN / 32; ++c) {
+#pragma unroll
+                    for (int k = 0; k < 32; k += 2) {
+                        const float p0 = (c * 32 + k < n_ok) ? fast_exp2(fmaf(__uint_as_float(sr[c][k]), p.scale_log2, neg_m)) : 0.f;
+                        const float p1 =
+                            (c * 32 + k + 1 < n_ok) ? fast_exp2(fmaf(__uint_as_float(sr[c][k + 1]), p.scale_log2, neg_m)) : 0.f;
+                        l0 += p0;
+                        l1 += p1;
+                        packed[c * 16 + (k >> 1)] = pack2<kBf16>(p0, p1);
+                    }
                 }
             }
+            l += l0 + l1;
             if (i >= 1) {
                 // PV of the previous block must be finished before P is overwritten or O is rescaled
                 if (!wait_or_abort(bar(kBarPFree), uint32_t(i - 1) & 1u, s_abort)) {
