@@ -196,13 +196,201 @@ def run_reference_arm(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def _init_device():
+    """Per-rank device set-up shared by every workload. -> torch, llaisys, rank, local_rank, world, dist"""
+    import torch
+
+    import llaisys_b200 as llaisys
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU stand-in")
+    torch.cuda.set_device(local_rank)
+    llaisys.set_context_runtime(llaisys.DeviceType.NVIDIA, local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    return torch, llaisys, rank, local_rank, world, dist
+
+
+def _peaks():
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        d = json.loads(peaks_file.read_text())
+        return float(d["hbm_gbs"]), float(d["bf16_tflops_sustained"]), "measured"
+    return 6650.0, 1400.0, "fallback"
+
+
+def run_prefill_workload(args) -> None:
+    """--workload config3: chunked prefill. 8 sequences per GPU, existing context ~ U{0..8192}, a 512-token chunk
+    appended and then attended causally. A step = append of the chunk rows + the tcgen05 prefill kernel."""
+    torch, llaisys, rank, local_rank, world, dist = _init_device()
+    dev = llaisys.DeviceType.NVIDIA
+    g = torch.Generator().manual_seed(3 + rank)
+    B, chunk, layers = 8, 512, max(2, args.layers)
+    context = torch.randint(0, 8193, (B,), generator=g).tolist()
+    kv_lens = [c + chunk for c in context]
+    cache = llaisys.PagedKVCache(POOL_PAGES, NKVH, D, nlayer=layers, dtype=llaisys.DataType.BF16, device=dev,
+                                 device_id=local_rank, max_seqs=B,
+                                 max_pages_per_seq=max(-(-k // PAGE) for k in kv_lens))
+    perm = torch.randperm(POOL_PAGES, generator=g).tolist()
+    seqs, at = [], 0
+    for k in kv_lens:
+        n = -(-k // PAGE)
+        s = cache.add_seq()
+        cache.assign_pages(s, perm[at:at + n])
+        at += n
+        seqs.append(s)
+    cache.flush()
+    stream = torch.cuda.Stream()
+    cg = torch.Generator(device="cuda").manual_seed(300 + rank)
+    ids = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    lens = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
+    starts = torch.tensor([i * chunk for i in range(B + 1)], dtype=torch.int32, device="cuda")
+    ctx_t = torch.tensor(context, dtype=torch.int32, device="cuda")
+    # rows of the existing contexts (filled once) and of the chunks (appended every step)
+    old_seq = torch.repeat_interleave(ids, ctx_t.long())
+    old_pos = (torch.arange(old_seq.numel(), device="cuda", dtype=torch.int32)
+               - torch.repeat_interleave(torch.cumsum(ctx_t, 0) - ctx_t, ctx_t.long()).int())
+    new_seq = torch.repeat_interleave(ids, chunk)
+    new_pos = (torch.arange(chunk, device="cuda", dtype=torch.int32).repeat(B) + torch.repeat_interleave(ctx_t, chunk))
+    torch.cuda.synchronize()
+    n_old = old_seq.numel()
+    for layer in range(layers):
+        k_rows = torch.randn((n_old, NKVH, D), generator=cg, device="cuda").bfloat16()
+        v_rows = torch.randn((n_old, NKVH, D), generator=cg, device="cuda").bfloat16()
+        cache.append_dev(layer, k_rows, v_rows, old_seq, old_pos, n_old, stream.cuda_stream)
+        stream.synchronize()
+    q = torch.randn((B * chunk, NH, D), generator=cg, device="cuda").bfloat16()
+    k_new = torch.randn((B * chunk, NKVH, D), generator=cg, device="cuda").bfloat16()
+    v_new = torch.randn((B * chunk, NKVH, D), generator=cg, device="cuda").bfloat16()
+    out = torch.empty_like(q)
+    scale, max_kv = 1.0 / D ** 0.5, max(kv_lens)
+    torch.cuda.synchronize()
+
+    def do_append(i):
+        cache.append_dev(i % layers, k_new, v_new, new_seq, new_pos, B * chunk, stream.cuda_stream)
+
+    def do_attend(i):
+        cache.prefill_dev(i % layers, out, q, ids, starts, lens, B, B * chunk, chunk, max_kv, NH, scale,
+                          stream.cuda_stream)
+
+    def do_step(i):
+        do_append(i)
+        do_attend(i)
+
+    for i in range(max(3, args.warmup)):
+        do_step(i)
+    stream.synchronize()
+    cache.check()
+    chunk_steps = max(layers, min(args.steps, 40) // layers * layers)
+    reps = max(1, min(args.steps, 400) // chunk_steps)
+    steps = chunk_steps * reps
+
+    def capture(body):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(chunk_steps):
+                body(i)
+        return graph
+
+    def timed(graph):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            graph.replay()
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+        stream.synchronize()
+        return e0.elapsed_time(e1)
+
+    g_step, g_att, g_app = capture(do_step), capture(do_attend), capture(do_append)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local_rank) as clocks:
+        elapsed_ms = timed(g_step)
+    attend_ms, append_ms = timed(g_att) / steps, timed(g_app) / steps
+    cache.check()
+
+    # end to end: host index arrays, pinned host q / k / v / out, copies and a synchronise per step
+    e2e = None
+    if not args.no_e2e:
+        api, cs = llaisys.RuntimeAPI(dev), llaisys.context_stream()
+        q_h, k_h, v_h = (t.cpu().pin_memory() for t in (q, k_new, v_new))
+        out_h = torch.empty_like(q_h).pin_memory()
+        q_d, k_d, v_d, out_d = (torch.empty_like(t) for t in (q, k_new, v_new, out))
+        new_seq_h, new_pos_h = new_seq.cpu().numpy(), new_pos.cpu().numpy()
+        H2D, D2H = llaisys.MemcpyKind.H2D, llaisys.MemcpyKind.D2H
+
+        def step_e2e(i):
+            for dst, src in ((q_d, q_h), (k_d, k_h), (v_d, v_h)):
+                api.memcpy_async(dst, src, src.numel() * 2, H2D, cs)
+            cache.append(i % layers, k_d, v_d, new_seq_h, new_pos_h)
+            cache.prefill(i % layers, out_d, q_d, seqs, [chunk] * B, kv_lens, NH, scale)
+            api.memcpy_async(out_h, out_d, out_h.numel() * 2, D2H, cs)
+            api.stream_synchronize(cs)
+
+        n_e2e = max(10, min(args.steps, 100))
+        for i in range(2):
+            step_e2e(i)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(n_e2e):
+            step_e2e(i)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        step_e2e(0)
+        do_step(0)
+        stream.synchronize()
+        e2e = {"value": world * B * chunk * n_e2e / e2e_s, "unit": "tokens/s",
+               "h2d_bytes_per_step": (q_h.numel() + k_h.numel() + v_h.numel()) * 2,
+               "d2h_bytes_per_step": out_h.numel() * 2, "steps": n_e2e,
+               "matches_device_path": bool(torch.equal(out_h.view(torch.int16), out.cpu().view(torch.int16)))}
+
+    stats = torch.tensor([elapsed_ms, attend_ms, append_ms], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        elapsed_ms, attend_ms, append_ms = (float(x) for x in stats)
+    if rank == 0:
+        hbm_peak, tensor_peak, kind = _peaks()
+        flops = sum(4 * NH * D * (chunk * c + chunk * (chunk + 1) // 2) for c in context)
+        achieved = flops / (attend_ms * 1e-3) / 1e12
+        line = {
+            "metric": "prefill tokens/s (paged KV append of a 512-token chunk + causal chunk attention, one layer)",
+            "value": world * B * chunk * steps / (elapsed_ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": elapsed_ms / steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "config3", "batch_per_gpu": B, "context": context, "chunk": chunk,
+                       "heads": "12q/2kv", "head_dim": D, "page_size": PAGE, "pool_pages": POOL_PAGES,
+                       "parallelism": f"sequences sharded over {world} GPU(s), no collective",
+                       "l2": f"layer pool rotates over {layers} x {cache.layer_bytes() >> 20} MiB between steps"},
+            "roofline": {"bound": "tensor", "kernel": "paged_prefill_tc_kernel", "achieved": achieved,
+                         "peak": tensor_peak, "peak_kind": f"sustained bf16, of {kind}", "unit": "TFLOP/s",
+                         "frac": achieved / tensor_peak, "frac_of_nominal_2250": achieved / 2250.0, "traffic": None,
+                         "algorithmic_flops_per_launch": flops, "kernel_ms_mean": attend_ms,
+                         "append_kernel_ms_mean": append_ms},
+            "e2e": e2e, "gpu_launches": 2 * steps, "timing": f"CUDA graphs of {chunk_steps} steps x {reps} replays",
+            "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="north_star", choices=["north_star", "config2"])
+    ap.add_argument("--workload", default="north_star", choices=["north_star", "config2", "config3"])
     ap.add_argument("--layers", type=int, default=4, help="pools to rotate over between steps (L2 flush)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-API leg (profiling runs)")
@@ -212,6 +400,9 @@ def main() -> None:
 
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload == "config3":
+        run_prefill_workload(args)
         return
 
     import torch

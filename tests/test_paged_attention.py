@@ -245,6 +245,51 @@ def test_prefill_config3_reduced_nvidia(cuda_device):
 
 
 @pytest.mark.gpu
+def test_prefill_config3_full_size_nvidia(cuda_device):
+    """Configuration 3 at full size: 8 sequences, context ~ U{0..8192}, 512-token chunk, 16384-page pool
+    (the CPU oracle needs a few seconds per long sequence)."""
+    check_prefill(NVIDIA, "bf16", workloads.config3(), workloads.POOL_PAGES)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_prefill_ragged_chunks_and_block_boundaries_nvidia(cuda_device, dname):
+    """Chunks and contexts on both sides of the kernel's tile sizes (128 query rows, 64-key blocks, 16-token pages),
+    a chunk with no context, a one-token chunk, and a sequence without a chunk, in one ragged batch."""
+    g = torch.Generator().manual_seed(17)
+    dt = helpers.TORCH_DTYPE[dname]
+    q_lens = [1, 127, 128, 129, 300, 64, 0, 5]
+    ctxs = [200, 0, 63, 64, 65, 1000, 30, 15]
+    kv_lens = [c + q for c, q in zip(ctxs, q_lens)]
+    cache = llaisys.PagedKVCache(512, 2, 128, dtype=helpers.LL_DTYPE[dname], device=NVIDIA, max_seqs=len(q_lens),
+                                 max_pages_per_seq=80)
+    seqs, ks, vs, qs = [], [], [], []
+    for ql, kl in zip(q_lens, kv_lens):
+        s = cache.add_seq()
+        cache.reserve(s, kl)
+        seqs.append(s)
+        ks.append(workloads.randn((kl, 2, 128), dt, g))
+        vs.append(workloads.randn((kl, 2, 128), dt, g))
+        qs.append(workloads.randn((ql, 12, 128), dt, g))
+    helpers.append_all(cache, 0, seqs, ks, vs, NVIDIA)
+    q = torch.cat(qs).cuda()
+    out = torch.full_like(q, float("nan"))
+    cache.prefill(0, out, q, seqs, q_lens, kv_lens, 12, 128 ** -0.5)
+    cache.check()
+    out = out.cpu()
+    assert not out.float().isnan().any()
+    at = 0
+    for i, ql in enumerate(q_lens):
+        if ql:
+            expect = attention.self_attention(qs[i], ks[i], vs[i], 128 ** -0.5)
+            assert helpers.max_abs(out[at:at + ql], expect) <= helpers.MAX_ABS[dname], (i, ql, kv_lens[i])
+            f64 = attention.self_attention_f64(qs[i], ks[i], vs[i], 128 ** -0.5)
+            ulp = {"f16": 1e-3, "bf16": 8e-3}[dname]
+            assert helpers.max_abs(out[at:at + ql], f64) <= ulp * max(1.0, f64.abs().max().item()), (i, ql)
+        at += ql
+
+
+@pytest.mark.gpu
 def test_kernel_flags_bad_metadata_instead_of_faulting_nvidia(cuda_device):
     """Device-array entry points do no host validation; a position past the block table is skipped and reported
     by check(), and the cache stays usable."""
