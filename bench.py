@@ -135,6 +135,7 @@ def reference_cpu_rate(ctx: list[int], seed: int, min_seconds: float, max_seqs: 
 
     from oracle import attention, workloads
 
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
     g = torch.Generator().manual_seed(seed)
     sample = ctx[:max_seqs]
     qs = [workloads.randn((1, NH, D), torch.bfloat16, g) for _ in sample]
@@ -168,6 +169,8 @@ def run_reference_arm(args) -> None:
 
     from oracle import attention, workloads
 
+    # launchers such as torch.distributed.run export OMP_NUM_THREADS=1; the CPU arm is meant to use the whole host
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
     g = torch.Generator().manual_seed(2)
     sample = ctx[:per_step]
     qs = [workloads.randn((1, NH, D), torch.bfloat16, g) for _ in sample]
