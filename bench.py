@@ -520,6 +520,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=4, help="pools to rotate over between steps (L2 flush)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-API leg (profiling runs)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="launch kernels without programmatic stream serialisation (on by default for decode workloads)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -567,6 +569,7 @@ def main() -> None:
         at += n
         seqs.append(s)
     cache.flush()
+    cache.set_launch_overlap(not args.no_overlap)
     stream = torch.cuda.Stream()
     cg = torch.Generator(device="cuda").manual_seed(200 + rank)
     seq_ids_dev = torch.tensor(seqs, dtype=torch.int32, device="cuda")
@@ -732,7 +735,9 @@ def main() -> None:
                        "heads": "12q/2kv", "head_dim": D, "page_size": PAGE, "pool_pages": POOL_PAGES,
                        "parallelism": f"sequences sharded over {world} GPU(s), no collective",
                        "l2": f"inputs larger than L2: layer pool rotates over {layers} x "
-                             f"{cache.layer_bytes() >> 20} MiB between steps"},
+                             f"{cache.layer_bytes() >> 20} MiB between steps",
+                       "launch": "plain" if args.no_overlap else "programmatic dependent launch: a kernel's set-up and "
+                                 "first K/V copies overlap the previous kernel's tail"},
             "roofline": {"bound": "hbm", "kernel": "paged_decode_tma_kernel", "achieved": achieved, "peak": peak,
                          "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                          "frac_of_nominal_8000": achieved / 8000.0, "traffic": NCU_TRAFFIC_BYTES[args.workload],

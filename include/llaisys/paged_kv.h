@@ -84,6 +84,17 @@ LLAISYS_API size_t llaisysPagedKVLayerBytes(llaisysPagedKV_t kv);
  * reach the device at the next data-path call, or at llaisysPagedKVFlush. */
 LLAISYS_API const int32_t *llaisysPagedKVBlockTableData(llaisysPagedKV_t kv);
 LLAISYS_API int llaisysPagedKVFlush(llaisysPagedKV_t kv);
+/* Opt-in (default off), meant for decode loops (append one row per sequence, decode, repeat): launch the append and
+ * decode kernels with programmatic stream serialisation, so that a decode kernel's set-up and its copies of OLDER
+ * pages overlap the tail of the kernels before it on the stream. A decode kernel touches q, each sequence's LAST
+ * page, scratch and outputs only after the kernel directly before it has completed, and lets its own successor start
+ * only after that; the append kernel waits for its predecessor before doing anything. Contract while overlap is on:
+ *   - the kernel directly before a decode call on the stream writes K/V only into each sequence's last page (by the
+ *     kv_lens of that decode call) -- true for a one-row-per-sequence append; after a multi-page append (a prefill
+ *     chunk) put any non-overlapping kernel, a copy or a synchronisation before the first decode call;
+ *   - index arrays and block-table rows passed to a call were written before that directly preceding kernel started
+ *     (true for host-array calls, whose staging copies break the chain, and for device arrays prepared per batch). */
+LLAISYS_API int llaisysPagedKVSetLaunchOverlap(llaisysPagedKV_t kv, int enable);
 /* Synchronises the cache's stream and reports LLAISYS_E_KERNEL if any kernel since the last
  * check met an out-of-range page or position (the kernel skips such an access). */
 LLAISYS_API int llaisysPagedKVCheck(llaisysPagedKV_t kv);

@@ -132,6 +132,10 @@ void *llaisysPagedKVPoolData(llaisysPagedKV_t kv, size_t layer) {
 }
 size_t llaisysPagedKVLayerBytes(llaisysPagedKV_t kv) { return kv ? kv->impl.layerBytes() : 0; }
 const int32_t *llaisysPagedKVBlockTableData(llaisysPagedKV_t kv) { return kv ? kv->impl.blockTableData() : nullptr; }
+int llaisysPagedKVSetLaunchOverlap(llaisysPagedKV_t kv, int enable) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.setLaunchOverlap(enable != 0); });
+}
 int llaisysPagedKVFlush(llaisysPagedKV_t kv) {
     KV_OR_FAIL(kv);
     return guarded([&] { kv->impl.flush(); });

@@ -29,6 +29,10 @@ struct KVView {
     int32_t d = 0;
     // Optional TMA view of the same memory (page pools only): a 128-byte tensor-map blob in HOST memory over the
     // whole multi-layer pool, and the index of this layer's page 0 in it (layer * num_pages).
+    // Launch append / decode with programmatic stream serialisation: the kernel's set-up and its first K/V copies may
+    // overlap the tail of the previous kernel on the stream. Contract for the caller: index arrays and block tables were
+    // written before that previous kernel started (K/V rows, q and outputs are only touched after it completed).
+    bool overlap_launch = false;
     const void *tma_desc = nullptr;      // box = K and V of a page, 64 dims (decode)
     const void *tma_tile_desc = nullptr; // box = one half-tile: 16 slots x 64 dims (prefill)
     int64_t tma_page0 = 0;

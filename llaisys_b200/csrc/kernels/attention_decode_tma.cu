@@ -180,29 +180,33 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const long long x0 = (long long)blockIdx.x * span;
     const long long x1 = min(total, x0 + span);
 
-    // -- sequences without any token: the output row is zero (partial: o = 0, m = -inf, l = 0) ----------
-    if (tid < kD) {
-        for (int pair = blockIdx.x; pair < n_pairs; pair += gridDim.x) {
-            const int s = pair / p.nkvh, kvh = pair - s * p.nkvh;
-            if (cum[s + 1] - cum[s] != 0) {
-                continue;
-            }
-            for (int h = 0; h < p.group; ++h) {
-                const long long row = (long long)s * p.nh + kvh * p.group + h;
-                if (p.part != nullptr) {
-                    p.part[row * (kD + 2) + tid] = 0.f;
-                    if (tid == 0) {
-                        p.part[row * (kD + 2) + kD] = -INFINITY;
-                        p.part[row * (kD + 2) + kD + 1] = 0.f;
+    auto write_empty_pairs = [&]() {
+        // -- sequences without any token: the output row is zero (partial: o = 0, m = -inf, l = 0) ----------
+        if (tid < kD) {
+            for (int pair = blockIdx.x; pair < n_pairs; pair += gridDim.x) {
+                const int s = pair / p.nkvh, kvh = pair - s * p.nkvh;
+                if (cum[s + 1] - cum[s] != 0) {
+                    continue;
+                }
+                for (int h = 0; h < p.group; ++h) {
+                    const long long row = (long long)s * p.nh + kvh * p.group + h;
+                    if (p.part != nullptr) {
+                        p.part[row * (kD + 2) + tid] = 0.f;
+                        if (tid == 0) {
+                            p.part[row * (kD + 2) + kD] = -INFINITY;
+                            p.part[row * (kD + 2) + kD + 1] = 0.f;
+                        }
+                    } else {
+                        store_out<kBf16>(p.out, row * kD + tid, 0.f);
                     }
-                } else {
-                    store_out<kBf16>(p.out, row * kD + tid, 0.f);
                 }
             }
         }
-    }
+    };
     if (x0 >= x1) {
-        return;
+        grid_dependency_wait(); // outputs may still be in use by the previous kernel on the stream
+        write_empty_pairs();
+        return; // exiting counts as this CTA's launch_dependents
     }
 
     // -- first page of the span ----------------------------------------------------------------------------
@@ -229,7 +233,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     // ======================================= producer warp ================================================
     if (warp == kProducerWarp) {
         int n = 0; // pages issued so far; page n uses slot n % kSlots for the (n / kSlots)-th time
-        bool dead = false;
+        bool dead = false, waited = false;
         while (cur.remaining > 0 && !dead) {
             const Segment sg = next_segment(cur, cum, p);
             if (sg.n <= 0) {
@@ -237,6 +241,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             }
             const int seq_row = p.seq_ids ? p.seq_ids[sg.s] : sg.s;
             const long long tbase = (long long)seq_row * p.table_stride + sg.j0;
+            const int pair_np = cum[sg.s + 1] - cum[sg.s];
             for (int base = 0; base < sg.n && !dead; base += kIssueLanes) {
                 // One page per lane: kIssueLanes lanes fetch their table entries in one coalesced read and each lane
                 // issues the copies of its own page, so the per-instruction latency of TMA issue is paid once
@@ -245,6 +250,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 // page order, so every wait ends. No more lanes than ring slots take part in a round: two lanes
                 // on one slot would wait for consecutive phases of the same barrier, and a parity wait cannot tell
                 // phase k + 1 from phase k - 1.
+                if (!waited && sg.j0 + min(base + kIssueLanes, sg.n) == pair_np) {
+                    grid_dependency_wait(); // this round reaches the sequence's last page: its newest rows come from the
+                    waited = true;          // previous kernel on the stream (everything before it was there long ago)
+                }
                 const bool active = lane < kIssueLanes && base + lane < sg.n;
                 int ok = 1;
                 if (active) {
@@ -291,6 +300,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     // merges all partials of the pair -- off the consumers' critical path, so the ring keeps draining meanwhile.
     const uint32_t epi_ready = bars_u32 + 2 * kSlots * 8, epi_done = bars_u32 + (2 * kSlots + 1) * 8;
     if (warp == kEpilogueWarp) {
+        grid_dependency_wait(); // counters and partials are shared with the previous launch
         int k = 0; // cut segments handled so far
         while (cur.remaining > 0) {
             const Segment sg = next_segment(cur, cum, p);
@@ -345,6 +355,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const int k_tok = lm_r + 8 * (lm_mi & 1), k_cc0 = lm_mi >> 1;
     const int v_tok = lm_r + 8 * (lm_mi >> 1), v_cc0 = lm_mi & 1;
 
+    // q, the newest K/V rows and every output belong to the stream's order: nothing of them is touched before the
+    // previous kernel has completed. (The ring is already filling: the producer copies older pages meanwhile.)
+    grid_dependency_wait();
+    // Only now may the successor on the stream be scheduled: whatever starts early behind this grid can then rely on
+    // everything BEFORE this grid's predecessor being complete (see the overlap contract in paged_kv.h).
+    grid_launch_dependents();
+    write_empty_pairs();
     float m2[2], l[2], o_acc[8][4];
     uint32_t qf[8][2];
     auto reset_state = [&]() {
@@ -586,7 +603,7 @@ size_t smem_bytes(int group, int n_seqs) {
 }
 
 template <bool kBf16>
-void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, int grid, size_t smem) {
+void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, int grid, size_t smem, bool overlap) {
     static std::once_flag once[64];
     int dev = 0;
     LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
@@ -599,7 +616,17 @@ void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, i
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 optin - int(attr.sharedSizeBytes)));
     });
-    paged_decode_tma_kernel<kBf16><<<grid, kThreads, smem, s>>>(tmap, p);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(unsigned(kThreads));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<kBf16>, tmap, p));
 }
 
 } // namespace
@@ -681,9 +708,9 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
     const size_t smem = smem_bytes(group, batch.n_seqs);
     auto s = static_cast<cudaStream_t>(stream);
     if (bf16) {
-        launch<true>(s, tmap, p, grid, smem);
+        launch<true>(s, tmap, p, grid, smem, kv.overlap_launch);
     } else {
-        launch<false>(s, tmap, p, grid, smem);
+        launch<false>(s, tmap, p, grid, smem, kv.overlap_launch);
     }
     check_launch("paged_decode_tma");
     return 0;

@@ -129,6 +129,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tensor_map
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
 }
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may start while its
+// predecessor in the stream is still running. grid_dependency_wait() returns once the predecessor grid has completed
+// and its memory is visible (immediately for an ordinary launch); grid_launch_dependents() lets the successor's CTAs
+// be scheduled as soon as every CTA of this grid has called it or exited.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
 }

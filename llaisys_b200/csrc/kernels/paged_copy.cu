@@ -44,6 +44,10 @@ __global__ void paged_append_kernel(uint4 *__restrict__ k_pool, uint4 *__restric
                                     const int32_t *__restrict__ table, const int32_t *__restrict__ seq_ids,
                                     const int32_t *__restrict__ positions, CopyGeom g, int32_t n_rows,
                                     int32_t max_blocks, int32_t *error_flag) {
+    // Under a programmatic launch this grid may start early: let the next kernel do the same, then wait for the
+    // previous one (it may still be reading the pages this grid writes).
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int32_t vecs_per_row = g.vecs_per_head_row * g.nkvh; // per K (or V) row
     const int64_t total = int64_t(n_rows) * 2 * vecs_per_row;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
@@ -124,9 +128,19 @@ void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const voi
     const CopyGeom g = make_geom(kv, elem_size);
     const int block = 256;
     const int grid = grid_for(int64_t(n_rows) * 2 * g.vecs_per_head_row * g.nkvh, block);
-    paged_append_kernel<<<grid, block, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<uint4 *>(kv.k_base), static_cast<uint4 *>(kv.v_base), static_cast<const uint4 *>(k_rows),
-        static_cast<const uint4 *>(v_rows), kv.block_table, seq_ids, positions, g, n_rows, max_blocks, error_flag);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(unsigned(block));
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = kv.overlap_launch ? 1 : 0;
+    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_append_kernel, static_cast<uint4 *>(kv.k_base),
+                                          static_cast<uint4 *>(kv.v_base), static_cast<const uint4 *>(k_rows),
+                                          static_cast<const uint4 *>(v_rows), kv.block_table, seq_ids, positions, g, n_rows,
+                                          max_blocks, error_flag));
     check_launch("paged_append");
 }
 

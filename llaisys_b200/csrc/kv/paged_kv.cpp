@@ -245,6 +245,7 @@ kernels::KVView PagedKV::view(size_t layer) const {
     v.num_pages = int32_t(_cfg.num_pages);
     v.nkvh = int32_t(_cfg.nkvh);
     v.d = int32_t(_cfg.head_dim);
+    v.overlap_launch = _overlap;
     if (_has_tma_tile) {
         v.tma_tile_desc = _tma_tile_desc;
         v.tma_page0 = int64_t(layer) * int64_t(_cfg.num_pages);

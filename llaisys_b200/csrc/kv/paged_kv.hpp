@@ -52,6 +52,7 @@ public:
     std::byte *poolData(size_t layer) const;
     size_t layerBytes() const { return _layer_bytes; }
     const int32_t *blockTableData() const { return reinterpret_cast<const int32_t *>(_table_dev->memory()); }
+    void setLaunchOverlap(bool enable) { _overlap = enable; }
     void flush(); // queue uploads of the table rows that changed since the last flush
     void check(); // synchronise, throw LLAISYS_E_KERNEL if a kernel flagged bad metadata
 
@@ -113,6 +114,7 @@ private:
     alignas(64) unsigned char _tma_desc[128] = {};      // decode: box = K and V of a page
     alignas(64) unsigned char _tma_tile_desc[128] = {}; // prefill: box = one half-tile
     bool _has_tma = false, _has_tma_tile = false;
+    bool _overlap = false; // launch append / decode with programmatic stream serialisation
 };
 
 // Picks the kernel for a batch on an NVIDIA device and queues it: split-KV decode or tensor-core prefill where

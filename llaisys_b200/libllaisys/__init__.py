@@ -141,6 +141,7 @@ PROTOTYPES: dict[str, tuple] = {
     "llaisysPagedKVLayerBytes": (c_size_t, [_KV]),
     "llaisysPagedKVBlockTableData": (c_void_p, [_KV]),
     "llaisysPagedKVFlush": (c_int, [_KV]),
+    "llaisysPagedKVSetLaunchOverlap": (c_int, [_KV, c_int]),
     "llaisysPagedKVCheck": (c_int, [_KV]),
     "llaisysPagedKVAppend": (c_int, [_KV, c_size_t, c_void_p, c_void_p, _I32P, _I32P, c_size_t]),
     "llaisysPagedKVGather": (c_int, [_KV, c_size_t, c_int32, c_size_t, c_void_p, c_void_p]),

@@ -107,6 +107,10 @@ class PagedKVCache:
     def block_table_ptr(self) -> int:
         return LIB_LLAISYS.llaisysPagedKVBlockTableData(self._kv)
 
+    def set_launch_overlap(self, enable: bool) -> None:
+        """Opt in to programmatic dependent launch of append / decode (see llaisysPagedKVSetLaunchOverlap)."""
+        _check(LIB_LLAISYS.llaisysPagedKVSetLaunchOverlap(self._kv, 1 if enable else 0))
+
     def flush(self) -> None:
         _check(LIB_LLAISYS.llaisysPagedKVFlush(self._kv))
 

@@ -290,6 +290,42 @@ def test_prefill_ragged_chunks_and_block_boundaries_nvidia(cuda_device, dname):
 
 
 @pytest.mark.gpu
+def test_back_to_back_steps_with_launch_overlap_nvidia(cuda_device):
+    """Sixteen decode steps queued without any host synchronisation, with programmatic dependent launch enabled: each
+    step appends one new row per sequence and attends over the grown context. Every step's output must match the
+    oracle -- the kernels may only overlap in the parts that do not depend on their predecessor."""
+    steps, nseq = 16, 5
+    batch = workloads.decode_batch(nseq, 40, 900, seed=61, pool_pages=512)
+    cache, seqs = helpers.build_cache(NVIDIA, "bf16", [p for p in batch.pages], num_pages=512, nkvh=2, d=128)
+    cache.set_launch_overlap(True)
+    start = [c - steps for c in batch.ctx]  # context before the first step
+    helpers.append_all(cache, 0, seqs, batch.k, batch.v, NVIDIA, hi=start)
+    cache.flush()
+    stream = llaisys.context_stream()
+    ids = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    g = torch.Generator().manual_seed(62)
+    qs = [workloads.randn((nseq, 12, 128), torch.bfloat16, g) for _ in range(steps)]
+    # everything the kernels index with is prepared before the first launch
+    pos_dev = [torch.tensor([st + t for st in start], dtype=torch.int32, device="cuda") for t in range(steps)]
+    len_dev = [torch.tensor([st + t + 1 for st in start], dtype=torch.int32, device="cuda") for t in range(steps)]
+    k_new = [torch.stack([batch.k[i][start[i] + t] for i in range(nseq)]).cuda() for t in range(steps)]
+    v_new = [torch.stack([batch.v[i][start[i] + t] for i in range(nseq)]).cuda() for t in range(steps)]
+    q_dev = [q.cuda() for q in qs]
+    outs = [torch.full((nseq, 12, 128), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(steps)]
+    torch.cuda.synchronize()
+    for t in range(steps):
+        cache.append_dev(0, k_new[t], v_new[t], ids, pos_dev[t], nseq, stream)
+        cache.decode_dev(0, outs[t], q_dev[t], ids, len_dev[t], nseq, max(batch.ctx), 12, batch.scale, stream)
+    cache.check()
+    for t in range(steps):
+        got = outs[t].cpu()
+        for i in range(nseq):
+            n = start[i] + t + 1
+            expect = attention.self_attention(qs[t][i:i + 1], batch.k[i][:n], batch.v[i][:n], batch.scale)
+            assert helpers.max_abs(got[i:i + 1], expect) <= helpers.MAX_ABS["bf16"], (t, i)
+
+
+@pytest.mark.gpu
 def test_kernel_flags_bad_metadata_instead_of_faulting_nvidia(cuda_device):
     """Device-array entry points do no host validation; a position past the block table is skipped and reported
     by check(), and the cache stays usable."""
