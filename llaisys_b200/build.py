@@ -92,9 +92,9 @@ def build(force: bool = False, verbose: bool = False, with_cuda: bool = True, pt
             # nvcc links the static CUDA runtime, so the library needs only the driver at run time and loads
             # (reporting zero devices) on a machine without one.
             cmd = [nvcc, *GENCODE, "-shared", "-o", str(OUT), *map(str, objs), "-Xcompiler", "-fopenmp",
-                   "-Xlinker", "--no-undefined"]
+                   "-Xlinker", "--no-undefined", "-ldl"]
         else:
-            cmd = ["g++", "-shared", "-fopenmp", "-o", str(OUT), *map(str, objs), "-Wl,--no-undefined"]
+            cmd = ["g++", "-shared", "-fopenmp", "-o", str(OUT), *map(str, objs), "-Wl,--no-undefined", "-ldl"]
         if verbose:
             print(" ".join(cmd), flush=True)
         res = subprocess.run(cmd, capture_output=True, text=True)

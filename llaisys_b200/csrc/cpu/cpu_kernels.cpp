@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstring>
 #include <limits>
+#include <type_traits>
 #include <vector>
 
 namespace llaisys::cpu {
@@ -286,6 +287,179 @@ void lse_merge(llaisysDataType_t dtype, void *out, const float *parts, int32_t n
     default:
         EXCEPTION_UNSUPPORTED_DATATYPE(dtype);
     }
+}
+
+
+// ---- the remaining operators -----------------------------------------------------------------------------------
+
+namespace {
+
+template <typename T>
+void argmax_typed(int64_t *idx_out, T *val_out, const T *vals, size_t rows, size_t n) {
+#pragma omp parallel for if (rows > 1)
+    for (int64_t r = 0; r < int64_t(rows); ++r) {
+        const T *row = vals + size_t(r) * n;
+        size_t best = 0;
+        float best_v = load_f32(row);
+        for (size_t i = 1; i < n; ++i) {
+            const float v = load_f32(row + i);
+            if (v > best_v) { // strict: the first of equal maxima wins
+                best_v = v;
+                best = i;
+            }
+        }
+        idx_out[r] = int64_t(best);
+        if (val_out != nullptr) {
+            val_out[r] = row[best];
+        }
+    }
+}
+
+template <typename T>
+void linear_typed(T *out, const T *in, const T *w, const T *bias, size_t m, size_t n, size_t k) {
+    // Convert once to f32 rows (bf16/f16 conversions are the expensive part on the host), then blocked dot products
+    // with a double accumulator so that the reference's f32 tolerance (1e-5 relative at K = 4096) holds.
+    std::vector<float> in_f(m * k), w_f;
+    for (size_t i = 0; i < m * k; ++i) {
+        in_f[i] = load_f32(in + i);
+    }
+    const bool convert_w = !std::is_same_v<T, float>;
+    if (convert_w) {
+        w_f.resize(n * k);
+#pragma omp parallel for
+        for (int64_t i = 0; i < int64_t(n * k); ++i) {
+            w_f[size_t(i)] = load_f32(w + i);
+        }
+    }
+    const float *wp = convert_w ? w_f.data() : reinterpret_cast<const float *>(w);
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int64_t i = 0; i < int64_t(m); ++i) {
+        for (int64_t j = 0; j < int64_t(n); ++j) {
+            const float *a = in_f.data() + size_t(i) * k;
+            const float *b = wp + size_t(j) * k;
+            double acc = 0.0;
+            size_t x = 0;
+            for (; x + 8 <= k; x += 8) {
+                float part = 0.f;
+                for (size_t u = 0; u < 8; ++u) {
+                    part += a[x + u] * b[x + u];
+                }
+                acc += part;
+            }
+            for (; x < k; ++x) {
+                acc += double(a[x]) * b[x];
+            }
+            if (bias != nullptr) {
+                acc += load_f32(bias + j);
+            }
+            out[size_t(i) * n + size_t(j)] = utils::cast<T>(float(acc));
+        }
+    }
+}
+
+template <typename T>
+void rms_norm_typed(T *out, const T *in, const T *w, float eps, size_t rows, size_t d) {
+#pragma omp parallel for if (rows > 8)
+    for (int64_t r = 0; r < int64_t(rows); ++r) {
+        const T *x = in + size_t(r) * d;
+        double ss = 0.0;
+        for (size_t i = 0; i < d; ++i) {
+            const float v = load_f32(x + i);
+            ss += double(v) * v;
+        }
+        const float inv = 1.f / std::sqrt(float(ss / double(d)) + eps);
+        for (size_t i = 0; i < d; ++i) {
+            out[size_t(r) * d + i] = utils::cast<T>(load_f32(w + i) * load_f32(x + i) * inv);
+        }
+    }
+}
+
+template <typename T>
+void rope_typed(T *out, const T *in, const int64_t *pos, float theta, size_t seq, size_t heads, size_t d) {
+    const size_t half = d / 2;
+    std::vector<float> divisor(half);
+    for (size_t j = 0; j < half; ++j) {
+        divisor[j] = std::pow(theta, 2.f * float(j) / float(d)); // the divisor theta^(2j/d), in f32 like the oracle
+    }
+#pragma omp parallel for if (seq * heads > 64)
+    for (int64_t s = 0; s < int64_t(seq); ++s) {
+        const float p = float(pos[s]);
+        for (size_t h = 0; h < heads; ++h) {
+            const T *x = in + (size_t(s) * heads + h) * d;
+            T *y = out + (size_t(s) * heads + h) * d;
+            for (size_t j = 0; j < half; ++j) {
+                const float ang = p / divisor[j];
+                const float sn = std::sin(ang), cs = std::cos(ang);
+                const float a = load_f32(x + j), b = load_f32(x + j + half);
+                y[j] = utils::cast<T>(a * cs - b * sn);
+                y[j + half] = utils::cast<T>(b * cs + a * sn);
+            }
+        }
+    }
+}
+
+template <typename T>
+void swiglu_typed(T *out, const T *gate, const T *up, size_t n) {
+#pragma omp parallel for if (n > 65536)
+    for (int64_t i = 0; i < int64_t(n); ++i) {
+        const float g = load_f32(gate + i);
+        out[i] = utils::cast<T>(load_f32(up + i) * (g / (1.f + std::exp(-g))));
+    }
+}
+
+} // namespace
+
+#define LLAISYS_DISPATCH_FLOAT(dtype, CALL)            \
+    switch (dtype) {                                   \
+    case LLAISYS_DTYPE_F32: {                          \
+        using T = float;                               \
+        CALL;                                          \
+        return;                                        \
+    }                                                  \
+    case LLAISYS_DTYPE_F16: {                          \
+        using T = fp16_t;                              \
+        CALL;                                          \
+        return;                                        \
+    }                                                  \
+    case LLAISYS_DTYPE_BF16: {                         \
+        using T = bf16_t;                              \
+        CALL;                                          \
+        return;                                        \
+    }                                                  \
+    default:                                           \
+        EXCEPTION_UNSUPPORTED_DATATYPE(dtype);         \
+    }
+
+void argmax_rows(llaisysDataType_t dtype, int64_t *idx_out, void *val_out, const void *vals, size_t rows, size_t n) {
+    LLAISYS_DISPATCH_FLOAT(dtype, argmax_typed(idx_out, static_cast<T *>(val_out), static_cast<const T *>(vals), rows, n));
+}
+
+void embedding(size_t elem_size, void *out, const int64_t *index, const void *weight, size_t n, size_t d, size_t vocab) {
+    const size_t row = d * elem_size;
+    for (size_t i = 0; i < n; ++i) {
+        CHECK_ARGUMENT(index[i] >= 0 && size_t(index[i]) < vocab, "embedding: index out of range");
+        std::memcpy(static_cast<std::byte *>(out) + i * row, static_cast<const std::byte *>(weight) + size_t(index[i]) * row, row);
+    }
+}
+
+void linear(llaisysDataType_t dtype, void *out, const void *in, const void *weight, const void *bias, size_t m, size_t n,
+            size_t k) {
+    LLAISYS_DISPATCH_FLOAT(dtype, linear_typed(static_cast<T *>(out), static_cast<const T *>(in), static_cast<const T *>(weight),
+                                               static_cast<const T *>(bias), m, n, k));
+}
+
+void rms_norm(llaisysDataType_t dtype, void *out, const void *in, const void *weight, float eps, size_t rows, size_t d) {
+    LLAISYS_DISPATCH_FLOAT(dtype, rms_norm_typed(static_cast<T *>(out), static_cast<const T *>(in),
+                                                 static_cast<const T *>(weight), eps, rows, d));
+}
+
+void rope(llaisysDataType_t dtype, void *out, const void *in, const int64_t *pos, float theta, size_t seq, size_t heads,
+          size_t d) {
+    LLAISYS_DISPATCH_FLOAT(dtype, rope_typed(static_cast<T *>(out), static_cast<const T *>(in), pos, theta, seq, heads, d));
+}
+
+void swiglu(llaisysDataType_t dtype, void *out, const void *gate, const void *up, size_t n) {
+    LLAISYS_DISPATCH_FLOAT(dtype, swiglu_typed(static_cast<T *>(out), static_cast<const T *>(gate), static_cast<const T *>(up), n));
 }
 
 } // namespace llaisys::cpu

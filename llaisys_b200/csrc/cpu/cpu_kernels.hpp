@@ -26,4 +26,23 @@ int attention(llaisysDataType_t dtype, const kernels::KVView &kv, const kernels:
 
 void lse_merge(llaisysDataType_t dtype, void *out, const float *parts, int32_t n_parts, int32_t n_rows, int32_t d);
 
+// ---- the remaining operators of the ABI (specs: reference README.md:157-302; oracles: reference test/ops/*.py).
+// All arithmetic in f32 (f64 accumulation for the long dot products of linear), one rounding to the tensor dtype.
+
+// Row-wise maximum: idx_out[r] (int64) = first index of the largest element of vals[r, :], val_out[r] = that element
+// (val_out may be null).
+void argmax_rows(llaisysDataType_t dtype, int64_t *idx_out, void *val_out, const void *vals, size_t rows, size_t n);
+// out[i, :] = weight[index[i], :]
+void embedding(size_t elem_size, void *out, const int64_t *index, const void *weight, size_t n, size_t d, size_t vocab);
+// out[M, N] = in[M, K] . weight[N, K]^T (+ bias[N])
+void linear(llaisysDataType_t dtype, void *out, const void *in, const void *weight, const void *bias, size_t m, size_t n,
+            size_t k);
+// out[r, :] = weight * in[r, :] / sqrt(mean(in[r, :]^2) + eps)
+void rms_norm(llaisysDataType_t dtype, void *out, const void *in, const void *weight, float eps, size_t rows, size_t d);
+// Rotary embedding with the half-split pairing (x[j], x[j + d/2]); angle = pos / theta^(2j/d) in f32.
+void rope(llaisysDataType_t dtype, void *out, const void *in, const int64_t *pos, float theta, size_t seq, size_t heads,
+          size_t d);
+// out = up * gate / (1 + exp(-gate))
+void swiglu(llaisysDataType_t dtype, void *out, const void *gate, const void *up, size_t n);
+
 } // namespace llaisys::cpu

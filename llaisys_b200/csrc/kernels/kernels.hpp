@@ -18,6 +18,21 @@ void add(stream_t stream, llaisysDataType_t dtype, void *c, const void *a, const
 void rearrange(stream_t stream, size_t elem_size, size_t ndim, const size_t *shape, const ptrdiff_t *dst_strides,
                const ptrdiff_t *src_strides, void *dst, const void *src);
 
+// The operators around the attention path (specs: reference README.md:157-302). HBM-bound single-pass kernels; linear is
+// a cuBLAS GEMM (f32 accumulation) followed by the bias add.
+void argmax_rows(stream_t stream, llaisysDataType_t dtype, int64_t *idx_out, void *val_out, const void *vals, size_t rows,
+                 size_t n);
+void embedding(stream_t stream, size_t elem_size, void *out, const int64_t *index, const void *weight, size_t n, size_t d,
+               size_t vocab);
+void linear(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, const void *bias,
+            size_t m, size_t n, size_t k);
+void bias_add(stream_t stream, llaisysDataType_t dtype, void *out, const void *bias, size_t rows, size_t n);
+void rms_norm(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, float eps, size_t rows,
+              size_t d);
+void rope(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const int64_t *pos, float theta, size_t seq,
+          size_t heads, size_t d);
+void swiglu(stream_t stream, llaisysDataType_t dtype, void *out, const void *gate, const void *up, size_t n);
+
 // K1: row i of k_rows / v_rows [n_rows, nkvh, d] -> token positions[i] of the sequence in table row seq_ids[i].
 // 16-byte vector copies; a row whose block or page is out of range is skipped and flagged.
 void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const void *k_rows, const void *v_rows,

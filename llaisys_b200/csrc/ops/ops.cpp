@@ -166,13 +166,120 @@ void self_attention(tensor_t attn_val, tensor_t q, tensor_t k, tensor_t v, float
     }
 }
 
-// The remaining operators of the ABI are declared by the reference and left unimplemented there
-// (src/ops/{argmax,embedding,linear,rms_norm,rope,swiglu}/op.cpp:4-6); they are outside the attention path.
-void argmax(tensor_t, tensor_t, tensor_t) { TO_BE_IMPLEMENTED(); }
-void embedding(tensor_t, tensor_t, tensor_t) { TO_BE_IMPLEMENTED(); }
-void linear(tensor_t, tensor_t, tensor_t, tensor_t) { TO_BE_IMPLEMENTED(); }
-void rms_norm(tensor_t, tensor_t, tensor_t, float) { TO_BE_IMPLEMENTED(); }
-void rope(tensor_t, tensor_t, tensor_t, float) { TO_BE_IMPLEMENTED(); }
-void swiglu(tensor_t, tensor_t, tensor_t) { TO_BE_IMPLEMENTED(); }
+// ---- the remaining operators of the ABI (stubs in the reference: src/ops/*/op.cpp:4-6; specs README.md:157-302) ----
+
+#ifdef ENABLE_NVIDIA_API
+#define LLAISYS_ON_DEVICE(TENSOR, CPU_CALL, CUDA_CALL)             \
+    switch ((TENSOR)->deviceType()) {                              \
+    case LLAISYS_DEVICE_CPU:                                       \
+        CPU_CALL;                                                  \
+        return;                                                    \
+    case LLAISYS_DEVICE_NVIDIA: {                                  \
+        llaisysStream_t stream = enter_device(*(TENSOR));          \
+        CUDA_CALL;                                                 \
+        return;                                                    \
+    }                                                              \
+    default:                                                       \
+        EXCEPTION_UNSUPPORTED_DEVICE;                              \
+    }
+#else
+#define LLAISYS_ON_DEVICE(TENSOR, CPU_CALL, CUDA_CALL) \
+    switch ((TENSOR)->deviceType()) {                  \
+    case LLAISYS_DEVICE_CPU:                           \
+        CPU_CALL;                                      \
+        return;                                        \
+    default:                                           \
+        EXCEPTION_UNSUPPORTED_DEVICE;                  \
+    }
+#endif
+
+// vals 1-D [n] -> max_idx [1] int64, max_val [1] of the dtype of vals (reference: README.md:157-167)
+void argmax(tensor_t max_idx, tensor_t max_val, tensor_t vals) {
+    CHECK_SAME_DEVICE(max_idx, max_val, vals);
+    CHECK_ARGUMENT(max_idx->dtype() == LLAISYS_DTYPE_I64, "Argmax: max_idx must be int64");
+    CHECK_SAME_DTYPE(max_val->dtype(), vals->dtype());
+    CHECK_ARGUMENT(max_idx->numel() == 1 && max_val->numel() == 1 && vals->numel() >= 1, "Argmax: shapes");
+    ASSERT(vals->isContiguous(), "Argmax: vals must be contiguous.");
+    LLAISYS_ON_DEVICE(vals,
+                      cpu::argmax_rows(vals->dtype(), reinterpret_cast<int64_t *>(max_idx->data()), max_val->data(),
+                                       vals->data(), 1, vals->numel()),
+                      kernels::argmax_rows(stream, vals->dtype(), reinterpret_cast<int64_t *>(max_idx->data()),
+                                           max_val->data(), vals->data(), 1, vals->numel()));
+}
+
+// out [n, d] = weight[index[n], :] (reference: README.md:169-177)
+void embedding(tensor_t out, tensor_t index, tensor_t weight) {
+    CHECK_SAME_DEVICE(out, index, weight);
+    CHECK_ARGUMENT(index->dtype() == LLAISYS_DTYPE_I64, "Embedding: index must be int64");
+    CHECK_SAME_DTYPE(out->dtype(), weight->dtype());
+    CHECK_ARGUMENT(index->ndim() == 1 && out->ndim() == 2 && weight->ndim() == 2, "Embedding: index 1-D, out and weight 2-D");
+    CHECK_ARGUMENT(out->shape()[0] == index->shape()[0] && out->shape()[1] == weight->shape()[1], "Embedding: shapes");
+    ASSERT(out->isContiguous() && index->isContiguous() && weight->isContiguous(), "Embedding: tensors must be contiguous.");
+    const size_t n = index->shape()[0], d = weight->shape()[1], vocab = weight->shape()[0];
+    LLAISYS_ON_DEVICE(out,
+                      cpu::embedding(out->elementSize(), out->data(), reinterpret_cast<const int64_t *>(index->data()),
+                                     weight->data(), n, d, vocab),
+                      kernels::embedding(stream, out->elementSize(), out->data(),
+                                         reinterpret_cast<const int64_t *>(index->data()), weight->data(), n, d, vocab));
+}
+
+// out [M, N] = in [M, K] . weight [N, K]^T + bias [N]; bias may be null (reference: README.md:179-196)
+void linear(tensor_t out, tensor_t in, tensor_t weight, tensor_t bias) {
+    CHECK_SAME_DEVICE(out, in, weight);
+    CHECK_SAME_DTYPE(out->dtype(), in->dtype(), weight->dtype());
+    CHECK_ARGUMENT(out->ndim() == 2 && in->ndim() == 2 && weight->ndim() == 2, "Linear: tensors must be 2-D");
+    const size_t m = in->shape()[0], k = in->shape()[1], n = weight->shape()[0];
+    CHECK_ARGUMENT(weight->shape()[1] == k && out->shape()[0] == m && out->shape()[1] == n, "Linear: shapes");
+    ASSERT(out->isContiguous() && in->isContiguous() && weight->isContiguous(), "Linear: tensors must be contiguous.");
+    const std::byte *bias_ptr = nullptr;
+    if (bias) {
+        CHECK_SAME_DEVICE(out, bias);
+        CHECK_SAME_DTYPE(out->dtype(), bias->dtype());
+        CHECK_ARGUMENT(bias->numel() == n, "Linear: bias must have one element per output column");
+        ASSERT(bias->isContiguous(), "Linear: bias must be contiguous.");
+        bias_ptr = bias->data();
+    }
+    LLAISYS_ON_DEVICE(out, cpu::linear(out->dtype(), out->data(), in->data(), weight->data(), bias_ptr, m, n, k),
+                      kernels::linear(stream, out->dtype(), out->data(), in->data(), weight->data(), bias_ptr, m, n, k));
+}
+
+// per row: out = weight * in / sqrt(mean(in^2) + eps) (reference: README.md:198-213)
+void rms_norm(tensor_t out, tensor_t in, tensor_t weight, float eps) {
+    CHECK_SAME_DEVICE(out, in, weight);
+    CHECK_SAME_DTYPE(out->dtype(), in->dtype(), weight->dtype());
+    CHECK_SAME_SHAPE(out->shape(), in->shape());
+    CHECK_ARGUMENT(in->ndim() == 2 && weight->ndim() == 1 && weight->shape()[0] == in->shape()[1], "RmsNorm: shapes");
+    ASSERT(out->isContiguous() && in->isContiguous() && weight->isContiguous(), "RmsNorm: tensors must be contiguous.");
+    const size_t rows = in->shape()[0], d = in->shape()[1];
+    LLAISYS_ON_DEVICE(out, cpu::rms_norm(out->dtype(), out->data(), in->data(), weight->data(), eps, rows, d),
+                      kernels::rms_norm(stream, out->dtype(), out->data(), in->data(), weight->data(), eps, rows, d));
+}
+
+// out, in [seq, heads, d]; pos_ids [seq] int64 (reference: README.md:215-242)
+void rope(tensor_t out, tensor_t in, tensor_t pos_ids, float theta) {
+    CHECK_SAME_DEVICE(out, in, pos_ids);
+    CHECK_SAME_DTYPE(out->dtype(), in->dtype());
+    CHECK_SAME_SHAPE(out->shape(), in->shape());
+    CHECK_ARGUMENT(pos_ids->dtype() == LLAISYS_DTYPE_I64, "ROPE: pos_ids must be int64");
+    CHECK_ARGUMENT(in->ndim() == 3 && pos_ids->ndim() == 1 && pos_ids->shape()[0] == in->shape()[0], "ROPE: shapes");
+    CHECK_ARGUMENT(in->shape()[2] % 2 == 0, "ROPE: head dimension must be even");
+    ASSERT(out->isContiguous() && in->isContiguous() && pos_ids->isContiguous(), "ROPE: tensors must be contiguous.");
+    const size_t seq = in->shape()[0], heads = in->shape()[1], d = in->shape()[2];
+    LLAISYS_ON_DEVICE(out,
+                      cpu::rope(out->dtype(), out->data(), in->data(), reinterpret_cast<const int64_t *>(pos_ids->data()),
+                                theta, seq, heads, d),
+                      kernels::rope(stream, out->dtype(), out->data(), in->data(),
+                                    reinterpret_cast<const int64_t *>(pos_ids->data()), theta, seq, heads, d));
+}
+
+// out = up * gate / (1 + exp(-gate)) (reference: README.md:268-280)
+void swiglu(tensor_t out, tensor_t gate, tensor_t up) {
+    CHECK_SAME_DEVICE(out, gate, up);
+    CHECK_SAME_DTYPE(out->dtype(), gate->dtype(), up->dtype());
+    CHECK_SAME_SHAPE(out->shape(), gate->shape(), up->shape());
+    ASSERT(out->isContiguous() && gate->isContiguous() && up->isContiguous(), "SwiGLU: tensors must be contiguous.");
+    LLAISYS_ON_DEVICE(out, cpu::swiglu(out->dtype(), out->data(), gate->data(), up->data(), out->numel()),
+                      kernels::swiglu(stream, out->dtype(), out->data(), gate->data(), up->data(), out->numel()));
+}
 
 } // namespace llaisys::ops

@@ -16,7 +16,9 @@ ROOT = Path(__file__).resolve().parents[1]
 SHIM = "import sys, llaisys_b200; sys.modules['llaisys'] = llaisys_b200; import runpy; " \
        "sys.argv = sys.argv[1:]; runpy.run_path(sys.argv[0], run_name='__main__')"
 
-SCRIPTS = ["test/test_runtime.py", "test/test_tensor.py", "test/ops/add.py", "test/ops/self_attention.py"]
+SCRIPTS = ["test/test_runtime.py", "test/test_tensor.py", "test/ops/add.py", "test/ops/self_attention.py",
+           "test/ops/argmax.py", "test/ops/embedding.py", "test/ops/linear.py", "test/ops/rms_norm.py", "test/ops/rope.py",
+           "test/ops/swiglu.py"]
 
 
 def run_script(script: str, device: str):
