@@ -161,6 +161,22 @@ def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if args.workload == "config4":
+        rate, threads, sample = model_cpu_rate(QWEN2_1P5B, 20.0)
+        print(json.dumps({
+            "impl": "reference", "metric": "decode tokens/s (Qwen2-1.5B architecture, greedy, paged KV cache)",
+            "value": rate, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1e3 / rate, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": {"workload": "config4", "batch": 64},
+            "cpu_baseline": {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}), flush=True)
+        return
+    if args.workload not in ("north_star", "config2"):
+        print(json.dumps({"impl": "reference", "unavailable":
+                          f"the CPU arm covers north_star, config2 and config4; {args.workload} has no bounded CPU sample"}),
+              flush=True)
+        return
     ctx = workload_lengths(args.workload, seed=2)
     per_step = max(1, min(4, len(ctx)))
     args.steps = min(args.steps, 200)  # bounded: the CPU arm needs seconds per step, not microseconds
@@ -387,6 +403,163 @@ def run_prefill_workload(args) -> None:
         dist.destroy_process_group()
 
 
+QWEN2_1P5B = dict(hidden_size=1536, num_hidden_layers=28, num_attention_heads=12, num_key_value_heads=2, head_dim=128,
+                  intermediate_size=8960, vocab_size=151936, max_position_embeddings=4096, rms_norm_eps=1e-6,
+                  rope_theta=10000.0, eos_token_id=-1, tie_word_embeddings=False)
+
+
+def qwen2_random_weights(cfg: dict, seed: int, device: str, std: float = 0.02):
+    """Yields (Hugging Face parameter name, tensor) of a random-init model: matrices, embeddings and biases N(0, std),
+    norm weights 1 (what a freshly initialised checkpoint holds)."""
+    import torch
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    hs, qd = cfg["hidden_size"], cfg["num_attention_heads"] * cfg["head_dim"]
+    kd, di, voc = cfg["num_key_value_heads"] * cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"]
+
+    def normal(*shape):
+        return torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * std
+
+    yield "model.embed_tokens.weight", normal(voc, hs)
+    yield "lm_head.weight", normal(voc, hs)
+    yield "model.norm.weight", torch.ones(hs, device=device)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        yield p + "input_layernorm.weight", torch.ones(hs, device=device)
+        yield p + "post_attention_layernorm.weight", torch.ones(hs, device=device)
+        for name, rows in (("q", qd), ("k", kd), ("v", kd)):
+            yield p + f"self_attn.{name}_proj.weight", normal(rows, hs)
+            yield p + f"self_attn.{name}_proj.bias", normal(rows)
+        yield p + "self_attn.o_proj.weight", normal(hs, qd)
+        yield p + "mlp.gate_proj.weight", normal(di, hs)
+        yield p + "mlp.up_proj.weight", normal(di, hs)
+        yield p + "mlp.down_proj.weight", normal(hs, di)
+
+
+def model_cpu_rate(cfg: dict, min_seconds: float):
+    """The oracle model (reference operator definitions composed in torch) on the host cores, bf16: one sequence with a
+    short prompt, then greedy decode steps until min_seconds have passed. -> decode tokens/s, threads, description"""
+    import torch
+
+    from oracle.qwen2 import Qwen2Oracle
+
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
+    state = {k: v for k, v in qwen2_random_weights(cfg, 4, "cpu")}
+    oracle = Qwen2Oracle(cfg, state, torch.bfloat16)
+    del state
+    g = torch.Generator().manual_seed(4)
+    prompt = torch.randint(0, cfg["vocab_size"], (64,), generator=g).tolist()
+    token = int(oracle.forward(prompt).argmax())
+    n, t0 = 0, time.perf_counter()
+    while n < 3 or time.perf_counter() - t0 < min_seconds:
+        token = int(oracle.forward([token]).argmax())
+        n += 1
+    rate = n / (time.perf_counter() - t0)
+    return rate, torch.get_num_threads(), f"1 of the 64 sequences, 64-token prompt (not 2048), {n} greedy decode steps, bf16"
+
+
+def run_model_workload(args) -> None:
+    """--workload config4: greedy decode of a random-init Qwen2-1.5B-architecture model, bf16. 64 sequences (sharded
+    over the N GPUs: strong scaling), 2048-token random prompts, then decode steps on the paged cache. One bench step =
+    one decode step of the whole batch through all 28 layers (embedding -> ... -> argmax), replayed as a CUDA graph
+    with the loop state on the device; device time comes from CUDA events inside the library around the replays."""
+    torch, llaisys, rank, local_rank, world, dist = _init_device()
+    cfg = QWEN2_1P5B
+    total_seqs, prompt_len = 64, 2048
+    if total_seqs % world:
+        raise SystemExit("config4 shards 64 sequences: --gpus must divide 64")
+    B = total_seqs // world
+    steps = args.steps if args.steps != 2000 else 256  # the configuration's 256 greedy steps unless told otherwise
+    warm = max(3, min(args.warmup, 8))
+    n_e2e = 0 if args.no_e2e else 32
+    max_tokens = prompt_len + warm + steps + 1 + n_e2e + 16
+
+    model = llaisys.models.Qwen2(config=cfg, device=llaisys.DeviceType.NVIDIA, device_id=local_rank,
+                                 dtype=llaisys.DataType.BF16, max_seq_len=max_tokens)
+    weight_bytes = 0
+    for name, value in qwen2_random_weights(cfg, 4, "cuda"):  # the same weights on every rank
+        model.load_tensor(name, value)
+        if "embed_tokens" not in name:
+            weight_bytes += value.numel() * 2  # every matrix is read once per decode step; the embedding only B rows
+    model.configure_cache(B, max_tokens)
+    seqs = [model.add_seq() for _ in range(B)]
+    g = torch.Generator().manual_seed(100 + rank)
+    prompts = torch.randint(0, cfg["vocab_size"], (B, prompt_len), generator=g).tolist()
+
+    # prefill, eight sequences per call (bounds the activation workspace), timed on the host with a synchronise
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    nxt = []
+    for i in range(0, B, 8):
+        nxt += model.step(seqs[i:i + 8], prompts[i:i + 8])
+    prefill_s = time.perf_counter() - t0
+
+    nxt = model.decode_loop(seqs, nxt, warm)[-1].tolist()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    with ClockSampler(local_rank) as clocks:
+        log = model.decode_loop(seqs, nxt, steps + 1)  # first step eager and untimed, `steps` timed graph replays
+    step_ms = model.last_loop_ms
+    nxt = log[-1].tolist()
+    assert log.shape == (steps + 1, B) and 0 <= int(log.min()) and int(log.max()) < cfg["vocab_size"]
+    ctx_mid = prompt_len + warm + 1 + steps // 2
+
+    e2e = None
+    if n_e2e:
+        # the public per-step call: host token lists in, host tokens out, index arrays uploaded every step
+        cur = model.step(seqs, [[t] for t in nxt])
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n_e2e - 1):
+            cur = model.step(seqs, [[t] for t in cur])
+        e2e_s = time.perf_counter() - t0
+        e2e = {"value": total_seqs * (n_e2e - 1) / e2e_s, "unit": "tokens/s", "steps": n_e2e - 1,
+               "h2d_bytes_per_step": B * (4 * 8 + 5 * 4) + 4, "d2h_bytes_per_step": B * 8,
+               "what": "Qwen2.step(): host tokens in, host greedy tokens out, one synchronise per step"}
+
+    stats = torch.tensor([step_ms, prefill_s], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        step_ms, prefill_s = (float(x) for x in stats)
+        if e2e is not None:
+            rate = torch.tensor([e2e["value"]], device="cuda", dtype=torch.float64)
+            dist.all_reduce(rate, op=dist.ReduceOp.MIN)
+            e2e["value"] = float(rate)
+    if rank == 0:
+        hbm_peak, _, kind = _peaks()
+        kv_bytes = cfg["num_hidden_layers"] * B * ctx_mid * (2 * NKVH * D * 2)
+        achieved = (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9
+        own = cfg["num_hidden_layers"] * 12 + 6  # per layer: 2 norms, 3 bias adds, 2 ropes, append, decode, 2 adds, swiglu
+        line = {
+            "metric": "decode tokens/s (Qwen2-1.5B architecture, greedy, paged KV cache)",
+            "value": total_seqs * 1e3 / step_ms, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (random-init weights N(0, 0.02), random-token prompts)",
+            "config": {"workload": "config4", "batch": total_seqs, "batch_per_gpu": B, "prompt": prompt_len,
+                       "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"], "heads": "12q/2kv",
+                       "head_dim": D, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                       "page_size": PAGE, "parallelism": f"sequences sharded over {world} GPU(s), no collective",
+                       "l2": "every step reads all weights and the whole KV cache (several GB): larger than L2"},
+            "roofline": {"bound": "hbm", "kernel": "whole decode step (paged decode attention + cuBLAS projections)",
+                         "achieved": achieved, "peak": hbm_peak, "peak_kind": f"copy bandwidth, of {kind}",
+                         "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None,
+                         "algorithmic_bytes_per_step": {"weights": weight_bytes, "kv_cache_mid_loop": kv_bytes}},
+            "prefill": {"tokens_per_s": total_seqs * prompt_len / prefill_s, "seconds": prefill_s,
+                        "what": "2048-token prompts, 8 sequences per call, host clock"},
+            "e2e": e2e, "gpu_launches": own * steps,
+            "library_launches": (cfg["num_hidden_layers"] * 7 + 1) * steps,
+            "timing": "CUDA events around the graph replays, max over ranks", "clocks": clocks.summary(),
+        }
+        if not args.no_cpu_baseline and world == 1:
+            rate, threads, sample = model_cpu_rate(cfg, 12.0)
+            line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_longctx_workload(args) -> None:
     """--workload config5: ONE 131072-token sequence, 28 layers, KV range split across the N GPUs (strong scaling).
 
@@ -516,7 +689,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="north_star", choices=["north_star", "config2", "config3", "config5"])
+    ap.add_argument("--workload", default="north_star", choices=["north_star", "config2", "config3", "config4", "config5"])
     ap.add_argument("--layers", type=int, default=4, help="pools to rotate over between steps (L2 flush)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-API leg (profiling runs)")
@@ -534,6 +707,9 @@ def main() -> None:
         return
     if args.workload == "config5":
         run_longctx_workload(args)
+        return
+    if args.workload == "config4":
+        run_model_workload(args)
         return
 
     import torch

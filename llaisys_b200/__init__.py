@@ -11,8 +11,9 @@ from .runtime import RuntimeAPI, context_stream, set_context_runtime
 from .tensor import Tensor
 from .ops import Ops
 from .paged_kv import LlaisysError, PagedKVCache, decode_no_alloc, lse_merge
+from . import models
 
 __all__ = [
-    "RuntimeAPI", "DeviceType", "DataType", "MemcpyKind", "Stream", "Tensor", "Ops",
+    "RuntimeAPI", "DeviceType", "DataType", "MemcpyKind", "Stream", "Tensor", "Ops", "models",
     "PagedKVCache", "lse_merge", "decode_no_alloc", "LlaisysError", "Status", "context_stream", "set_context_runtime",
 ]

@@ -6,13 +6,11 @@
 #include "llaisys/tensor.h"
 
 #include "../device/runtime_api.hpp"
+#include "handles.hpp"
 #include "../ops/ops.hpp"
 
 #include <algorithm>
 
-struct LlaisysTensor {
-    llaisys::tensor_t tensor;
-};
 
 namespace {
 llaisysTensor_t wrap(llaisys::tensor_t t) { return new LlaisysTensor{std::move(t)}; }

@@ -33,6 +33,18 @@ void rope(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, c
           size_t heads, size_t d);
 void swiglu(stream_t stream, llaisysDataType_t dtype, void *out, const void *gate, const void *up, size_t n);
 
+// Device-resident decode loop support: state hand-over between steps, CUDA graph capture / replay, event timing.
+void advance_decode_state(stream_t stream, int64_t *tokens, const int64_t *next, int64_t *pos64, int32_t *pos32,
+                          int32_t *kv_lens, int64_t *log, int32_t *step_counter, int n);
+void graph_capture_begin(stream_t stream);
+void *graph_capture_end(stream_t stream); // instantiated executable graph
+void graph_launch(void *exec, stream_t stream);
+void graph_destroy(void *exec);
+void *event_create();
+void event_record(void *event, stream_t stream);
+float event_elapsed_ms(void *start, void *stop); // synchronises on `stop`
+void event_destroy(void *event);
+
 // K1: row i of k_rows / v_rows [n_rows, nkvh, d] -> token positions[i] of the sequence in table row seq_ids[i].
 // 16-byte vector copies; a row whose block or page is out of range is skipped and flagged.
 void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const void *k_rows, const void *v_rows,

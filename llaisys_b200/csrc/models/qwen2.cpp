@@ -1,0 +1,521 @@
+#include "qwen2.hpp"
+
+#include "../common/check.hpp"
+#include "../common/dtypes.hpp"
+#include "../cpu/cpu_kernels.hpp"
+#include "llaisys/paged_kv.h"
+#ifdef ENABLE_NVIDIA_API
+#include "../kernels/kernels.hpp"
+#endif
+
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <limits>
+
+namespace llaisys::models {
+
+namespace {
+constexpr size_t kPageSize = 16;
+constexpr size_t kNotLive = std::numeric_limits<size_t>::max();
+
+[[noreturn]] void fail(int code, const std::string &msg) { throw kv::StatusError(code, msg); }
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+} // namespace
+
+// ---- construction -------------------------------------------------------------------------------------------------
+
+Qwen2::Qwen2(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int device_id)
+    : _meta(meta), _device(device), _device_id(device_id) {
+    if (meta.dtype != LLAISYS_DTYPE_F32 && meta.dtype != LLAISYS_DTYPE_F16 && meta.dtype != LLAISYS_DTYPE_BF16) {
+        fail(LLAISYS_E_INVALID, "qwen2: dtype must be F32, F16 or BF16");
+    }
+    if (meta.nlayer == 0 || meta.hs == 0 || meta.nh == 0 || meta.nkvh == 0 || meta.dh == 0 || meta.di == 0 || meta.voc == 0 ||
+        meta.nh % meta.nkvh != 0 || meta.dh % 2 != 0) {
+        fail(LLAISYS_E_INVALID, "qwen2: inconsistent model dimensions");
+    }
+    _elem = utils::dsize(meta.dtype);
+    _on_gpu = device != LLAISYS_DEVICE_CPU;
+    auto &rt = enter();
+    _stream = rt.stream();
+
+    const size_t L = meta.nlayer, hs = meta.hs, qd = meta.nh * meta.dh, kd = meta.nkvh * meta.dh, di = meta.di;
+    _weights.in_embed = makeWeight({meta.voc, hs});
+    _weights.out_embed = makeWeight({meta.voc, hs});
+    _weights.out_norm_w = makeWeight({hs});
+    const std::vector<size_t> shapes[12] = {{hs},     {qd, hs}, {qd}, {kd, hs}, {kd},     {kd, hs},
+                                            {kd},     {hs, qd}, {hs}, {di, hs}, {di, hs}, {hs, di}};
+    for (int w = 0; w < 12; ++w) {
+        _per_layer[w].resize(L);
+        for (size_t l = 0; l < L; ++l) {
+            _per_layer[w][l] = makeWeight(shapes[w]);
+        }
+    }
+    _weights.attn_norm_w = _per_layer[0].data();
+    _weights.attn_q_w = _per_layer[1].data();
+    _weights.attn_q_b = _per_layer[2].data();
+    _weights.attn_k_w = _per_layer[3].data();
+    _weights.attn_k_b = _per_layer[4].data();
+    _weights.attn_v_w = _per_layer[5].data();
+    _weights.attn_v_b = _per_layer[6].data();
+    _weights.attn_o_w = _per_layer[7].data();
+    _weights.mlp_norm_w = _per_layer[8].data();
+    _weights.mlp_gate_w = _per_layer[9].data();
+    _weights.mlp_up_w = _per_layer[10].data();
+    _weights.mlp_down_w = _per_layer[11].data();
+}
+
+Qwen2::~Qwen2() {
+    for (llaisysTensor_t h : _all_weights) {
+        delete h;
+    }
+}
+
+core::Runtime &Qwen2::enter() const {
+    auto &ctx = core::context();
+    ctx.setDevice(_device, _device_id);
+    return ctx.runtime();
+}
+
+llaisysTensor_t Qwen2::makeWeight(const std::vector<size_t> &shape) {
+    auto *h = new LlaisysTensor{Tensor::create(shape, _meta.dtype, _device, _device_id)};
+    _all_weights.push_back(h);
+    return h;
+}
+
+std::vector<Qwen2::Layer> Qwen2::layerPointers() const {
+    std::vector<Layer> layers(_meta.nlayer);
+    for (size_t l = 0; l < _meta.nlayer; ++l) {
+        auto p = [&](int w) { return static_cast<const std::byte *>(_per_layer[w][l]->tensor->data()); };
+        layers[l] = Layer{p(0), p(1), p(2), p(3), p(4), p(5), p(6), p(7), p(8), p(9), p(10), p(11)};
+    }
+    return layers;
+}
+
+// ---- cache and sequences --------------------------------------------------------------------------------------------
+
+void Qwen2::configureCache(size_t max_seqs, size_t max_tokens) {
+    if (max_seqs == 0 || max_tokens == 0) {
+        fail(LLAISYS_E_INVALID, "qwen2: cache sizes must be positive");
+    }
+    kv::PagedKVConfig cfg;
+    cfg.device_type = _device;
+    cfg.device_id = _device_id;
+    cfg.dtype = _meta.dtype;
+    cfg.nlayer = _meta.nlayer;
+    cfg.page_size = kPageSize;
+    cfg.nkvh = _meta.nkvh;
+    cfg.head_dim = _meta.dh;
+    cfg.max_seqs = max_seqs;
+    cfg.max_pages_per_seq = (max_tokens + kPageSize - 1) / kPageSize;
+    cfg.num_pages = cfg.max_seqs * cfg.max_pages_per_seq;
+    _cache = std::make_unique<kv::PagedKV>(cfg);
+    _max_tokens_per_seq = cfg.max_pages_per_seq * kPageSize;
+    _seq_len.assign(max_seqs, kNotLive);
+    _implicit_seq = -1;
+}
+
+size_t &Qwen2::seqLen(int32_t seq) {
+    if (!_cache || seq < 0 || size_t(seq) >= _seq_len.size() || _seq_len[seq] == kNotLive) {
+        fail(LLAISYS_E_NO_SEQ, "qwen2: sequence " + std::to_string(seq) + " does not exist");
+    }
+    return _seq_len[seq];
+}
+
+int32_t Qwen2::seqAdd() {
+    if (!_cache) {
+        fail(LLAISYS_E_INVALID, "qwen2: call llaisysQwen2ModelConfigureCache first");
+    }
+    const int32_t s = _cache->seqAdd();
+    _seq_len[s] = 0;
+    return s;
+}
+
+void Qwen2::seqFree(int32_t seq) {
+    seqLen(seq);
+    _cache->seqFree(seq);
+    _seq_len[seq] = kNotLive;
+    if (seq == _implicit_seq) {
+        _implicit_seq = -1;
+    }
+}
+
+void Qwen2::reset() {
+    if (_implicit_seq >= 0) {
+        seqFree(_implicit_seq);
+    }
+}
+
+int64_t Qwen2::infer(const int64_t *tokens, size_t n) {
+    if (n == 0 || tokens == nullptr) {
+        fail(LLAISYS_E_INVALID, "qwen2: infer needs at least one token");
+    }
+    if (!_cache) {
+        configureCache(1, std::max<size_t>(_meta.maxseq, n + 1));
+    }
+    if (_implicit_seq < 0) {
+        _implicit_seq = seqAdd();
+    }
+    const int32_t n32 = int32_t(n);
+    int64_t next = 0;
+    step(&_implicit_seq, &n32, 1, tokens, &next);
+    return next;
+}
+
+// ---- workspace -------------------------------------------------------------------------------------------------------
+
+void Qwen2::ensureWorkspace(size_t n_tokens, size_t n_seqs) {
+    auto &rt = enter();
+    if (n_tokens > _ws_tokens) {
+        _ws_tokens = n_tokens;
+        const size_t hs = _meta.hs, qd = _meta.nh * _meta.dh, kd = _meta.nkvh * _meta.dh;
+        _x = rt.allocateDeviceStorage(n_tokens * hs * _elem);
+        _h = rt.allocateDeviceStorage(n_tokens * hs * _elem);
+        _q = rt.allocateDeviceStorage(n_tokens * qd * _elem);
+        _k = rt.allocateDeviceStorage(n_tokens * kd * _elem);
+        _v = rt.allocateDeviceStorage(n_tokens * kd * _elem);
+        _attn = rt.allocateDeviceStorage(n_tokens * qd * _elem);
+        _gate = rt.allocateDeviceStorage(n_tokens * _meta.di * _elem);
+        _up = rt.allocateDeviceStorage(n_tokens * _meta.di * _elem);
+    }
+    if (n_seqs > _ws_seqs) {
+        _ws_seqs = n_seqs;
+        _x_last = rt.allocateDeviceStorage(n_seqs * _meta.hs * _elem);
+        _logits = rt.allocateDeviceStorage(n_seqs * _meta.voc * _elem);
+    }
+    // tokens, pos64, last_rows, next (int64) then seq32, pos32, kv_lens, q_starts, seq_list (int32), 16-byte aligned
+    const size_t need = align_up(n_tokens * 8, 16) * 2 + align_up(n_seqs * 8, 16) * 2 + align_up(n_tokens * 4, 16) * 2 +
+                        align_up(n_seqs * 4, 16) * 2 + align_up((n_seqs + 1) * 4, 16);
+    if (need > _meta_bytes) {
+        _meta_bytes = need * 2;
+        _meta_block = rt.allocateDeviceStorage(_meta_bytes);
+    }
+}
+
+Qwen2::StepArrays Qwen2::carveStepArrays(size_t n_tokens, size_t n_seqs) {
+    StepArrays a;
+    size_t at = 0;
+    auto take = [&](size_t bytes) {
+        const size_t here = at;
+        at += align_up(bytes, 16);
+        return here;
+    };
+    std::byte *base = _meta_block->memory();
+    a.tokens = reinterpret_cast<int64_t *>(base + take(n_tokens * 8));
+    a.pos64 = reinterpret_cast<int64_t *>(base + take(n_tokens * 8));
+    a.last_rows = reinterpret_cast<int64_t *>(base + take(n_seqs * 8));
+    a.next = reinterpret_cast<int64_t *>(base + take(n_seqs * 8));
+    a.seq32 = reinterpret_cast<int32_t *>(base + take(n_tokens * 4));
+    a.pos32 = reinterpret_cast<int32_t *>(base + take(n_tokens * 4));
+    a.kv_lens = reinterpret_cast<int32_t *>(base + take(n_seqs * 4));
+    a.seq_list = reinterpret_cast<int32_t *>(base + take(n_seqs * 4));
+    a.q_starts = reinterpret_cast<int32_t *>(base + take((n_seqs + 1) * 4));
+    return a;
+}
+
+void Qwen2::copyToDevice(void *dst, const void *src, size_t bytes) {
+    auto &rt = enter();
+    if (_on_gpu) {
+        rt.api()->memcpy_async(dst, src, bytes, LLAISYS_MEMCPY_H2D, _stream);
+    } else {
+        std::memcpy(dst, src, bytes);
+    }
+}
+
+void Qwen2::copyToHost(void *dst, const void *src, size_t bytes) {
+    auto &rt = enter();
+    if (_on_gpu) {
+        rt.api()->memcpy_async(dst, src, bytes, LLAISYS_MEMCPY_D2H, _stream);
+        rt.synchronize();
+    } else {
+        std::memcpy(dst, src, bytes);
+    }
+}
+
+// ---- operator shims ----------------------------------------------------------------------------------------------------
+
+#ifdef ENABLE_NVIDIA_API
+#define QWEN2_DISPATCH(CPU_CALL, CUDA_CALL) \
+    if (_on_gpu) {                          \
+        CUDA_CALL;                          \
+    } else {                                \
+        CPU_CALL;                           \
+    }
+#else
+#define QWEN2_DISPATCH(CPU_CALL, CUDA_CALL) CPU_CALL;
+#endif
+
+void Qwen2::opEmbedding(void *out, const int64_t *idx, const void *w, size_t n, size_t d, size_t vocab) {
+    QWEN2_DISPATCH(cpu::embedding(_elem, out, idx, w, n, d, vocab), kernels::embedding(_stream, _elem, out, idx, w, n, d, vocab));
+}
+void Qwen2::opLinear(void *out, const void *in, const void *w, const void *b, size_t m, size_t n, size_t k) {
+    QWEN2_DISPATCH(cpu::linear(_meta.dtype, out, in, w, b, m, n, k), kernels::linear(_stream, _meta.dtype, out, in, w, b, m, n, k));
+}
+void Qwen2::opRmsNorm(void *out, const void *in, const void *w, size_t rows, size_t d) {
+    QWEN2_DISPATCH(cpu::rms_norm(_meta.dtype, out, in, w, _meta.epsilon, rows, d),
+                   kernels::rms_norm(_stream, _meta.dtype, out, in, w, _meta.epsilon, rows, d));
+}
+void Qwen2::opRope(void *out, const void *in, const int64_t *pos, size_t seq, size_t heads) {
+    QWEN2_DISPATCH(cpu::rope(_meta.dtype, out, in, pos, _meta.theta, seq, heads, _meta.dh),
+                   kernels::rope(_stream, _meta.dtype, out, in, pos, _meta.theta, seq, heads, _meta.dh));
+}
+void Qwen2::opSwiglu(void *out, const void *gate, const void *up, size_t n) {
+    QWEN2_DISPATCH(cpu::swiglu(_meta.dtype, out, gate, up, n), kernels::swiglu(_stream, _meta.dtype, out, gate, up, n));
+}
+void Qwen2::opAdd(void *c, const void *a, const void *b, size_t n) {
+    QWEN2_DISPATCH(cpu::add(_meta.dtype, c, a, b, n), kernels::add(_stream, _meta.dtype, c, a, b, n));
+}
+void Qwen2::opArgmax(int64_t *idx, const void *vals, size_t rows, size_t n) {
+    QWEN2_DISPATCH(cpu::argmax_rows(_meta.dtype, idx, nullptr, vals, rows, n),
+                   kernels::argmax_rows(_stream, _meta.dtype, idx, nullptr, vals, rows, n));
+}
+
+// ---- the network ---------------------------------------------------------------------------------------------------------
+
+void Qwen2::forward(const StepArrays &a, size_t T, size_t n_seqs, size_t max_q_len, size_t max_kv_len, bool decode_only) {
+    const size_t hs = _meta.hs, qd = _meta.nh * _meta.dh, kd = _meta.nkvh * _meta.dh, di = _meta.di;
+    const float scale = 1.f / std::sqrt(float(_meta.dh));
+    std::byte *x = _x->memory(), *h = _h->memory(), *q = _q->memory(), *k = _k->memory(), *v = _v->memory();
+    std::byte *attn = _attn->memory(), *gate = _gate->memory(), *up = _up->memory();
+    const std::vector<Layer> layers = layerPointers();
+
+    opEmbedding(x, a.tokens, _weights.in_embed->tensor->data(), T, hs, _meta.voc);
+    for (size_t l = 0; l < _meta.nlayer; ++l) {
+        const Layer &w = layers[l];
+        opRmsNorm(h, x, w.attn_norm, T, hs);
+        opLinear(q, h, w.q_w, w.q_b, T, qd, hs);
+        opLinear(k, h, w.k_w, w.k_b, T, kd, hs);
+        opLinear(v, h, w.v_w, w.v_b, T, kd, hs);
+        opRope(q, q, a.pos64, T, _meta.nh);
+        opRope(k, k, a.pos64, T, _meta.nkvh);
+        _cache->appendDev(l, k, v, a.seq32, a.pos32, T, _stream);
+        if (decode_only) {
+            _cache->decodeDev(l, attn, nullptr, q, a.seq_list, a.kv_lens, n_seqs, max_kv_len, _meta.nh, scale, _stream);
+        } else {
+            _cache->prefillDev(l, attn, q, a.seq_list, a.q_starts, a.kv_lens, n_seqs, T, max_q_len, max_kv_len, _meta.nh,
+                               scale, _stream);
+        }
+        opLinear(h, attn, w.o_w, nullptr, T, hs, qd);
+        opAdd(x, x, h, T * hs);
+        opRmsNorm(h, x, w.mlp_norm, T, hs);
+        opLinear(gate, h, w.gate_w, nullptr, T, di, hs);
+        opLinear(up, h, w.up_w, nullptr, T, di, hs);
+        opSwiglu(gate, gate, up, T * di);
+        opLinear(h, gate, w.down_w, nullptr, T, hs, di);
+        opAdd(x, x, h, T * hs);
+    }
+    // the last token of every sequence -> final norm -> vocabulary projection -> greedy choice
+    opEmbedding(_x_last->memory(), a.last_rows, x, n_seqs, hs, T);
+    opRmsNorm(_x_last->memory(), _x_last->memory(), _weights.out_norm_w->tensor->data(), n_seqs, hs);
+    opLinear(_logits->memory(), _x_last->memory(), _weights.out_embed->tensor->data(), nullptr, n_seqs, _meta.voc, hs);
+    opArgmax(a.next, _logits->memory(), n_seqs, _meta.voc);
+    _last_n_seqs = n_seqs;
+}
+
+void Qwen2::step(const int32_t *seq_ids, const int32_t *n_tokens, size_t n_seqs, const int64_t *tokens, int64_t *next_out) {
+    if (n_seqs == 0) {
+        return;
+    }
+    if (seq_ids == nullptr || n_tokens == nullptr || tokens == nullptr || next_out == nullptr) {
+        fail(LLAISYS_E_INVALID, "qwen2: null argument");
+    }
+    size_t T = 0, max_q = 0, max_kv = 0;
+    for (size_t i = 0; i < n_seqs; ++i) {
+        const size_t len = seqLen(seq_ids[i]);
+        if (n_tokens[i] < 1) {
+            fail(LLAISYS_E_INVALID, "qwen2: every sequence of a step needs at least one new token");
+        }
+        if (len + size_t(n_tokens[i]) > _max_tokens_per_seq) {
+            fail(LLAISYS_E_INVALID, "qwen2: sequence would exceed the configured maximum length");
+        }
+        for (size_t j = 0; j < i; ++j) {
+            if (seq_ids[j] == seq_ids[i]) {
+                fail(LLAISYS_E_INVALID, "qwen2: a sequence appears twice in one step");
+            }
+        }
+        T += size_t(n_tokens[i]);
+        max_q = std::max(max_q, size_t(n_tokens[i]));
+        max_kv = std::max(max_kv, len + size_t(n_tokens[i]));
+    }
+    for (size_t i = 0; i < T; ++i) {
+        if (tokens[i] < 0 || size_t(tokens[i]) >= _meta.voc) {
+            fail(LLAISYS_E_INVALID, "qwen2: token id out of range");
+        }
+    }
+    for (size_t i = 0; i < n_seqs; ++i) {
+        _cache->seqReserve(seq_ids[i], seqLen(seq_ids[i]) + size_t(n_tokens[i]));
+    }
+    enter();
+    ensureWorkspace(T, n_seqs);
+    const StepArrays a = carveStepArrays(T, n_seqs);
+    // the same carving over a host image, then one copy
+    _meta_host.assign(_meta_bytes, std::byte{0});
+    std::byte *dev0 = _meta_block->memory(), *host0 = _meta_host.data();
+    auto host = [&](auto *dev_ptr) { return reinterpret_cast<decltype(dev_ptr)>(host0 + (reinterpret_cast<std::byte *>(dev_ptr) - dev0)); };
+    size_t row = 0;
+    bool decode_only = true;
+    host(a.q_starts)[0] = 0;
+    for (size_t i = 0; i < n_seqs; ++i) {
+        const size_t len = seqLen(seq_ids[i]), n = size_t(n_tokens[i]);
+        decode_only = decode_only && n == 1;
+        for (size_t t = 0; t < n; ++t, ++row) {
+            host(a.tokens)[row] = tokens[row];
+            host(a.pos64)[row] = int64_t(len + t);
+            host(a.pos32)[row] = int32_t(len + t);
+            host(a.seq32)[row] = seq_ids[i];
+        }
+        host(a.kv_lens)[i] = int32_t(len + n);
+        host(a.seq_list)[i] = seq_ids[i];
+        host(a.q_starts)[i + 1] = int32_t(row);
+        host(a.last_rows)[i] = int64_t(row) - 1;
+    }
+    copyToDevice(dev0, host0, _meta_bytes);
+    _cache->flush();
+    forward(a, T, n_seqs, max_q, max_kv, decode_only);
+    copyToHost(next_out, a.next, n_seqs * sizeof(int64_t));
+    for (size_t i = 0; i < n_seqs; ++i) {
+        seqLen(seq_ids[i]) += size_t(n_tokens[i]);
+    }
+    _cache->check();
+}
+
+void Qwen2::decodeLoop(const int32_t *seq_ids, size_t n_seqs, const int64_t *first_tokens, size_t n_steps,
+                       int64_t *tokens_out) {
+    if (n_seqs == 0 || n_steps == 0) {
+        return;
+    }
+    if (seq_ids == nullptr || first_tokens == nullptr || tokens_out == nullptr) {
+        fail(LLAISYS_E_INVALID, "qwen2: null argument");
+    }
+    size_t max_kv = 0;
+    for (size_t i = 0; i < n_seqs; ++i) {
+        const size_t len = seqLen(seq_ids[i]);
+        if (len + n_steps > _max_tokens_per_seq) {
+            fail(LLAISYS_E_INVALID, "qwen2: sequence would exceed the configured maximum length");
+        }
+        if (first_tokens[i] < 0 || size_t(first_tokens[i]) >= _meta.voc) {
+            fail(LLAISYS_E_INVALID, "qwen2: token id out of range");
+        }
+        max_kv = std::max(max_kv, len + n_steps);
+    }
+    for (size_t i = 0; i < n_seqs; ++i) {
+        _cache->seqReserve(seq_ids[i], seqLen(seq_ids[i]) + n_steps); // every page of the loop, up front
+    }
+    auto &rt = enter();
+    ensureWorkspace(n_seqs, n_seqs);
+    const StepArrays a = carveStepArrays(n_seqs, n_seqs);
+    _meta_host.assign(_meta_bytes, std::byte{0});
+    std::byte *dev0 = _meta_block->memory(), *host0 = _meta_host.data();
+    auto host = [&](auto *dev_ptr) { return reinterpret_cast<decltype(dev_ptr)>(host0 + (reinterpret_cast<std::byte *>(dev_ptr) - dev0)); };
+    for (size_t i = 0; i < n_seqs; ++i) {
+        const size_t len = seqLen(seq_ids[i]);
+        host(a.tokens)[i] = first_tokens[i];
+        host(a.pos64)[i] = int64_t(len);
+        host(a.pos32)[i] = int32_t(len);
+        host(a.seq32)[i] = seq_ids[i];
+        host(a.kv_lens)[i] = int32_t(len + 1);
+        host(a.seq_list)[i] = seq_ids[i];
+        host(a.q_starts)[i] = int32_t(i);
+        host(a.last_rows)[i] = int64_t(i);
+    }
+    host(a.q_starts)[n_seqs] = int32_t(n_seqs);
+    copyToDevice(dev0, host0, _meta_bytes);
+    _cache->flush();
+    // the token log and the step counter the advance kernel writes through
+    core::storage_t log = rt.allocateDeviceStorage(n_steps * n_seqs * sizeof(int64_t));
+    core::storage_t counter = rt.allocateDeviceStorage(sizeof(int32_t));
+    const int32_t zero = 0;
+    copyToDevice(counter->memory(), &zero, sizeof(zero));
+    auto *log_dev = reinterpret_cast<int64_t *>(log->memory());
+    auto *counter_dev = reinterpret_cast<int32_t *>(counter->memory());
+
+    auto one_step = [&]() {
+        forward(a, n_seqs, n_seqs, 1, max_kv, true);
+#ifdef ENABLE_NVIDIA_API
+        if (_on_gpu) {
+            kernels::advance_decode_state(_stream, a.tokens, a.next, a.pos64, a.pos32, a.kv_lens, log_dev, counter_dev,
+                                          int(n_seqs));
+            return;
+        }
+#endif
+        int32_t &step = *counter_dev;
+        for (size_t i = 0; i < n_seqs; ++i) {
+            a.tokens[i] = a.next[i];
+            log_dev[size_t(step) * n_seqs + i] = a.next[i];
+            a.pos64[i] += 1;
+            a.pos32[i] += 1;
+            a.kv_lens[i] += 1;
+        }
+        ++step;
+    };
+
+    if (_on_gpu) {
+#ifdef ENABLE_NVIDIA_API
+        one_step(); // eager: sizes every lazily grown scratch before the capture
+        size_t timed_steps = 0;
+        float ms = 0.f;
+        if (n_steps > 1) {
+            rt.synchronize();
+            kernels::graph_capture_begin(_stream);
+            try {
+                one_step();
+            } catch (...) {
+                kernels::graph_destroy(kernels::graph_capture_end(_stream));
+                throw;
+            }
+            void *exec = kernels::graph_capture_end(_stream);
+            void *e0 = kernels::event_create(), *e1 = kernels::event_create();
+            kernels::event_record(e0, _stream);
+            for (size_t s = 1; s < n_steps; ++s) {
+                kernels::graph_launch(exec, _stream);
+            }
+            kernels::event_record(e1, _stream);
+            ms = kernels::event_elapsed_ms(e0, e1);
+            timed_steps = n_steps - 1;
+            kernels::event_destroy(e0);
+            kernels::event_destroy(e1);
+            kernels::graph_destroy(exec);
+        }
+        _last_loop_ms = timed_steps ? double(ms) / double(timed_steps) : 0.0;
+#endif
+    } else {
+        const auto t0 = std::chrono::steady_clock::now();
+        for (size_t s = 0; s < n_steps; ++s) {
+            one_step();
+        }
+        _last_loop_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() / double(n_steps);
+    }
+    copyToHost(tokens_out, log_dev, n_steps * n_seqs * sizeof(int64_t));
+    for (size_t i = 0; i < n_seqs; ++i) {
+        seqLen(seq_ids[i]) += n_steps;
+    }
+    _cache->check();
+}
+
+void Qwen2::lastLogits(float *out_host, size_t capacity_floats) {
+    const size_t n = _last_n_seqs * _meta.voc;
+    if (n == 0) {
+        fail(LLAISYS_E_INVALID, "qwen2: no step has run yet");
+    }
+    if (out_host == nullptr || capacity_floats < n) {
+        fail(LLAISYS_E_INVALID, "qwen2: logits buffer too small");
+    }
+    std::vector<std::byte> raw(n * _elem);
+    copyToHost(raw.data(), _logits->memory(), raw.size());
+    for (size_t i = 0; i < n; ++i) {
+        switch (_meta.dtype) {
+        case LLAISYS_DTYPE_F32:
+            out_host[i] = reinterpret_cast<const float *>(raw.data())[i];
+            break;
+        case LLAISYS_DTYPE_F16:
+            out_host[i] = utils::cast<float>(reinterpret_cast<const fp16_t *>(raw.data())[i]);
+            break;
+        default:
+            out_host[i] = utils::cast<float>(reinterpret_cast<const bf16_t *>(raw.data())[i]);
+            break;
+        }
+    }
+}
+
+} // namespace llaisys::models

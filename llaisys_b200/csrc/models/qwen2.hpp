@@ -1,0 +1,95 @@
+// Qwen2 decoder (RMSNorm, GQA attention with q/k/v biases and half-split RoPE, SwiGLU MLP, untied output embedding)
+// on the library's operators and the paged KV cache. The reference declares this model's C API and leaves it
+// unimplemented (include/llaisys/models/qwen2.h:7-40; python/llaisys/models/qwen2.py:11-33 is a stub).
+//
+// All state of a forward pass lives on the model's device: activations in a workspace sized for the largest batch
+// seen, per-step index arrays (tokens, positions, sequence rows, lengths) in one staging block. A decode loop keeps
+// even the loop-carried state there: the chosen tokens feed the next step's embedding lookup, positions and lengths
+// are advanced by a kernel, and on NVIDIA one step is captured as a CUDA graph and replayed.
+#pragma once
+
+#include "../capi/handles.hpp"
+#include "../kv/paged_kv.hpp"
+#include "llaisys/models/qwen2.h"
+
+#include <memory>
+#include <vector>
+
+namespace llaisys::models {
+
+class Qwen2 {
+public:
+    Qwen2(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int device_id);
+    ~Qwen2();
+    Qwen2(const Qwen2 &) = delete;
+    Qwen2 &operator=(const Qwen2 &) = delete;
+
+    LlaisysQwen2Weights *weights() { return &_weights; }
+    const LlaisysQwen2Meta &meta() const { return _meta; }
+
+    void configureCache(size_t max_seqs, size_t max_tokens);
+    int32_t seqAdd();
+    void seqFree(int32_t seq);
+    void reset();
+    int64_t infer(const int64_t *tokens, size_t n);
+    void step(const int32_t *seq_ids, const int32_t *n_tokens, size_t n_seqs, const int64_t *tokens, int64_t *next_out);
+    void decodeLoop(const int32_t *seq_ids, size_t n_seqs, const int64_t *first_tokens, size_t n_steps,
+                    int64_t *tokens_out);
+    void lastLogits(float *out_host, size_t capacity_floats);
+    double lastLoopMs() const { return _last_loop_ms; }
+
+private:
+    struct Layer {
+        const std::byte *attn_norm, *q_w, *q_b, *k_w, *k_b, *v_w, *v_b, *o_w, *mlp_norm, *gate_w, *up_w, *down_w;
+    };
+    // device pointers of one step's index arrays (all inside _meta_block)
+    struct StepArrays {
+        int64_t *tokens = nullptr, *pos64 = nullptr, *last_rows = nullptr, *next = nullptr;
+        int32_t *seq32 = nullptr, *pos32 = nullptr, *kv_lens = nullptr, *q_starts = nullptr, *seq_list = nullptr;
+    };
+
+    core::Runtime &enter() const;
+    llaisysTensor_t makeWeight(const std::vector<size_t> &shape);
+    std::vector<Layer> layerPointers() const;
+    void ensureWorkspace(size_t n_tokens, size_t n_seqs);
+    StepArrays carveStepArrays(size_t n_tokens, size_t n_seqs);
+    size_t &seqLen(int32_t seq);
+    // the network itself: activations for n_tokens rows -> logits and greedy tokens for n_seqs rows
+    void forward(const StepArrays &a, size_t n_tokens, size_t n_seqs, size_t max_q_len, size_t max_kv_len, bool decode_only);
+
+    // operator shims: CPU loops or CUDA launches on the runtime stream, on raw device pointers
+    void opEmbedding(void *out, const int64_t *idx, const void *w, size_t n, size_t d, size_t vocab);
+    void opLinear(void *out, const void *in, const void *w, const void *b, size_t m, size_t n, size_t k);
+    void opRmsNorm(void *out, const void *in, const void *w, size_t rows, size_t d);
+    void opRope(void *out, const void *in, const int64_t *pos, size_t seq, size_t heads);
+    void opSwiglu(void *out, const void *gate, const void *up, size_t n);
+    void opAdd(void *c, const void *a, const void *b, size_t n);
+    void opArgmax(int64_t *idx, const void *vals, size_t rows, size_t n);
+    void copyToDevice(void *dst, const void *src, size_t bytes);
+    void copyToHost(void *dst, const void *src, size_t bytes);
+
+    LlaisysQwen2Meta _meta;
+    llaisysDeviceType_t _device;
+    int _device_id;
+    size_t _elem = 0;
+    bool _on_gpu = false;
+    llaisysStream_t _stream = nullptr;
+
+    LlaisysQwen2Weights _weights{};
+    std::vector<llaisysTensor_t> _all_weights; // owns every handle in _weights
+    std::vector<llaisysTensor_t> _per_layer[12];
+
+    std::unique_ptr<kv::PagedKV> _cache;
+    size_t _max_tokens_per_seq = 0;
+    std::vector<size_t> _seq_len; // by sequence id; SIZE_MAX = not live
+    int32_t _implicit_seq = -1;
+
+    // workspace
+    core::storage_t _x, _h, _q, _k, _v, _attn, _gate, _up, _x_last, _logits, _meta_block;
+    size_t _ws_tokens = 0, _ws_seqs = 0, _meta_bytes = 0;
+    std::vector<std::byte> _meta_host;
+    size_t _last_n_seqs = 0;
+    double _last_loop_ms = 0.0;
+};
+
+} // namespace llaisys::models

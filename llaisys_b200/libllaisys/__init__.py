@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import sys
-from ctypes import (CFUNCTYPE, POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t,
+from ctypes import (CFUNCTYPE, POINTER, Structure, c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_size_t,
                     c_ssize_t, c_uint8, c_void_p)
 from enum import IntEnum
 from pathlib import Path
@@ -93,6 +93,25 @@ _KV = llaisysPagedKV_t
 _I32P = POINTER(c_int32)
 
 # name -> (restype, argtypes). Every symbol declared in include/llaisys/*.h appears here exactly once.
+
+
+class LlaisysQwen2Meta(Structure):
+    """struct LlaisysQwen2Meta (reference: include/llaisys/models/qwen2.h:7-13)."""
+    _fields_ = [("dtype", llaisysDataType_t), ("nlayer", c_size_t), ("hs", c_size_t), ("nh", c_size_t),
+                ("nkvh", c_size_t), ("dh", c_size_t), ("di", c_size_t), ("maxseq", c_size_t), ("voc", c_size_t),
+                ("epsilon", c_float), ("theta", c_float), ("end_token", c_int64)]
+
+
+class LlaisysQwen2Weights(Structure):
+    """struct LlaisysQwen2Weights (reference: include/llaisys/models/qwen2.h:15-31)."""
+    _fields_ = [("in_embed", llaisysTensor_t), ("out_embed", llaisysTensor_t), ("out_norm_w", llaisysTensor_t)] + [
+        (name, POINTER(llaisysTensor_t)) for name in (
+            "attn_norm_w", "attn_q_w", "attn_q_b", "attn_k_w", "attn_k_b", "attn_v_w", "attn_v_b", "attn_o_w",
+            "mlp_norm_w", "mlp_gate_w", "mlp_up_w", "mlp_down_w")]
+
+
+_MODEL = c_void_p
+
 PROTOTYPES: dict[str, tuple] = {
     # runtime.h
     "llaisysGetRuntimeAPI": (POINTER(LlaisysRuntimeAPI), [llaisysDeviceType_t]),
@@ -165,6 +184,19 @@ PROTOTYPES: dict[str, tuple] = {
     "llaisysPagedAttentionDecodeNoAlloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t,
                                                    c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t,
                                                    llaisysDataType_t, c_float, c_void_p, llaisysStream_t]),
+    # include/llaisys/models/qwen2.h
+    "llaisysQwen2ModelCreate": (_MODEL, [POINTER(LlaisysQwen2Meta), llaisysDeviceType_t, POINTER(c_int), c_int]),
+    "llaisysQwen2ModelDestroy": (None, [_MODEL]),
+    "llaisysQwen2ModelWeights": (POINTER(LlaisysQwen2Weights), [_MODEL]),
+    "llaisysQwen2ModelInfer": (c_int64, [_MODEL, POINTER(c_int64), c_size_t]),
+    "llaisysQwen2ModelConfigureCache": (c_int, [_MODEL, c_size_t, c_size_t]),
+    "llaisysQwen2ModelSeqAdd": (c_int, [_MODEL, _I32P]),
+    "llaisysQwen2ModelSeqFree": (c_int, [_MODEL, c_int32]),
+    "llaisysQwen2ModelReset": (c_int, [_MODEL]),
+    "llaisysQwen2ModelStep": (c_int, [_MODEL, _I32P, _I32P, c_size_t, POINTER(c_int64), POINTER(c_int64)]),
+    "llaisysQwen2ModelDecodeLoop": (c_int, [_MODEL, _I32P, c_size_t, POINTER(c_int64), c_size_t, POINTER(c_int64)]),
+    "llaisysQwen2ModelLastLogits": (c_int, [_MODEL, POINTER(c_float), c_size_t]),
+    "llaisysQwen2ModelLastLoopMs": (c_double, [_MODEL]),
 }
 
 
@@ -199,5 +231,5 @@ LIB_LLAISYS = load_shared_library()
 __all__ = [
     "LIB_LLAISYS", "PROTOTYPES", "LlaisysRuntimeAPI", "llaisysStream_t", "llaisysTensor_t", "llaisysPagedKV_t",
     "llaisysDataType_t", "DataType", "llaisysDeviceType_t", "DeviceType", "llaisysMemcpyKind_t", "MemcpyKind",
-    "Status", "library_path",
+    "Status", "library_path", "LlaisysQwen2Meta", "LlaisysQwen2Weights",
 ]
