@@ -530,7 +530,8 @@ def run_model_workload(args) -> None:
         hbm_peak, _, kind = _peaks()
         kv_bytes = cfg["num_hidden_layers"] * B * ctx_mid * (2 * NKVH * D * 2)
         achieved = (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9
-        own = cfg["num_hidden_layers"] * 12 + 6  # per layer: 2 norms, 3 bias adds, 2 ropes, append, decode, 2 adds, swiglu
+        # per layer: 2 norms, bias+rope+append, decode attention, activation; per step: embedding, norm, argmax, 2 x advance
+        own = cfg["num_hidden_layers"] * 5 + 5
         line = {
             "metric": "decode tokens/s (Qwen2-1.5B architecture, greedy, paged KV cache)",
             "value": total_seqs * 1e3 / step_ms, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm,
@@ -548,7 +549,7 @@ def run_model_workload(args) -> None:
             "prefill": {"tokens_per_s": total_seqs * prompt_len / prefill_s, "seconds": prefill_s,
                         "what": "2048-token prompts, 8 sequences per call, host clock"},
             "e2e": e2e, "gpu_launches": own * steps,
-            "library_launches": (cfg["num_hidden_layers"] * 7 + 1) * steps,
+            "library_launches": (cfg["num_hidden_layers"] * 4 + 1) * steps,
             "timing": "CUDA events around the graph replays, max over ranks", "clocks": clocks.summary(),
         }
         if not args.no_cpu_baseline and world == 1:

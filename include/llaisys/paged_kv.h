@@ -140,6 +140,14 @@ LLAISYS_API int llaisysLseMerge(llaisysDeviceType_t device_type, int device_id, 
 LLAISYS_API int llaisysPagedKVAppendDev(llaisysPagedKV_t kv, size_t layer, const void *k_rows, const void *v_rows,
                                         const int32_t *seq_ids_dev, const int32_t *positions_dev, size_t n_rows,
                                         llaisysStream_t stream);
+/* The step before attention, fused: qkv is the packed q|k|v projection [n_rows, (nh + 2 nkvh) * head_dim] of the cache's
+ * dtype, bias an optional row of the same width (NULL = none). q and k heads get the half-split rotary embedding of the
+ * reference's rope operator (angle = position / theta^(2j/d), computed in float; reference: README.md rope section,
+ * test/ops/rope.py:11-32); rotated q is written to q_out [n_rows, nh, head_dim], rotated k and plain v go to token
+ * positions_dev[i] of sequence seq_ids_dev[i]. One rounding to the dtype, after bias and rotation. */
+LLAISYS_API int llaisysPagedKVRopeAppendDev(llaisysPagedKV_t kv, size_t layer, void *q_out, const void *qkv,
+                                            const void *bias, const int32_t *seq_ids_dev, const int32_t *positions_dev,
+                                            size_t n_rows, size_t nh, float theta, llaisysStream_t stream);
 LLAISYS_API int llaisysPagedAttentionDecodeDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
                                                const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
                                                size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream);

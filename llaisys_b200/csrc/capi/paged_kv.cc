@@ -211,6 +211,13 @@ int llaisysPagedKVAppendDev(llaisysPagedKV_t kv, size_t layer, const void *k_row
     KV_OR_FAIL(kv);
     return guarded([&] { kv->impl.appendDev(layer, k_rows, v_rows, seq_ids_dev, positions_dev, n_rows, stream); });
 }
+int llaisysPagedKVRopeAppendDev(llaisysPagedKV_t kv, size_t layer, void *q_out, const void *qkv, const void *bias,
+                                const int32_t *seq_ids_dev, const int32_t *positions_dev, size_t n_rows, size_t nh,
+                                float theta, llaisysStream_t stream) {
+    KV_OR_FAIL(kv);
+    return guarded(
+        [&] { kv->impl.ropeAppendDev(layer, q_out, qkv, bias, seq_ids_dev, positions_dev, n_rows, nh, theta, stream); });
+}
 int llaisysPagedAttentionDecodeDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
                                    const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
                                    size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream) {

@@ -316,7 +316,7 @@ void argmax_typed(int64_t *idx_out, T *val_out, const T *vals, size_t rows, size
 }
 
 template <typename T>
-void linear_typed(T *out, const T *in, const T *w, const T *bias, size_t m, size_t n, size_t k) {
+void linear_typed(T *out, const T *in, const T *w, const T *bias, size_t m, size_t n, size_t k, bool accumulate) {
     // Convert once to f32 rows (bf16/f16 conversions are the expensive part on the host), then blocked dot products
     // with a double accumulator so that the reference's f32 tolerance (1e-5 relative at K = 4096) holds.
     std::vector<float> in_f(m * k), w_f;
@@ -351,6 +351,9 @@ void linear_typed(T *out, const T *in, const T *w, const T *bias, size_t m, size
             }
             if (bias != nullptr) {
                 acc += load_f32(bias + j);
+            }
+            if (accumulate) {
+                acc += load_f32(out + size_t(i) * n + size_t(j));
             }
             out[size_t(i) * n + size_t(j)] = utils::cast<T>(float(acc));
         }
@@ -399,6 +402,67 @@ void rope_typed(T *out, const T *in, const int64_t *pos, float theta, size_t seq
 }
 
 template <typename T>
+void swiglu_packed_typed(T *out, const T *gu, size_t rows, size_t di) {
+#pragma omp parallel for if (rows * di > 65536)
+    for (int64_t r = 0; r < int64_t(rows); ++r) {
+        for (size_t i = 0; i < di; ++i) {
+            const float g = load_f32(gu + size_t(r) * 2 * di + i), u = load_f32(gu + size_t(r) * 2 * di + di + i);
+            out[size_t(r) * di + i] = utils::cast<T>(u * (g / (1.f + std::exp(-g))));
+        }
+    }
+}
+
+// The fused step before attention (same arithmetic as the CUDA kernel): bias, rotary embedding of the q and k heads,
+// q to its own tensor, k and v into their page slots. f32 arithmetic, one rounding.
+template <typename T>
+int paged_rope_append_typed(const KVView &kv, T *q_out, const T *qkv, const T *bias, const int32_t *seq_ids,
+                            const int32_t *positions, int32_t n_rows, int32_t nh, float theta, int32_t max_blocks) {
+    int err = 0;
+    const int32_t d = kv.d, half = d / 2, heads = nh + 2 * kv.nkvh;
+    std::vector<float> divisor(static_cast<size_t>(half));
+    for (int32_t j = 0; j < half; ++j) {
+        divisor[size_t(j)] = std::pow(theta, 2.f * float(j) / float(d));
+    }
+    auto *kp = static_cast<std::byte *>(kv.k_base);
+    auto *vp = static_cast<std::byte *>(kv.v_base);
+    for (int32_t r = 0; r < n_rows; ++r) {
+        const int64_t off = slot_offset_bytes(kv, sizeof(T), seq_ids[r], positions[r], max_blocks, &err);
+        const float p = float(positions[r]);
+        for (int32_t h = 0; h < heads; ++h) {
+            const T *x = qkv + (size_t(r) * heads + h) * d;
+            const T *b = bias ? bias + size_t(h) * d : nullptr;
+            const bool is_q = h < nh, is_v = h >= nh + kv.nkvh;
+            T *y = nullptr;
+            if (is_q) {
+                y = q_out + (size_t(r) * nh + h) * d;
+            } else if (off >= 0) {
+                const int32_t kvh = is_v ? h - nh - kv.nkvh : h - nh;
+                y = reinterpret_cast<T *>((is_v ? vp : kp) + off + int64_t(kvh) * kv.head_stride * int64_t(sizeof(T)));
+            } else {
+                continue;
+            }
+            for (int32_t j = 0; j < half; ++j) {
+                float lo = load_f32(x + j), hi = load_f32(x + j + half);
+                if (b != nullptr) {
+                    lo += load_f32(b + j);
+                    hi += load_f32(b + j + half);
+                }
+                if (!is_v) {
+                    const float ang = p / divisor[size_t(j)];
+                    const float sn = std::sin(ang), cs = std::cos(ang);
+                    const float a0 = lo, b0 = hi;
+                    lo = a0 * cs - b0 * sn;
+                    hi = b0 * cs + a0 * sn;
+                }
+                y[j] = utils::cast<T>(lo);
+                y[j + half] = utils::cast<T>(hi);
+            }
+        }
+    }
+    return err;
+}
+
+template <typename T>
 void swiglu_typed(T *out, const T *gate, const T *up, size_t n) {
 #pragma omp parallel for if (n > 65536)
     for (int64_t i = 0; i < int64_t(n); ++i) {
@@ -414,17 +478,17 @@ void swiglu_typed(T *out, const T *gate, const T *up, size_t n) {
     case LLAISYS_DTYPE_F32: {                          \
         using T = float;                               \
         CALL;                                          \
-        return;                                        \
+        break;                                         \
     }                                                  \
     case LLAISYS_DTYPE_F16: {                          \
         using T = fp16_t;                              \
         CALL;                                          \
-        return;                                        \
+        break;                                         \
     }                                                  \
     case LLAISYS_DTYPE_BF16: {                         \
         using T = bf16_t;                              \
         CALL;                                          \
-        return;                                        \
+        break;                                         \
     }                                                  \
     default:                                           \
         EXCEPTION_UNSUPPORTED_DATATYPE(dtype);         \
@@ -443,9 +507,22 @@ void embedding(size_t elem_size, void *out, const int64_t *index, const void *we
 }
 
 void linear(llaisysDataType_t dtype, void *out, const void *in, const void *weight, const void *bias, size_t m, size_t n,
-            size_t k) {
+            size_t k, bool accumulate) {
     LLAISYS_DISPATCH_FLOAT(dtype, linear_typed(static_cast<T *>(out), static_cast<const T *>(in), static_cast<const T *>(weight),
-                                               static_cast<const T *>(bias), m, n, k));
+                                               static_cast<const T *>(bias), m, n, k, accumulate));
+}
+
+void swiglu_packed(llaisysDataType_t dtype, void *out, const void *gate_up, size_t rows, size_t di) {
+    LLAISYS_DISPATCH_FLOAT(dtype, swiglu_packed_typed(static_cast<T *>(out), static_cast<const T *>(gate_up), rows, di));
+}
+
+int paged_rope_append(llaisysDataType_t dtype, const kernels::KVView &kv, void *q_out, const void *qkv, const void *bias,
+                      const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t nh, float theta,
+                      int32_t max_blocks) {
+    LLAISYS_DISPATCH_FLOAT(dtype, return paged_rope_append_typed(kv, static_cast<T *>(q_out), static_cast<const T *>(qkv),
+                                                                 static_cast<const T *>(bias), seq_ids, positions, n_rows, nh,
+                                                                 theta, max_blocks));
+    return 0;
 }
 
 void rms_norm(llaisysDataType_t dtype, void *out, const void *in, const void *weight, float eps, size_t rows, size_t d) {

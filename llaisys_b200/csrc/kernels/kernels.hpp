@@ -24,8 +24,15 @@ void argmax_rows(stream_t stream, llaisysDataType_t dtype, int64_t *idx_out, voi
                  size_t n);
 void embedding(stream_t stream, size_t elem_size, void *out, const int64_t *index, const void *weight, size_t n, size_t d,
                size_t vocab);
+// accumulate: out += in . W^T (the residual add of a decoder block folded into the projection; one rounding of the sum)
 void linear(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, const void *bias,
-            size_t m, size_t n, size_t k);
+            size_t m, size_t n, size_t k, bool accumulate = false);
+// out[r, i] = up * silu(gate) with gate = gu[r, i], up = gu[r, di + i]: the activation on a packed gate|up projection.
+void swiglu_packed(stream_t stream, llaisysDataType_t dtype, void *out, const void *gate_up, size_t rows, size_t di);
+// Row-wise argmax with every row split over several CTAs (a vocabulary-sized row on one CTA leaves the GPU idle).
+// scratch: 12 * rows bytes, zero before the first call; the kernel leaves it zero again.
+void argmax_rows_split(stream_t stream, llaisysDataType_t dtype, int64_t *idx_out, const void *vals, size_t rows, size_t n,
+                       void *scratch);
 void bias_add(stream_t stream, llaisysDataType_t dtype, void *out, const void *bias, size_t rows, size_t n);
 void rms_norm(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, float eps, size_t rows,
               size_t d);
@@ -50,6 +57,12 @@ void event_destroy(void *event);
 void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const void *k_rows, const void *v_rows,
                   const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t max_blocks,
                   int32_t *error_flag);
+
+// K1b: bias + rotary embedding + append in one pass over the packed projection qkv [n_rows, (nh + 2 nkvh) * d]: rotated q
+// -> q_out [n_rows, nh, d]; rotated k and plain v -> their page slots (same addressing and flags as K1).
+void paged_rope_append(stream_t stream, llaisysDataType_t dtype, const KVView &kv, void *q_out, const void *qkv,
+                       const void *bias, const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t nh,
+                       float theta, int32_t max_blocks, int32_t *error_flag);
 
 // K5: tokens [0, n_tokens) of table row seq_row -> k_out, v_out [n_tokens, nkvh, d].
 void paged_gather(stream_t stream, size_t elem_size, const KVView &kv, int32_t seq_row, int32_t n_tokens,

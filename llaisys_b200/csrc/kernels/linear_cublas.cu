@@ -67,7 +67,7 @@ cublasHandle_t handle_for_current_device() {
 } // namespace
 
 void linear(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, const void *bias,
-            size_t m, size_t n, size_t k) {
+            size_t m, size_t n, size_t k, bool accumulate) {
     if (m == 0 || n == 0) {
         return;
     }
@@ -90,7 +90,7 @@ void linear(stream_t stream, llaisysDataType_t dtype, void *out, const void *in,
     cublasStatus_t st = cublas_api().set_stream(h, static_cast<cudaStream_t>(stream));
     ASSERT(st == CUBLAS_STATUS_SUCCESS, "cublasSetStream failed with status " << int(st));
     // Row-major out[M, N] = in[M, K] . W[N, K]^T is column-major out^T[N, M] = W^T(as stored)[K, N]^T . in^T[K, M].
-    const float alpha = 1.f, beta = 0.f;
+    const float alpha = 1.f, beta = accumulate ? 1.f : 0.f; // accumulate: out += in . W^T, one rounding of the sum
     st = cublas_api().gemm_ex(h, CUBLAS_OP_T, CUBLAS_OP_N, int(n), int(m), int(k), &alpha, weight, type, int(k), in, type,
                               int(k), &beta, out, type, int(n), CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
     ASSERT(st == CUBLAS_STATUS_SUCCESS, "cublasGemmEx failed with status " << int(st));

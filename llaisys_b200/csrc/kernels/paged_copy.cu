@@ -117,6 +117,114 @@ int grid_for(int64_t threads, int block) {
     return int(want < cap ? (want ? want : 1) : cap);
 }
 
+// K1b: the step just before attention, fused. Input is the packed projection output qkv [rows, (nh + 2 nkvh) * d] (plus
+// an optional bias row); q and k heads get the half-split rotary embedding (angle = pos / theta^(2j/d) in f32, as the
+// rope operator), q goes to a contiguous [rows, nh, d] tensor, k and v go straight into their page slots. One thread
+// handles VEC elements of the lower half of a head row and the matching VEC of the upper half (VEC = 16 bytes of T, or
+// 1 when d is not a multiple of 2 VEC): f32 arithmetic, one rounding.
+template <typename T, int VEC>
+struct alignas(sizeof(T) * VEC) Pack {
+    T v[VEC];
+};
+
+template <typename T, int VEC>
+__global__ void paged_rope_append_kernel(unsigned char *__restrict__ k_pool, unsigned char *__restrict__ v_pool,
+                                         T *__restrict__ q_out, const T *__restrict__ qkv, const T *__restrict__ bias,
+                                         const int32_t *__restrict__ table, const int32_t *__restrict__ seq_ids,
+                                         const int32_t *__restrict__ positions, CopyGeom g, int32_t n_rows, int32_t nh,
+                                         int32_t d, float theta, int32_t max_blocks, int32_t *error_flag) {
+    using P = Pack<T, VEC>;
+    const int32_t half = d / 2;
+    const int32_t vec_per_head = half / VEC;
+    const int32_t heads = nh + 2 * g.nkvh;
+    const int64_t total = int64_t(n_rows) * heads * vec_per_head;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    const int64_t row_elems = int64_t(heads) * d;
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int32_t row = int32_t(i / (heads * vec_per_head));
+        const int32_t r = int32_t(i - int64_t(row) * heads * vec_per_head);
+        const int32_t head = r / vec_per_head;
+        const int32_t j0 = (r - head * vec_per_head) * VEC;
+        const int32_t pos = positions[row];
+        const int64_t in_off = int64_t(row) * row_elems + int64_t(head) * d + j0;
+        P lo = *reinterpret_cast<const P *>(qkv + in_off);
+        P hi = *reinterpret_cast<const P *>(qkv + in_off + half);
+        float a[VEC], b[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            a[e] = to_f32(lo.v[e]);
+            b[e] = to_f32(hi.v[e]);
+        }
+        if (bias != nullptr) {
+            const P blo = *reinterpret_cast<const P *>(bias + int64_t(head) * d + j0);
+            const P bhi = *reinterpret_cast<const P *>(bias + int64_t(head) * d + j0 + half);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                a[e] += to_f32(blo.v[e]);
+                b[e] += to_f32(bhi.v[e]);
+            }
+        }
+        const bool is_v = head >= nh + g.nkvh;
+        if (!is_v) {
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                const float ang = float(pos) / powf(theta, 2.f * float(j0 + e) / float(d));
+                float sn, cs;
+                sincosf(ang, &sn, &cs);
+                const float x = a[e], y = b[e];
+                a[e] = x * cs - y * sn;
+                b[e] = y * cs + x * sn;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            lo.v[e] = from_f32<T>(a[e]);
+            hi.v[e] = from_f32<T>(b[e]);
+        }
+        if (head < nh) {
+            T *dst = q_out + (int64_t(row) * nh + head) * d + j0;
+            *reinterpret_cast<P *>(dst) = lo;
+            *reinterpret_cast<P *>(dst + half) = hi;
+            continue;
+        }
+        int32_t page, slot;
+        if (!resolve_slot(table, g, seq_ids[row], pos, max_blocks, error_flag, page, slot)) {
+            continue;
+        }
+        const int32_t kvh = is_v ? head - nh - g.nkvh : head - nh;
+        const int64_t off_b = int64_t(page) * g.page_stride_b + int64_t(kvh) * g.head_stride_b +
+                              int64_t(slot) * g.token_stride_b + int64_t(j0) * int64_t(sizeof(T));
+        unsigned char *dst = (is_v ? v_pool : k_pool) + off_b;
+        *reinterpret_cast<P *>(dst) = lo;
+        *reinterpret_cast<P *>(dst + int64_t(half) * int64_t(sizeof(T))) = hi;
+    }
+}
+
+template <typename T>
+void launch_rope_append(cudaStream_t s, const KVView &kv, void *q_out, const void *qkv, const void *bias,
+                        const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t nh, float theta,
+                        int32_t max_blocks, int32_t *error_flag) {
+    constexpr int kVec = 16 / int(sizeof(T));
+    const CopyGeom g = make_geom(kv, sizeof(T));
+    const int32_t d = kv.d;
+    auto aligned = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool wide = d % (2 * kVec) == 0 && aligned(q_out) && aligned(qkv) && aligned(bias) && aligned(kv.k_base) &&
+                      aligned(kv.v_base);
+    const int64_t threads = int64_t(n_rows) * (nh + 2 * kv.nkvh) * (d / 2 / (wide ? kVec : 1));
+    const int block = 256, grid = grid_for(threads, block);
+    auto *kp = static_cast<unsigned char *>(kv.k_base);
+    auto *vp = static_cast<unsigned char *>(kv.v_base);
+    if (wide) {
+        paged_rope_append_kernel<T, kVec><<<grid, block, 0, s>>>(kp, vp, static_cast<T *>(q_out), static_cast<const T *>(qkv),
+                                                                 static_cast<const T *>(bias), kv.block_table, seq_ids,
+                                                                 positions, g, n_rows, nh, d, theta, max_blocks, error_flag);
+    } else {
+        paged_rope_append_kernel<T, 1><<<grid, block, 0, s>>>(kp, vp, static_cast<T *>(q_out), static_cast<const T *>(qkv),
+                                                              static_cast<const T *>(bias), kv.block_table, seq_ids, positions,
+                                                              g, n_rows, nh, d, theta, max_blocks, error_flag);
+    }
+}
+
 } // namespace
 
 void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const void *k_rows, const void *v_rows,
@@ -157,6 +265,31 @@ void paged_gather(stream_t stream, size_t elem_size, const KVView &kv, int32_t s
         static_cast<uint4 *>(v_out), kv.block_table, g, seq_row, n_tokens,
         kv.block_table ? kv.table_stride : INT32_MAX, error_flag);
     check_launch("paged_gather");
+}
+
+void paged_rope_append(stream_t stream, llaisysDataType_t dtype, const KVView &kv, void *q_out, const void *qkv,
+                       const void *bias, const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t nh,
+                       float theta, int32_t max_blocks, int32_t *error_flag) {
+    if (n_rows <= 0) {
+        return;
+    }
+    CHECK_ARGUMENT(kv.d % 2 == 0, "rope append: head_dim must be even");
+    auto s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+    case LLAISYS_DTYPE_F32:
+        launch_rope_append<float>(s, kv, q_out, qkv, bias, seq_ids, positions, n_rows, nh, theta, max_blocks, error_flag);
+        break;
+    case LLAISYS_DTYPE_F16:
+        launch_rope_append<__half>(s, kv, q_out, qkv, bias, seq_ids, positions, n_rows, nh, theta, max_blocks, error_flag);
+        break;
+    case LLAISYS_DTYPE_BF16:
+        launch_rope_append<__nv_bfloat16>(s, kv, q_out, qkv, bias, seq_ids, positions, n_rows, nh, theta, max_blocks,
+                                          error_flag);
+        break;
+    default:
+        EXCEPTION_UNSUPPORTED_DATATYPE(dtype);
+    }
+    check_launch("paged_rope_append");
 }
 
 } // namespace llaisys::kernels

@@ -381,6 +381,33 @@ void PagedKV::appendDev(size_t layer, const void *k_rows, const void *v_rows, co
 #endif
 }
 
+void PagedKV::ropeAppendDev(size_t layer, void *q_out, const void *qkv, const void *bias, const int32_t *seq_ids_dev,
+                            const int32_t *positions_dev, size_t n_rows, size_t nh, float theta, llaisysStream_t stream) {
+    checkLayer(layer);
+    KV_REQUIRE(n_rows <= kMaxInt32 && nh > 0 && nh <= 4096, LLAISYS_E_INVALID, "paged KV rope append: bad sizes");
+    KV_REQUIRE(_cfg.head_dim % 2 == 0, LLAISYS_E_INVALID, "paged KV rope append: head_dim must be even");
+    if (n_rows == 0) {
+        return;
+    }
+    KV_REQUIRE(q_out && qkv && seq_ids_dev && positions_dev, LLAISYS_E_INVALID, "paged KV rope append: null argument");
+    const kernels::KVView v = view(layer);
+    if (!onDevice()) {
+        const int err = cpu::paged_rope_append(_cfg.dtype, v, q_out, qkv, bias, seq_ids_dev, positions_dev, int32_t(n_rows),
+                                               int32_t(nh), theta, int32_t(_cfg.max_pages_per_seq));
+        *reinterpret_cast<int32_t *>(_error_dev->memory()) |= err;
+        return;
+    }
+#ifdef ENABLE_NVIDIA_API
+    enter();
+    kernels::paged_rope_append(stream, _cfg.dtype, v, q_out, qkv, bias, seq_ids_dev, positions_dev, int32_t(n_rows),
+                               int32_t(nh), theta, int32_t(_cfg.max_pages_per_seq),
+                               reinterpret_cast<int32_t *>(_error_dev->memory()));
+#else
+    (void)stream;
+    fail(LLAISYS_E_UNSUPPORTED, "this build has no NVIDIA backend");
+#endif
+}
+
 void PagedKV::decodeDev(size_t layer, void *out, float *part, const void *q, const int32_t *seq_ids_dev,
                         const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len, size_t nh, float scale,
                         llaisysStream_t stream) {

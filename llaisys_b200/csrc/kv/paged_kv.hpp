@@ -68,6 +68,9 @@ public:
     // ---- data path: device index arrays, explicit stream (no validation, no staging) ----
     void appendDev(size_t layer, const void *k_rows, const void *v_rows, const int32_t *seq_ids_dev,
                    const int32_t *positions_dev, size_t n_rows, llaisysStream_t stream);
+    // qkv [n_rows, (nh + 2 nkvh) * d] (+ optional bias row) -> rotated q in q_out [n_rows, nh, d], rotated k and v appended
+    void ropeAppendDev(size_t layer, void *q_out, const void *qkv, const void *bias, const int32_t *seq_ids_dev,
+                       const int32_t *positions_dev, size_t n_rows, size_t nh, float theta, llaisysStream_t stream);
     void decodeDev(size_t layer, void *out, float *part, const void *q, const int32_t *seq_ids_dev,
                    const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len, size_t nh, float scale,
                    llaisysStream_t stream);

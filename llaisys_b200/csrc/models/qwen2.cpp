@@ -44,13 +44,30 @@ Qwen2::Qwen2(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int devic
     _weights.in_embed = makeWeight({meta.voc, hs});
     _weights.out_embed = makeWeight({meta.voc, hs});
     _weights.out_norm_w = makeWeight({hs});
-    const std::vector<size_t> shapes[12] = {{hs},     {qd, hs}, {qd}, {kd, hs}, {kd},     {kd, hs},
-                                            {kd},     {hs, qd}, {hs}, {di, hs}, {di, hs}, {hs, di}};
-    for (int w = 0; w < 12; ++w) {
-        _per_layer[w].resize(L);
-        for (size_t l = 0; l < L; ++l) {
-            _per_layer[w][l] = makeWeight(shapes[w]);
-        }
+    for (auto &v : _per_layer) {
+        v.resize(L);
+    }
+    _qkv_w.resize(L);
+    _qkv_b.resize(L);
+    _gate_up_w.resize(L);
+    const std::vector<std::byte> zeros((qd + 2 * kd) * _elem);
+    for (size_t l = 0; l < L; ++l) {
+        _qkv_w[l] = Tensor::create({qd + 2 * kd, hs}, meta.dtype, device, device_id);
+        _qkv_b[l] = Tensor::create({qd + 2 * kd}, meta.dtype, device, device_id);
+        _qkv_b[l]->load(zeros.data()); // a caller that loads no biases gets none
+        _gate_up_w[l] = Tensor::create({2 * di, hs}, meta.dtype, device, device_id);
+        _per_layer[0][l] = makeWeight({hs});
+        _per_layer[1][l] = wrap(_qkv_w[l]->slice(0, 0, qd));
+        _per_layer[2][l] = wrap(_qkv_b[l]->slice(0, 0, qd));
+        _per_layer[3][l] = wrap(_qkv_w[l]->slice(0, qd, qd + kd));
+        _per_layer[4][l] = wrap(_qkv_b[l]->slice(0, qd, qd + kd));
+        _per_layer[5][l] = wrap(_qkv_w[l]->slice(0, qd + kd, qd + 2 * kd));
+        _per_layer[6][l] = wrap(_qkv_b[l]->slice(0, qd + kd, qd + 2 * kd));
+        _per_layer[7][l] = makeWeight({hs, qd});
+        _per_layer[8][l] = makeWeight({hs});
+        _per_layer[9][l] = wrap(_gate_up_w[l]->slice(0, 0, di));
+        _per_layer[10][l] = wrap(_gate_up_w[l]->slice(0, di, 2 * di));
+        _per_layer[11][l] = makeWeight({hs, di});
     }
     _weights.attn_norm_w = _per_layer[0].data();
     _weights.attn_q_w = _per_layer[1].data();
@@ -78,17 +95,22 @@ core::Runtime &Qwen2::enter() const {
     return ctx.runtime();
 }
 
-llaisysTensor_t Qwen2::makeWeight(const std::vector<size_t> &shape) {
-    auto *h = new LlaisysTensor{Tensor::create(shape, _meta.dtype, _device, _device_id)};
+llaisysTensor_t Qwen2::wrap(tensor_t t) {
+    auto *h = new LlaisysTensor{std::move(t)};
     _all_weights.push_back(h);
     return h;
+}
+
+llaisysTensor_t Qwen2::makeWeight(const std::vector<size_t> &shape) {
+    return wrap(Tensor::create(shape, _meta.dtype, _device, _device_id));
 }
 
 std::vector<Qwen2::Layer> Qwen2::layerPointers() const {
     std::vector<Layer> layers(_meta.nlayer);
     for (size_t l = 0; l < _meta.nlayer; ++l) {
         auto p = [&](int w) { return static_cast<const std::byte *>(_per_layer[w][l]->tensor->data()); };
-        layers[l] = Layer{p(0), p(1), p(2), p(3), p(4), p(5), p(6), p(7), p(8), p(9), p(10), p(11)};
+        auto packed = [](const tensor_t &t) { return static_cast<const std::byte *>(t->data()); };
+        layers[l] = Layer{p(0), packed(_qkv_w[l]), packed(_qkv_b[l]), p(7), p(8), packed(_gate_up_w[l]), p(11)};
     }
     return layers;
 }
@@ -172,17 +194,20 @@ void Qwen2::ensureWorkspace(size_t n_tokens, size_t n_seqs) {
         const size_t hs = _meta.hs, qd = _meta.nh * _meta.dh, kd = _meta.nkvh * _meta.dh;
         _x = rt.allocateDeviceStorage(n_tokens * hs * _elem);
         _h = rt.allocateDeviceStorage(n_tokens * hs * _elem);
+        _qkv = rt.allocateDeviceStorage(n_tokens * (qd + 2 * kd) * _elem);
         _q = rt.allocateDeviceStorage(n_tokens * qd * _elem);
-        _k = rt.allocateDeviceStorage(n_tokens * kd * _elem);
-        _v = rt.allocateDeviceStorage(n_tokens * kd * _elem);
         _attn = rt.allocateDeviceStorage(n_tokens * qd * _elem);
-        _gate = rt.allocateDeviceStorage(n_tokens * _meta.di * _elem);
-        _up = rt.allocateDeviceStorage(n_tokens * _meta.di * _elem);
+        _gate_up = rt.allocateDeviceStorage(n_tokens * 2 * _meta.di * _elem);
+        _act = rt.allocateDeviceStorage(n_tokens * _meta.di * _elem);
     }
     if (n_seqs > _ws_seqs) {
         _ws_seqs = n_seqs;
         _x_last = rt.allocateDeviceStorage(n_seqs * _meta.hs * _elem);
         _logits = rt.allocateDeviceStorage(n_seqs * _meta.voc * _elem);
+        // keys and counters of the split argmax: zero once, the kernel leaves them zero
+        _argmax_scratch = rt.allocateDeviceStorage(n_seqs * 12);
+        const std::vector<std::byte> zeros(n_seqs * 12);
+        copyToDevice(_argmax_scratch->memory(), zeros.data(), zeros.size());
     }
     // tokens, pos64, last_rows, next (int64) then seq32, pos32, kv_lens, q_starts, seq_list (int32), 16-byte aligned
     const size_t need = align_up(n_tokens * 8, 16) * 2 + align_up(n_seqs * 8, 16) * 2 + align_up(n_tokens * 4, 16) * 2 +
@@ -249,26 +274,21 @@ void Qwen2::copyToHost(void *dst, const void *src, size_t bytes) {
 void Qwen2::opEmbedding(void *out, const int64_t *idx, const void *w, size_t n, size_t d, size_t vocab) {
     QWEN2_DISPATCH(cpu::embedding(_elem, out, idx, w, n, d, vocab), kernels::embedding(_stream, _elem, out, idx, w, n, d, vocab));
 }
-void Qwen2::opLinear(void *out, const void *in, const void *w, const void *b, size_t m, size_t n, size_t k) {
-    QWEN2_DISPATCH(cpu::linear(_meta.dtype, out, in, w, b, m, n, k), kernels::linear(_stream, _meta.dtype, out, in, w, b, m, n, k));
+void Qwen2::opLinear(void *out, const void *in, const void *w, size_t m, size_t n, size_t k, bool accumulate) {
+    QWEN2_DISPATCH(cpu::linear(_meta.dtype, out, in, w, nullptr, m, n, k, accumulate),
+                   kernels::linear(_stream, _meta.dtype, out, in, w, nullptr, m, n, k, accumulate));
 }
 void Qwen2::opRmsNorm(void *out, const void *in, const void *w, size_t rows, size_t d) {
     QWEN2_DISPATCH(cpu::rms_norm(_meta.dtype, out, in, w, _meta.epsilon, rows, d),
                    kernels::rms_norm(_stream, _meta.dtype, out, in, w, _meta.epsilon, rows, d));
 }
-void Qwen2::opRope(void *out, const void *in, const int64_t *pos, size_t seq, size_t heads) {
-    QWEN2_DISPATCH(cpu::rope(_meta.dtype, out, in, pos, _meta.theta, seq, heads, _meta.dh),
-                   kernels::rope(_stream, _meta.dtype, out, in, pos, _meta.theta, seq, heads, _meta.dh));
-}
-void Qwen2::opSwiglu(void *out, const void *gate, const void *up, size_t n) {
-    QWEN2_DISPATCH(cpu::swiglu(_meta.dtype, out, gate, up, n), kernels::swiglu(_stream, _meta.dtype, out, gate, up, n));
-}
-void Qwen2::opAdd(void *c, const void *a, const void *b, size_t n) {
-    QWEN2_DISPATCH(cpu::add(_meta.dtype, c, a, b, n), kernels::add(_stream, _meta.dtype, c, a, b, n));
+void Qwen2::opSwigluPacked(void *out, const void *gate_up, size_t rows, size_t di) {
+    QWEN2_DISPATCH(cpu::swiglu_packed(_meta.dtype, out, gate_up, rows, di),
+                   kernels::swiglu_packed(_stream, _meta.dtype, out, gate_up, rows, di));
 }
 void Qwen2::opArgmax(int64_t *idx, const void *vals, size_t rows, size_t n) {
     QWEN2_DISPATCH(cpu::argmax_rows(_meta.dtype, idx, nullptr, vals, rows, n),
-                   kernels::argmax_rows(_stream, _meta.dtype, idx, nullptr, vals, rows, n));
+                   kernels::argmax_rows_split(_stream, _meta.dtype, idx, vals, rows, n, _argmax_scratch->memory()));
 }
 
 // ---- the network ---------------------------------------------------------------------------------------------------------
@@ -276,39 +296,38 @@ void Qwen2::opArgmax(int64_t *idx, const void *vals, size_t rows, size_t n) {
 void Qwen2::forward(const StepArrays &a, size_t T, size_t n_seqs, size_t max_q_len, size_t max_kv_len, bool decode_only) {
     const size_t hs = _meta.hs, qd = _meta.nh * _meta.dh, kd = _meta.nkvh * _meta.dh, di = _meta.di;
     const float scale = 1.f / std::sqrt(float(_meta.dh));
-    std::byte *x = _x->memory(), *h = _h->memory(), *q = _q->memory(), *k = _k->memory(), *v = _v->memory();
-    std::byte *attn = _attn->memory(), *gate = _gate->memory(), *up = _up->memory();
+    std::byte *x = _x->memory(), *h = _h->memory(), *qkv = _qkv->memory(), *q = _q->memory();
+    std::byte *attn = _attn->memory(), *gate_up = _gate_up->memory(), *act = _act->memory();
     const std::vector<Layer> layers = layerPointers();
 
+    // Per layer: norm, packed q|k|v projection, [bias + rope + append], attention, output projection accumulated into the
+    // residual stream, norm, packed gate|up projection, activation, down projection accumulated into the stream.
     opEmbedding(x, a.tokens, _weights.in_embed->tensor->data(), T, hs, _meta.voc);
     for (size_t l = 0; l < _meta.nlayer; ++l) {
         const Layer &w = layers[l];
         opRmsNorm(h, x, w.attn_norm, T, hs);
-        opLinear(q, h, w.q_w, w.q_b, T, qd, hs);
-        opLinear(k, h, w.k_w, w.k_b, T, kd, hs);
-        opLinear(v, h, w.v_w, w.v_b, T, kd, hs);
-        opRope(q, q, a.pos64, T, _meta.nh);
-        opRope(k, k, a.pos64, T, _meta.nkvh);
-        _cache->appendDev(l, k, v, a.seq32, a.pos32, T, _stream);
+        opLinear(qkv, h, w.qkv_w, T, qd + 2 * kd, hs);
+        _cache->ropeAppendDev(l, q, qkv, w.qkv_b, a.seq32, a.pos32, T, _meta.nh, _meta.theta, _stream);
         if (decode_only) {
             _cache->decodeDev(l, attn, nullptr, q, a.seq_list, a.kv_lens, n_seqs, max_kv_len, _meta.nh, scale, _stream);
         } else {
             _cache->prefillDev(l, attn, q, a.seq_list, a.q_starts, a.kv_lens, n_seqs, T, max_q_len, max_kv_len, _meta.nh,
                                scale, _stream);
         }
-        opLinear(h, attn, w.o_w, nullptr, T, hs, qd);
-        opAdd(x, x, h, T * hs);
+        opLinear(x, attn, w.o_w, T, hs, qd, true);
         opRmsNorm(h, x, w.mlp_norm, T, hs);
-        opLinear(gate, h, w.gate_w, nullptr, T, di, hs);
-        opLinear(up, h, w.up_w, nullptr, T, di, hs);
-        opSwiglu(gate, gate, up, T * di);
-        opLinear(h, gate, w.down_w, nullptr, T, hs, di);
-        opAdd(x, x, h, T * hs);
+        opLinear(gate_up, h, w.gate_up_w, T, 2 * di, hs);
+        opSwigluPacked(act, gate_up, T, di);
+        opLinear(x, act, w.down_w, T, hs, di, true);
     }
     // the last token of every sequence -> final norm -> vocabulary projection -> greedy choice
-    opEmbedding(_x_last->memory(), a.last_rows, x, n_seqs, hs, T);
-    opRmsNorm(_x_last->memory(), _x_last->memory(), _weights.out_norm_w->tensor->data(), n_seqs, hs);
-    opLinear(_logits->memory(), _x_last->memory(), _weights.out_embed->tensor->data(), nullptr, n_seqs, _meta.voc, hs);
+    const std::byte *last = x;
+    if (!decode_only) {
+        opEmbedding(_x_last->memory(), a.last_rows, x, n_seqs, hs, T);
+        last = _x_last->memory();
+    }
+    opRmsNorm(_x_last->memory(), last, _weights.out_norm_w->tensor->data(), n_seqs, hs);
+    opLinear(_logits->memory(), _x_last->memory(), _weights.out_embed->tensor->data(), n_seqs, _meta.voc, hs);
     opArgmax(a.next, _logits->memory(), n_seqs, _meta.voc);
     _last_n_seqs = n_seqs;
 }

@@ -39,8 +39,10 @@ public:
     double lastLoopMs() const { return _last_loop_ms; }
 
 private:
+    // q|k|v and gate|up live packed in one matrix each (one projection launch instead of three / two); the handles the
+    // caller loads through are row slices of the packed tensors
     struct Layer {
-        const std::byte *attn_norm, *q_w, *q_b, *k_w, *k_b, *v_w, *v_b, *o_w, *mlp_norm, *gate_w, *up_w, *down_w;
+        const std::byte *attn_norm, *qkv_w, *qkv_b, *o_w, *mlp_norm, *gate_up_w, *down_w;
     };
     // device pointers of one step's index arrays (all inside _meta_block)
     struct StepArrays {
@@ -49,6 +51,7 @@ private:
     };
 
     core::Runtime &enter() const;
+    llaisysTensor_t wrap(tensor_t t);
     llaisysTensor_t makeWeight(const std::vector<size_t> &shape);
     std::vector<Layer> layerPointers() const;
     void ensureWorkspace(size_t n_tokens, size_t n_seqs);
@@ -59,11 +62,9 @@ private:
 
     // operator shims: CPU loops or CUDA launches on the runtime stream, on raw device pointers
     void opEmbedding(void *out, const int64_t *idx, const void *w, size_t n, size_t d, size_t vocab);
-    void opLinear(void *out, const void *in, const void *w, const void *b, size_t m, size_t n, size_t k);
+    void opLinear(void *out, const void *in, const void *w, size_t m, size_t n, size_t k, bool accumulate = false);
     void opRmsNorm(void *out, const void *in, const void *w, size_t rows, size_t d);
-    void opRope(void *out, const void *in, const int64_t *pos, size_t seq, size_t heads);
-    void opSwiglu(void *out, const void *gate, const void *up, size_t n);
-    void opAdd(void *c, const void *a, const void *b, size_t n);
+    void opSwigluPacked(void *out, const void *gate_up, size_t rows, size_t di);
     void opArgmax(int64_t *idx, const void *vals, size_t rows, size_t n);
     void copyToDevice(void *dst, const void *src, size_t bytes);
     void copyToHost(void *dst, const void *src, size_t bytes);
@@ -78,6 +79,7 @@ private:
     LlaisysQwen2Weights _weights{};
     std::vector<llaisysTensor_t> _all_weights; // owns every handle in _weights
     std::vector<llaisysTensor_t> _per_layer[12];
+    std::vector<tensor_t> _qkv_w, _qkv_b, _gate_up_w; // packed per-layer matrices behind the q/k/v and gate/up handles
 
     std::unique_ptr<kv::PagedKV> _cache;
     size_t _max_tokens_per_seq = 0;
@@ -85,7 +87,7 @@ private:
     int32_t _implicit_seq = -1;
 
     // workspace
-    core::storage_t _x, _h, _q, _k, _v, _attn, _gate, _up, _x_last, _logits, _meta_block;
+    core::storage_t _x, _h, _qkv, _q, _attn, _gate_up, _act, _x_last, _logits, _meta_block, _argmax_scratch;
     size_t _ws_tokens = 0, _ws_seqs = 0, _meta_bytes = 0;
     std::vector<std::byte> _meta_host;
     size_t _last_n_seqs = 0;

@@ -174,6 +174,8 @@ PROTOTYPES: dict[str, tuple] = {
                                 c_size_t, c_size_t]),
     "llaisysPagedKVAppendDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                         llaisysStream_t]),
+    "llaisysPagedKVRopeAppendDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                            c_size_t, c_float, llaisysStream_t]),
     "llaisysPagedAttentionDecodeDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                                c_size_t, c_size_t, c_float, llaisysStream_t]),
     "llaisysPagedAttentionDecodePartialDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p,

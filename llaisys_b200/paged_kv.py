@@ -159,6 +159,13 @@ class PagedKVCache:
         _check(LIB_LLAISYS.llaisysPagedKVAppendDev(self._kv, layer, _addr(k_rows), _addr(v_rows), _addr(seq_ids_dev),
                                                    _addr(positions_dev), n_rows, stream))
 
+    def rope_append_dev(self, layer: int, q_out, qkv, bias, seq_ids_dev, positions_dev, n_rows: int, nh: int,
+                        theta: float, stream) -> None:
+        """Bias + rotary embedding + append over a packed q|k|v projection (device index arrays, explicit stream)."""
+        _check(LIB_LLAISYS.llaisysPagedKVRopeAppendDev(self._kv, layer, _addr(q_out), _addr(qkv),
+                                                       _addr(bias) if bias is not None else None, _addr(seq_ids_dev),
+                                                       _addr(positions_dev), n_rows, nh, theta, stream))
+
     def decode_dev(self, layer: int, out, q, seq_ids_dev, kv_lens_dev, n_seqs: int, max_kv_len: int, nh: int,
                    scale: float, stream) -> None:
         _check(LIB_LLAISYS.llaisysPagedAttentionDecodeDev(self._kv, layer, _addr(out), _addr(q), _addr(seq_ids_dev),
