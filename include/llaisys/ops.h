@@ -21,6 +21,9 @@ LLAISYS_EXTERN_C LLAISYS_API void llaisysArgmax(llaisysTensor_t max_idx, llaisys
 LLAISYS_EXTERN_C LLAISYS_API void llaisysEmbedding(llaisysTensor_t out, llaisysTensor_t index, llaisysTensor_t weight);
 LLAISYS_EXTERN_C LLAISYS_API void llaisysLinear(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight,
                                                 llaisysTensor_t bias);
+/* New (no counterpart in the reference): out += in . weight^T, the sum rounded once -- the residual add of a decoder
+ * block folded into its projection. Same shape rules and error behaviour as llaisysLinear. */
+LLAISYS_EXTERN_C LLAISYS_API void llaisysLinearAccumulate(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight);
 LLAISYS_EXTERN_C LLAISYS_API void llaisysRearrange(llaisysTensor_t out, llaisysTensor_t in);
 LLAISYS_EXTERN_C LLAISYS_API void llaisysRmsNorm(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight,
                                                  float eps);

@@ -65,6 +65,9 @@ void llaisysEmbedding(llaisysTensor_t out, llaisysTensor_t index, llaisysTensor_
 void llaisysLinear(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight, llaisysTensor_t bias) {
     llaisys::ops::linear(out->tensor, in->tensor, weight->tensor, unwrap_optional(bias));
 }
+void llaisysLinearAccumulate(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight) {
+    llaisys::ops::linear_ex(out->tensor, in->tensor, weight->tensor, nullptr, true);
+}
 void llaisysRearrange(llaisysTensor_t out, llaisysTensor_t in) { llaisys::ops::rearrange(out->tensor, in->tensor); }
 void llaisysRmsNorm(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight, float eps) {
     llaisys::ops::rms_norm(out->tensor, in->tensor, weight->tensor, eps);

@@ -26,6 +26,7 @@
 // No cluster launch, no multicast.
 #include "kernels.hpp"
 #include "mma_utils.cuh"
+#include "tcgen05_utils.cuh"
 
 #include <cuda.h>
 
@@ -58,7 +59,6 @@ constexpr int kColS = 0, kColO = 2 * kBlockN;    // S buffers at columns 0 and k
 constexpr int kAlignSlack = 256;                 // spare bytes in front of the operands (two CTAs must fit one SM)
 constexpr int kMaxSortedSeqs = 256;              // batches up to this size are scheduled longest sequence first
 static_assert(kBlockN % 64 == 0 && kColO + kD <= kTmemCols, "TMEM budget");
-constexpr uint32_t kWaitLimit = 1u << 20; // polls before a wait gives up (about a second at worst)
 constexpr int kErrTimeout = 8;
 constexpr float kRescaleThreshold = 8.f;     // log2 units
 
@@ -88,116 +88,6 @@ struct PrefillParams {
     float scale_log2;
     int32_t *error_flag;
 };
-
-// ---- tcgen05 wrappers ---------------------------------------------------------------------------------
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_dst), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-// D[tmem] (+)= A[smem] . B[smem]; accumulate = 0 overwrites D.
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n"
-                 ".reg .pred p;\n"
-                 "setp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-                 "}\n" ::"r"(d_tmem),
-                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-                 : "memory");
-}
-// The mbarrier gets one arrival when every tcgen05.mma issued so far by this thread has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-
-// 32 consecutive f32 columns of this thread's TMEM lane. The _nowait form only issues the load: the registers are
-// valid after tmem_wait_ld().
-__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        v[i] = __uint_as_float(r[i]);
-    }
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
-                 "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
-                 "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])),
-                 "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])),
-                 "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
-                 "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
-                 "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])),
-                 "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])),
-                 "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
-                 "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
-                 "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
-                 "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle. Fields (bit positions): start address >> 4 [0,14),
-// leading byte offset >> 4 [16,30), stride byte offset >> 4 [32,46), descriptor version 1 [46,48),
-// layout type 2 = SWIZZLE_128B [61,64).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= uint64_t((addr & 0x3FFFFu) >> 4);
-    d |= uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= uint64_t(1) << 46;
-    d |= uint64_t(2) << 61;
-    return d;
-}
-
-// Instruction descriptor for kind::f16: D f32 [4,6) = 1; A/B format [7,10) / [10,13): 0 = f16, 1 = bf16;
-// A major bit 15, B major bit 16 (0 = K-major, 1 = MN-major); N >> 3 at [17,23); M >> 4 at [24,29).
-__host__ __device__ constexpr uint32_t make_idesc(bool bf16, bool b_mn_major, int m, int n) {
-    return (1u << 4) | (uint32_t(bf16 ? 1 : 0) << 7) | (uint32_t(bf16 ? 1 : 0) << 10) | (uint32_t(b_mn_major ? 1 : 0) << 16) |
-           (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
-}
-
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) {
-            return true;
-        }
-        if ((i & 1023u) == 1023u && *abort_flag != 0) {
-            return false;
-        }
-    }
-    return false;
-}
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 2)

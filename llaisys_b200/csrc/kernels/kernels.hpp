@@ -27,6 +27,13 @@ void embedding(stream_t stream, size_t elem_size, void *out, const int64_t *inde
 // accumulate: out += in . W^T (the residual add of a decoder block folded into the projection; one rounding of the sum)
 void linear(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, const void *bias,
             size_t m, size_t n, size_t k, bool accumulate = false);
+// K6: the tcgen05 weight-streaming kernel behind linear() for at most 128 rows of 16-bit activations (K a multiple of 64,
+// N a multiple of 64, not vocabulary-sized). False = shape not covered, nothing launched. overlap: programmatic launch
+// (the weight stream starts under the previous kernel's tail). linear_tc_status synchronises the stream and returns (and
+// clears) the kernel's error word: 0, or 16 when a bounded wait ran out.
+bool linear_tc(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, size_t m, size_t n,
+               size_t k, bool accumulate, bool overlap);
+int linear_tc_status(stream_t stream);
 // out[r, i] = up * silu(gate) with gate = gu[r, i], up = gu[r, di + i]: the activation on a packed gate|up projection.
 void swiglu_packed(stream_t stream, llaisysDataType_t dtype, void *out, const void *gate_up, size_t rows, size_t di);
 // Row-wise argmax with every row split over several CTAs (a vocabulary-sized row on one CTA leaves the GPU idle).

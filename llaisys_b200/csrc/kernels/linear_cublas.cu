@@ -1,11 +1,14 @@
-// linear on the device: out[M, N] = in[M, K] . weight[N, K]^T through cuBLAS (a plain library GEMM; the hand-written
-// kernels of this library are the attention path), plus the bias add.
+// linear on the device: out[M, N] = in[M, K] . weight[N, K]^T. Decode-sized calls (at most 128 rows, 16-bit) go to the
+// hand-written weight-streaming kernel (skinny_gemm_tc.cu); everything else is a plain library GEMM through cuBLAS.
 //
 // cuBLAS is opened with dlopen at the first call instead of being linked: the library then loads on machines without
 // it, and inside a process that already carries a cuBLAS (PyTorch ships its own) the loader hands back that copy
 // rather than mapping a second one.
 #include "device_utils.cuh"
 #include "kernels.hpp"
+
+#include <cstdlib>
+#include <string>
 
 #include <cublas_v2.h>
 #include <dlfcn.h>
@@ -69,6 +72,22 @@ cublasHandle_t handle_for_current_device() {
 void linear(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, const void *bias,
             size_t m, size_t n, size_t k, bool accumulate) {
     if (m == 0 || n == 0) {
+        return;
+    }
+    // Decode-sized calls may take the hand-written streaming kernel (skinny_gemm_tc.cu). Measured on B200 against cuBLAS
+    // (graph replays, weights rotated beyond L2): it wins where the activations are a small fraction of the traffic and K is
+    // long enough to split over a cluster (8 x 8960 -> 1536: 12.5 vs 17.2 us); at 64 rows every CTA re-reads the
+    // activations from L2 and cuBLAS's paired-CTA kernels are faster (64 x 1536 -> 17920: 16.5 vs 11.8 us), so those stay
+    // with the library. LLAISYS_LINEAR_PATH=tc forces the kernel wherever it applies, =cublas never uses it.
+    const char *path = std::getenv("LLAISYS_LINEAR_PATH");
+    const bool force_tc = path != nullptr && std::string(path) == "tc";
+    const bool never_tc = path != nullptr && std::string(path) == "cublas";
+    const bool prefer_tc = m <= 16 && k >= 4096;
+    if (!never_tc && (force_tc || prefer_tc) && m <= 128 &&
+        linear_tc(stream, dtype, out, in, weight, m, n, k, accumulate, false)) {
+        if (bias != nullptr) {
+            bias_add(stream, dtype, out, bias, m, n);
+        }
         return;
     }
     ASSERT(cublas_api().ok, "linear on NVIDIA needs cuBLAS (libcublas.so.12 was not found)");

@@ -396,7 +396,7 @@ void Qwen2::step(const int32_t *seq_ids, const int32_t *n_tokens, size_t n_seqs,
     for (size_t i = 0; i < n_seqs; ++i) {
         seqLen(seq_ids[i]) += size_t(n_tokens[i]);
     }
-    _cache->check();
+    checkKernels();
 }
 
 void Qwen2::decodeLoop(const int32_t *seq_ids, size_t n_seqs, const int64_t *first_tokens, size_t n_steps,
@@ -509,7 +509,21 @@ void Qwen2::decodeLoop(const int32_t *seq_ids, size_t n_seqs, const int64_t *fir
     for (size_t i = 0; i < n_seqs; ++i) {
         seqLen(seq_ids[i]) += n_steps;
     }
+    checkKernels();
+}
+
+// Error words of the kernels a step ran: the cache's (bad block-table entries, a wait that ran out in an attention
+// kernel) and the projection kernel's.
+void Qwen2::checkKernels() {
     _cache->check();
+#ifdef ENABLE_NVIDIA_API
+    if (_on_gpu) {
+        const int status = kernels::linear_tc_status(_stream);
+        if (status != 0) {
+            fail(LLAISYS_E_KERNEL, "qwen2: the projection kernel reported error word " + std::to_string(status));
+        }
+    }
+#endif
 }
 
 void Qwen2::lastLogits(float *out_host, size_t capacity_floats) {

@@ -66,6 +66,7 @@ private:
     void opRmsNorm(void *out, const void *in, const void *w, size_t rows, size_t d);
     void opSwigluPacked(void *out, const void *gate_up, size_t rows, size_t di);
     void opArgmax(int64_t *idx, const void *vals, size_t rows, size_t n);
+    void checkKernels();
     void copyToDevice(void *dst, const void *src, size_t bytes);
     void copyToHost(void *dst, const void *src, size_t bytes);
 

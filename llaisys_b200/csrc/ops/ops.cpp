@@ -224,7 +224,11 @@ void embedding(tensor_t out, tensor_t index, tensor_t weight) {
 }
 
 // out [M, N] = in [M, K] . weight [N, K]^T + bias [N]; bias may be null (reference: README.md:179-196)
-void linear(tensor_t out, tensor_t in, tensor_t weight, tensor_t bias) {
+void linear(tensor_t out, tensor_t in, tensor_t weight, tensor_t bias) { linear_ex(out, in, weight, bias, false); }
+
+// accumulate: out += in . weight^T (+ bias), the sum rounded once -- a decoder block's residual add folded into its
+// projection. No counterpart in the reference.
+void linear_ex(tensor_t out, tensor_t in, tensor_t weight, tensor_t bias, bool accumulate) {
     CHECK_SAME_DEVICE(out, in, weight);
     CHECK_SAME_DTYPE(out->dtype(), in->dtype(), weight->dtype());
     CHECK_ARGUMENT(out->ndim() == 2 && in->ndim() == 2 && weight->ndim() == 2, "Linear: tensors must be 2-D");
@@ -239,8 +243,8 @@ void linear(tensor_t out, tensor_t in, tensor_t weight, tensor_t bias) {
         ASSERT(bias->isContiguous(), "Linear: bias must be contiguous.");
         bias_ptr = bias->data();
     }
-    LLAISYS_ON_DEVICE(out, cpu::linear(out->dtype(), out->data(), in->data(), weight->data(), bias_ptr, m, n, k),
-                      kernels::linear(stream, out->dtype(), out->data(), in->data(), weight->data(), bias_ptr, m, n, k));
+    LLAISYS_ON_DEVICE(out, cpu::linear(out->dtype(), out->data(), in->data(), weight->data(), bias_ptr, m, n, k, accumulate),
+                      kernels::linear(stream, out->dtype(), out->data(), in->data(), weight->data(), bias_ptr, m, n, k, accumulate));
 }
 
 // per row: out = weight * in / sqrt(mean(in^2) + eps) (reference: README.md:198-213)

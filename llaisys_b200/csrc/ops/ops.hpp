@@ -9,6 +9,7 @@ void add(tensor_t c, tensor_t a, tensor_t b);
 void argmax(tensor_t max_idx, tensor_t max_val, tensor_t vals);
 void embedding(tensor_t out, tensor_t index, tensor_t weight);
 void linear(tensor_t out, tensor_t in, tensor_t weight, tensor_t bias); // bias may be null
+void linear_ex(tensor_t out, tensor_t in, tensor_t weight, tensor_t bias, bool accumulate); // accumulate: out += ...
 void rearrange(tensor_t out, tensor_t in);
 void rms_norm(tensor_t out, tensor_t in, tensor_t weight, float eps);
 void rope(tensor_t out, tensor_t in, tensor_t pos_ids, float theta);

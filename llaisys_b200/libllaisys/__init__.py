@@ -138,6 +138,7 @@ PROTOTYPES: dict[str, tuple] = {
     "llaisysArgmax": (None, [_T, _T, _T]),
     "llaisysEmbedding": (None, [_T, _T, _T]),
     "llaisysLinear": (None, [_T, _T, _T, _T]),
+    "llaisysLinearAccumulate": (None, [_T, _T, _T]),
     "llaisysRearrange": (None, [_T, _T]),
     "llaisysRmsNorm": (None, [_T, _T, _T, c_float]),
     "llaisysROPE": (None, [_T, _T, _T, c_float]),

@@ -29,6 +29,11 @@ class Ops:
         LIB_LLAISYS.llaisysLinear(_h(out), _h(inp), _h(weight), _h(bias))
 
     @staticmethod
+    def linear_accumulate(out: Tensor, inp: Tensor, weight: Tensor) -> None:
+        """out += inp . weight^T (new: the residual add of a decoder block folded into its projection)."""
+        LIB_LLAISYS.llaisysLinearAccumulate(_h(out), _h(inp), _h(weight))
+
+    @staticmethod
     def rearrange(out: Tensor, inp: Tensor) -> None:
         LIB_LLAISYS.llaisysRearrange(_h(out), _h(inp))
 
