@@ -134,6 +134,10 @@ __global__ void paged_rope_append_kernel(unsigned char *__restrict__ k_pool, uns
                                          const int32_t *__restrict__ positions, CopyGeom g, int32_t n_rows, int32_t nh,
                                          int32_t d, float theta, int32_t max_blocks, int32_t *error_flag) {
     using P = Pack<T, VEC>;
+    // Under a programmatic launch: let the next kernel (the decode attention) start its set-up, then wait for the
+    // projection that produced qkv.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int32_t half = d / 2;
     const int32_t vec_per_head = half / VEC;
     const int32_t heads = nh + 2 * g.nkvh;
@@ -214,14 +218,24 @@ void launch_rope_append(cudaStream_t s, const KVView &kv, void *q_out, const voi
     const int block = 256, grid = grid_for(threads, block);
     auto *kp = static_cast<unsigned char *>(kv.k_base);
     auto *vp = static_cast<unsigned char *>(kv.v_base);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(unsigned(block));
+    cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = kv.overlap_launch ? 1 : 0;
+    T *qo = static_cast<T *>(q_out);
+    const T *qi = static_cast<const T *>(qkv), *bi = static_cast<const T *>(bias);
+    const int32_t *table = kv.block_table;
     if (wide) {
-        paged_rope_append_kernel<T, kVec><<<grid, block, 0, s>>>(kp, vp, static_cast<T *>(q_out), static_cast<const T *>(qkv),
-                                                                 static_cast<const T *>(bias), kv.block_table, seq_ids,
-                                                                 positions, g, n_rows, nh, d, theta, max_blocks, error_flag);
+        LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_rope_append_kernel<T, kVec>, kp, vp, qo, qi, bi, table, seq_ids,
+                                              positions, g, n_rows, nh, d, theta, max_blocks, error_flag));
     } else {
-        paged_rope_append_kernel<T, 1><<<grid, block, 0, s>>>(kp, vp, static_cast<T *>(q_out), static_cast<const T *>(qkv),
-                                                              static_cast<const T *>(bias), kv.block_table, seq_ids, positions,
-                                                              g, n_rows, nh, d, theta, max_blocks, error_flag);
+        LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_rope_append_kernel<T, 1>, kp, vp, qo, qi, bi, table, seq_ids,
+                                              positions, g, n_rows, nh, d, theta, max_blocks, error_flag));
     }
 }
 

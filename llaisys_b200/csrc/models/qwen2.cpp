@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 
@@ -133,6 +134,9 @@ void Qwen2::configureCache(size_t max_seqs, size_t max_tokens) {
     cfg.max_pages_per_seq = (max_tokens + kPageSize - 1) / kPageSize;
     cfg.num_pages = cfg.max_seqs * cfg.max_pages_per_seq;
     _cache = std::make_unique<kv::PagedKV>(cfg);
+    // [bias + rope + append] -> decode attention run as a programmatic pair: the attention kernel's set-up and its copies
+    // of older pages overlap the append (which writes each sequence's last page only, as the overlap contract asks)
+    _cache->setLaunchOverlap(_on_gpu && std::getenv("LLAISYS_MODEL_NO_OVERLAP") == nullptr);
     _max_tokens_per_seq = cfg.max_pages_per_seq * kPageSize;
     _seq_len.assign(max_seqs, kNotLive);
     _implicit_seq = -1;
