@@ -76,6 +76,27 @@ LLAISYS_API int64_t llaisysPagedKVSeqNumPages(llaisysPagedKV_t kv, int32_t seq);
 /* Copies up to `cap` block-table entries of the sequence into pages_out. */
 LLAISYS_API int llaisysPagedKVSeqPages(llaisysPagedKV_t kv, int32_t seq, int32_t *pages_out, size_t cap);
 
+/* ---- prefix sharing (block manager, host only) -------------------------------------------- */
+/* Pages are reference-counted. A sequence's whole pages can be published under the chain of their token ids and found
+ * again by later sequences that start with the same tokens (the KV-cache pool with prefix matching the reference's
+ * README.md:412 and :424 ask for); shared pages are never written again, because a sequence only appends behind the
+ * tokens it holds. When the last holder of a published page goes, the page stays findable ("cached") until the pool
+ * needs it; cached pages count as free and the one released longest ago is reused first. */
+
+/* Registers the full pages of the sequence under tokens[0, n_tokens): the ids of the tokens whose K/V it holds. */
+LLAISYS_API int llaisysPagedKVSeqPublish(llaisysPagedKV_t kv, int32_t seq, const int64_t *tokens, size_t n_tokens);
+/* Attaches to an EMPTY sequence the published pages matching the longest whole-page prefix of tokens[0, n_tokens);
+ * *matched_out = tokens covered (a multiple of the page size). The caller appends from position *matched_out. */
+LLAISYS_API int llaisysPagedKVSeqMatchPrefix(llaisysPagedKV_t kv, int32_t seq, const int64_t *tokens, size_t n_tokens,
+                                             size_t *matched_out);
+/* New sequence sharing the parent's first n_tokens: whole pages by reference, a partial last page by copy (every
+ * layer; the copies are queued on the calling thread's stream behind the work already queued there). */
+LLAISYS_API int llaisysPagedKVSeqFork(llaisysPagedKV_t kv, int32_t parent, size_t n_tokens, int32_t *child_out);
+/* Number of sequences holding the page (0 = free or cached), -1 for a bad handle or page. */
+LLAISYS_API int llaisysPagedKVPageRefCount(llaisysPagedKV_t kv, int32_t page);
+/* Cached pages: released by every holder, still findable by prefix (included in llaisysPagedKVNumFreePages). */
+LLAISYS_API size_t llaisysPagedKVNumCachedPages(llaisysPagedKV_t kv);
+
 /* ---- device-side views ----------------------------------------------------------------- */
 
 LLAISYS_API void *llaisysPagedKVPoolData(llaisysPagedKV_t kv, size_t layer); /* pool[layer]          */

@@ -205,6 +205,30 @@ int llaisysLseMerge(llaisysDeviceType_t device_type, int device_id, void *out, l
     });
 }
 
+int llaisysPagedKVSeqPublish(llaisysPagedKV_t kv, int32_t seq, const int64_t *tokens, size_t n_tokens) {
+    KV_OR_FAIL(kv);
+    return guarded([&] { kv->impl.seqPublish(seq, tokens, n_tokens); });
+}
+int llaisysPagedKVSeqMatchPrefix(llaisysPagedKV_t kv, int32_t seq, const int64_t *tokens, size_t n_tokens,
+                                 size_t *matched_out) {
+    KV_OR_FAIL(kv);
+    if (matched_out == nullptr) {
+        llaisys::kernels::set_last_error("paged KV match: matched_out is null");
+        return LLAISYS_E_INVALID;
+    }
+    return guarded([&] { *matched_out = kv->impl.seqMatchPrefix(seq, tokens, n_tokens); });
+}
+int llaisysPagedKVSeqFork(llaisysPagedKV_t kv, int32_t parent, size_t n_tokens, int32_t *child_out) {
+    KV_OR_FAIL(kv);
+    if (child_out == nullptr) {
+        llaisys::kernels::set_last_error("paged KV fork: child_out is null");
+        return LLAISYS_E_INVALID;
+    }
+    return guarded([&] { *child_out = kv->impl.seqFork(parent, n_tokens); });
+}
+int llaisysPagedKVPageRefCount(llaisysPagedKV_t kv, int32_t page) { return kv ? kv->impl.pageRefCount(page) : -1; }
+size_t llaisysPagedKVNumCachedPages(llaisysPagedKV_t kv) { return kv ? kv->impl.numCachedPages() : 0; }
+
 int llaisysPagedKVAppendDev(llaisysPagedKV_t kv, size_t layer, const void *k_rows, const void *v_rows,
                             const int32_t *seq_ids_dev, const int32_t *positions_dev, size_t n_rows,
                             llaisysStream_t stream) {

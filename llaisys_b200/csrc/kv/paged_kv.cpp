@@ -87,7 +87,9 @@ PagedKV::PagedKV(const PagedKVConfig &cfg) : _cfg(cfg) {
         std::memset(_error_dev->memory(), 0, _error_dev->size());
     }
 
-    _page_owner.assign(cfg.num_pages, -1);
+    _page_ref.assign(cfg.num_pages, 0);
+    _page_key.assign(cfg.num_pages, 0);
+    _lru_pos.assign(cfg.num_pages, _lru.end());
     _free_pages.resize(cfg.num_pages);
     for (size_t i = 0; i < cfg.num_pages; ++i) {
         _free_pages[i] = int32_t(cfg.num_pages - 1 - i); // page 0 is handed out first
@@ -129,6 +131,8 @@ int32_t PagedKV::seqAdd() {
     Seq &s = _seqs[id];
     s.live = true;
     s.n_pages = 0;
+    s.n_chained = 0;
+    s.chain_key = 0;
     ++_n_live;
     return id;
 }
@@ -142,14 +146,13 @@ void PagedKV::seqReserve(int32_t seq, size_t n_tokens) {
     KV_REQUIRE(want_pages <= _cfg.max_pages_per_seq, LLAISYS_E_INVALID, "paged KV: ", n_tokens,
                " tokens need more than max_pages_per_seq = ", _cfg.max_pages_per_seq, " pages");
     const size_t extra = want_pages - size_t(s.n_pages);
-    KV_REQUIRE(extra <= _free_pages.size(), LLAISYS_E_NO_PAGES, "paged KV: need ", extra, " more pages, ",
-               _free_pages.size(), " free");
+    KV_REQUIRE(extra <= numFreePages(), LLAISYS_E_NO_PAGES, "paged KV: need ", extra, " more pages, ", numFreePages(),
+               " free");
     int32_t *row = _table_host.data() + size_t(seq) * _cfg.max_pages_per_seq;
     const int32_t first = s.n_pages;
     for (size_t i = 0; i < extra; ++i) {
-        const int32_t page = _free_pages.back();
-        _free_pages.pop_back();
-        _page_owner[page] = seq;
+        const int32_t page = takePage();
+        _page_ref[page] = 1;
         row[s.n_pages++] = page;
     }
     markDirty(seq, first, s.n_pages);
@@ -163,26 +166,26 @@ void PagedKV::seqAssignPages(int32_t seq, const int32_t *pages, size_t n_pages) 
     KV_REQUIRE(pages != nullptr, LLAISYS_E_INVALID, "paged KV: pages is null");
     KV_REQUIRE(size_t(s.n_pages) + n_pages <= _cfg.max_pages_per_seq, LLAISYS_E_INVALID,
                "paged KV: sequence would exceed max_pages_per_seq = ", _cfg.max_pages_per_seq);
-    // Validate everything before changing anything (all-or-nothing). A provisional owner mark catches a page
+    // Validate everything before changing anything (all-or-nothing). A provisional reference mark catches a page
     // named twice in the same request; marks are rolled back if a later entry fails.
     for (size_t i = 0; i < n_pages; ++i) {
         const int32_t p = pages[i];
         const bool in_range = p >= 0 && size_t(p) < _cfg.num_pages;
-        if (!in_range || _page_owner[p] != -1) {
+        if (!in_range || _page_ref[p] != 0) {
             for (size_t k = 0; k < i; ++k) {
-                _page_owner[pages[k]] = -1;
+                _page_ref[pages[k]] = 0;
             }
             KV_REQUIRE(in_range, LLAISYS_E_INVALID, "paged KV: page ", p, " is out of range");
             fail(LLAISYS_E_NO_PAGES, "paged KV: page ", p, " is not free");
         }
-        _page_owner[p] = -2;
+        _page_ref[p] = -1;
     }
     for (size_t i = 0; i < n_pages; ++i) {
-        _page_owner[pages[i]] = seq;
+        unpublish(pages[i]); // a cached page named explicitly stops being findable: its contents are about to change
+        _page_ref[pages[i]] = 1;
     }
     // remove the claimed pages from the free stack in one pass
-    _free_pages.erase(std::remove_if(_free_pages.begin(), _free_pages.end(),
-                                     [&](int32_t p) { return _page_owner[p] != -1; }),
+    _free_pages.erase(std::remove_if(_free_pages.begin(), _free_pages.end(), [&](int32_t p) { return _page_ref[p] != 0; }),
                       _free_pages.end());
     int32_t *row = _table_host.data() + size_t(seq) * _cfg.max_pages_per_seq;
     const int32_t first = s.n_pages;
@@ -196,13 +199,168 @@ void PagedKV::seqFree(int32_t seq) {
     Seq &s = liveSeq(seq);
     const int32_t *row = _table_host.data() + size_t(seq) * _cfg.max_pages_per_seq;
     for (int32_t i = s.n_pages; i-- > 0;) { // reverse, so a re-reserve pops them in the original order
-        _page_owner[row[i]] = -1;
-        _free_pages.push_back(row[i]);
+        releasePage(row[i]);
     }
     s.live = false;
     s.n_pages = 0;
     --_n_live;
     _free_seq_ids.push_back(seq);
+}
+
+// ---- page life cycle and prefix sharing ---------------------------------------------------------------------------
+
+int32_t PagedKV::pageRefCount(int32_t page) const {
+    if (page < 0 || size_t(page) >= _cfg.num_pages) {
+        return -1;
+    }
+    return _page_ref[page];
+}
+
+void PagedKV::unpublish(int32_t page) {
+    if (_page_key[page] != 0) {
+        _prefix_index.erase(_page_key[page]);
+        _page_key[page] = 0;
+    }
+    if (_lru_pos[page] != _lru.end()) {
+        _lru.erase(_lru_pos[page]);
+        _lru_pos[page] = _lru.end();
+        if (_page_ref[page] == 0) {
+            _free_pages.push_back(page);
+        }
+    }
+}
+
+int32_t PagedKV::takePage() {
+    if (!_free_pages.empty()) {
+        const int32_t page = _free_pages.back();
+        _free_pages.pop_back();
+        return page;
+    }
+    KV_REQUIRE(!_lru.empty(), LLAISYS_E_NO_PAGES, "paged KV: no free page");
+    const int32_t page = _lru.front(); // the cached page released longest ago
+    unpublish(page);                   // moves it to the free stack
+    _free_pages.pop_back();
+    return page;
+}
+
+void PagedKV::releasePage(int32_t page) {
+    if (--_page_ref[page] > 0) {
+        return;
+    }
+    if (_page_key[page] != 0) {
+        _lru.push_back(page);
+        _lru_pos[page] = std::prev(_lru.end());
+    } else {
+        _free_pages.push_back(page);
+    }
+}
+
+// 64-bit chain key: the parent's key and the page's token ids through a multiply-xorshift mix; never 0.
+uint64_t PagedKV::chainKey(uint64_t parent, const int64_t *tokens) const {
+    uint64_t h = parent ^ 0x9e3779b97f4a7c15ull;
+    for (size_t i = 0; i < _cfg.page_size; ++i) {
+        h ^= uint64_t(tokens[i]) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        h *= 0xff51afd7ed558ccdull;
+        h ^= h >> 33;
+    }
+    return h == 0 ? 1 : h;
+}
+
+void PagedKV::seqPublish(int32_t seq, const int64_t *tokens, size_t n_tokens) {
+    Seq &s = liveSeq(seq);
+    KV_REQUIRE(n_tokens <= size_t(s.n_pages) * _cfg.page_size, LLAISYS_E_INVALID, "paged KV publish: ", n_tokens,
+               " tokens exceed the sequence's pages");
+    const size_t full = n_tokens / _cfg.page_size;
+    if (full <= size_t(s.n_chained)) {
+        return;
+    }
+    KV_REQUIRE(tokens != nullptr, LLAISYS_E_INVALID, "paged KV publish: tokens is null");
+    const int32_t *row = _table_host.data() + size_t(seq) * _cfg.max_pages_per_seq;
+    uint64_t parent = s.chain_key;
+    for (size_t i = size_t(s.n_chained); i < full; ++i) {
+        const int64_t *chunk = tokens + i * _cfg.page_size;
+        const uint64_t key = chainKey(parent, chunk);
+        const int32_t page = row[i];
+        if (_page_key[page] == 0 && _prefix_index.find(key) == _prefix_index.end()) {
+            _prefix_index.emplace(key, PrefixEntry{page, parent, std::vector<int64_t>(chunk, chunk + _cfg.page_size)});
+            _page_key[page] = key;
+        }
+        // else: this page is already published, or another page already holds the same prefix -- nothing to add
+        parent = key;
+    }
+    s.n_chained = int32_t(full);
+    s.chain_key = parent;
+}
+
+size_t PagedKV::seqMatchPrefix(int32_t seq, const int64_t *tokens, size_t n_tokens) {
+    Seq &s = liveSeq(seq);
+    KV_REQUIRE(s.n_pages == 0, LLAISYS_E_INVALID, "paged KV match: the sequence already owns pages");
+    size_t full = n_tokens / _cfg.page_size;
+    full = std::min(full, _cfg.max_pages_per_seq);
+    if (full == 0) {
+        return 0;
+    }
+    KV_REQUIRE(tokens != nullptr, LLAISYS_E_INVALID, "paged KV match: tokens is null");
+    int32_t *row = _table_host.data() + size_t(seq) * _cfg.max_pages_per_seq;
+    uint64_t parent = 0;
+    for (size_t i = 0; i < full; ++i) {
+        const int64_t *chunk = tokens + i * _cfg.page_size;
+        const uint64_t key = chainKey(parent, chunk);
+        auto it = _prefix_index.find(key);
+        if (it == _prefix_index.end() || it->second.parent != parent ||
+            !std::equal(chunk, chunk + _cfg.page_size, it->second.tokens.begin())) {
+            break;
+        }
+        const int32_t page = it->second.page;
+        if (_page_ref[page]++ == 0) { // cached: back in use
+            _lru.erase(_lru_pos[page]);
+            _lru_pos[page] = _lru.end();
+        }
+        row[s.n_pages++] = page;
+        parent = key;
+    }
+    if (s.n_pages > 0) {
+        markDirty(seq, 0, s.n_pages);
+    }
+    s.n_chained = s.n_pages;
+    s.chain_key = parent;
+    return size_t(s.n_pages) * _cfg.page_size;
+}
+
+int32_t PagedKV::seqFork(int32_t parent, size_t n_tokens) {
+    const Seq &ps = liveSeq(parent);
+    KV_REQUIRE(n_tokens <= size_t(ps.n_pages) * _cfg.page_size, LLAISYS_E_INVALID, "paged KV fork: ", n_tokens,
+               " tokens exceed the parent's pages");
+    const size_t full = n_tokens / _cfg.page_size, rest = n_tokens % _cfg.page_size;
+    KV_REQUIRE(rest == 0 || numFreePages() >= 1, LLAISYS_E_NO_PAGES, "paged KV fork: no page for the copy of the last page");
+    const int32_t child = seqAdd();
+    Seq &cs = _seqs[child];
+    const int32_t *prow = _table_host.data() + size_t(parent) * _cfg.max_pages_per_seq;
+    int32_t *crow = _table_host.data() + size_t(child) * _cfg.max_pages_per_seq;
+    for (size_t i = 0; i < full; ++i) {
+        ++_page_ref[prow[i]];
+        crow[cs.n_pages++] = prow[i];
+    }
+    if (rest != 0) {
+        const int32_t src = prow[full], dst = takePage();
+        _page_ref[dst] = 1;
+        crow[cs.n_pages++] = dst;
+        const size_t page_bytes = _page_elems * _elem;
+        auto &rt = enter();
+        for (size_t l = 0; l < _cfg.nlayer; ++l) {
+            std::byte *base = _pool->memory() + l * _layer_bytes;
+            if (onDevice()) {
+                rt.api()->memcpy_async(base + size_t(dst) * page_bytes, base + size_t(src) * page_bytes, page_bytes,
+                                       LLAISYS_MEMCPY_D2D, rt.stream());
+            } else {
+                std::memcpy(base + size_t(dst) * page_bytes, base + size_t(src) * page_bytes, page_bytes);
+            }
+        }
+    }
+    if (cs.n_pages > 0) {
+        markDirty(child, 0, cs.n_pages);
+    }
+    return child;
 }
 
 int64_t PagedKV::seqNumPages(int32_t seq) const {

@@ -9,8 +9,10 @@
 #include "../kernels/args.hpp"
 #include "../tensor/tensor.hpp"
 
+#include <list>
 #include <stdexcept>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 namespace llaisys::kv {
@@ -43,7 +45,24 @@ public:
     void seqReserve(int32_t seq, size_t n_tokens);
     void seqAssignPages(int32_t seq, const int32_t *pages, size_t n_pages);
     void seqFree(int32_t seq);
-    size_t numFreePages() const { return _free_pages.size(); }
+    // Pages a reserve can still get: never-used or released pages plus cached ones (released, but still findable by
+    // prefix; the least recently released is evicted first).
+    size_t numFreePages() const { return _free_pages.size() + _lru.size(); }
+    size_t numCachedPages() const { return _lru.size(); }
+    int32_t pageRefCount(int32_t page) const;
+
+    // ---- prefix sharing (host only, except the one-page copy of a fork) ----
+    // New sequence that shares the parent's first n_tokens: whole pages by reference, a partial last page by copy (all
+    // layers, queued on the calling thread's stream after everything already queued there).
+    int32_t seqFork(int32_t parent, size_t n_tokens);
+    // Registers the sequence's full pages under the chain of their token ids (tokens[0, n_tokens) are the ids of the
+    // tokens whose K/V the sequence holds), so that later sequences starting with the same tokens can find them.
+    // Incremental: pages hashed by an earlier call (or attached by a match) are not hashed again, so a caller may
+    // publish after every step; the tokens of those pages must be the ones given before.
+    void seqPublish(int32_t seq, const int64_t *tokens, size_t n_tokens);
+    // Attaches to an EMPTY sequence the published pages matching the longest whole-page prefix of tokens[0, n_tokens);
+    // -> number of tokens covered (a multiple of the page size).
+    size_t seqMatchPrefix(int32_t seq, const int64_t *tokens, size_t n_tokens);
     size_t numSeqs() const { return _n_live; }
     int64_t seqNumPages(int32_t seq) const;
     void seqPages(int32_t seq, int32_t *pages_out, size_t cap) const;
@@ -84,8 +103,21 @@ private:
         int32_t n_pages = 0;
         int32_t dirty_lo = 0, dirty_hi = 0; // table entries [lo, hi) not yet on the device
         bool queued_dirty = false;
+        // prefix chain: pages [0, n_chained) have been hashed, chain_key is the key of page n_chained - 1
+        int32_t n_chained = 0;
+        uint64_t chain_key = 0;
     };
 
+    struct PrefixEntry {
+        int32_t page;
+        uint64_t parent; // key of the page before it in the chain (0 for the first)
+        std::vector<int64_t> tokens; // the page's token ids, to tell a match from a hash collision
+    };
+
+    int32_t takePage();           // from the free stack, else evict the oldest cached page
+    void releasePage(int32_t page); // one reference less; at zero the page becomes cached (if published) or free
+    void unpublish(int32_t page);
+    uint64_t chainKey(uint64_t parent, const int64_t *tokens) const;
     Seq &liveSeq(int32_t seq);
     const Seq &liveSeq(int32_t seq) const;
     void markDirty(int32_t seq, int32_t lo, int32_t hi);
@@ -101,7 +133,11 @@ private:
 
     // block manager
     std::vector<int32_t> _free_pages; // stack; back() is handed out next
-    std::vector<int32_t> _page_owner; // sequence id, or -1 when free
+    std::vector<int32_t> _page_ref;   // sequences holding the page; 0 = free or cached
+    std::vector<uint64_t> _page_key;  // prefix-chain key the page is published under, 0 = not published
+    std::list<int32_t> _lru;          // cached pages (ref 0, published), least recently released first
+    std::vector<std::list<int32_t>::iterator> _lru_pos;
+    std::unordered_map<uint64_t, PrefixEntry> _prefix_index;
     std::vector<Seq> _seqs;
     std::vector<int32_t> _free_seq_ids;
     std::vector<int32_t> _table_host; // [max_seqs][max_pages_per_seq]

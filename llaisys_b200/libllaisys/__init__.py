@@ -175,6 +175,11 @@ PROTOTYPES: dict[str, tuple] = {
                                 c_size_t, c_size_t]),
     "llaisysPagedKVAppendDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                         llaisysStream_t]),
+    "llaisysPagedKVSeqPublish": (c_int, [_KV, c_int32, POINTER(c_int64), c_size_t]),
+    "llaisysPagedKVSeqMatchPrefix": (c_int, [_KV, c_int32, POINTER(c_int64), c_size_t, POINTER(c_size_t)]),
+    "llaisysPagedKVSeqFork": (c_int, [_KV, c_int32, c_size_t, _I32P]),
+    "llaisysPagedKVPageRefCount": (c_int, [_KV, c_int32]),
+    "llaisysPagedKVNumCachedPages": (c_size_t, [_KV]),
     "llaisysPagedKVRopeAppendDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                             c_size_t, c_float, llaisysStream_t]),
     "llaisysPagedAttentionDecodeDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,

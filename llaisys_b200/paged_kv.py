@@ -80,6 +80,35 @@ class PagedKVCache:
     def free_seq(self, seq: int) -> None:
         _check(LIB_LLAISYS.llaisysPagedKVSeqFree(self._kv, seq))
 
+    # ---- prefix sharing ----
+
+    def publish(self, seq: int, tokens: Sequence[int]) -> None:
+        """Makes the sequence's full pages findable under the ids of the tokens they hold."""
+        arr = np.ascontiguousarray(tokens, dtype=np.int64)
+        _check(LIB_LLAISYS.llaisysPagedKVSeqPublish(self._kv, seq, arr.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)),
+                                                    arr.size))
+
+    def match_prefix(self, seq: int, tokens: Sequence[int]) -> int:
+        """Attaches published pages matching the longest whole-page prefix of `tokens` to the empty sequence `seq`;
+        -> tokens covered."""
+        arr = np.ascontiguousarray(tokens, dtype=np.int64)
+        matched = ctypes.c_size_t(0)
+        _check(LIB_LLAISYS.llaisysPagedKVSeqMatchPrefix(self._kv, seq, arr.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)),
+                                                        arr.size, ctypes.byref(matched)))
+        return int(matched.value)
+
+    def fork(self, parent: int, n_tokens: int) -> int:
+        """New sequence sharing the parent's first n_tokens (whole pages by reference, a partial last page copied)."""
+        child = ctypes.c_int32(-1)
+        _check(LIB_LLAISYS.llaisysPagedKVSeqFork(self._kv, parent, n_tokens, ctypes.byref(child)))
+        return child.value
+
+    def page_ref_count(self, page: int) -> int:
+        return int(LIB_LLAISYS.llaisysPagedKVPageRefCount(self._kv, page))
+
+    def num_cached_pages(self) -> int:
+        return int(LIB_LLAISYS.llaisysPagedKVNumCachedPages(self._kv))
+
     def num_free_pages(self) -> int:
         return int(LIB_LLAISYS.llaisysPagedKVNumFreePages(self._kv))
 
