@@ -60,6 +60,11 @@ LLAISYS_API int64_t llaisysQwen2ModelInfer(struct LlaisysQwen2Model *model, int6
  * called before the first batched call; llaisysQwen2ModelInfer sizes a one-sequence cache of meta.maxseq by itself. */
 LLAISYS_API int llaisysQwen2ModelConfigureCache(struct LlaisysQwen2Model *model, size_t max_seqs, size_t max_tokens);
 LLAISYS_API int llaisysQwen2ModelSeqAdd(struct LlaisysQwen2Model *model, int32_t *seq_out);
+/* As SeqAdd, but the new sequence starts from cached K/V: the model publishes the full pages of every sequence it runs
+ * under their token ids, and this call attaches the pages matching the longest whole-page prefix of tokens[0, n) that
+ * still leaves one token to run. *matched_out = tokens covered; feed tokens[*matched_out, n) to the first Step. */
+LLAISYS_API int llaisysQwen2ModelSeqAddWithPrefix(struct LlaisysQwen2Model *model, const int64_t *tokens, size_t n,
+                                                  int32_t *seq_out, size_t *matched_out);
 LLAISYS_API int llaisysQwen2ModelSeqFree(struct LlaisysQwen2Model *model, int32_t seq);
 /* Forgets the implicit sequence of llaisysQwen2ModelInfer. */
 LLAISYS_API int llaisysQwen2ModelReset(struct LlaisysQwen2Model *model);

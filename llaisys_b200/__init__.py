@@ -12,8 +12,9 @@ from .tensor import Tensor
 from .ops import Ops
 from .paged_kv import LlaisysError, PagedKVCache, decode_no_alloc, lse_merge
 from . import models
+from .serving import Engine
 
 __all__ = [
-    "RuntimeAPI", "DeviceType", "DataType", "MemcpyKind", "Stream", "Tensor", "Ops", "models",
+    "RuntimeAPI", "DeviceType", "DataType", "MemcpyKind", "Stream", "Tensor", "Ops", "models", "Engine",
     "PagedKVCache", "lse_merge", "decode_no_alloc", "LlaisysError", "Status", "context_stream", "set_context_runtime",
 ]

@@ -7,10 +7,7 @@
 
 #include <iostream>
 
-struct LlaisysQwen2Model {
-    llaisys::models::Qwen2 impl;
-    LlaisysQwen2Model(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int device_id) : impl(meta, device, device_id) {}
-};
+#include "qwen2_handle.hpp"
 
 namespace llaisys::kernels {
 void set_last_error(const std::string &msg);
@@ -74,6 +71,13 @@ int llaisysQwen2ModelSeqAdd(LlaisysQwen2Model *model, int32_t *seq_out) {
         return null_model();
     }
     return guarded([&] { *seq_out = model->impl.seqAdd(); });
+}
+int llaisysQwen2ModelSeqAddWithPrefix(LlaisysQwen2Model *model, const int64_t *tokens, size_t n, int32_t *seq_out,
+                                      size_t *matched_out) {
+    if (model == nullptr || seq_out == nullptr || matched_out == nullptr) {
+        return null_model();
+    }
+    return guarded([&] { *seq_out = model->impl.seqAddWithPrefix(tokens, n, matched_out); });
 }
 int llaisysQwen2ModelSeqFree(LlaisysQwen2Model *model, int32_t seq) {
     return model ? guarded([&] { model->impl.seqFree(seq); }) : null_model();

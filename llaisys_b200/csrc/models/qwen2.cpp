@@ -85,6 +85,9 @@ Qwen2::Qwen2(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int devic
 }
 
 Qwen2::~Qwen2() {
+    for (ModelObserver *o : std::vector<ModelObserver *>(_observers)) {
+        o->modelDestroyed();
+    }
     for (llaisysTensor_t h : _all_weights) {
         delete h;
     }
@@ -139,6 +142,7 @@ void Qwen2::configureCache(size_t max_seqs, size_t max_tokens) {
     _cache->setLaunchOverlap(_on_gpu && std::getenv("LLAISYS_MODEL_NO_OVERLAP") == nullptr);
     _max_tokens_per_seq = cfg.max_pages_per_seq * kPageSize;
     _seq_len.assign(max_seqs, kNotLive);
+    _seq_tokens.assign(max_seqs, {});
     _implicit_seq = -1;
 }
 
@@ -155,13 +159,52 @@ int32_t Qwen2::seqAdd() {
     }
     const int32_t s = _cache->seqAdd();
     _seq_len[s] = 0;
+    _seq_tokens[s].clear();
     return s;
+}
+
+int32_t Qwen2::seqAddWithPrefix(const int64_t *tokens, size_t n, size_t *matched) {
+    const int32_t s = seqAdd();
+    size_t got = 0;
+    if (n > 1 && tokens != nullptr) {
+        try {
+            got = _cache->seqMatchPrefix(s, tokens, n - 1); // whole pages inside the first n - 1 tokens
+        } catch (...) {
+            seqFree(s);
+            throw;
+        }
+        _seq_tokens[s].assign(tokens, tokens + got);
+    }
+    _seq_len[s] = got;
+    if (matched != nullptr) {
+        *matched = got;
+    }
+    return s;
+}
+
+void Qwen2::seqReserve(int32_t seq, size_t n_tokens) {
+    seqLen(seq);
+    if (n_tokens > _max_tokens_per_seq) {
+        fail(LLAISYS_E_INVALID, "qwen2: sequence would exceed the configured maximum length");
+    }
+    _cache->seqReserve(seq, n_tokens);
+}
+
+// The sequence now holds K/V for n more tokens: remember their ids and publish the pages they completed.
+void Qwen2::recordTokens(int32_t seq, const int64_t *tokens, size_t n) {
+    std::vector<int64_t> &held = _seq_tokens[seq];
+    const size_t before = held.size() / kPageSize;
+    held.insert(held.end(), tokens, tokens + n);
+    if (held.size() / kPageSize != before) {
+        _cache->seqPublish(seq, held.data(), held.size());
+    }
 }
 
 void Qwen2::seqFree(int32_t seq) {
     seqLen(seq);
     _cache->seqFree(seq);
     _seq_len[seq] = kNotLive;
+    _seq_tokens[seq].clear();
     if (seq == _implicit_seq) {
         _implicit_seq = -1;
     }
@@ -397,8 +440,10 @@ void Qwen2::step(const int32_t *seq_ids, const int32_t *n_tokens, size_t n_seqs,
     _cache->flush();
     forward(a, T, n_seqs, max_q, max_kv, decode_only);
     copyToHost(next_out, a.next, n_seqs * sizeof(int64_t));
-    for (size_t i = 0; i < n_seqs; ++i) {
+    for (size_t i = 0, at = 0; i < n_seqs; ++i) {
         seqLen(seq_ids[i]) += size_t(n_tokens[i]);
+        recordTokens(seq_ids[i], tokens + at, size_t(n_tokens[i]));
+        at += size_t(n_tokens[i]);
     }
     checkKernels();
 }
@@ -510,8 +555,14 @@ void Qwen2::decodeLoop(const int32_t *seq_ids, size_t n_seqs, const int64_t *fir
         _last_loop_ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count() / double(n_steps);
     }
     copyToHost(tokens_out, log_dev, n_steps * n_seqs * sizeof(int64_t));
+    std::vector<int64_t> fed(n_steps);
     for (size_t i = 0; i < n_seqs; ++i) {
         seqLen(seq_ids[i]) += n_steps;
+        fed[0] = first_tokens[i]; // step s consumed the token step s - 1 produced
+        for (size_t st = 1; st < n_steps; ++st) {
+            fed[st] = tokens_out[(st - 1) * n_seqs + i];
+        }
+        recordTokens(seq_ids[i], fed.data(), n_steps);
     }
     checkKernels();
 }

@@ -17,8 +17,27 @@
 
 namespace llaisys::models {
 
+// Objects that borrow a model (a serving engine) hear about its destruction instead of touching freed memory when the
+// owner destroys the two in the wrong order.
+struct ModelObserver {
+    virtual void modelDestroyed() = 0;
+
+protected:
+    ~ModelObserver() = default;
+};
+
 class Qwen2 {
 public:
+    void addObserver(ModelObserver *o) { _observers.push_back(o); }
+    void removeObserver(ModelObserver *o) {
+        for (size_t i = 0; i < _observers.size(); ++i) {
+            if (_observers[i] == o) {
+                _observers.erase(_observers.begin() + ptrdiff_t(i));
+                return;
+            }
+        }
+    }
+
     Qwen2(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int device_id);
     ~Qwen2();
     Qwen2(const Qwen2 &) = delete;
@@ -29,6 +48,13 @@ public:
 
     void configureCache(size_t max_seqs, size_t max_tokens);
     int32_t seqAdd();
+    // New sequence that starts from the cached K/V of the longest published whole-page prefix of tokens[0, n) that leaves
+    // at least one token to run; *matched = tokens already covered (feed tokens[*matched, n) to step()).
+    int32_t seqAddWithPrefix(const int64_t *tokens, size_t n, size_t *matched);
+    void seqReserve(int32_t seq, size_t n_tokens); // pages for n_tokens now, so that later steps cannot run out
+    size_t seqLength(int32_t seq) { return seqLen(seq); }
+    size_t freePages() const { return _cache ? _cache->numFreePages() : 0; }
+    size_t maxTokensPerSeq() const { return _max_tokens_per_seq; }
     void seqFree(int32_t seq);
     void reset();
     int64_t infer(const int64_t *tokens, size_t n);
@@ -85,12 +111,15 @@ private:
     std::unique_ptr<kv::PagedKV> _cache;
     size_t _max_tokens_per_seq = 0;
     std::vector<size_t> _seq_len; // by sequence id; SIZE_MAX = not live
+    std::vector<std::vector<int64_t>> _seq_tokens; // ids of the tokens each sequence holds (keys of the prefix cache)
+    void recordTokens(int32_t seq, const int64_t *tokens, size_t n);
     int32_t _implicit_seq = -1;
 
     // workspace
     core::storage_t _x, _h, _qkv, _q, _attn, _gate_up, _act, _x_last, _logits, _meta_block, _argmax_scratch;
     size_t _ws_tokens = 0, _ws_seqs = 0, _meta_bytes = 0;
     std::vector<std::byte> _meta_host;
+    std::vector<ModelObserver *> _observers;
     size_t _last_n_seqs = 0;
     double _last_loop_ms = 0.0;
 };

@@ -110,6 +110,11 @@ class LlaisysQwen2Weights(Structure):
             "mlp_norm_w", "mlp_gate_w", "mlp_up_w", "mlp_down_w")]
 
 
+class LlaisysEngineEvent(Structure):
+    """struct LlaisysEngineEvent (include/llaisys/serving.h)."""
+    _fields_ = [("request", c_int64), ("token", c_int64), ("finished", c_int32), ("reserved", c_int32)]
+
+
 _MODEL = c_void_p
 
 PROTOTYPES: dict[str, tuple] = {
@@ -199,12 +204,22 @@ PROTOTYPES: dict[str, tuple] = {
     "llaisysQwen2ModelInfer": (c_int64, [_MODEL, POINTER(c_int64), c_size_t]),
     "llaisysQwen2ModelConfigureCache": (c_int, [_MODEL, c_size_t, c_size_t]),
     "llaisysQwen2ModelSeqAdd": (c_int, [_MODEL, _I32P]),
+    "llaisysQwen2ModelSeqAddWithPrefix": (c_int, [_MODEL, POINTER(c_int64), c_size_t, _I32P, POINTER(c_size_t)]),
     "llaisysQwen2ModelSeqFree": (c_int, [_MODEL, c_int32]),
     "llaisysQwen2ModelReset": (c_int, [_MODEL]),
     "llaisysQwen2ModelStep": (c_int, [_MODEL, _I32P, _I32P, c_size_t, POINTER(c_int64), POINTER(c_int64)]),
     "llaisysQwen2ModelDecodeLoop": (c_int, [_MODEL, _I32P, c_size_t, POINTER(c_int64), c_size_t, POINTER(c_int64)]),
     "llaisysQwen2ModelLastLogits": (c_int, [_MODEL, POINTER(c_float), c_size_t]),
     "llaisysQwen2ModelLastLoopMs": (c_double, [_MODEL]),
+    # include/llaisys/serving.h
+    "llaisysEngineCreate": (c_int, [POINTER(c_void_p), _MODEL, c_size_t, c_size_t, c_size_t]),
+    "llaisysEngineDestroy": (None, [c_void_p]),
+    "llaisysEngineSubmit": (c_int, [c_void_p, POINTER(c_int64), c_size_t, c_size_t, c_int64, POINTER(c_int64)]),
+    "llaisysEngineStep": (c_int, [c_void_p, POINTER(LlaisysEngineEvent), c_size_t, POINTER(c_size_t)]),
+    "llaisysEngineCancel": (c_int, [c_void_p, c_int64]),
+    "llaisysEngineNumWaiting": (c_size_t, [c_void_p]),
+    "llaisysEngineNumRunning": (c_size_t, [c_void_p]),
+    "llaisysEngineCounter": (c_size_t, [c_void_p, c_int]),
 }
 
 
@@ -239,5 +254,5 @@ LIB_LLAISYS = load_shared_library()
 __all__ = [
     "LIB_LLAISYS", "PROTOTYPES", "LlaisysRuntimeAPI", "llaisysStream_t", "llaisysTensor_t", "llaisysPagedKV_t",
     "llaisysDataType_t", "DataType", "llaisysDeviceType_t", "DeviceType", "llaisysMemcpyKind_t", "MemcpyKind",
-    "Status", "library_path", "LlaisysQwen2Meta", "LlaisysQwen2Weights",
+    "Status", "library_path", "LlaisysQwen2Meta", "LlaisysQwen2Weights", "LlaisysEngineEvent",
 ]

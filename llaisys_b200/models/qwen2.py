@@ -190,6 +190,15 @@ class Qwen2:
         _check(LIB_LLAISYS.llaisysQwen2ModelSeqAdd(self._model, ctypes.byref(seq)))
         return seq.value
 
+    def add_seq_with_prefix(self, tokens: Sequence[int]) -> tuple[int, int]:
+        """New sequence that reuses cached K/V of earlier sequences starting with the same tokens (whole pages, leaving
+        at least one token to run). -> (sequence id, tokens already covered); feed tokens[covered:] to step()."""
+        arr = np.ascontiguousarray(tokens, dtype=np.int64)
+        seq, matched = c_int32(-1), ctypes.c_size_t(0)
+        _check(LIB_LLAISYS.llaisysQwen2ModelSeqAddWithPrefix(self._model, arr.ctypes.data_as(ctypes.POINTER(c_int64)),
+                                                             arr.size, ctypes.byref(seq), ctypes.byref(matched)))
+        return seq.value, int(matched.value)
+
     def free_seq(self, seq: int) -> None:
         _check(LIB_LLAISYS.llaisysQwen2ModelSeqFree(self._model, seq))
 
