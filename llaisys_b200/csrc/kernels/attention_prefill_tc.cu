@@ -30,6 +30,7 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -317,26 +318,36 @@ __global__ void __launch_bounds__(kThreads, 2)
             mbar_arrive(bar(kBarSFree + buf)); // S[buf] may be overwritten by QK^T of block i + 2
             // Most blocks lie wholly below the diagonal: the whole warp then skips the mask (warp-uniform choice).
             const bool plain = __all_sync(0xffffffffu, n_ok >= kBlockN) && p.scale_log2 > 0.f;
-            float mx = -INFINITY;
+            // Row maximum as eight independent chains (a single chain of 64 dependent max operations would cost more than
+            // the exponentials that follow).
+            float mx8[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                mx8[u] = -INFINITY;
+            }
             if (plain) {
 #pragma unroll
                 for (int c = 0; c < kBlockN / 32; ++c) {
 #pragma unroll
                     for (int k = 0; k < 32; ++k) {
-                        mx = fmaxf(mx, __uint_as_float(sr[c][k]));
+                        mx8[k & 7] = fmaxf(mx8[k & 7], __uint_as_float(sr[c][k]));
                     }
                 }
-                mx *= p.scale_log2;
             } else {
 #pragma unroll
                 for (int c = 0; c < kBlockN / 32; ++c) {
 #pragma unroll
                     for (int k = 0; k < 32; ++k) {
                         if (c * 32 + k < n_ok) {
-                            mx = fmaxf(mx, __uint_as_float(sr[c][k]) * p.scale_log2);
+                            mx8[k & 7] = fmaxf(mx8[k & 7], __uint_as_float(sr[c][k]) * p.scale_log2);
                         }
                     }
                 }
+            }
+            float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
+                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+            if (plain) {
+                mx *= p.scale_log2;
             }
             // The running max only moves when it grew by more than 2^8: P and the row sum both use m_used, so the
             // result is exact either way, and O is rescaled rarely.
@@ -351,16 +362,25 @@ __global__ void __launch_bounds__(kThreads, 2)
             // P sit on the block-to-block dependency chain.
             const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
             uint32_t packed[kBlockN / 2];
-            float l0 = 0.f, l1 = 0.f; // two independent sums: shorter dependency chains
+            float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f; // independent sums: short dependency chains
             if (plain) {
 #pragma unroll
                 for (int c = 0; c < kBlockN / 32; ++c) {
 #pragma unroll
                     for (int k = 0; k < 32; k += 2) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][k]), p.scale_log2, neg_m));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][k + 1]), p.scale_log2, neg_m));
-                        l0 += p0;
-                        l1 += p1;
+                        const float x0 = fmaf(__uint_as_float(sr[c][k]), p.scale_log2, neg_m);
+                        const float x1 = fmaf(__uint_as_float(sr[c][k + 1]), p.scale_log2, neg_m);
+                        // (computing a share of these on the FMA pipe with a polynomial was measured: 1 to 3 pairs of every
+                        // 8 made the kernel 2 to 8 % slower -- the softmax warps are short of issue slots, not of MUFU rate)
+                        const float p0 = fast_exp2(x0);
+                        const float p1 = fast_exp2(x1);
+                        if (k & 2) {
+                            l2 += p0;
+                            l3 += p1;
+                        } else {
+                            l0 += p0;
+                            l1 += p1;
+                        }
                         packed[c * 16 + (k >> 1)] = pack2<kBf16>(p0, p1);
                     }
                 }
@@ -378,7 +398,7 @@ __global__ void __launch_bounds__(kThreads, 2)
                     }
                 }
             }
-            l += l0 + l1;
+            l += (l0 + l1) + (l2 + l3);
             if (i >= 1) {
                 // PV of the previous block must be finished before P is overwritten or O is rescaled
                 if (!wait_or_abort(bar(kBarPFree), uint32_t(i - 1) & 1u, s_abort)) {
