@@ -468,22 +468,31 @@ def run_model_workload(args) -> None:
     total_seqs, prompt_len = 64, 2048
     if total_seqs % world:
         raise SystemExit("config4 shards 64 sequences: --gpus must divide 64")
-    B = total_seqs // world
+    tp = bool(args.tp) and world > 1
+    if tp and cfg["num_key_value_heads"] % world:
+        raise SystemExit("--tp shards by KV head: --gpus must divide 2 for this model")
+    # sequence sharding: each GPU runs its share of the 64 sequences on a full weight replica, no collective;
+    # --tp: every GPU runs all 64 sequences on its share of the heads and MLP rows, two NCCL all-reduces per layer
+    B = total_seqs if tp else total_seqs // world
     steps = args.steps if args.steps != 2000 else 256  # the configuration's 256 greedy steps unless told otherwise
     warm = max(3, min(args.warmup, 8))
     n_e2e = 0 if args.no_e2e else 32
     max_tokens = prompt_len + warm + steps + 1 + n_e2e + 16
 
     model = llaisys.models.Qwen2(config=cfg, device=llaisys.DeviceType.NVIDIA, device_id=local_rank,
-                                 dtype=llaisys.DataType.BF16, max_seq_len=max_tokens)
+                                 dtype=llaisys.DataType.BF16, max_seq_len=max_tokens,
+                                 tp_group=dist.group.WORLD if tp else None)
     weight_bytes = 0
     for name, value in qwen2_random_weights(cfg, 4, "cuda"):  # the same weights on every rank
         model.load_tensor(name, value)
         if "embed_tokens" not in name:
-            weight_bytes += value.numel() * 2  # every matrix is read once per decode step; the embedding only B rows
+            # every matrix is read once per decode step (the embedding only B rows); per GPU, so a sharded matrix counts
+            # with its share
+            sharded = tp and ("_proj." in name)
+            weight_bytes += value.numel() * 2 // (world if sharded else 1)
     model.configure_cache(B, max_tokens)
     seqs = [model.add_seq() for _ in range(B)]
-    g = torch.Generator().manual_seed(100 + rank)
+    g = torch.Generator().manual_seed(100 + (0 if tp else rank))  # tensor-parallel ranks must feed the same tokens
     prompts = torch.randint(0, cfg["vocab_size"], (B, prompt_len), generator=g).tolist()
 
     # prefill, eight sequences per call (bounds the activation workspace), timed on the host with a synchronise
@@ -528,7 +537,7 @@ def run_model_workload(args) -> None:
             e2e["value"] = float(rate)
     if rank == 0:
         hbm_peak, _, kind = _peaks()
-        kv_bytes = cfg["num_hidden_layers"] * B * ctx_mid * (2 * NKVH * D * 2)
+        kv_bytes = cfg["num_hidden_layers"] * B * ctx_mid * (2 * (NKVH // world if tp else NKVH) * D * 2)
         achieved = (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9
         # per layer: 2 norms, bias+rope+append, decode attention, activation; per step: embedding, norm, argmax, 2 x advance
         own = cfg["num_hidden_layers"] * 5 + 5
@@ -540,7 +549,8 @@ def run_model_workload(args) -> None:
             "config": {"workload": "config4", "batch": total_seqs, "batch_per_gpu": B, "prompt": prompt_len,
                        "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"], "heads": "12q/2kv",
                        "head_dim": D, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                       "page_size": PAGE, "parallelism": f"sequences sharded over {world} GPU(s), no collective",
+                       "page_size": PAGE, "parallelism": (f"tensor parallel over {world} GPUs (heads and MLP rows), 2 NCCL all-reduces per layer"
+                                       if tp else f"sequences sharded over {world} GPU(s), no collective"),
                        "l2": "every step reads all weights and the whole KV cache (several GB): larger than L2"},
             "roofline": {"bound": "hbm", "kernel": "whole decode step (paged decode attention + cuBLAS projections)",
                          "achieved": achieved, "peak": hbm_peak, "peak_kind": f"copy bandwidth, of {kind}",
@@ -692,6 +702,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="north_star", choices=["north_star", "config2", "config3", "config4", "config5"])
     ap.add_argument("--layers", type=int, default=4, help="pools to rotate over between steps (L2 flush)")
+    ap.add_argument("--tp", action="store_true", help="config4 on several GPUs: tensor parallelism instead of sequence sharding")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-API leg (profiling runs)")
     ap.add_argument("--no-overlap", action="store_true",

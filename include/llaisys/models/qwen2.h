@@ -84,6 +84,28 @@ LLAISYS_API int llaisysQwen2ModelLastLogits(struct LlaisysQwen2Model *model, flo
  * over all steps on CPU. 0 when the loop had a single step. */
 LLAISYS_API double llaisysQwen2ModelLastLoopMs(struct LlaisysQwen2Model *model);
 
+/* ---- new: tensor parallelism (no counterpart in the reference, which names it as future work: README.md:426-427) -- */
+
+/* As llaisysQwen2ModelCreate, for rank tp_rank of tp_world processes that share ONE model (one process per GPU). meta
+ * holds the whole model's dimensions; tp_world must divide nkvh, nh and di. The rank holds query heads
+ * [r nh/W, (r+1) nh/W) with their KV heads and rows [r di/W, (r+1) di/W) of the MLP: the weight handles have the
+ * sharded shapes -- attn_q_w [nh/W * dh, hs], attn_k_w / attn_v_w [nkvh/W * dh, hs] and their biases, attn_o_w
+ * [hs, nh/W * dh], mlp_gate_w / mlp_up_w [di/W, hs], mlp_down_w [hs, di/W] -- and take the matching slices of the
+ * checkpoint; embeddings, norms and out_embed are replicated. Every rank must make the same calls with the same tokens;
+ * every rank gets the same logits and tokens. Two all-reduces of [tokens, hs] per layer (after the output and down
+ * projections) run through the collective set below. */
+LLAISYS_API struct LlaisysQwen2Model *llaisysQwen2ModelCreateTP(const struct LlaisysQwen2Meta *meta,
+                                                                llaisysDeviceType_t device, int device_id, int tp_rank,
+                                                                int tp_world);
+/* NCCL all-reduce on the model's stream. unique_id: the 128 bytes rank 0 got from llaisysNcclUniqueId and sent to the
+ * other ranks over any host channel. Collective call: every rank of the group must make it. */
+LLAISYS_API int llaisysNcclUniqueId(void *out_128_bytes);
+LLAISYS_API int llaisysQwen2ModelSetAllReduceNccl(struct LlaisysQwen2Model *model, const void *unique_id_128_bytes);
+/* Host all-reduce for CPU models: fn sums `count` elements of `dtype` (llaisysDataType_t) at `buf` in place over the
+ * ranks and returns 0. */
+typedef int (*llaisysAllReduceFn)(void *buf, size_t count, int dtype, void *user);
+LLAISYS_API int llaisysQwen2ModelSetAllReduceCallback(struct LlaisysQwen2Model *model, llaisysAllReduceFn fn, void *user);
+
 #ifdef __cplusplus
 }
 #endif

@@ -54,6 +54,45 @@ LlaisysQwen2Model *llaisysQwen2ModelCreate(const LlaisysQwen2Meta *meta, llaisys
     return model;
 }
 
+LlaisysQwen2Model *llaisysQwen2ModelCreateTP(const LlaisysQwen2Meta *meta, llaisysDeviceType_t device, int device_id,
+                                             int tp_rank, int tp_world) {
+    if (meta == nullptr) {
+        std::cerr << "[ERROR] llaisysQwen2ModelCreateTP: meta is null" << std::endl;
+        return nullptr;
+    }
+    LlaisysQwen2Model *model = nullptr;
+    const int rc = guarded([&] { model = new LlaisysQwen2Model(*meta, device, device_id, tp_rank, tp_world); });
+    if (rc != LLAISYS_OK) {
+        std::cerr << "[ERROR] llaisysQwen2ModelCreateTP: " << llaisysGetLastError() << std::endl;
+        return nullptr;
+    }
+    return model;
+}
+
+int llaisysNcclUniqueId(void *out_128_bytes) {
+    return guarded([&] { llaisys::comm::ncclUniqueIdBytes(out_128_bytes); });
+}
+
+int llaisysQwen2ModelSetAllReduceNccl(LlaisysQwen2Model *model, const void *unique_id_128_bytes) {
+    if (model == nullptr) {
+        return null_model();
+    }
+    return guarded([&] {
+        llaisys::core::context().setDevice(model->impl.deviceType(), model->impl.deviceId());
+        model->impl.setCollective(
+            llaisys::comm::Collective::nccl(unique_id_128_bytes, model->impl.tpRank(), model->impl.tpWorld()));
+    });
+}
+
+int llaisysQwen2ModelSetAllReduceCallback(LlaisysQwen2Model *model, llaisysAllReduceFn fn, void *user) {
+    if (model == nullptr) {
+        return null_model();
+    }
+    return guarded([&] {
+        model->impl.setCollective(llaisys::comm::Collective::callback(fn, user, model->impl.tpRank(), model->impl.tpWorld()));
+    });
+}
+
 void llaisysQwen2ModelDestroy(LlaisysQwen2Model *model) { delete model; }
 
 LlaisysQwen2Weights *llaisysQwen2ModelWeights(LlaisysQwen2Model *model) { return model ? model->impl.weights() : nullptr; }

@@ -5,5 +5,6 @@
 
 struct LlaisysQwen2Model {
     llaisys::models::Qwen2 impl;
-    LlaisysQwen2Model(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int device_id) : impl(meta, device, device_id) {}
+    LlaisysQwen2Model(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int device_id, int tp_rank = 0, int tp_world = 1)
+        : impl(meta, device, device_id, tp_rank, tp_world) {}
 };

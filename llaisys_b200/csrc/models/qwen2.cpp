@@ -27,8 +27,26 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // ---- construction -------------------------------------------------------------------------------------------------
 
-Qwen2::Qwen2(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int device_id)
-    : _meta(meta), _device(device), _device_id(device_id) {
+namespace {
+LlaisysQwen2Meta shard_meta(LlaisysQwen2Meta meta, int tp_rank, int tp_world) {
+    if (tp_world < 1 || tp_rank < 0 || tp_rank >= tp_world) {
+        fail(LLAISYS_E_INVALID, "qwen2: bad tensor-parallel rank or world size");
+    }
+    const size_t w = size_t(tp_world);
+    if (meta.nkvh % w != 0 || meta.nh % w != 0 || meta.di % w != 0) {
+        fail(LLAISYS_E_INVALID, "qwen2: the tensor-parallel world size must divide nkvh, nh and di");
+    }
+    meta.nh /= w;
+    meta.nkvh /= w;
+    meta.di /= w;
+    return meta;
+}
+} // namespace
+
+Qwen2::Qwen2(const LlaisysQwen2Meta &global_meta, llaisysDeviceType_t device, int device_id, int tp_rank, int tp_world)
+    : _meta(shard_meta(global_meta, tp_rank, tp_world)), _tp_rank(tp_rank), _tp_world(tp_world), _device(device),
+      _device_id(device_id) {
+    const LlaisysQwen2Meta &meta = _meta;
     if (meta.dtype != LLAISYS_DTYPE_F32 && meta.dtype != LLAISYS_DTYPE_F16 && meta.dtype != LLAISYS_DTYPE_BF16) {
         fail(LLAISYS_E_INVALID, "qwen2: dtype must be F32, F16 or BF16");
     }
@@ -333,6 +351,30 @@ void Qwen2::opSwigluPacked(void *out, const void *gate_up, size_t rows, size_t d
     QWEN2_DISPATCH(cpu::swiglu_packed(_meta.dtype, out, gate_up, rows, di),
                    kernels::swiglu_packed(_stream, _meta.dtype, out, gate_up, rows, di));
 }
+void Qwen2::opAdd(void *c, const void *a, const void *b, size_t n) {
+    QWEN2_DISPATCH(cpu::add(_meta.dtype, c, a, b, n), kernels::add(_stream, _meta.dtype, c, a, b, n));
+}
+
+void Qwen2::setCollective(std::unique_ptr<comm::Collective> c) {
+    if (!c || c->rank() != _tp_rank || c->world() != _tp_world) {
+        fail(LLAISYS_E_INVALID, "qwen2: the collective's rank / world size differ from the model's");
+    }
+    _tp = std::move(c);
+}
+
+void Qwen2::projectIntoStream(void *x, void *tmp, const void *in, const void *w, size_t m, size_t n, size_t k) {
+    if (_tp_world == 1) {
+        opLinear(x, in, w, m, n, k, true); // the residual add folded into the projection
+        return;
+    }
+    if (!_tp) {
+        fail(LLAISYS_E_INVALID, "qwen2: a sharded model needs its all-reduce (llaisysQwen2ModelSetAllReduce...) before the first step");
+    }
+    opLinear(tmp, in, w, m, n, k);
+    _tp->allReduceSum(tmp, m * n, _meta.dtype, _stream);
+    opAdd(x, x, tmp, m * n);
+}
+
 void Qwen2::opArgmax(int64_t *idx, const void *vals, size_t rows, size_t n) {
     QWEN2_DISPATCH(cpu::argmax_rows(_meta.dtype, idx, nullptr, vals, rows, n),
                    kernels::argmax_rows_split(_stream, _meta.dtype, idx, vals, rows, n, _argmax_scratch->memory()));
@@ -361,11 +403,11 @@ void Qwen2::forward(const StepArrays &a, size_t T, size_t n_seqs, size_t max_q_l
             _cache->prefillDev(l, attn, q, a.seq_list, a.q_starts, a.kv_lens, n_seqs, T, max_q_len, max_kv_len, _meta.nh,
                                scale, _stream);
         }
-        opLinear(x, attn, w.o_w, T, hs, qd, true);
+        projectIntoStream(x, h, attn, w.o_w, T, hs, qd);
         opRmsNorm(h, x, w.mlp_norm, T, hs);
         opLinear(gate_up, h, w.gate_up_w, T, 2 * di, hs);
         opSwigluPacked(act, gate_up, T, di);
-        opLinear(x, act, w.down_w, T, hs, di, true);
+        projectIntoStream(x, h, act, w.down_w, T, hs, di);
     }
     // the last token of every sequence -> final norm -> vocabulary projection -> greedy choice
     const std::byte *last = x;

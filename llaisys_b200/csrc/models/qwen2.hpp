@@ -9,6 +9,7 @@
 #pragma once
 
 #include "../capi/handles.hpp"
+#include "../comm/collective.hpp"
 #include "../kv/paged_kv.hpp"
 #include "llaisys/models/qwen2.h"
 
@@ -38,13 +39,22 @@ public:
         }
     }
 
-    Qwen2(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int device_id);
+    // tp_rank / tp_world: tensor parallelism by heads. Rank r holds query heads [r nh/W, (r+1) nh/W), the KV heads they
+    // use, and rows [r di/W, (r+1) di/W) of the MLP; the output and down projections produce partial sums that one
+    // all-reduce each turns into the full activation (set the collective before the first step). Embeddings, norms and
+    // the vocabulary projection are replicated, so every rank computes the same logits and tokens.
+    Qwen2(const LlaisysQwen2Meta &meta, llaisysDeviceType_t device, int device_id, int tp_rank = 0, int tp_world = 1);
+    void setCollective(std::unique_ptr<comm::Collective> c);
+    llaisysDeviceType_t deviceType() const { return _device; }
+    int deviceId() const { return _device_id; }
+    int tpRank() const { return _tp_rank; }
+    int tpWorld() const { return _tp_world; }
     ~Qwen2();
     Qwen2(const Qwen2 &) = delete;
     Qwen2 &operator=(const Qwen2 &) = delete;
 
     LlaisysQwen2Weights *weights() { return &_weights; }
-    const LlaisysQwen2Meta &meta() const { return _meta; }
+    const LlaisysQwen2Meta &meta() const { return _meta; } // this rank's share: nh, nkvh and di are per-rank under TP
 
     void configureCache(size_t max_seqs, size_t max_tokens);
     int32_t seqAdd();
@@ -91,12 +101,17 @@ private:
     void opLinear(void *out, const void *in, const void *w, size_t m, size_t n, size_t k, bool accumulate = false);
     void opRmsNorm(void *out, const void *in, const void *w, size_t rows, size_t d);
     void opSwigluPacked(void *out, const void *gate_up, size_t rows, size_t di);
+    void opAdd(void *c, const void *a, const void *b, size_t n);
+    // x += in . w^T, through an all-reduce of the partial product when the model is sharded
+    void projectIntoStream(void *x, void *tmp, const void *in, const void *w, size_t m, size_t n, size_t k);
     void opArgmax(int64_t *idx, const void *vals, size_t rows, size_t n);
     void checkKernels();
     void copyToDevice(void *dst, const void *src, size_t bytes);
     void copyToHost(void *dst, const void *src, size_t bytes);
 
-    LlaisysQwen2Meta _meta;
+    LlaisysQwen2Meta _meta; // per-rank dimensions
+    int _tp_rank = 0, _tp_world = 1;
+    std::unique_ptr<comm::Collective> _tp;
     llaisysDeviceType_t _device;
     int _device_id;
     size_t _elem = 0;

@@ -116,6 +116,7 @@ class LlaisysEngineEvent(Structure):
 
 
 _MODEL = c_void_p
+ALL_REDUCE_FN = CFUNCTYPE(c_int, c_void_p, c_size_t, c_int, c_void_p)  # llaisysAllReduceFn
 
 PROTOTYPES: dict[str, tuple] = {
     # runtime.h
@@ -211,6 +212,10 @@ PROTOTYPES: dict[str, tuple] = {
     "llaisysQwen2ModelDecodeLoop": (c_int, [_MODEL, _I32P, c_size_t, POINTER(c_int64), c_size_t, POINTER(c_int64)]),
     "llaisysQwen2ModelLastLogits": (c_int, [_MODEL, POINTER(c_float), c_size_t]),
     "llaisysQwen2ModelLastLoopMs": (c_double, [_MODEL]),
+    "llaisysQwen2ModelCreateTP": (_MODEL, [POINTER(LlaisysQwen2Meta), llaisysDeviceType_t, c_int, c_int, c_int]),
+    "llaisysNcclUniqueId": (c_int, [c_void_p]),
+    "llaisysQwen2ModelSetAllReduceNccl": (c_int, [_MODEL, c_void_p]),
+    "llaisysQwen2ModelSetAllReduceCallback": (c_int, [_MODEL, ALL_REDUCE_FN, c_void_p]),
     # include/llaisys/serving.h
     "llaisysEngineCreate": (c_int, [POINTER(c_void_p), _MODEL, c_size_t, c_size_t, c_size_t]),
     "llaisysEngineDestroy": (None, [c_void_p]),
@@ -254,5 +259,5 @@ LIB_LLAISYS = load_shared_library()
 __all__ = [
     "LIB_LLAISYS", "PROTOTYPES", "LlaisysRuntimeAPI", "llaisysStream_t", "llaisysTensor_t", "llaisysPagedKV_t",
     "llaisysDataType_t", "DataType", "llaisysDeviceType_t", "DeviceType", "llaisysMemcpyKind_t", "MemcpyKind",
-    "Status", "library_path", "LlaisysQwen2Meta", "LlaisysQwen2Weights", "LlaisysEngineEvent",
+    "Status", "library_path", "LlaisysQwen2Meta", "LlaisysQwen2Weights", "LlaisysEngineEvent", "ALL_REDUCE_FN",
 ]

@@ -29,7 +29,10 @@ def _torch_dtype(dtype: DataType):
 class Qwen2:
     def __init__(self, model_path=None, device: DeviceType = DeviceType.CPU, *, device_id: int = 0,
                  config: Mapping | None = None, state_dict: Mapping | None = None, dtype: DataType | None = None,
-                 max_seq_len: int | None = None):
+                 max_seq_len: int | None = None, tp_group=None):
+        """tp_group: a torch.distributed process group (gloo for CPU models, nccl for NVIDIA) whose ranks share this
+        model by tensor parallelism: every rank constructs it with the same checkpoint and then makes the same calls;
+        each loads only its slices of the attention and MLP matrices."""
         if model_path is not None:
             model_path = Path(model_path)
             config = json.loads((model_path / "config.json").read_text())
@@ -52,10 +55,20 @@ class Qwen2:
         self.dtype = dtype
         self.device = device
         self.device_id = device_id
-        ids = (c_int * 1)(device_id)
-        self._model = LIB_LLAISYS.llaisysQwen2ModelCreate(ctypes.byref(self.meta), int(device), ids, 1)
+        self.tp_rank, self.tp_world = 0, 1
+        if tp_group is not None:
+            import torch.distributed as dist
+            self.tp_rank, self.tp_world = dist.get_rank(tp_group), dist.get_world_size(tp_group)
+        if self.tp_world > 1:
+            self._model = LIB_LLAISYS.llaisysQwen2ModelCreateTP(ctypes.byref(self.meta), int(device), device_id,
+                                                                self.tp_rank, self.tp_world)
+        else:
+            ids = (c_int * 1)(device_id)
+            self._model = LIB_LLAISYS.llaisysQwen2ModelCreate(ctypes.byref(self.meta), int(device), ids, 1)
         if not self._model:
             raise RuntimeError("llaisysQwen2ModelCreate failed: " + (LIB_LLAISYS.llaisysGetLastError() or b"").decode())
+        if self.tp_world > 1:
+            self._connect(tp_group)
         self._weights = LIB_LLAISYS.llaisysQwen2ModelWeights(self._model).contents
         self._loaded: set[str] = set()
         self._tied_embedding = None
@@ -106,6 +119,46 @@ class Qwen2:
                 return getattr(self._weights, slot)[layer]
         return None
 
+    def _connect(self, group) -> None:
+        """Gives the sharded model its all-reduce: NCCL on the model's stream for NVIDIA (the unique id travels through
+        the process group), a callback into the (gloo) process group for CPU."""
+        import torch
+        import torch.distributed as dist
+
+        if self.device == DeviceType.NVIDIA:
+            box = [None]
+            if self.tp_rank == 0:
+                uid = ctypes.create_string_buffer(128)
+                _check(LIB_LLAISYS.llaisysNcclUniqueId(uid))
+                box[0] = uid.raw
+            dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0), group=group)
+            uid = ctypes.create_string_buffer(box[0], 128)
+            _check(LIB_LLAISYS.llaisysQwen2ModelSetAllReduceNccl(self._model, uid))
+            return
+        torch_types = {int(DataType.F32): torch.float32, int(DataType.F16): torch.float16,
+                       int(DataType.BF16): torch.bfloat16}
+
+        def all_reduce(buf, count, dtype, _user):
+            try:
+                tdt = torch_types[dtype]
+                raw = (ctypes.c_char * (count * torch.empty((), dtype=tdt).element_size())).from_address(buf)
+                tensor = torch.frombuffer(raw, dtype=tdt)
+                if tdt == torch.float32:
+                    dist.all_reduce(tensor, group=group)
+                else:  # sum 16-bit activations in f32, as NCCL does internally
+                    wide = tensor.float()
+                    dist.all_reduce(wide, group=group)
+                    tensor.copy_(wide)
+                return 0
+            except Exception:  # never unwind through the C frames
+                import traceback
+                traceback.print_exc()
+                return 1
+
+        from ..libllaisys import ALL_REDUCE_FN
+        self._all_reduce_cb = ALL_REDUCE_FN(all_reduce)  # keep the trampoline alive as long as the model
+        _check(LIB_LLAISYS.llaisysQwen2ModelSetAllReduceCallback(self._model, self._all_reduce_cb, None))
+
     def _load(self, name: str, value) -> None:
         """Copies one checkpoint tensor (torch, any float dtype, host or device) into the model's weight of that name;
         names the model has no slot for (rotary caches and the like) are skipped."""
@@ -113,7 +166,14 @@ class Qwen2:
         if handle is None:
             return
         shape = self._shape_of(handle)
-        host = value.detach().to(device="cpu", dtype=_torch_dtype(self.dtype)).contiguous()
+        host = value.detach()
+        if self.tp_world > 1 and tuple(host.shape) != shape and host.ndim == len(shape):
+            # this rank's slice: the one dimension that is tp_world times the model's (rows of q/k/v/gate/up and their
+            # biases, columns of the output and down projections)
+            for dim, (have, want) in enumerate(zip(host.shape, shape)):
+                if have == want * self.tp_world:
+                    host = host.narrow(dim, self.tp_rank * want, want)
+        host = host.to(device="cpu", dtype=_torch_dtype(self.dtype)).contiguous()
         if tuple(host.shape) != shape:
             raise ValueError(f"{name}: checkpoint shape {tuple(host.shape)} != model shape {shape}")
         LIB_LLAISYS.tensorLoad(handle, host.data_ptr())
