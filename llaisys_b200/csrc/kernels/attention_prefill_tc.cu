@@ -33,6 +33,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <string>
 
 namespace llaisys::kernels {
 
@@ -90,7 +91,14 @@ struct PrefillParams {
     int32_t *error_flag;
 };
 
-template <bool kBf16>
+// kPTmem: P goes from the softmax threads to the PV product through tensor memory (packed 16-bit pairs written over
+// the first 32 columns of the S buffer they were computed from, read back as the A operand) instead of through shared
+// memory. The kernel is bound by shared-memory bandwidth -- per 64-key block a CTA moves 32 KiB of TMA writes, 48 KiB
+// of QK^T operand reads, 32 KiB of PV operand reads and 16 KiB of P stores through a 128 B/clk port, about twice the
+// 512 clocks its MMAs need -- and this takes the P store and the P read (32 KiB of 128) off that port. It also frees
+// the softmax threads from waiting for the previous PV before they hand over P: consecutive P tiles sit in alternate
+// S buffers, and the tensor pipe runs its instructions in issue order (QK^T of block i + 2 is issued after PV of block i).
+template <bool kBf16, bool kPTmem>
 __global__ void __launch_bounds__(kThreads, 2)
     paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, PrefillParams p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -247,11 +255,17 @@ __global__ void __launch_bounds__(kThreads, 2)
                 const uint32_t v_u32 = kv_u32 + (j & 1) * kStageBytes + kKvOperandBytes;
 #pragma unroll
                 for (int kk = 0; kk < kBlockN / 16; ++kk) {
-                    // A = P rows x 16 keys (K-major: 32 bytes into the 128-byte row per step, next half after 4 steps)
-                    const uint64_t a = smem_desc_sw128(p_u32 + (kk >> 2) * kPHalfBytes + (kk & 3) * 32, 0, 1024);
                     // B = 16 keys x 128 dims of V, MN-major: 8-key groups 1 KiB apart, the two 64-dim halves one
                     // half-operand apart
                     const uint64_t b = smem_desc_sw128(v_u32 + kk * 2048, kKvHalfBytes, 1024);
+                    if constexpr (kPTmem) {
+                        // A = P rows x 16 keys from tensor memory: 8 columns of packed pairs per step, in S buffer j & 1
+                        umma_f16_ts(tmem_o, tmem_base + kColS + (j & 1) * kBlockN + kk * 8, b, idesc_pv,
+                                    (j > 0 || kk > 0) ? 1u : 0u);
+                        continue;
+                    }
+                    // A = P rows x 16 keys (K-major: 32 bytes into the 128-byte row per step, next half after 4 steps)
+                    const uint64_t a = smem_desc_sw128(p_u32 + (kk >> 2) * kPHalfBytes + (kk & 3) * 32, 0, 1024);
                     umma_f16(tmem_o, a, b, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(bar(kBarPFree));
@@ -314,8 +328,10 @@ __global__ void __launch_bounds__(kThreads, 2)
                 tmem_ld32_nowait(tmem_s + c * 32, sr[c]);
             }
             tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(bar(kBarSFree + buf)); // S[buf] may be overwritten by QK^T of block i + 2
+            if constexpr (!kPTmem) {
+                tc_fence_before();
+                mbar_arrive(bar(kBarSFree + buf)); // S[buf] may be overwritten by QK^T of block i + 2
+            }
             // Most blocks lie wholly below the diagonal: the whole warp then skips the mask (warp-uniform choice).
             const bool plain = __all_sync(0xffffffffu, n_ok >= kBlockN) && p.scale_log2 > 0.f;
             // Row maximum as eight independent chains (a single chain of 64 dependent max operations would cost more than
@@ -399,14 +415,16 @@ __global__ void __launch_bounds__(kThreads, 2)
                 }
             }
             l += (l0 + l1) + (l2 + l3);
-            if (i >= 1) {
-                // PV of the previous block must be finished before P is overwritten or O is rescaled
+            // PV of the previous block must be finished before O is rescaled -- and, on the shared-memory path, before P
+            // is overwritten. With P in tensor memory only a rescale has to wait.
+            const bool any_grow = __any_sync(0xffffffffu, grow);
+            if (i >= 1 && (!kPTmem || any_grow)) {
                 if (!wait_or_abort(bar(kBarPFree), uint32_t(i - 1) & 1u, s_abort)) {
                     dead = true;
                     break;
                 }
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
+                if (any_grow) {
 #pragma unroll
                     for (int c = 0; c < kD / 32; ++c) {
                         float v[32];
@@ -420,6 +438,16 @@ __global__ void __launch_bounds__(kThreads, 2)
                     tmem_wait_st();
                     tc_fence_before();
                 }
+            }
+            if constexpr (kPTmem) {
+                // 64 keys = 32 columns of packed pairs over the first half of S[buf]; the same arrival tells the tensor
+                // pipe that P is there and (S having been read above) that the buffer may be rewritten after this PV
+                tmem_st32_words(tmem_s, packed);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar(kBarSFree + buf));
+                mbar_arrive(bar(kBarPFull));
+                continue;
             }
 #pragma unroll
             for (int cc = 0; cc < kBlockN / 8; ++cc) { // 16-byte chunk (8 keys) of this row, swizzled K-major layout
@@ -498,16 +526,30 @@ EncodeTiledFn prefill_encode_fn() {
 constexpr size_t kSmemBytes = kAlignSlack + kQBytes + kPBytes + kStages * kStageBytes + kNumBars * sizeof(uint64_t) + 8 +
                               kMaxSortedSeqs * sizeof(int16_t);
 
-template <bool kBf16>
-void launch(cudaStream_t s, const CUtensorMap &tmap, const PrefillParams &p, int grid) {
+template <bool kBf16, bool kPTmem>
+void launch_variant(cudaStream_t s, const CUtensorMap &tmap, const PrefillParams &p, int grid) {
     static std::once_flag once[64];
     int dev = 0;
     LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
     std::call_once(once[dev & 63], [] {
-        LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_tc_kernel<kBf16>,
+        LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_tc_kernel<kBf16, kPTmem>,
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
     });
-    paged_prefill_tc_kernel<kBf16><<<grid, kThreads, kSmemBytes, s>>>(tmap, p);
+    paged_prefill_tc_kernel<kBf16, kPTmem><<<grid, kThreads, kSmemBytes, s>>>(tmap, p);
+}
+
+template <bool kBf16>
+void launch(cudaStream_t s, const CUtensorMap &tmap, const PrefillParams &p, int grid) {
+    // LLAISYS_PREFILL_P=smem keeps P on the shared-memory path (the earlier design), for comparison
+    static const bool p_tmem = [] {
+        const char *e = std::getenv("LLAISYS_PREFILL_P");
+        return e == nullptr || std::string(e) != "smem";
+    }();
+    if (p_tmem) {
+        launch_variant<kBf16, true>(s, tmap, p, grid);
+    } else {
+        launch_variant<kBf16, false>(s, tmap, p, grid);
+    }
 }
 
 } // namespace
