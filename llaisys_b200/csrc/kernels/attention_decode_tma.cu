@@ -2,11 +2,13 @@
 //
 // Same mathematics, work decomposition ("even page split" over persistent CTAs, two per SM) and fused
 // log-sum-exp combine as attention_decode.cu; what changes is how K/V reach shared memory and who moves them:
-//   * one PRODUCER warp per CTA walks the CTA's span of pages, reads the block table 32 entries at a time, and
-//     an elected lane issues the copies: each (page, kv-head) is four 2 KiB TMA tiles (K low/high 64 dims, V
-//     low/high 64 dims; cp.async.bulk.tensor.2d over one tensor map that views the whole pool as rows of 128
-//     elements), landing in one 8 KiB slot of a 12-slot ring with the hardware 128-byte swizzle, completion
-//     counted on the slot's "full" mbarrier;
+//   * one PRODUCER warp per CTA walks the CTA's span of pages, reads the block table 32 entries at a time, and up
+//     to 12 of its lanes issue the copies of a round in parallel: each (page, kv-head) is two 4 KiB boxes of one 4-D
+//     tensor map over the pool, [page and K|V][kv-head][slot][128 elements] with box {64 dims, 16 slots, 1 head, K and
+//     V} (cp.async.bulk.tensor.4d; low 64 dims, then high 64 dims), landing in one 8 KiB slot of a 12-slot ring with the
+//     hardware 128-byte swizzle, completion counted on the slot's "full" mbarrier;
+//   * a sixth EPILOGUE warp counts the CTAs that have finished a (sequence, kv-head) pair and, for the last one to
+//     arrive, merges the pair's partial results (log-sum-exp combine) while the consumers go on;
 //   * four CONSUMER warps take pages round-robin: wait on "full", 8 + 8 mma.sync m16n8k16 with conflict-free
 //     ldmatrix reads (the swizzle XORs the 16-byte chunk index with token % 8), then hand the slot back through
 //     its "empty" mbarrier. They execute ~100 instructions per page and never compute an address in global

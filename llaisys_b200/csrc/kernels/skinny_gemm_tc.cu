@@ -90,15 +90,6 @@ __device__ __forceinline__ float unpack_hi(uint32_t w) {
 }
 
 template <bool kBf16>
-__device__ __forceinline__ float load_elem(const void *base, long long idx) {
-    if constexpr (kBf16) {
-        return __bfloat162float(static_cast<const __nv_bfloat16 *>(base)[idx]);
-    } else {
-        return __half2float(static_cast<const __half *>(base)[idx]);
-    }
-}
-
-template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
     skinny_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w, GemmParams p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
