@@ -36,6 +36,8 @@ import threading
 import time
 from pathlib import Path
 
+import numpy as np
+
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
@@ -851,23 +853,14 @@ def main() -> None:
     args.steps = steps
 
     # ---- end to end through the host-array API, host buffers, copies inside the timed region ---------------------
-    api = llaisys.RuntimeAPI(dev)
-    ctx_stream = llaisys.context_stream()
     q_h, k_h, v_h = (t.cpu().pin_memory() for t in (q, k_new, v_new))
     out_h = torch.empty_like(q_h).pin_memory()
-    q_d, k_d, v_d, out_d = (torch.empty_like(t) for t in (q, k_new, v_new, out))
-    last_pos = [c - 1 for c in ctx]
-    H2D, D2H = llaisys.MemcpyKind.H2D, llaisys.MemcpyKind.D2H
+    seqs_np, ctx_np = np.asarray(seqs, dtype=np.int32), np.asarray(ctx, dtype=np.int32)
 
     def step_e2e(i: int):
-        layer = i % layers
-        api.memcpy_async(q_d, q_h, q_h.numel() * 2, H2D, ctx_stream)
-        api.memcpy_async(k_d, k_h, k_h.numel() * 2, H2D, ctx_stream)
-        api.memcpy_async(v_d, v_h, v_h.numel() * 2, H2D, ctx_stream)
-        cache.append(layer, k_d, v_d, seqs, last_pos)
-        cache.decode(layer, out_d, q_d, seqs, ctx, NH, scale)
-        api.memcpy_async(out_h, out_d, out_h.numel() * 2, D2H, ctx_stream)
-        api.stream_synchronize(ctx_stream)  # the step's result is read on the host every step
+        # the library's host-buffer step: pinned q / new K,V rows in, both kernels, attention output back, one
+        # synchronise -- one call per decode step, as a serving loop without device-resident activations makes it
+        cache.decode_step_host(i % layers, out_h, q_h, k_h, v_h, seqs_np, ctx_np, NH, scale)
 
     e2e_steps, e2e_s, same = 0, float("nan"), None
     if not args.no_e2e:
@@ -933,8 +926,9 @@ def main() -> None:
                          "append_kernel_ms_mean": append_ms},
             "e2e": None if args.no_e2e else {
                 "value": total_tokens * e2e_steps / e2e_s, "unit": "tokens/s",
-                "h2d_bytes_per_step": (q_h.numel() + k_h.numel() + v_h.numel()) * 2,
-                "d2h_bytes_per_step": out_h.numel() * 2, "steps": e2e_steps, "matches_device_path": same},
+                "h2d_bytes_per_step": (q_h.numel() + k_h.numel() + v_h.numel()) * 2 + 3 * B * 4,  # + three index arrays
+                "d2h_bytes_per_step": out_h.numel() * 2, "steps": e2e_steps, "matches_device_path": same,
+                "what": "PagedKVCache.decode_step_host(): pinned host q / K,V rows in, attention out, one synchronise"},
             "gpu_launches": 2 * args.steps, "timing": f"CUDA graphs of {chunk} steps x {reps} replays",
             "clocks": clocks.summary(),
         }

@@ -205,6 +205,15 @@ int llaisysLseMerge(llaisysDeviceType_t device_type, int device_id, void *out, l
     });
 }
 
+int llaisysPagedDecodeStepHost(llaisysPagedKV_t kv, size_t layer, void *out_host, const void *q_host, const void *k_new_host,
+                               const void *v_new_host, const int32_t *seq_ids, const int32_t *kv_lens, size_t n_seqs,
+                               size_t nh, float scale) {
+    KV_OR_FAIL(kv);
+    return guarded([&] {
+        kv->impl.decodeStepHost(layer, out_host, q_host, k_new_host, v_new_host, seq_ids, kv_lens, n_seqs, nh, scale);
+    });
+}
+
 int llaisysPagedKVSeqPublish(llaisysPagedKV_t kv, int32_t seq, const int64_t *tokens, size_t n_tokens) {
     KV_OR_FAIL(kv);
     return guarded([&] { kv->impl.seqPublish(seq, tokens, n_tokens); });

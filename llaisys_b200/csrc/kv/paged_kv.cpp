@@ -722,6 +722,57 @@ void PagedKV::decode(size_t layer, void *out, float *part, const void *q, const 
     decodeDev(layer, out, part, q, dev, dev + n_seqs, n_seqs, max_kv, nh, scale, enter().stream());
 }
 
+void PagedKV::decodeStepHost(size_t layer, void *out_host, const void *q_host, const void *k_new_host,
+                             const void *v_new_host, const int32_t *seq_ids, const int32_t *kv_lens, size_t n_seqs,
+                             size_t nh, float scale) {
+    checkLayer(layer);
+    if (n_seqs == 0) {
+        return;
+    }
+    KV_REQUIRE(out_host && q_host && k_new_host && v_new_host && seq_ids && kv_lens, LLAISYS_E_INVALID,
+               "paged decode step: null argument");
+    KV_REQUIRE(nh > 0 && nh % _cfg.nkvh == 0, LLAISYS_E_INVALID, "paged attention: nh = ", nh,
+               " is not a multiple of nkvh = ", _cfg.nkvh);
+    KV_REQUIRE(n_seqs <= kMaxInt32, LLAISYS_E_INVALID, "paged decode step: too many sequences");
+    size_t max_kv = 0;
+    std::vector<int32_t> &pos = _step_positions;
+    pos.resize(n_seqs);
+    for (size_t i = 0; i < n_seqs; ++i) {
+        const Seq &s = liveSeq(seq_ids[i]);
+        KV_REQUIRE(kv_lens[i] >= 1 && size_t(kv_lens[i]) <= size_t(s.n_pages) * _cfg.page_size, LLAISYS_E_INVALID,
+                   "paged decode step: kv_len ", kv_lens[i], " is outside the ", s.n_pages,
+                   " page(s) reserved for sequence ", seq_ids[i]);
+        pos[i] = kv_lens[i] - 1;
+        max_kv = std::max(max_kv, size_t(kv_lens[i]));
+    }
+    flush();
+    if (!onDevice()) {
+        appendDev(layer, k_new_host, v_new_host, seq_ids, pos.data(), n_seqs, nullptr);
+        decodeDev(layer, out_host, nullptr, q_host, seq_ids, kv_lens, n_seqs, max_kv, nh, scale, nullptr);
+        return;
+    }
+    auto &rt = enter();
+    const size_t q_bytes = n_seqs * nh * _cfg.head_dim * _elem, kv_bytes = n_seqs * _cfg.nkvh * _cfg.head_dim * _elem;
+    const size_t need = 2 * q_bytes + 2 * kv_bytes; // q | out | k | v, each a multiple of 16 bytes
+    if (need > _step_cap) {
+        _step_cap = need * 2;
+        _step_dev = rt.allocateDeviceStorage(_step_cap);
+    }
+    std::byte *q_d = _step_dev->memory(), *out_d = q_d + q_bytes, *k_d = out_d + q_bytes, *v_d = k_d + kv_bytes;
+    const int32_t *arrays[3] = {seq_ids, pos.data(), kv_lens};
+    const size_t lens[3] = {n_seqs, n_seqs, n_seqs};
+    int32_t *idx = stage(arrays, lens, 3);
+    const auto *api = rt.api();
+    llaisysStream_t stream = rt.stream();
+    api->memcpy_async(k_d, k_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
+    api->memcpy_async(v_d, v_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
+    api->memcpy_async(q_d, q_host, q_bytes, LLAISYS_MEMCPY_H2D, stream);
+    appendDev(layer, k_d, v_d, idx, idx + n_seqs, n_seqs, stream);
+    decodeDev(layer, out_d, nullptr, q_d, idx, idx + 2 * n_seqs, n_seqs, max_kv, nh, scale, stream);
+    api->memcpy_async(out_host, out_d, q_bytes, LLAISYS_MEMCPY_D2H, stream);
+    api->stream_synchronize(stream);
+}
+
 void PagedKV::prefill(size_t layer, void *out, const void *q, const int32_t *seq_ids, const int32_t *q_lens,
                       const int32_t *kv_lens, size_t n_seqs, size_t nh, float scale) {
     checkLayer(layer);

@@ -83,6 +83,11 @@ public:
                 size_t n_seqs, size_t nh, float scale);
     void prefill(size_t layer, void *out, const void *q, const int32_t *seq_ids, const int32_t *q_lens,
                  const int32_t *kv_lens, size_t n_seqs, size_t nh, float scale);
+    // One decode step from HOST buffers, synchronous: row i of k_new / v_new [n_seqs, nkvh, d] becomes token
+    // kv_lens[i] - 1 of sequence seq_ids[i], then out[i] = attention of q[i] over its kv_lens[i] tokens. On a device
+    // cache: copies in, both kernels, copy out and one synchronise, all queued by this one call.
+    void decodeStepHost(size_t layer, void *out_host, const void *q_host, const void *k_new_host, const void *v_new_host,
+                        const int32_t *seq_ids, const int32_t *kv_lens, size_t n_seqs, size_t nh, float scale);
 
     // ---- data path: device index arrays, explicit stream (no validation, no staging) ----
     void appendDev(size_t layer, const void *k_rows, const void *v_rows, const int32_t *seq_ids_dev,
@@ -145,9 +150,10 @@ private:
     size_t _n_live = 0;
 
     // device memory (host memory for a CPU cache)
-    core::storage_t _pool, _table_dev, _error_dev, _meta_dev, _partials, _counters;
+    core::storage_t _pool, _table_dev, _error_dev, _meta_dev, _partials, _counters, _step_dev;
+    size_t _step_cap = 0;
     size_t _meta_cap = 0, _partials_floats = 0, _counters_len = 0;
-    std::vector<int32_t> _stage_buf;
+    std::vector<int32_t> _stage_buf, _step_positions;
 
     // TMA view of the pool (NVIDIA, 16-bit, head_dim 128, page 16 only); _has_tma is false otherwise
     alignas(64) unsigned char _tma_desc[128] = {};      // decode: box = K and V of a page

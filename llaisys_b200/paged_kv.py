@@ -166,6 +166,17 @@ class PagedKVCache:
         _check(LIB_LLAISYS.llaisysPagedAttentionDecode(self._kv, layer, _addr(out), _addr(q), sp, lp, s.size, nh,
                                                        scale))
 
+    def decode_step_host(self, layer: int, out, q, k_new, v_new, seq_ids, kv_lens, nh: int, scale: float) -> None:
+        """One decode step from host buffers, synchronous: k_new[i] / v_new[i] become token kv_lens[i] - 1 of sequence
+        seq_ids[i], then out[i] = attention of q[i] over kv_lens[i] tokens. out, q, k_new, v_new are HOST tensors
+        (pinned ones copy asynchronously); seq_ids / kv_lens may be int32 numpy arrays (used as they are) or lists."""
+        s, sp = _i32(seq_ids)
+        l, lp = _i32(kv_lens)
+        if s.size != l.size:
+            raise ValueError("seq_ids and kv_lens must have the same length")
+        _check(LIB_LLAISYS.llaisysPagedDecodeStepHost(self._kv, layer, _addr(out), _addr(q), _addr(k_new), _addr(v_new),
+                                                      sp, lp, s.size, nh, scale))
+
     def decode_partial(self, layer: int, part, q, seq_ids, kv_lens, nh: int, scale: float) -> None:
         s, sp = _i32(seq_ids)
         l, lp = _i32(kv_lens)

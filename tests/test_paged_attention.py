@@ -177,6 +177,50 @@ def test_data_path_argument_errors_cpu():
     cache.check()
 
 
+def check_decode_step_host(device):
+    """The one-call host-buffer step must leave the cache and the output exactly as append + decode do."""
+    dev = helpers.torch_device(device)
+    batch = workloads.decode_batch(5, 1, 300, seed=8, pool_pages=128)
+    nkvh, d, nh = workloads.NKVH, workloads.D, workloads.NH
+    outs = []
+    for fused in (False, True):
+        cache, seqs = helpers.build_cache(device, "bf16", batch.pages, num_pages=128, nkvh=nkvh, d=d)
+        last = [c - 1 for c in batch.ctx]
+        helpers.append_all(cache, 0, seqs, batch.k, batch.v, device, hi=last)
+        k_new = torch.stack([k[-1] for k in batch.k]).contiguous()
+        v_new = torch.stack([v[-1] for v in batch.v]).contiguous()
+        out = torch.empty_like(batch.q)
+        if fused:
+            cache.decode_step_host(0, out, batch.q, k_new, v_new, np.asarray(seqs, np.int32),
+                                   np.asarray(batch.ctx, np.int32), nh, batch.scale)
+        else:
+            cache.append(0, k_new.to(dev), v_new.to(dev), seqs, last)
+            out_d = torch.empty_like(batch.q, device=dev)
+            cache.decode(0, out_d, batch.q.to(dev), seqs, batch.ctx, nh, batch.scale)
+            out = out_d.cpu()
+        cache.check()
+        k_all = torch.empty_like(batch.k[0], device=dev)
+        v_all = torch.empty_like(batch.v[0], device=dev)
+        cache.gather(0, seqs[0], batch.ctx[0], k_all, v_all)
+        outs.append((out.clone(), k_all.cpu(), v_all.cpu()))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(helpers.tensor_words(a), helpers.tensor_words(b))
+    expect = attention.self_attention(batch.q[:1], batch.k[0], batch.v[0], batch.scale)
+    assert (outs[1][0][:1].float() - expect.float()).abs().max().item() <= 2e-2
+    with pytest.raises(LlaisysError):  # position 0 of a sequence needs kv_len >= 1
+        cache.decode_step_host(0, out, batch.q, k_new, v_new, np.asarray(seqs, np.int32),
+                               np.zeros(len(seqs), np.int32), nh, batch.scale)
+
+
+def test_decode_step_host_cpu():
+    check_decode_step_host(CPU)
+
+
+@pytest.mark.gpu
+def test_decode_step_host_nvidia(cuda_device):
+    check_decode_step_host(NVIDIA)
+
+
 def test_lse_merge_cpu():
     g = torch.Generator().manual_seed(9)
     q = workloads.randn((1, 12, 128), torch.float32, g)
