@@ -93,11 +93,10 @@ struct PrefillParams {
 
 // kPTmem: P goes from the softmax threads to the PV product through tensor memory (packed 16-bit pairs written over
 // the first 32 columns of the S buffer they were computed from, read back as the A operand) instead of through shared
-// memory. The kernel is bound by shared-memory bandwidth -- per 64-key block a CTA moves 32 KiB of TMA writes, 48 KiB
-// of QK^T operand reads, 32 KiB of PV operand reads and 16 KiB of P stores through a 128 B/clk port, about twice the
-// 512 clocks its MMAs need -- and this takes the P store and the P read (32 KiB of 128) off that port. It also frees
-// the softmax threads from waiting for the previous PV before they hand over P: consecutive P tiles sit in alternate
-// S buffers, and the tensor pipe runs its instructions in issue order (QK^T of block i + 2 is issued after PV of block i).
+// memory: per 64-key block this takes a 16 KiB store and a 16 KiB operand read off the shared-memory port (which also
+// carries 32 KiB of TMA writes, 48 KiB of QK^T operand reads and 16 KiB of V reads) and the proxy fence out of the
+// softmax-to-tensor-pipe chain. Consecutive P tiles sit in alternate S buffers; QK^T of block i + 2, which overwrites
+// the buffer of P(i), is issued after PV of block i.
 template <bool kBf16, bool kPTmem>
 __global__ void __launch_bounds__(kThreads, 2)
     paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, PrefillParams p) {
@@ -278,6 +277,7 @@ __global__ void __launch_bounds__(kThreads, 2)
                 if (ok && i >= 2) {
                     ok = wait_or_abort(bar(kBarSFree + buf), uint32_t((i >> 1) - 1) & 1u, s_abort);
                 }
+
                 if (!ok) {
                     break;
                 }
@@ -415,10 +415,13 @@ __global__ void __launch_bounds__(kThreads, 2)
                 }
             }
             l += (l0 + l1) + (l2 + l3);
-            // PV of the previous block must be finished before O is rescaled -- and, on the shared-memory path, before P
-            // is overwritten. With P in tensor memory only a rescale has to wait.
+            // PV of the previous block must be finished before O is rescaled and, on the shared-memory path, before P is
+            // overwritten. With P in tensor memory the hand-over itself would not need this wait, but every phase of the
+            // barrier has to be observed in order: a parity wait cannot tell "two phases behind" from "done", and a
+            // thread that skipped phases passed the final wait before the last two products had finished (rare wrong
+            // rows in tiles that ran alone on their SM).
             const bool any_grow = __any_sync(0xffffffffu, grow);
-            if (i >= 1 && (!kPTmem || any_grow)) {
+            if (i >= 1) {
                 if (!wait_or_abort(bar(kBarPFree), uint32_t(i - 1) & 1u, s_abort)) {
                     dead = true;
                     break;
