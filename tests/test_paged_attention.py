@@ -184,8 +184,9 @@ def test_data_path_argument_errors_cpu():
     cache.check()
 
 
-def check_decode_step_host(device):
-    """The one-call host-buffer step must leave the cache and the output exactly as append + decode do."""
+def check_decode_step_host(device, pinned=False):
+    """The one-call host-buffer step must leave the cache and the output exactly as append + decode do, with pageable
+    and with page-locked host buffers."""
     dev = helpers.torch_device(device)
     batch = workloads.decode_batch(5, 1, 300, seed=8, pool_pages=128)
     nkvh, d, nh = workloads.NKVH, workloads.D, workloads.NH
@@ -198,7 +199,10 @@ def check_decode_step_host(device):
         v_new = torch.stack([v[-1] for v in batch.v]).contiguous()
         out = torch.empty_like(batch.q)
         if fused:
-            cache.decode_step_host(0, out, batch.q, k_new, v_new, np.asarray(seqs, np.int32),
+            q_host = batch.q
+            if pinned:
+                out, q_host, k_new, v_new = (t.pin_memory() for t in (out, batch.q, k_new, v_new))
+            cache.decode_step_host(0, out, q_host, k_new, v_new, np.asarray(seqs, np.int32),
                                    np.asarray(batch.ctx, np.int32), nh, batch.scale)
         else:
             cache.append(0, k_new.to(dev), v_new.to(dev), seqs, last)
@@ -224,8 +228,9 @@ def test_decode_step_host_cpu():
 
 
 @pytest.mark.gpu
-def test_decode_step_host_nvidia(cuda_device):
-    check_decode_step_host(NVIDIA)
+@pytest.mark.parametrize("pinned", [False, True])
+def test_decode_step_host_nvidia(cuda_device, pinned):
+    check_decode_step_host(NVIDIA, pinned)
 
 
 def test_lse_merge_cpu():
