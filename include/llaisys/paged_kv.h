@@ -214,6 +214,32 @@ LLAISYS_API int llaisysPagedAttentionDecodeNoAlloc(int device_id, void *out, con
                                                    size_t nh, size_t nkvh, llaisysDataType_t dtype, float scale,
                                                    int32_t *error_flag_dev, llaisysStream_t stream);
 
+/* ---- split-KV decode across the GPUs of one node through peer memory --------------------------------------------- */
+/* For ONE long sequence whose KV range is cut across ranks (one process per GPU): instead of an all-gather through a
+ * collective library, every rank writes its partial (o, m, l) rows straight into slots of all the other ranks' exchange
+ * buffers over NVLink (buffers mapped with CUDA IPC), stamps a flag, and merges once the flags of all writers carry the
+ * step. Everything is queued on the given stream and can be captured in a CUDA graph. Waits for peers are bounded
+ * (about a second): a wait that runs out flags an error (llaisysPeerExchangeStatus) instead of hanging. */
+typedef struct LlaisysPeerExchange *llaisysPeerExchange_t;
+
+/* slot_floats: capacity for one rank's partial = rows * (head_dim + 2) floats, a multiple of 4. world <= 16. The
+ * calling thread's current device (llaisysSetContextRuntime) must be the rank's GPU. */
+LLAISYS_API int llaisysPeerExchangeCreate(llaisysPeerExchange_t *ex_out, int device_id, int rank, int world,
+                                          size_t slot_floats);
+LLAISYS_API void llaisysPeerExchangeDestroy(llaisysPeerExchange_t ex);
+/* 64 bytes that let the other ranks map this rank's buffer; send them over any host channel. */
+LLAISYS_API int llaisysPeerExchangeHandle(llaisysPeerExchange_t ex, void *out_64_bytes);
+/* handles: world * 64 bytes, entry i from rank i. Every rank must call it once before the first step. */
+LLAISYS_API int llaisysPeerExchangeConnect(llaisysPeerExchange_t ex, const void *handles);
+/* Partial decode of this rank's slice (as llaisysPagedAttentionDecodePartialDev) + exchange + merge into out
+ * [n_seqs, nh, head_dim]. Every rank passes the same q and its LOCAL sequences / lengths. */
+LLAISYS_API int llaisysPagedAttentionDecodeSplitDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
+                                                    const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
+                                                    size_t max_kv_len, size_t nh, float scale, llaisysPeerExchange_t ex,
+                                                    llaisysStream_t stream);
+/* Synchronises the stream; 0, or 1 when a wait for a peer ran out since the last call (cleared by the call). */
+LLAISYS_API int llaisysPeerExchangeStatus(llaisysPeerExchange_t ex, llaisysStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -2,6 +2,9 @@
 // failure becomes a status code plus a thread-local message (llaisysGetLastError).
 #include "llaisys/paged_kv.h"
 
+#include "../comm/peer_exchange.hpp"
+#include "../core/core.hpp"
+
 #include "../cpu/cpu_kernels.hpp"
 #include "../kv/paged_kv.hpp"
 #ifdef ENABLE_NVIDIA_API
@@ -213,6 +216,94 @@ int llaisysPagedDecodeStepHost(llaisysPagedKV_t kv, size_t layer, void *out_host
         kv->impl.decodeStepHost(layer, out_host, q_host, k_new_host, v_new_host, seq_ids, kv_lens, n_seqs, nh, scale);
     });
 }
+
+#ifdef ENABLE_NVIDIA_API
+struct LlaisysPeerExchange {
+    llaisys::comm::PeerExchange impl;
+    int device_id;
+    LlaisysPeerExchange(int device, int rank, int world, size_t slot_floats) : impl(rank, world, slot_floats), device_id(device) {}
+};
+#else
+struct LlaisysPeerExchange {};
+#endif
+
+int llaisysPeerExchangeCreate(llaisysPeerExchange_t *ex_out, int device_id, int rank, int world, size_t slot_floats) {
+    if (ex_out == nullptr) {
+        llaisys::kernels::set_last_error("peer exchange: null output");
+        return LLAISYS_E_INVALID;
+    }
+#ifdef ENABLE_NVIDIA_API
+    return guarded([&] {
+        llaisys::core::context().setDevice(LLAISYS_DEVICE_NVIDIA, device_id);
+        *ex_out = new LlaisysPeerExchange(device_id, rank, world, slot_floats);
+    });
+#else
+    (void)device_id, (void)rank, (void)world, (void)slot_floats;
+    llaisys::kernels::set_last_error("this build has no NVIDIA backend");
+    return LLAISYS_E_UNSUPPORTED;
+#endif
+}
+void llaisysPeerExchangeDestroy(llaisysPeerExchange_t ex) {
+#ifdef ENABLE_NVIDIA_API
+    if (ex != nullptr) {
+        try {
+            llaisys::core::context().setDevice(LLAISYS_DEVICE_NVIDIA, ex->device_id);
+        } catch (...) {
+        }
+    }
+#endif
+    delete ex;
+}
+#ifdef ENABLE_NVIDIA_API
+#define EX_OR_FAIL(ex)                                                  \
+    if ((ex) == nullptr) {                                              \
+        llaisys::kernels::set_last_error("peer exchange: null handle"); \
+        return LLAISYS_E_INVALID;                                       \
+    }
+int llaisysPeerExchangeHandle(llaisysPeerExchange_t ex, void *out_64_bytes) {
+    EX_OR_FAIL(ex);
+    return guarded([&] { ex->impl.localHandle(out_64_bytes); });
+}
+int llaisysPeerExchangeConnect(llaisysPeerExchange_t ex, const void *handles) {
+    EX_OR_FAIL(ex);
+    return guarded([&] {
+        llaisys::core::context().setDevice(LLAISYS_DEVICE_NVIDIA, ex->device_id);
+        ex->impl.connect(handles);
+    });
+}
+int llaisysPagedAttentionDecodeSplitDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q, const int32_t *seq_ids_dev,
+                                        const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len, size_t nh, float scale,
+                                        llaisysPeerExchange_t ex, llaisysStream_t stream) {
+    KV_OR_FAIL(kv);
+    EX_OR_FAIL(ex);
+    return guarded([&] {
+        const auto &cfg = kv->impl.config();
+        const size_t rows = n_seqs * nh;
+        if (rows * (cfg.head_dim + 2) > ex->impl.slotFloats()) {
+            throw llaisys::kv::StatusError(LLAISYS_E_INVALID, "split decode: the exchange's slots are too small for this batch");
+        }
+        kv->impl.decodeDev(layer, nullptr, ex->impl.localPartial(), q, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale,
+                           stream);
+        ex->impl.exchangeAndMerge(stream, cfg.dtype, out, int(rows), int(cfg.head_dim));
+    });
+}
+int llaisysPeerExchangeStatus(llaisysPeerExchange_t ex, llaisysStream_t stream) {
+    if (ex == nullptr) {
+        return -1;
+    }
+    int status = -1;
+    const int rc = guarded([&] { status = ex->impl.status(stream); });
+    return rc == LLAISYS_OK ? status : -1;
+}
+#else
+int llaisysPeerExchangeHandle(llaisysPeerExchange_t, void *) { return LLAISYS_E_UNSUPPORTED; }
+int llaisysPeerExchangeConnect(llaisysPeerExchange_t, const void *) { return LLAISYS_E_UNSUPPORTED; }
+int llaisysPagedAttentionDecodeSplitDev(llaisysPagedKV_t, size_t, void *, const void *, const int32_t *, const int32_t *, size_t,
+                                        size_t, size_t, float, llaisysPeerExchange_t, llaisysStream_t) {
+    return LLAISYS_E_UNSUPPORTED;
+}
+int llaisysPeerExchangeStatus(llaisysPeerExchange_t, llaisysStream_t) { return -1; }
+#endif
 
 int llaisysPagedKVSeqPublish(llaisysPagedKV_t kv, int32_t seq, const int64_t *tokens, size_t n_tokens) {
     KV_OR_FAIL(kv);

@@ -1,0 +1,233 @@
+#include "peer_exchange.hpp"
+
+#include "../kernels/device_utils.cuh"
+#include "../kv/paged_kv.hpp"
+#include "llaisys/paged_kv.h"
+
+#include <algorithm>
+#include <cstring>
+#include <string>
+
+namespace llaisys::comm {
+
+namespace {
+
+[[noreturn]] void fail(int code, const std::string &msg) { throw kv::StatusError(code, msg); }
+
+void cuda_ok(cudaError_t rc, const char *what) {
+    if (rc != cudaSuccess) {
+        (void)cudaGetLastError();
+        fail(LLAISYS_E_DEVICE, std::string(what) + ": " + cudaGetErrorString(rc));
+    }
+}
+
+constexpr uint32_t kSpinLimit = 4u << 20; // polls of ~0.2 us each: gives up after about a second
+constexpr int kErrPeerTimeout = 1;
+
+struct PeerTable {
+    unsigned char *base[kMaxPeers]; // every rank's buffer as this rank sees it
+};
+
+__device__ __forceinline__ void store_release_sys(uint32_t *addr, uint32_t value) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(addr), "r"(value) : "memory");
+}
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t *addr) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+
+// grid (blocks, world): block row y copies the local partial into slot `rank` (of the step's parity) on rank y.
+__global__ void peer_push_kernel(PeerTable t, const float4 *__restrict__ src, size_t n_vec, size_t slot_floats, int rank,
+                                 int world, size_t epoch_offset) {
+    const uint32_t step = *reinterpret_cast<const uint32_t *>(t.base[rank] + epoch_offset) + 1;
+    float *dst_f = reinterpret_cast<float *>(t.base[blockIdx.y]) + (size_t(step & 1u) * world + rank) * slot_floats;
+    float4 *dst = reinterpret_cast<float4 *>(dst_f);
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
+        dst[i] = src[i];
+    }
+    __threadfence_system(); // this thread's peer stores are visible to the whole system before the grid can end
+}
+
+// One thread per destination rank: everything the push kernel stored is ordered before the flag.
+__global__ void peer_signal_kernel(PeerTable t, int rank, int world, size_t flags_offset, size_t epoch_offset) {
+    const uint32_t step = *reinterpret_cast<const uint32_t *>(t.base[rank] + epoch_offset) + 1;
+    if (int(threadIdx.x) < world) {
+        __threadfence_system();
+        store_release_sys(reinterpret_cast<uint32_t *>(t.base[threadIdx.x] + flags_offset) + rank, step);
+    }
+}
+
+// Waits for every writer's flag, then merges: out[r] = sum_p w_p o_p[r] / sum_p w_p with w_p = l_p exp(m_p - M)
+// (the same arithmetic as the library's LSE merge; one warp per row).
+template <typename T>
+__global__ void peer_merge_kernel(T *__restrict__ out, unsigned char *local_base, size_t slot_floats, int world, int n_rows,
+                                  int d, size_t flags_offset, size_t epoch_offset, size_t error_offset) {
+    const uint32_t step = *reinterpret_cast<const uint32_t *>(local_base + epoch_offset) + 1;
+    if (int(threadIdx.x) < world) {
+        const uint32_t *flag = reinterpret_cast<const uint32_t *>(local_base + flags_offset) + threadIdx.x;
+        uint32_t spins = 0;
+        // flags only grow; a value ahead of the step means the writer is already one step further (allowed)
+        while (int32_t(load_acquire_sys(flag) - step) < 0) {
+            if (++spins > kSpinLimit) {
+                atomicOr(reinterpret_cast<int *>(local_base + error_offset), kErrPeerTimeout);
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    __syncthreads();
+    const int warps_per_block = blockDim.x >> 5;
+    const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= n_rows) {
+        return;
+    }
+    const float *parts = reinterpret_cast<const float *>(local_base) + size_t(step & 1u) * world * slot_floats;
+    const float *base = parts + size_t(row) * (d + 2);
+    float m_all = -INFINITY;
+    for (int p = 0; p < world; ++p) {
+        if (base[p * slot_floats + d + 1] > 0.f) {
+            m_all = fmaxf(m_all, base[p * slot_floats + d]);
+        }
+    }
+    float l_all = 0.f;
+    for (int p = 0; p < world; ++p) {
+        const float l = base[p * slot_floats + d + 1];
+        if (l > 0.f) {
+            l_all += l * expf(base[p * slot_floats + d] - m_all);
+        }
+    }
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    for (int dim = lane; dim < d; dim += 32) {
+        float o = 0.f;
+        for (int p = 0; p < world; ++p) {
+            const float l = base[p * slot_floats + d + 1];
+            if (l > 0.f) {
+                o = fmaf(l * expf(base[p * slot_floats + d] - m_all), base[p * slot_floats + dim], o);
+            }
+        }
+        out[size_t(row) * d + dim] = kernels::from_f32<T>(o * inv);
+    }
+}
+
+__global__ void peer_bump_kernel(unsigned char *local_base, size_t epoch_offset) {
+    *reinterpret_cast<uint32_t *>(local_base + epoch_offset) += 1;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+} // namespace
+
+PeerExchange::PeerExchange(int rank, int world, size_t slot_floats) : _rank(rank), _world(world), _slot_floats(slot_floats) {
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || slot_floats == 0 || slot_floats % 4 != 0) {
+        fail(LLAISYS_E_INVALID, "peer exchange: bad rank, world size (at most 16) or slot size (a multiple of 4 floats)");
+    }
+    const size_t slots_bytes = 2 * size_t(world) * slot_floats * sizeof(float);
+    _flags_offset = align_up(slots_bytes, 256);
+    _epoch_offset = _flags_offset + align_up(size_t(world) * sizeof(uint32_t), 256);
+    _error_offset = _epoch_offset + 256;
+    _bytes = _error_offset + 256;
+    cuda_ok(cudaMalloc(&_base, _bytes), "peer exchange: cudaMalloc");
+    cuda_ok(cudaMemset(_base, 0, _bytes), "peer exchange: cudaMemset");
+    cuda_ok(cudaMalloc(&_local_part, slot_floats * sizeof(float)), "peer exchange: cudaMalloc");
+    cuda_ok(cudaMemset(_local_part, 0, slot_floats * sizeof(float)), "peer exchange: cudaMemset");
+    cuda_ok(cudaDeviceSynchronize(), "peer exchange: synchronize");
+    _peer.assign(size_t(world), nullptr);
+    _peer[size_t(rank)] = _base;
+    _connected = world == 1;
+}
+
+PeerExchange::~PeerExchange() {
+    (void)cudaDeviceSynchronize();
+    for (int p = 0; p < _world; ++p) {
+        if (p != _rank && _peer[size_t(p)] != nullptr) {
+            (void)cudaIpcCloseMemHandle(_peer[size_t(p)]);
+        }
+    }
+    (void)cudaFree(_local_part);
+    (void)cudaFree(_base);
+    (void)cudaGetLastError();
+}
+
+void PeerExchange::localHandle(void *out_64_bytes) const {
+    static_assert(sizeof(cudaIpcMemHandle_t) == kIpcHandleBytes, "IPC handle size");
+    if (out_64_bytes == nullptr) {
+        fail(LLAISYS_E_INVALID, "peer exchange: null output");
+    }
+    cudaIpcMemHandle_t h;
+    cuda_ok(cudaIpcGetMemHandle(&h, _base), "peer exchange: cudaIpcGetMemHandle");
+    memcpy(out_64_bytes, &h, sizeof(h));
+}
+
+void PeerExchange::connect(const void *handles) {
+    if (handles == nullptr) {
+        fail(LLAISYS_E_INVALID, "peer exchange: null handles");
+    }
+    if (_connected) {
+        fail(LLAISYS_E_INVALID, "peer exchange: already connected");
+    }
+    for (int p = 0; p < _world; ++p) {
+        if (p == _rank) {
+            continue;
+        }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const unsigned char *>(handles) + size_t(p) * kIpcHandleBytes, sizeof(h));
+        void *mapped = nullptr;
+        cuda_ok(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess), "peer exchange: cudaIpcOpenMemHandle");
+        _peer[size_t(p)] = static_cast<unsigned char *>(mapped);
+    }
+    _connected = true;
+}
+
+void PeerExchange::exchangeAndMerge(llaisysStream_t stream, llaisysDataType_t dtype, void *out, int n_rows, int d) {
+    if (!_connected) {
+        fail(LLAISYS_E_INVALID, "peer exchange: connect() has not been called");
+    }
+    if (n_rows <= 0 || d <= 0 || out == nullptr || size_t(n_rows) * size_t(d + 2) > _slot_floats ||
+        (size_t(n_rows) * size_t(d + 2)) % 4 != 0) {
+        fail(LLAISYS_E_INVALID, "peer exchange: rows do not fit the slot (or are not a multiple of 16 bytes)");
+    }
+    auto s = static_cast<cudaStream_t>(stream);
+    PeerTable t{};
+    for (int p = 0; p < _world; ++p) {
+        t.base[p] = _peer[size_t(p)];
+    }
+    const size_t n_vec = size_t(n_rows) * size_t(d + 2) / 4;
+    const unsigned blocks = unsigned(std::min<size_t>((n_vec + 255) / 256, 64));
+    peer_push_kernel<<<dim3(blocks, unsigned(_world)), 256, 0, s>>>(t, reinterpret_cast<const float4 *>(_local_part), n_vec,
+                                                                    _slot_floats, _rank, _world, _epoch_offset);
+    peer_signal_kernel<<<1, 32, 0, s>>>(t, _rank, _world, _flags_offset, _epoch_offset);
+    const int block = 128, grid = (n_rows + 3) / 4;
+    switch (dtype) {
+    case LLAISYS_DTYPE_F32:
+        peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<float *>(out), _base, _slot_floats, _world, n_rows, d,
+                                                 _flags_offset, _epoch_offset, _error_offset);
+        break;
+    case LLAISYS_DTYPE_F16:
+        peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<__half *>(out), _base, _slot_floats, _world, n_rows, d,
+                                                 _flags_offset, _epoch_offset, _error_offset);
+        break;
+    case LLAISYS_DTYPE_BF16:
+        peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<__nv_bfloat16 *>(out), _base, _slot_floats, _world, n_rows, d,
+                                                 _flags_offset, _epoch_offset, _error_offset);
+        break;
+    default:
+        fail(LLAISYS_E_INVALID, "peer exchange: unsupported output type");
+    }
+    peer_bump_kernel<<<1, 1, 0, s>>>(_base, _epoch_offset);
+    kernels::check_launch("peer_exchange");
+}
+
+int PeerExchange::status(llaisysStream_t stream) {
+    auto s = static_cast<cudaStream_t>(stream);
+    int host = 0;
+    cuda_ok(cudaMemcpyAsync(&host, _base + _error_offset, sizeof(host), cudaMemcpyDeviceToHost, s), "peer exchange: status");
+    cuda_ok(cudaStreamSynchronize(s), "peer exchange: status");
+    if (host != 0) {
+        cuda_ok(cudaMemsetAsync(_base + _error_offset, 0, sizeof(host), s), "peer exchange: status");
+    }
+    return host;
+}
+
+} // namespace llaisys::comm

@@ -200,6 +200,13 @@ PROTOTYPES: dict[str, tuple] = {
     "llaisysPagedAttentionDecodeNoAlloc": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_size_t,
                                                    c_void_p, c_void_p, c_size_t, c_size_t, c_size_t, c_size_t,
                                                    llaisysDataType_t, c_float, c_void_p, llaisysStream_t]),
+    "llaisysPeerExchangeCreate": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_size_t]),
+    "llaisysPeerExchangeDestroy": (None, [c_void_p]),
+    "llaisysPeerExchangeHandle": (c_int, [c_void_p, c_void_p]),
+    "llaisysPeerExchangeConnect": (c_int, [c_void_p, c_void_p]),
+    "llaisysPagedAttentionDecodeSplitDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                                    c_size_t, c_size_t, c_float, c_void_p, llaisysStream_t]),
+    "llaisysPeerExchangeStatus": (c_int, [c_void_p, llaisysStream_t]),
     # include/llaisys/models/qwen2.h
     "llaisysQwen2ModelCreate": (_MODEL, [POINTER(LlaisysQwen2Meta), llaisysDeviceType_t, POINTER(c_int), c_int]),
     "llaisysQwen2ModelDestroy": (None, [_MODEL]),

@@ -5,8 +5,9 @@ Two modes, matching how the path shards:
     pool and block tables and there is NO data-path collective;
   * one very long sequence: the KV range is cut into page-aligned slices, one per rank; each rank runs the
     partial decode over its slice and the (o, m, l) partials are merged after ONE all-gather
-    (NCCL over NVLink on GPUs, gloo on CPU ranks). Peer data always lands in local memory first; no kernel
-    reads another GPU's memory.
+    (NCCL over NVLink on GPUs, gloo on CPU ranks) -- or, on the GPUs of one node, after every rank has written
+    its partial straight into the other ranks' exchange buffers over NVLink (`PeerExchange`, peer stores into
+    IPC-mapped memory; no kernel ever READS another GPU's memory).
 """
 from __future__ import annotations
 
@@ -63,6 +64,58 @@ def split_decode(cache: PagedKVCache, layer: int, out: torch.Tensor, q: torch.Te
         torch.cuda.ExternalStream(_context_stream()).wait_stream(torch.cuda.current_stream())
     lse_merge(out, gathered, world, n_seqs * nh, d, dtype=cache.dtype, device=cache.device,
               device_id=cache.device_id)
+
+
+class PeerExchange:
+    """Per-rank exchange buffer for split-KV decode through peer memory (include/llaisys/paged_kv.h,
+    llaisysPeerExchange*): every rank creates one, the IPC handles travel through the process group, and each
+    `split_decode` step is then partial decode + peer stores + flags + merge, all on the library's stream
+    (capturable in a CUDA graph). One process per GPU, all on one node."""
+
+    def __init__(self, max_rows: int, head_dim: int, *, device_id: int, group=None):
+        import ctypes
+
+        from .libllaisys import LIB_LLAISYS
+        from .paged_kv import _check
+
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        slot = -(-max_rows * (head_dim + 2) // 4) * 4
+        self._ex = ctypes.c_void_p()
+        _check(LIB_LLAISYS.llaisysPeerExchangeCreate(ctypes.byref(self._ex), device_id, self.rank, self.world, slot))
+        mine = ctypes.create_string_buffer(64)
+        _check(LIB_LLAISYS.llaisysPeerExchangeHandle(self._ex, mine))
+        handles: list = [None] * self.world
+        dist.all_gather_object(handles, mine.raw, group=group)
+        _check(LIB_LLAISYS.llaisysPeerExchangeConnect(self._ex, ctypes.create_string_buffer(b"".join(handles), 64 * self.world)))
+        dist.barrier(group=group)  # nobody pushes before everybody has mapped everybody
+
+    def split_decode(self, cache: PagedKVCache, layer: int, out, q, seq_ids_dev, kv_lens_dev, n_seqs: int,
+                     max_kv_len: int, nh: int, scale: float, stream) -> None:
+        """Decode over a KV range split across the ranks: every rank passes the same q and its LOCAL sequences and
+        lengths as device int32 arrays (0 is a valid length); out [n_seqs, nh, d] is the merged result on every rank."""
+        from .libllaisys import LIB_LLAISYS
+        from .paged_kv import _addr, _check
+
+        _check(LIB_LLAISYS.llaisysPagedAttentionDecodeSplitDev(cache._kv, layer, _addr(out), _addr(q), _addr(seq_ids_dev),
+                                                               _addr(kv_lens_dev), n_seqs, max_kv_len, nh, scale,
+                                                               self._ex, stream))
+
+    def check(self, stream) -> None:
+        """Synchronises the stream and raises if a wait for a peer ran out."""
+        from .libllaisys import LIB_LLAISYS
+
+        status = LIB_LLAISYS.llaisysPeerExchangeStatus(self._ex, stream)
+        if status != 0:
+            raise RuntimeError(f"peer exchange: a wait for another rank ran out (status {status})")
+
+    def close(self) -> None:
+        from .libllaisys import LIB_LLAISYS
+
+        if getattr(self, "_ex", None):
+            dist.barrier(group=self.group)  # nobody unmaps while a peer may still write
+            LIB_LLAISYS.llaisysPeerExchangeDestroy(self._ex)
+            self._ex = None
 
 
 def _context_stream() -> int:
