@@ -641,6 +641,39 @@ def run_longctx_workload(args) -> None:
     def only_decode():
         cache.decode_partial(0, part, q, seqs, lens, NH, scale)
 
+    def only_decode_one_layer():
+        cache.decode_partial(0, part[:1], q[:1], seqs[:1], [local], NH, scale)
+
+    # ---- the same step through peer memory: partial decode, NVLink stores into every rank's slots, flags, merge --
+    # (no collective library, no host work between the kernels: captured once, replayed)
+    peer = None
+    if world > 1:
+        peer = sharding.PeerExchange(n_layers * NH, D, device_id=local_rank)
+        seq_dev = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+        len_dev = torch.full((n_layers,), local, dtype=torch.int32, device="cuda")
+        out_p = torch.empty_like(q)
+
+        def peer_batched():
+            peer.split_decode(cache, 0, out_p, q, seq_dev, len_dev, n_layers, local, NH, scale, cs)
+
+        def peer_per_layer():
+            for layer in range(n_layers):
+                peer.split_decode(cache, 0, out_p[layer:layer + 1], q[layer:layer + 1], seq_dev[layer:layer + 1],
+                                  len_dev[layer:layer + 1], 1, local, NH, scale, cs)
+
+        def graphed(body):
+            body()  # eager once: sizes scratch before the capture
+            peer.check(cs)
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=ext):
+                body()
+
+            def replay():
+                with torch.cuda.stream(ext):
+                    graph.replay()
+            return replay
+
     def timed(body, n):
         for _ in range(3):
             body()
@@ -662,11 +695,26 @@ def run_longctx_workload(args) -> None:
         batched_ms = timed(step_batched, steps)
     per_layer_ms = timed(step_per_layer, max(5, steps // 10))
     decode_ms = timed(only_decode, steps)
+    decode_layer_ms = timed(only_decode_one_layer, steps)
     cache.check()
-    stats = torch.tensor([batched_ms, per_layer_ms, decode_ms], device="cuda", dtype=torch.float64)
+    peer_ms = peer_layer_ms = float("nan")
+    peer_same = None
+    if peer is not None:
+        step_batched()
+        torch.cuda.synchronize()
+        expect = out.clone()
+        peer_ms = timed(graphed(peer_batched), steps)
+        peer.check(cs)
+        peer_same = bool(torch.equal(out_p.view(torch.int16), expect.view(torch.int16)))  # same partials, same merge order
+        peer_layer_ms = timed(graphed(peer_per_layer), max(5, steps // 10))
+        peer.check(cs)
+    stats = torch.tensor([batched_ms, per_layer_ms, decode_ms, peer_ms, peer_layer_ms], device="cuda", dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        batched_ms, per_layer_ms, decode_ms = (float(x) for x in stats)
+        batched_ms, per_layer_ms, decode_ms, peer_ms, peer_layer_ms = (float(x) for x in stats)
+    nccl_ms, nccl_layer_ms = batched_ms, per_layer_ms
+    if peer is not None:  # the headline is the peer-memory path; the NCCL path is reported beside it
+        batched_ms, per_layer_ms = peer_ms, peer_layer_ms
     if rank == 0:
         hbm_peak, _, kind = _peaks()
         bytes_per_launch = n_layers * local * (2 * NKVH * D * 2) + 2 * n_layers * NH * D * 2 + 4 * n_layers * pages_per
@@ -677,8 +725,11 @@ def run_longctx_workload(args) -> None:
             "ms_per_step": batched_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "config5", "context": total_tokens, "layers": n_layers, "tokens_per_gpu": local,
-                       "heads": "12q/2kv", "head_dim": D, "page_size": PAGE, "mode": "batched: one launch, one all-gather, one merge",
-                       "parallelism": f"KV range split over {world} GPU(s), one NCCL all-gather of (o, m, l) per step",
+                       "heads": "12q/2kv", "head_dim": D, "page_size": PAGE,
+                       "mode": ("batched: one partial-decode launch, partials stored into every rank's exchange slots over "
+                                "NVLink (peer memory), flags, one merge; replayed as a CUDA graph") if peer is not None
+                       else "batched: one launch, one merge",
+                       "parallelism": f"KV range split over {world} GPU(s), (o, m, l) partials exchanged through peer memory",
                        "l2": f"{bytes_per_launch >> 20} MiB of K/V per GPU per step, larger than L2" if bytes_per_launch > 2e8
                        else f"{bytes_per_launch >> 20} MiB of K/V per GPU per step (fits L2 at this GPU count)"},
             "roofline": {"bound": "hbm", "kernel": "paged_decode_tma_kernel", "achieved": achieved, "peak": hbm_peak,
@@ -686,11 +737,19 @@ def run_longctx_workload(args) -> None:
                          "frac_of_nominal_8000": achieved / 8000.0, "traffic": None,
                          "algorithmic_bytes_per_launch": bytes_per_launch, "kernel_ms_mean": decode_ms},
             "per_layer": {"ms_per_step": per_layer_ms, "value": 1e3 / per_layer_ms,
-                          "note": "28 dependent rounds of partial decode + all-gather + merge"},
-            "e2e": None, "gpu_launches": 2 * steps, "timing": "CUDA events on the library stream, max over ranks",
+                          "note": "28 dependent rounds of partial decode + exchange + merge",
+                          "decode_kernel_ms_one_layer_host_driven": decode_layer_ms},
+            "nccl_all_gather": None if peer is None else {
+                "ms_per_step": nccl_ms, "per_layer_ms_per_step": nccl_layer_ms, "peer_path_matches": peer_same,
+                "note": "the same step with torch.distributed all_gather_into_tensor (NCCL) between the library calls, "
+                        "driven from the host"},
+            "e2e": None, "gpu_launches": (5 if peer is not None else 2) * steps,
+            "timing": "CUDA events on the library stream, max over ranks",
             "clocks": clocks.summary(),
         }
         print(json.dumps(line), flush=True)
+    if peer is not None:
+        peer.close()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

@@ -37,24 +37,20 @@ __device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t *addr) {
     return v;
 }
 
-// grid (blocks, world): block row y copies the local partial into slot `rank` (of the step's parity) on rank y.
+// One CTA per destination rank: copy the local partial into slot `rank` (of the step's parity) of that rank's buffer,
+// then -- all of the CTA's stores done and fenced at system scope -- stamp this rank's flag there with the step.
 __global__ void peer_push_kernel(PeerTable t, const float4 *__restrict__ src, size_t n_vec, size_t slot_floats, int rank,
-                                 int world, size_t epoch_offset) {
+                                 int world, size_t flags_offset, size_t epoch_offset) {
     const uint32_t step = *reinterpret_cast<const uint32_t *>(t.base[rank] + epoch_offset) + 1;
-    float *dst_f = reinterpret_cast<float *>(t.base[blockIdx.y]) + (size_t(step & 1u) * world + rank) * slot_floats;
-    float4 *dst = reinterpret_cast<float4 *>(dst_f);
-    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += size_t(gridDim.x) * blockDim.x) {
+    unsigned char *peer = t.base[blockIdx.x];
+    float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(peer) + (size_t(step & 1u) * world + rank) * slot_floats);
+    for (size_t i = threadIdx.x; i < n_vec; i += blockDim.x) {
         dst[i] = src[i];
     }
-    __threadfence_system(); // this thread's peer stores are visible to the whole system before the grid can end
-}
-
-// One thread per destination rank: everything the push kernel stored is ordered before the flag.
-__global__ void peer_signal_kernel(PeerTable t, int rank, int world, size_t flags_offset, size_t epoch_offset) {
-    const uint32_t step = *reinterpret_cast<const uint32_t *>(t.base[rank] + epoch_offset) + 1;
-    if (int(threadIdx.x) < world) {
-        __threadfence_system();
-        store_release_sys(reinterpret_cast<uint32_t *>(t.base[threadIdx.x] + flags_offset) + rank, step);
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        store_release_sys(reinterpret_cast<uint32_t *>(peer + flags_offset) + rank, step);
     }
 }
 
@@ -80,39 +76,44 @@ __global__ void peer_merge_kernel(T *__restrict__ out, unsigned char *local_base
     const int warps_per_block = blockDim.x >> 5;
     const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
-    if (row >= n_rows) {
-        return;
-    }
-    const float *parts = reinterpret_cast<const float *>(local_base) + size_t(step & 1u) * world * slot_floats;
-    const float *base = parts + size_t(row) * (d + 2);
-    float m_all = -INFINITY;
-    for (int p = 0; p < world; ++p) {
-        if (base[p * slot_floats + d + 1] > 0.f) {
-            m_all = fmaxf(m_all, base[p * slot_floats + d]);
+    if (row < n_rows) {
+        const float *parts = reinterpret_cast<const float *>(local_base) + size_t(step & 1u) * world * slot_floats;
+        const float *base = parts + size_t(row) * (d + 2);
+        float m_all = -INFINITY;
+        for (int p = 0; p < world; ++p) {
+            if (base[p * slot_floats + d + 1] > 0.f) {
+                m_all = fmaxf(m_all, base[p * slot_floats + d]);
+            }
         }
-    }
-    float l_all = 0.f;
-    for (int p = 0; p < world; ++p) {
-        const float l = base[p * slot_floats + d + 1];
-        if (l > 0.f) {
-            l_all += l * expf(base[p * slot_floats + d] - m_all);
-        }
-    }
-    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-    for (int dim = lane; dim < d; dim += 32) {
-        float o = 0.f;
+        float l_all = 0.f;
         for (int p = 0; p < world; ++p) {
             const float l = base[p * slot_floats + d + 1];
             if (l > 0.f) {
-                o = fmaf(l * expf(base[p * slot_floats + d] - m_all), base[p * slot_floats + dim], o);
+                l_all += l * expf(base[p * slot_floats + d] - m_all);
             }
         }
-        out[size_t(row) * d + dim] = kernels::from_f32<T>(o * inv);
+        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+        for (int dim = lane; dim < d; dim += 32) {
+            float o = 0.f;
+            for (int p = 0; p < world; ++p) {
+                const float l = base[p * slot_floats + d + 1];
+                if (l > 0.f) {
+                    o = fmaf(l * expf(base[p * slot_floats + d] - m_all), base[p * slot_floats + dim], o);
+                }
+            }
+            out[size_t(row) * d + dim] = kernels::from_f32<T>(o * inv);
+        }
     }
-}
-
-__global__ void peer_bump_kernel(unsigned char *local_base, size_t epoch_offset) {
-    *reinterpret_cast<uint32_t *>(local_base + epoch_offset) += 1;
+    // The CTA that finishes last moves the step counter on (every CTA read it at its start, before it could finish).
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t *done = reinterpret_cast<uint32_t *>(local_base + epoch_offset) + 1;
+        __threadfence();
+        if (atomicAdd(done, 1u) == gridDim.x - 1) {
+            *done = 0;
+            *reinterpret_cast<volatile uint32_t *>(local_base + epoch_offset) = step;
+        }
+    }
 }
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -194,10 +195,8 @@ void PeerExchange::exchangeAndMerge(llaisysStream_t stream, llaisysDataType_t dt
         t.base[p] = _peer[size_t(p)];
     }
     const size_t n_vec = size_t(n_rows) * size_t(d + 2) / 4;
-    const unsigned blocks = unsigned(std::min<size_t>((n_vec + 255) / 256, 64));
-    peer_push_kernel<<<dim3(blocks, unsigned(_world)), 256, 0, s>>>(t, reinterpret_cast<const float4 *>(_local_part), n_vec,
-                                                                    _slot_floats, _rank, _world, _epoch_offset);
-    peer_signal_kernel<<<1, 32, 0, s>>>(t, _rank, _world, _flags_offset, _epoch_offset);
+    peer_push_kernel<<<unsigned(_world), 512, 0, s>>>(t, reinterpret_cast<const float4 *>(_local_part), n_vec, _slot_floats,
+                                                      _rank, _world, _flags_offset, _epoch_offset);
     const int block = 128, grid = (n_rows + 3) / 4;
     switch (dtype) {
     case LLAISYS_DTYPE_F32:
@@ -215,7 +214,6 @@ void PeerExchange::exchangeAndMerge(llaisysStream_t stream, llaisysDataType_t dt
     default:
         fail(LLAISYS_E_INVALID, "peer exchange: unsupported output type");
     }
-    peer_bump_kernel<<<1, 1, 0, s>>>(_base, _epoch_offset);
     kernels::check_launch("peer_exchange");
 }
 

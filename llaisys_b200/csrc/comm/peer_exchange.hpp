@@ -3,10 +3,10 @@
 // NVLink; a flag per writer, stamped with the step number, tells the owner when a slot is complete.
 //
 // One step on rank r (all on the caller's stream, capturable in a CUDA graph):
-//   push    copy the local partial (o, m, l rows) into slot r of EVERY rank's buffer (plain peer stores),
-//   signal  system-scope fence, then flag[r] = step on every rank,
-//   merge   wait (bounded) until all of this rank's flags carry the step, then log-sum-exp merge the slots,
-//   bump    step += 1.
+//   push    one CTA per destination: copy the local partial (o, m, l rows) into slot r of that rank's buffer (plain
+//           peer stores), system-scope fence, then flag[r] = step there;
+//   merge   wait (bounded) until all of this rank's flags carry the step, log-sum-exp merge the slots; the last CTA to
+//           finish moves the device-side step counter on.
 // Slots are double-buffered by the step's parity: a rank can run at most one step ahead of the slowest (its next wait
 // needs that rank's next push), so a writer never overwrites a slot that is still being merged. No kernel waits
 // without a limit: a wait that runs out sets the error word and the merge runs on what is there.
@@ -41,7 +41,7 @@ public:
     void connect(const void *handles);
     // Device buffer the local partial decode writes to ([rows][d + 2] floats, at most slotFloats()).
     float *localPartial() const { return _local_part; }
-    // push + signal + merge + bump for n_rows rows of head dimension d; out is [n_rows, d] of dtype.
+    // push + merge for n_rows rows of head dimension d; out is [n_rows, d] of dtype.
     void exchangeAndMerge(llaisysStream_t stream, llaisysDataType_t dtype, void *out, int n_rows, int d);
     // Synchronises the stream, returns and clears the error word (0 = fine, 1 = a wait for a peer ran out).
     int status(llaisysStream_t stream);
