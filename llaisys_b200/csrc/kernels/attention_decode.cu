@@ -31,6 +31,8 @@
 // Rows past a sequence's length inside its last page are zero-filled by the copy (src-size 0), never read
 // from the pool; out-of-range block-table entries are skipped and flagged in the error word.
 #include "kernels.hpp"
+
+#include <cstdlib>
 #include "decode_epilogue.cuh"
 #include "mma_utils.cuh"
 
@@ -505,7 +507,14 @@ int sm_count() {
 
 int decode_grid_size(int32_t n_seqs, int32_t nkvh, int32_t max_kv_len) {
     const long long pages_bound = (long long)n_seqs * nkvh * ((max_kv_len + kPage - 1) / kPage);
-    const long long by_work = (pages_bound + kPagesPerStage - 1) / kPagesPerStage; // at least one stage per CTA
+    // at least one stage of pages per CTA (LLAISYS_DECODE_MIN_PAGES_PER_CTA: a measuring knob for small workloads,
+    // where fewer, longer spans mean fewer partial results to combine)
+    static const long long min_pages = [] {
+        const char *e = std::getenv("LLAISYS_DECODE_MIN_PAGES_PER_CTA");
+        const long long v = e ? std::atoll(e) : 0;
+        return v > kPagesPerStage ? v : (long long)kPagesPerStage;
+    }();
+    const long long by_work = (pages_bound + min_pages - 1) / min_pages;
     const long long cap = (long long)kCtasPerSm * sm_count();
     return int(by_work < 1 ? 1 : (by_work < cap ? by_work : cap));
 }
