@@ -527,7 +527,8 @@ def run_model_workload(args) -> None:
         e2e_s = time.perf_counter() - t0
         e2e = {"value": total_seqs * (n_e2e - 1) / e2e_s, "unit": "tokens/s", "steps": n_e2e - 1,
                "h2d_bytes_per_step": B * (4 * 8 + 5 * 4) + 4, "d2h_bytes_per_step": B * 8,
-               "what": "Qwen2.step(): host tokens in, host greedy tokens out, one synchronise per step"}
+               "what": "Qwen2.step() once per decode step: host tokens in (index arrays uploaded), the step replayed as a CUDA graph, "
+                       "host greedy tokens out, one synchronise per step"}
 
     stats = torch.tensor([step_ms, prefill_s], device="cuda", dtype=torch.float64)
     if dist is not None:

@@ -102,7 +102,19 @@ Qwen2::Qwen2(const LlaisysQwen2Meta &global_meta, llaisysDeviceType_t device, in
     _weights.mlp_down_w = _per_layer[11].data();
 }
 
+void Qwen2::dropStepGraphs() {
+#ifdef ENABLE_NVIDIA_API
+    for (StepGraph &g : _step_graphs) {
+        if (g.exec != nullptr) {
+            kernels::graph_destroy(g.exec);
+        }
+    }
+#endif
+    _step_graphs.clear();
+}
+
 Qwen2::~Qwen2() {
+    dropStepGraphs();
     for (ModelObserver *o : std::vector<ModelObserver *>(_observers)) {
         o->modelDestroyed();
     }
@@ -154,6 +166,7 @@ void Qwen2::configureCache(size_t max_seqs, size_t max_tokens) {
     cfg.max_seqs = max_seqs;
     cfg.max_pages_per_seq = (max_tokens + kPageSize - 1) / kPageSize;
     cfg.num_pages = cfg.max_seqs * cfg.max_pages_per_seq;
+    dropStepGraphs();
     _cache = std::make_unique<kv::PagedKV>(cfg);
     // [bias + rope + append] -> decode attention run as a programmatic pair: the attention kernel's set-up and its copies
     // of older pages overlap the append (which writes each sequence's last page only, as the overlap contract asks)
@@ -255,6 +268,7 @@ int64_t Qwen2::infer(const int64_t *tokens, size_t n) {
 void Qwen2::ensureWorkspace(size_t n_tokens, size_t n_seqs) {
     auto &rt = enter();
     if (n_tokens > _ws_tokens) {
+        ++_generation;
         _ws_tokens = n_tokens;
         const size_t hs = _meta.hs, qd = _meta.nh * _meta.dh, kd = _meta.nkvh * _meta.dh;
         _x = rt.allocateDeviceStorage(n_tokens * hs * _elem);
@@ -266,6 +280,7 @@ void Qwen2::ensureWorkspace(size_t n_tokens, size_t n_seqs) {
         _act = rt.allocateDeviceStorage(n_tokens * _meta.di * _elem);
     }
     if (n_seqs > _ws_seqs) {
+        ++_generation;
         _ws_seqs = n_seqs;
         _x_last = rt.allocateDeviceStorage(n_seqs * _meta.hs * _elem);
         _logits = rt.allocateDeviceStorage(n_seqs * _meta.voc * _elem);
@@ -278,6 +293,7 @@ void Qwen2::ensureWorkspace(size_t n_tokens, size_t n_seqs) {
     const size_t need = align_up(n_tokens * 8, 16) * 2 + align_up(n_seqs * 8, 16) * 2 + align_up(n_tokens * 4, 16) * 2 +
                         align_up(n_seqs * 4, 16) * 2 + align_up((n_seqs + 1) * 4, 16);
     if (need > _meta_bytes) {
+        ++_generation;
         _meta_bytes = need * 2;
         _meta_block = rt.allocateDeviceStorage(_meta_bytes);
     }
@@ -480,7 +496,44 @@ void Qwen2::step(const int32_t *seq_ids, const int32_t *n_tokens, size_t n_seqs,
     }
     copyToDevice(dev0, host0, _meta_bytes);
     _cache->flush();
-    forward(a, T, n_seqs, max_q, max_kv, decode_only);
+    bool replayed = false;
+#ifdef ENABLE_NVIDIA_API
+    if (_on_gpu && decode_only && _tp_world == 1) {
+        // The launch-bound case (nine kernels per layer): replay the step as a graph. The graph is captured with the
+        // cache's maximum length as the attention kernels' bound, so it is valid for every later step of this batch size.
+        if (_step_graphs.size() <= n_seqs) {
+            _step_graphs.resize(n_seqs + 1);
+        }
+        StepGraph &g = _step_graphs[n_seqs];
+        if (g.exec != nullptr && g.generation != _generation) {
+            kernels::graph_destroy(g.exec);
+            g = StepGraph{};
+        }
+        if (g.exec == nullptr && g.seen && g.generation == _generation) {
+            enter().synchronize();
+            kernels::graph_capture_begin(_stream);
+            try {
+                forward(a, T, n_seqs, 1, _max_tokens_per_seq, true);
+            } catch (...) {
+                kernels::graph_destroy(kernels::graph_capture_end(_stream));
+                throw;
+            }
+            g.exec = kernels::graph_capture_end(_stream);
+        }
+        if (g.exec != nullptr) {
+            kernels::graph_launch(g.exec, _stream);
+            _last_n_seqs = n_seqs;
+            replayed = true;
+        } else {
+            g.seen = true;
+            g.generation = _generation;
+            max_kv = _max_tokens_per_seq; // the eager step sizes scratch for what the capture will ask for
+        }
+    }
+#endif
+    if (!replayed) {
+        forward(a, T, n_seqs, max_q, max_kv, decode_only);
+    }
     copyToHost(next_out, a.next, n_seqs * sizeof(int64_t));
     for (size_t i = 0, at = 0; i < n_seqs; ++i) {
         seqLen(seq_ids[i]) += size_t(n_tokens[i]);

@@ -134,6 +134,17 @@ private:
     core::storage_t _x, _h, _qkv, _q, _attn, _gate_up, _act, _x_last, _logits, _meta_block, _argmax_scratch;
     size_t _ws_tokens = 0, _ws_seqs = 0, _meta_bytes = 0;
     std::vector<std::byte> _meta_host;
+    // Decode steps of step() (every sequence one token) replayed as CUDA graphs, one per batch size: the first step of
+    // a size runs eagerly (it sizes scratch), the second is captured, later ones are replayed. A graph is dropped when
+    // a buffer it points into is reallocated (generation) or the cache is reconfigured.
+    struct StepGraph {
+        void *exec = nullptr;
+        uint64_t generation = 0;
+        bool seen = false;
+    };
+    std::vector<StepGraph> _step_graphs; // by n_seqs
+    uint64_t _generation = 1;
+    void dropStepGraphs();
     std::vector<ModelObserver *> _observers;
     size_t _last_n_seqs = 0;
     double _last_loop_ms = 0.0;
