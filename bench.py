@@ -574,6 +574,107 @@ def run_model_workload(args) -> None:
         dist.destroy_process_group()
 
 
+def run_copy_workload(args) -> None:
+    """--workload copy: the data-movement kernels of the path alone, at a row count where bandwidth (not launch latency)
+    decides: K1 paged append, K1b bias + RoPE + append over a packed q|k|v projection, K5 gather. 65536 rows = 64
+    sequences x 1024 tokens into a 16384-page pool (random physical pages); layers rotate so that every launch misses L2.
+    Algorithmic bytes: append reads and writes each K and V row once (2 x 1 KiB per row) plus 8 B of indices; the fused
+    kernel reads the 4 KiB packed projection row and writes the 3 KiB q row and the 1 KiB of K and V; gather reads and
+    writes 1 KiB per token."""
+    torch, llaisys, rank, local_rank, world, dist = _init_device()
+    dev = llaisys.DeviceType.NVIDIA
+    B, ctx, layers = 64, 1024, max(4, args.layers)
+    rows = B * ctx
+    cache = llaisys.PagedKVCache(POOL_PAGES, NKVH, D, nlayer=layers, dtype=llaisys.DataType.BF16, device=dev,
+                                 device_id=local_rank, max_seqs=B, max_pages_per_seq=ctx // PAGE)
+    g = torch.Generator().manual_seed(7 + rank)
+    perm = torch.randperm(POOL_PAGES, generator=g).tolist()
+    seqs = []
+    for i in range(B):
+        s = cache.add_seq()
+        cache.assign_pages(s, perm[i * (ctx // PAGE):(i + 1) * (ctx // PAGE)])
+        seqs.append(s)
+    cache.flush()
+    stream = torch.cuda.Stream()
+    cs = stream.cuda_stream
+    k_rows = torch.randn((rows, NKVH, D), device="cuda").bfloat16()
+    v_rows = torch.randn((rows, NKVH, D), device="cuda").bfloat16()
+    qkv = torch.randn((rows, (NH + 2 * NKVH) * D), device="cuda").bfloat16()
+    bias = torch.randn(((NH + 2 * NKVH) * D,), device="cuda").bfloat16()
+    q_out = torch.empty((rows, NH, D), device="cuda", dtype=torch.bfloat16)
+    seq_of_row = torch.repeat_interleave(torch.tensor(seqs, dtype=torch.int32, device="cuda"), ctx)
+    pos_of_row = torch.arange(ctx, dtype=torch.int32, device="cuda").repeat(B)
+    k_out = torch.empty((ctx, NKVH, D), device="cuda", dtype=torch.bfloat16)
+    v_out = torch.empty_like(k_out)
+    torch.cuda.synchronize()
+    reps = max(5, min(args.steps, 50))
+
+    def timed(body):
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                body(i)
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(reps):
+                body(i)
+            e1.record(stream)
+        stream.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    with ClockSampler(local_rank) as clocks:
+        append_ms = timed(lambda i: cache.append_dev(i % layers, k_rows, v_rows, seq_of_row, pos_of_row, rows, cs))
+    fused_ms = timed(lambda i: cache.rope_append_dev(i % layers, q_out, qkv, bias, seq_of_row, pos_of_row, rows, NH, 10000.0, cs))
+
+    def gather_all(i):  # the gather entry point takes one sequence: 64 launches move the same 64 MiB back out
+        with torch.cuda.stream(stream):
+            for s in seqs:
+                cache.gather(i % layers, s, ctx, k_out, v_out)
+    # gather queues on the library's stream: time it there
+    ext = torch.cuda.ExternalStream(llaisys.context_stream())
+    for i in range(2):
+        gather_all(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(ext)
+    for i in range(reps):
+        gather_all(i)
+    e1.record(ext)
+    torch.cuda.synchronize()
+    gather_ms = e0.elapsed_time(e1) / reps
+    cache.check()
+    if rank == 0:
+        hbm_peak, _, kind = _peaks()
+        row_kv = 2 * NKVH * D * 2
+        append_bytes = rows * (2 * row_kv + 8)
+        fused_bytes = rows * ((NH + 2 * NKVH) * D * 2 + NH * D * 2 + row_kv + 8)
+        gather_bytes = rows * 2 * row_kv
+        line = {
+            "metric": "paged append rows/s (65536 rows of K and V into random pages, one layer)",
+            "value": world * rows / (append_ms * 1e-3), "unit": "rows/s", "n_gpus": world, "steps": reps, "warmup": 3,
+            "ms_per_step": append_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "copy", "rows": rows, "heads": "12q/2kv", "head_dim": D, "page_size": PAGE,
+                       "pool_pages": POOL_PAGES, "l2": f"layer pool rotates over {layers} x 256 MiB between launches"},
+            "roofline": {"bound": "hbm", "kernel": "paged_append_kernel", "achieved": append_bytes / (append_ms * 1e-3) / 1e9,
+                         "peak": hbm_peak, "peak_kind": f"of {kind}", "unit": "GB/s",
+                         "frac": append_bytes / (append_ms * 1e-3) / 1e9 / hbm_peak, "traffic": None,
+                         "algorithmic_bytes_per_launch": append_bytes, "kernel_ms_mean": append_ms},
+            "rope_append": {"kernel": "paged_rope_append_kernel", "ms": fused_ms, "algorithmic_bytes_per_launch": fused_bytes,
+                            "GB/s": fused_bytes / (fused_ms * 1e-3) / 1e9,
+                            "frac": fused_bytes / (fused_ms * 1e-3) / 1e9 / hbm_peak},
+            "gather": {"kernel": "paged_gather_kernel", "ms_for_64_launches": gather_ms,
+                       "algorithmic_bytes": gather_bytes, "GB/s": gather_bytes / (gather_ms * 1e-3) / 1e9,
+                       "note": "one launch per sequence (1024 tokens, 2 MiB moved each): latency-bound by design, it is "
+                               "a test and debugging entry point"},
+            "e2e": None, "gpu_launches": reps, "timing": "CUDA events around back-to-back launches", "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_longctx_workload(args) -> None:
     """--workload config5: ONE 131072-token sequence, 28 layers, KV range split across the N GPUs (strong scaling).
 
@@ -762,7 +863,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="north_star", choices=["north_star", "config2", "config3", "config4", "config5"])
+    ap.add_argument("--workload", default="north_star", choices=["north_star", "config2", "config3", "config4", "config5", "copy"])
     ap.add_argument("--layers", type=int, default=4, help="pools to rotate over between steps (L2 flush)")
     ap.add_argument("--tp", action="store_true", help="config4 on several GPUs: tensor parallelism instead of sequence sharding")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -784,6 +885,9 @@ def main() -> None:
         return
     if args.workload == "config4":
         run_model_workload(args)
+        return
+    if args.workload == "copy":
+        run_copy_workload(args)
         return
 
     import torch

@@ -39,6 +39,9 @@ __device__ __forceinline__ bool resolve_slot(const int32_t *__restrict__ table, 
     return true;
 }
 
+// One warp per new row. The row's slot is resolved once (the three dependent loads -- sequence id, position, table
+// entry -- are the same for the whole row), then lane l moves 16-byte piece l of the K row and of the V row: with 2
+// kv-heads of 128 16-bit dims a row of K is 512 B, one coalesced warp-wide read, written as two 256 B head-rows.
 __global__ void paged_append_kernel(uint4 *__restrict__ k_pool, uint4 *__restrict__ v_pool,
                                     const uint4 *__restrict__ k_rows, const uint4 *__restrict__ v_rows,
                                     const int32_t *__restrict__ table, const int32_t *__restrict__ seq_ids,
@@ -49,23 +52,23 @@ __global__ void paged_append_kernel(uint4 *__restrict__ k_pool, uint4 *__restric
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const int32_t vecs_per_row = g.vecs_per_head_row * g.nkvh; // per K (or V) row
-    const int64_t total = int64_t(n_rows) * 2 * vecs_per_row;
-    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int32_t row = int32_t(i / (2 * vecs_per_row));
-        const int32_t r = int32_t(i - int64_t(row) * 2 * vecs_per_row);
-        const int32_t is_v = r / vecs_per_row;
-        const int32_t in_row = r - is_v * vecs_per_row;
-        const int32_t kvh = in_row / g.vecs_per_head_row;
-        const int32_t vec = in_row - kvh * g.vecs_per_head_row;
+    const int lane = threadIdx.x & 31;
+    const int32_t warps = int32_t((gridDim.x * blockDim.x) >> 5);
+    for (int32_t row = int32_t((blockIdx.x * blockDim.x + threadIdx.x) >> 5); row < n_rows; row += warps) {
         int32_t page, slot;
         if (!resolve_slot(table, g, seq_ids[row], positions[row], max_blocks, error_flag, page, slot)) {
             continue;
         }
-        const uint4 val = (is_v ? v_rows : k_rows)[int64_t(row) * vecs_per_row + in_row];
-        const int64_t off_b = int64_t(page) * g.page_stride_b + int64_t(kvh) * g.head_stride_b +
-                              int64_t(slot) * g.token_stride_b;
-        (is_v ? v_pool : k_pool)[off_b / 16 + vec] = val;
+        const int64_t slot_vec = (int64_t(page) * g.page_stride_b + int64_t(slot) * g.token_stride_b) / 16;
+        for (int32_t in_row = lane; in_row < vecs_per_row; in_row += 32) {
+            const int32_t kvh = in_row / g.vecs_per_head_row;
+            const int32_t vec = in_row - kvh * g.vecs_per_head_row;
+            const int64_t dst = slot_vec + int64_t(kvh) * (g.head_stride_b / 16) + vec;
+            const int64_t src = int64_t(row) * vecs_per_row + in_row;
+            const uint4 kv = k_rows[src], vv = v_rows[src];
+            k_pool[dst] = kv;
+            v_pool[dst] = vv;
+        }
     }
 }
 
@@ -127,7 +130,7 @@ struct alignas(sizeof(T) * VEC) Pack {
     T v[VEC];
 };
 
-template <typename T, int VEC>
+template <typename T, int VEC, bool kPerHead>
 __global__ void paged_rope_append_kernel(unsigned char *__restrict__ k_pool, unsigned char *__restrict__ v_pool,
                                          T *__restrict__ q_out, const T *__restrict__ qkv, const T *__restrict__ bias,
                                          const int32_t *__restrict__ table, const int32_t *__restrict__ seq_ids,
@@ -137,70 +140,97 @@ __global__ void paged_rope_append_kernel(unsigned char *__restrict__ k_pool, uns
     // Under a programmatic launch: let the next kernel (the decode attention) start its set-up, then wait for the
     // projection that produced qkv.
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // theta^(2j/d) for the d/2 pair indices, once per CTA instead of one powf per element (before the wait: it depends
+    // on nothing the previous kernel writes)
+    extern __shared__ float s_divisor[];
     const int32_t half = d / 2;
+    for (int32_t j = threadIdx.x; j < half; j += blockDim.x) {
+        s_divisor[j] = powf(theta, 2.f * float(j) / float(d));
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // A thread owns VEC pair indices of one row and every head_groups-th head: the sines and cosines depend on
+    // (position, pair index) only, so they are computed once and reused for the thread's heads. Large calls (prefill)
+    // use few groups -- less transcendental work per byte; small ones (a decode step) one group per head -- the
+    // shortest dependent chain per thread.
     const int32_t vec_per_head = half / VEC;
     const int32_t heads = nh + 2 * g.nkvh;
-    const int64_t total = int64_t(n_rows) * heads * vec_per_head;
+    const int32_t head_groups = kPerHead ? heads : 4; // kPerHead: one head per thread (small calls)
+    const int64_t total = int64_t(n_rows) * head_groups * vec_per_head;
     const int64_t stride = int64_t(gridDim.x) * blockDim.x;
     const int64_t row_elems = int64_t(heads) * d;
     for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int32_t row = int32_t(i / (heads * vec_per_head));
-        const int32_t r = int32_t(i - int64_t(row) * heads * vec_per_head);
-        const int32_t head = r / vec_per_head;
-        const int32_t j0 = (r - head * vec_per_head) * VEC;
+        const int32_t row = int32_t(i / (head_groups * vec_per_head));
+        const int32_t r = int32_t(i - int64_t(row) * head_groups * vec_per_head);
+        const int32_t first_head = r / vec_per_head;
+        const int32_t j0 = (r - first_head * vec_per_head) * VEC;
         const int32_t pos = positions[row];
-        const int64_t in_off = int64_t(row) * row_elems + int64_t(head) * d + j0;
-        P lo = *reinterpret_cast<const P *>(qkv + in_off);
-        P hi = *reinterpret_cast<const P *>(qkv + in_off + half);
-        float a[VEC], b[VEC];
+        float sn[VEC], cs[VEC];
 #pragma unroll
         for (int e = 0; e < VEC; ++e) {
-            a[e] = to_f32(lo.v[e]);
-            b[e] = to_f32(hi.v[e]);
+            sincosf(float(pos) / s_divisor[j0 + e], &sn[e], &cs[e]);
         }
-        if (bias != nullptr) {
-            const P blo = *reinterpret_cast<const P *>(bias + int64_t(head) * d + j0);
-            const P bhi = *reinterpret_cast<const P *>(bias + int64_t(head) * d + j0 + half);
+        int32_t page = 0, slot = 0;
+        // The slot lookup (three dependent loads) is needed only by threads that reach a K or V head: a one-head thread
+        // of a small call does it on demand; a many-head thread of a large call starts it up front, under its other loads.
+        bool resolved = false, slot_ok = false;
+        if (head_groups < heads) {
+            slot_ok = resolve_slot(table, g, seq_ids[row], pos, max_blocks, error_flag, page, slot);
+            resolved = true;
+        }
+        for (int32_t head = first_head; head < heads; head += head_groups) {
+            const int64_t in_off = int64_t(row) * row_elems + int64_t(head) * d + j0;
+            P lo = *reinterpret_cast<const P *>(qkv + in_off);
+            P hi = *reinterpret_cast<const P *>(qkv + in_off + half);
+            float a[VEC], b[VEC];
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-                a[e] += to_f32(blo.v[e]);
-                b[e] += to_f32(bhi.v[e]);
+                a[e] = to_f32(lo.v[e]);
+                b[e] = to_f32(hi.v[e]);
             }
-        }
-        const bool is_v = head >= nh + g.nkvh;
-        if (!is_v) {
+            if (bias != nullptr) {
+                const P blo = *reinterpret_cast<const P *>(bias + int64_t(head) * d + j0);
+                const P bhi = *reinterpret_cast<const P *>(bias + int64_t(head) * d + j0 + half);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    a[e] += to_f32(blo.v[e]);
+                    b[e] += to_f32(bhi.v[e]);
+                }
+            }
+            const bool is_v = head >= nh + g.nkvh;
+            if (!is_v) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    const float x = a[e], y = b[e];
+                    a[e] = x * cs[e] - y * sn[e];
+                    b[e] = y * cs[e] + x * sn[e];
+                }
+            }
 #pragma unroll
             for (int e = 0; e < VEC; ++e) {
-                const float ang = float(pos) / powf(theta, 2.f * float(j0 + e) / float(d));
-                float sn, cs;
-                sincosf(ang, &sn, &cs);
-                const float x = a[e], y = b[e];
-                a[e] = x * cs - y * sn;
-                b[e] = y * cs + x * sn;
+                lo.v[e] = from_f32<T>(a[e]);
+                hi.v[e] = from_f32<T>(b[e]);
             }
-        }
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-            lo.v[e] = from_f32<T>(a[e]);
-            hi.v[e] = from_f32<T>(b[e]);
-        }
-        if (head < nh) {
-            T *dst = q_out + (int64_t(row) * nh + head) * d + j0;
+            if (head < nh) {
+                T *dst = q_out + (int64_t(row) * nh + head) * d + j0;
+                *reinterpret_cast<P *>(dst) = lo;
+                *reinterpret_cast<P *>(dst + half) = hi;
+                continue;
+            }
+            if (!resolved) {
+                slot_ok = resolve_slot(table, g, seq_ids[row], pos, max_blocks, error_flag, page, slot);
+                resolved = true;
+            }
+            if (!slot_ok) {
+                continue;
+            }
+            const int32_t kvh = is_v ? head - nh - g.nkvh : head - nh;
+            const int64_t off_b = int64_t(page) * g.page_stride_b + int64_t(kvh) * g.head_stride_b +
+                                  int64_t(slot) * g.token_stride_b + int64_t(j0) * int64_t(sizeof(T));
+            unsigned char *dst = (is_v ? v_pool : k_pool) + off_b;
             *reinterpret_cast<P *>(dst) = lo;
-            *reinterpret_cast<P *>(dst + half) = hi;
-            continue;
+            *reinterpret_cast<P *>(dst + int64_t(half) * int64_t(sizeof(T))) = hi;
         }
-        int32_t page, slot;
-        if (!resolve_slot(table, g, seq_ids[row], pos, max_blocks, error_flag, page, slot)) {
-            continue;
-        }
-        const int32_t kvh = is_v ? head - nh - g.nkvh : head - nh;
-        const int64_t off_b = int64_t(page) * g.page_stride_b + int64_t(kvh) * g.head_stride_b +
-                              int64_t(slot) * g.token_stride_b + int64_t(j0) * int64_t(sizeof(T));
-        unsigned char *dst = (is_v ? v_pool : k_pool) + off_b;
-        *reinterpret_cast<P *>(dst) = lo;
-        *reinterpret_cast<P *>(dst + int64_t(half) * int64_t(sizeof(T))) = hi;
     }
 }
 
@@ -214,13 +244,16 @@ void launch_rope_append(cudaStream_t s, const KVView &kv, void *q_out, const voi
     auto aligned = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
     const bool wide = d % (2 * kVec) == 0 && aligned(q_out) && aligned(qkv) && aligned(bias) && aligned(kv.k_base) &&
                       aligned(kv.v_base);
-    const int64_t threads = int64_t(n_rows) * (nh + 2 * kv.nkvh) * (d / 2 / (wide ? kVec : 1));
+    const bool per_head = n_rows <= 1024;
+    const int32_t head_groups = per_head ? nh + 2 * kv.nkvh : 4;
+    const int64_t threads = int64_t(n_rows) * head_groups * (d / 2 / (wide ? kVec : 1));
     const int block = 256, grid = grid_for(threads, block);
     auto *kp = static_cast<unsigned char *>(kv.k_base);
     auto *vp = static_cast<unsigned char *>(kv.v_base);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(grid));
     cfg.blockDim = dim3(unsigned(block));
+    cfg.dynamicSmemBytes = size_t(d / 2) * sizeof(float);
     cfg.stream = s;
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -230,12 +263,14 @@ void launch_rope_append(cudaStream_t s, const KVView &kv, void *q_out, const voi
     T *qo = static_cast<T *>(q_out);
     const T *qi = static_cast<const T *>(qkv), *bi = static_cast<const T *>(bias);
     const int32_t *table = kv.block_table;
+    auto go = [&](auto kernel) {
+        LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, kp, vp, qo, qi, bi, table, seq_ids, positions, g, n_rows, nh, d,
+                                              theta, max_blocks, error_flag));
+    };
     if (wide) {
-        LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_rope_append_kernel<T, kVec>, kp, vp, qo, qi, bi, table, seq_ids,
-                                              positions, g, n_rows, nh, d, theta, max_blocks, error_flag));
+        per_head ? go(paged_rope_append_kernel<T, kVec, true>) : go(paged_rope_append_kernel<T, kVec, false>);
     } else {
-        LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_rope_append_kernel<T, 1>, kp, vp, qo, qi, bi, table, seq_ids,
-                                              positions, g, n_rows, nh, d, theta, max_blocks, error_flag));
+        per_head ? go(paged_rope_append_kernel<T, 1, true>) : go(paged_rope_append_kernel<T, 1, false>);
     }
 }
 
@@ -249,7 +284,7 @@ void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const voi
     }
     const CopyGeom g = make_geom(kv, elem_size);
     const int block = 256;
-    const int grid = grid_for(int64_t(n_rows) * 2 * g.vecs_per_head_row * g.nkvh, block);
+    const int grid = grid_for(int64_t(n_rows) * 32, block); // one warp per row
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(grid));
     cfg.blockDim = dim3(unsigned(block));
