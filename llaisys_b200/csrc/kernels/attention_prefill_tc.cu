@@ -83,7 +83,10 @@ struct PrefillParams {
     int32_t table_stride, num_pages;
     const int32_t *seq_ids;
     const int32_t *kv_lens;
-    const int32_t *q_starts; // [n_seqs + 1]
+    const int32_t *q_starts; // [n_seqs + 1]; null in contiguous mode
+    int32_t contiguous;      // 1: K and V are plain [tokens, nkvh, 128] tensors of ONE sequence (no block table, two
+                             // 3-D tensor maps); q rows [0, const_q_len), const_kv_len keys
+    int32_t const_q_len, const_kv_len;
     int32_t n_seqs, nkvh, group, nh, q_blocks; // q_blocks = ceil(max_q_len / 128)
     const void *q;
     void *out;
@@ -99,7 +102,8 @@ struct PrefillParams {
 // the buffer of P(i), is issued after PV of block i.
 template <bool kBf16, bool kPTmem>
 __global__ void __launch_bounds__(kThreads, 2)
-    paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, PrefillParams p) {
+    paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_v,
+                            PrefillParams p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t raw_u32 = smem_u32(smem_raw);
     const uint32_t base_u32 = (raw_u32 + 1023u) & ~1023u; // swizzled operands need 1 KiB alignment
@@ -120,7 +124,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
 
     // ---- which tile: sequences by decreasing length (the order CTAs are handed out is the order they start) ------
-    const bool sorted = p.n_seqs <= kMaxSortedSeqs;
+    const bool sorted = p.n_seqs <= kMaxSortedSeqs && !p.contiguous;
     if (sorted) {
         for (int a = tid; a < p.n_seqs; a += kThreads) {
             const int len_a = p.kv_lens[a];
@@ -139,18 +143,18 @@ __global__ void __launch_bounds__(kThreads, 2)
     const int within = linear % per_seq;
     const int qb = p.q_blocks - 1 - within / p.nh; // late query blocks see the most keys: first
     const int h = within % p.nh;
-    const int q_start = p.q_starts[s];
-    const int q_len = p.q_starts[s + 1] - q_start;
+    const int q_start = p.contiguous ? 0 : p.q_starts[s];
+    const int q_len = p.contiguous ? p.const_q_len : p.q_starts[s + 1] - q_start;
     if (qb * kBlockM >= q_len) {
         return; // uniform over the CTA, before any mbarrier or TMEM allocation
     }
-    const int kv_len = min(max(p.kv_lens[s], q_len), p.table_stride * kPage);
+    const int kv_len = p.contiguous ? max(p.const_kv_len, q_len) : min(max(p.kv_lens[s], q_len), p.table_stride * kPage);
     const int off = kv_len - q_len;                                   // query t sees keys j <= t + off
     const int kv_hi = min(kv_len, qb * kBlockM + kBlockM + off);      // keys any row of this tile can see
     const int nblk = (kv_hi + kBlockN - 1) / kBlockN;
     const int n_pages = (kv_hi + kPage - 1) / kPage;
     const int kvh = h / p.group;
-    const int seq_row = p.seq_ids ? p.seq_ids[s] : s;
+    const int seq_row = (!p.contiguous && p.seq_ids) ? p.seq_ids[s] : s;
 
     // ---- set-up: barriers, TMEM, Q tile, cleared K/V ring ---------------------------------------------------
     if (tid == 0) {
@@ -210,10 +214,14 @@ __global__ void __launch_bounds__(kThreads, 2)
             const int n_pg = min(kPagesPerBlock, n_pages - first);
             int page = 0;
             if (lane < n_pg) {
-                page = p.block_table[tbase + first + lane];
-                if (page < 0 || page >= p.num_pages) {
-                    atomicOr(p.error_flag, kErrBadPage);
-                    page = 0;
+                if (p.contiguous) {
+                    page = first + lane; // block b of the tensor is its tokens [16 b, 16 b + 16)
+                } else {
+                    page = p.block_table[tbase + first + lane];
+                    if (page < 0 || page >= p.num_pages) {
+                        atomicOr(p.error_flag, kErrBadPage);
+                        page = 0;
+                    }
                 }
             }
             const int c3 = int((p.page0 + page) * 2);
@@ -233,8 +241,16 @@ __global__ void __launch_bounds__(kThreads, 2)
                 }
                 __syncwarp();
                 if (lane < n_pg) {
-                    tma_load_4d(dst + is_v * kKvOperandBytes, &tmap, 0, 0, kvh, c3 + is_v, bar(full));                  // dims 0-63
-                    tma_load_4d(dst + is_v * kKvOperandBytes + kKvHalfBytes, &tmap, 64, 0, kvh, c3 + is_v, bar(full)); // dims 64-127
+                    const uint32_t lo = dst + is_v * kKvOperandBytes, hi = lo + kKvHalfBytes; // dims 0-63, dims 64-127
+                    if (p.contiguous) {
+                        // [tokens][kv-heads][128] tensors: box = 64 dims x 1 head x 16 tokens; tokens past the end read as 0
+                        const CUtensorMap *m = is_v ? &tmap_v : &tmap;
+                        tma_load_3d(lo, m, 0, kvh, page * kPage, bar(full));
+                        tma_load_3d(hi, m, 64, kvh, page * kPage, bar(full));
+                    } else {
+                        tma_load_4d(lo, &tmap, 0, 0, kvh, c3 + is_v, bar(full));
+                        tma_load_4d(hi, &tmap, 64, 0, kvh, c3 + is_v, bar(full));
+                    }
                 }
             }
         }
@@ -530,7 +546,7 @@ constexpr size_t kSmemBytes = kAlignSlack + kQBytes + kPBytes + kStages * kStage
                               kMaxSortedSeqs * sizeof(int16_t);
 
 template <bool kBf16, bool kPTmem>
-void launch_variant(cudaStream_t s, const CUtensorMap &tmap, const PrefillParams &p, int grid) {
+void launch_variant(cudaStream_t s, const CUtensorMap &tmap, const CUtensorMap &tmap_v, const PrefillParams &p, int grid) {
     static std::once_flag once[64];
     int dev = 0;
     LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
@@ -538,20 +554,20 @@ void launch_variant(cudaStream_t s, const CUtensorMap &tmap, const PrefillParams
         LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_tc_kernel<kBf16, kPTmem>,
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, int(kSmemBytes)));
     });
-    paged_prefill_tc_kernel<kBf16, kPTmem><<<grid, kThreads, kSmemBytes, s>>>(tmap, p);
+    paged_prefill_tc_kernel<kBf16, kPTmem><<<grid, kThreads, kSmemBytes, s>>>(tmap, tmap_v, p);
 }
 
 template <bool kBf16>
-void launch(cudaStream_t s, const CUtensorMap &tmap, const PrefillParams &p, int grid) {
+void launch(cudaStream_t s, const CUtensorMap &tmap, const CUtensorMap &tmap_v, const PrefillParams &p, int grid) {
     // LLAISYS_PREFILL_P=smem keeps P on the shared-memory path (the earlier design), for comparison
     static const bool p_tmem = [] {
         const char *e = std::getenv("LLAISYS_PREFILL_P");
         return e == nullptr || std::string(e) != "smem";
     }();
     if (p_tmem) {
-        launch_variant<kBf16, true>(s, tmap, p, grid);
+        launch_variant<kBf16, true>(s, tmap, tmap_v, p, grid);
     } else {
-        launch_variant<kBf16, false>(s, tmap, p, grid);
+        launch_variant<kBf16, false>(s, tmap, tmap_v, p, grid);
     }
 }
 
@@ -588,24 +604,58 @@ int make_kv_tile_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total
     return 0;
 }
 
+namespace {
+
+// [tokens][nkvh][128] 16-bit tensor -> 3-D map (dims 128, nkvh, tokens) with a box of 64 dims x 1 head x 16 tokens: the
+// tile lands in shared memory exactly like a page-pool tile; rows past the last token are out of bounds and read as 0.
+bool contiguous_kv_map(CUtensorMap *out, const void *base, const KVView &kv, uint64_t tokens, bool bf16) {
+    EncodeTiledFn encode = prefill_encode_fn();
+    if (encode == nullptr || tokens == 0 || tokens >= (uint64_t(1) << 31)) {
+        return false;
+    }
+    const cuuint64_t dims[3] = {cuuint64_t(kD), cuuint64_t(kv.nkvh), cuuint64_t(tokens)};
+    const cuuint64_t strides[2] = {cuuint64_t(kv.head_stride) * 2, cuuint64_t(kv.token_stride) * 2};
+    const cuuint32_t box[3] = {64, 1, cuuint32_t(kPage)};
+    const cuuint32_t elem_strides[3] = {1, 1, 1};
+    return encode(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base),
+                  dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+} // namespace
+
 int attention_prefill_tc(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
                          const void *q, float scale, const AttnOut &out, int32_t *error_flag) {
     const bool bf16 = dtype == LLAISYS_DTYPE_BF16;
-    if (kv.tma_tile_desc == nullptr || !(bf16 || dtype == LLAISYS_DTYPE_F16) || kv.d != kD || kv.page_size != kPage ||
-        kv.nkvh <= 0 || kv.block_table == nullptr || batch.kv_lens == nullptr || batch.q_starts == nullptr ||
-        out.out == nullptr || out.part != nullptr || batch.nh % kv.nkvh != 0 || batch.n_seqs <= 0 ||
-        batch.max_q_len <= 0 || error_flag == nullptr || reinterpret_cast<uintptr_t>(q) % 16 != 0 ||
-        reinterpret_cast<uintptr_t>(out.out) % 16 != 0) {
+    if (!(bf16 || dtype == LLAISYS_DTYPE_F16) || kv.d != kD || kv.page_size != kPage || kv.nkvh <= 0 || out.out == nullptr ||
+        out.part != nullptr || batch.nh % kv.nkvh != 0 || batch.n_seqs <= 0 || batch.max_q_len <= 0 || error_flag == nullptr ||
+        reinterpret_cast<uintptr_t>(q) % 16 != 0 || reinterpret_cast<uintptr_t>(out.out) % 16 != 0) {
+        return -1;
+    }
+    // Two kinds of K/V: a page pool with a block table (one tensor map over the pool, made with the cache), or the
+    // legacy operator's plain [tokens, nkvh, 128] tensors of one sequence (two maps made here).
+    const bool paged = kv.block_table != nullptr;
+    if (paged && (kv.tma_tile_desc == nullptr || batch.kv_lens == nullptr || batch.q_starts == nullptr)) {
+        return -1;
+    }
+    const bool contiguous = !paged && batch.n_seqs == 1 && batch.q_starts == nullptr && batch.kv_lens == nullptr &&
+                            batch.seq_ids == nullptr && batch.const_q_len > 1 && batch.const_kv_len >= batch.const_q_len &&
+                            kv.head_stride == kD && kv.token_stride == int64_t(kv.nkvh) * kD &&
+                            reinterpret_cast<uintptr_t>(kv.k_base) % 16 == 0 && reinterpret_cast<uintptr_t>(kv.v_base) % 16 == 0;
+    if (!paged && !contiguous) {
         return -1;
     }
     PrefillParams p;
-    p.page0 = kv.tma_page0;
+    p.page0 = paged ? kv.tma_page0 : 0;
     p.block_table = kv.block_table;
     p.table_stride = kv.table_stride;
     p.num_pages = kv.num_pages;
     p.seq_ids = batch.seq_ids;
     p.kv_lens = batch.kv_lens;
     p.q_starts = batch.q_starts;
+    p.contiguous = contiguous ? 1 : 0;
+    p.const_q_len = batch.const_q_len;
+    p.const_kv_len = batch.const_kv_len;
     p.n_seqs = batch.n_seqs;
     p.nkvh = kv.nkvh;
     p.group = batch.nh / kv.nkvh;
@@ -619,13 +669,19 @@ int attention_prefill_tc(stream_t stream, llaisysDataType_t dtype, const KVView 
     if (grid > 0x7fffffffLL) {
         return -1;
     }
-    CUtensorMap tmap;
-    memcpy(&tmap, kv.tma_tile_desc, sizeof(tmap));
+    CUtensorMap tmap, tmap_v;
+    if (paged) {
+        memcpy(&tmap, kv.tma_tile_desc, sizeof(tmap));
+        tmap_v = tmap;
+    } else if (!contiguous_kv_map(&tmap, kv.k_base, kv, uint64_t(batch.const_kv_len), bf16) ||
+               !contiguous_kv_map(&tmap_v, kv.v_base, kv, uint64_t(batch.const_kv_len), bf16)) {
+        return -1;
+    }
     auto s = static_cast<cudaStream_t>(stream);
     if (bf16) {
-        launch<true>(s, tmap, p, int(grid));
+        launch<true>(s, tmap, tmap_v, p, int(grid));
     } else {
-        launch<false>(s, tmap, p, int(grid));
+        launch<false>(s, tmap, tmap_v, p, int(grid));
     }
     check_launch("paged_prefill_tc");
     return 0;

@@ -118,6 +118,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tensor_map
                  ::"r"(dst), "l"(tensor_map), "r"(x), "r"(y), "r"(bar)
                  : "memory");
 }
+// One 3-D box; c0 is in elements (c0 * element_size must be a multiple of 16 bytes), c1 and c2 are plain indices.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tensor_map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
+                 "l"(tensor_map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+                 : "memory");
+}
 // One 4-D box; c0 is in elements (c0 * element_size must be a multiple of 16 bytes), c1..c3 are plain indices.
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tensor_map, int c0, int c1, int c2, int c3,
                                             uint32_t bar) {

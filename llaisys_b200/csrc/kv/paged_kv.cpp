@@ -827,8 +827,10 @@ void run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const
             return;
         }
     }
-    if (batch.q_starts != nullptr) {
-        // LLAISYS_PREFILL_PATH=generic keeps chunks on the generic kernel (for A/B measurements)
+    if (batch.q_starts != nullptr || (view.block_table == nullptr && batch.const_q_len >= 16)) {
+        // chunks over a page pool, or the legacy operator's multi-token query over plain K/V tensors (from 16 rows on:
+        // below that the 128-row tensor-core tile is mostly padding). LLAISYS_PREFILL_PATH=generic keeps both on the
+        // generic kernel (for A/B measurements)
         static const bool allow_tc = [] {
             const char *e = std::getenv("LLAISYS_PREFILL_PATH");
             return !(e != nullptr && std::string(e) == "generic");

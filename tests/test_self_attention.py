@@ -78,3 +78,23 @@ def test_decode_lengths_around_page_and_split_boundaries_nvidia(cuda_device, kvl
     assert helpers.max_abs(got, attention.self_attention(q, k, v, scale)) <= helpers.MAX_ABS["bf16"]
     f64 = attention.self_attention_f64(q, k, v, scale)
     assert helpers.max_abs(got, f64) <= 8e-3 * max(1.0, f64.abs().max().item())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+@pytest.mark.parametrize("qlen,kvlen", [(16, 16), (100, 100), (130, 131), (512, 1024), (300, 2049), (2048, 2048)])
+def test_multi_token_queries_over_plain_tensors_nvidia(cuda_device, qlen, kvlen, dname):
+    """From 16 query rows on, 16-bit contiguous K/V with head_dim 128 take the tensor-core (tcgen05) kernel through
+    tensor maps made over the caller's tensors: lengths that end inside a 16-token tile, inside a 64-key block and
+    inside a 128-row query tile, and a square causal case with several query tiles."""
+    dt = helpers.TORCH_DTYPE[dname]
+    g = torch.Generator().manual_seed(qlen * 7 + kvlen)
+    q = workloads.randn((qlen, 12, 128), dt, g)
+    k = workloads.randn((kvlen, 2, 128), dt, g)
+    v = workloads.randn((kvlen, 2, 128), dt, g)
+    scale = 1.0 / 128 ** 0.5
+    got = helpers.run_self_attention(q, k, v, scale, llaisys.DeviceType.NVIDIA, dname)
+    assert helpers.max_abs(got, attention.self_attention(q, k, v, scale)) <= helpers.MAX_ABS[dname]
+    f64 = attention.self_attention_f64(q, k, v, scale)
+    ulp = {"f16": 1e-3, "bf16": 8e-3}[dname]
+    assert helpers.max_abs(got, f64) <= ulp * max(1.0, f64.abs().max().item())
