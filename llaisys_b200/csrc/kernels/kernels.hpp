@@ -103,9 +103,11 @@ int make_kv_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows
 
 // K4: chunked-prefill attention on tcgen05 for page pools that carry the half-tile tensor map
 // (KVView::tma_tile_desc): 16-bit K/V, head_dim 128, page 16, ragged causal chunks (batch.q_starts). Returns -1 if
-// the view or shape is not covered.
+// the view or shape is not covered, or the scratch is smaller than attention_prefill_tc_scratch asks for (partial
+// results of tiles that are split over CTAs, and their arrival counters, which must be zero between launches).
 int attention_prefill_tc(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
-                         const void *q, float scale, const AttnOut &out, int32_t *error_flag);
+                         const void *q, float scale, const AttnOut &out, const AttnScratch &scratch);
+void attention_prefill_tc_scratch(size_t *floats, size_t *counters);
 int make_kv_tile_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, uint32_t nkvh,
                             llaisysDataType_t dtype);
 

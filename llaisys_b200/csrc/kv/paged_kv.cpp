@@ -480,14 +480,21 @@ int32_t *PagedKV::stage(const int32_t *const *arrays, const size_t *lens, size_t
     return dev;
 }
 
-kernels::AttnScratch PagedKV::scratchFor(size_t n_seqs, size_t nh, size_t max_kv_len) {
+kernels::AttnScratch PagedKV::scratchFor(size_t n_seqs, size_t nh, size_t max_kv_len, bool chunks) {
     kernels::AttnScratch sc;
     sc.error_flag = reinterpret_cast<int32_t *>(_error_dev->memory());
 #ifdef ENABLE_NVIDIA_API
     if (onDevice()) {
         size_t floats = 0, counters = 0;
-        kernels::attention_decode_split_scratch(int32_t(n_seqs), int32_t(nh), int32_t(_cfg.nkvh),
-                                                int32_t(_cfg.head_dim), int32_t(max_kv_len), &floats, &counters);
+        if (chunks) {
+            // the tensor-core chunk kernel splits long tiles over CTAs: fixed workspace, whatever the batch
+            if (_cfg.head_dim == 128 && _elem == 2) {
+                kernels::attention_prefill_tc_scratch(&floats, &counters);
+            }
+        } else {
+            kernels::attention_decode_split_scratch(int32_t(n_seqs), int32_t(nh), int32_t(_cfg.nkvh),
+                                                    int32_t(_cfg.head_dim), int32_t(max_kv_len), &floats, &counters);
+        }
         auto &rt = enter();
         if (floats > _partials_floats) {
             _partials_floats = floats;
@@ -637,9 +644,7 @@ void PagedKV::prefillDev(size_t layer, void *out, const void *q, const int32_t *
         return;
     }
 #ifdef ENABLE_NVIDIA_API
-    kernels::AttnScratch sc;
-    sc.error_flag = reinterpret_cast<int32_t *>(_error_dev->memory());
-    enter();
+    const kernels::AttnScratch sc = scratchFor(n_seqs, nh, max_kv_len, true);
     run_attention_nvidia(stream, _cfg.dtype, v, b, q, scale, o, sc);
 #else
     (void)stream;
@@ -835,7 +840,7 @@ void run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const
             const char *e = std::getenv("LLAISYS_PREFILL_PATH");
             return !(e != nullptr && std::string(e) == "generic");
         }();
-        if (allow_tc && kernels::attention_prefill_tc(stream, dtype, view, batch, q, scale, out, scratch.error_flag) == 0) {
+        if (allow_tc && kernels::attention_prefill_tc(stream, dtype, view, batch, q, scale, out, scratch) == 0) {
             return;
         }
     }

@@ -130,7 +130,7 @@ private:
     kernels::KVView view(size_t layer) const;
     core::Runtime &enter() const;                   // make the cache's device current on this thread
     int32_t *stage(const int32_t *const *arrays, const size_t *lens, size_t n_arrays); // host arrays -> device
-    kernels::AttnScratch scratchFor(size_t n_seqs, size_t nh, size_t max_kv_len);
+    kernels::AttnScratch scratchFor(size_t n_seqs, size_t nh, size_t max_kv_len, bool chunks = false);
     bool onDevice() const { return _cfg.device_type != LLAISYS_DEVICE_CPU; }
 
     PagedKVConfig _cfg;

@@ -42,10 +42,16 @@ void nvidia_self_attention(llaisysStream_t stream, llaisysDataType_t dtype, cons
     }
     kernels::AttnScratch scratch;
     scratch.error_flag = reinterpret_cast<int32_t *>(sc.error->memory());
-    if (batch.const_q_len == 1) {
+    const bool chunk = batch.const_q_len >= 16 && view.d == 128 &&
+                       (dtype == LLAISYS_DTYPE_BF16 || dtype == LLAISYS_DTYPE_F16); // tensor-core kernel: split tiles
+    if (batch.const_q_len == 1 || chunk) {
         size_t floats = 0, counters = 0;
-        kernels::attention_decode_split_scratch(batch.n_seqs, batch.nh, view.nkvh, view.d, batch.max_kv_len, &floats,
-                                                &counters);
+        if (chunk) {
+            kernels::attention_prefill_tc_scratch(&floats, &counters);
+        } else {
+            kernels::attention_decode_split_scratch(batch.n_seqs, batch.nh, view.nkvh, view.d, batch.max_kv_len, &floats,
+                                                    &counters);
+        }
         if (floats > sc.partials_floats) {
             sc.partials = rt.allocateDeviceStorage(floats * sizeof(float));
             sc.partials_floats = floats;

@@ -346,6 +346,37 @@ def test_prefill_ragged_chunks_and_block_boundaries_nvidia(cuda_device, dname):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("nh,nkvh,ctx,chunk", [(12, 2, 6000, 256), (7, 1, 3000, 130), (4, 4, 9000, 64)])
+def test_prefill_one_long_sequence_split_over_ctas_nvidia(cuda_device, nh, nkvh, ctx, chunk):
+    """One sequence with a long context: a handful of tiles for a whole GPU, so the kernel cuts every tile's key range
+    into pieces run by different CTAs and merges their partial results. The merged rows must match the oracle, and
+    -- the merge order being fixed, not the order in which the pieces finish -- be the same bits on every launch."""
+    g = torch.Generator().manual_seed(nh * 1000 + ctx)
+    kv_len = ctx + chunk
+    cache = llaisys.PagedKVCache((kv_len + 15) // 16 + 4, nkvh, 128, dtype=llaisys.DataType.BF16, device=NVIDIA, max_seqs=1,
+                                 max_pages_per_seq=(kv_len + 15) // 16)
+    s = cache.add_seq()
+    cache.reserve(s, kv_len)
+    k = workloads.randn((kv_len, nkvh, 128), torch.bfloat16, g)
+    v = workloads.randn((kv_len, nkvh, 128), torch.bfloat16, g)
+    qh = workloads.randn((chunk, nh, 128), torch.bfloat16, g)
+    helpers.append_all(cache, 0, [s], [k], [v], NVIDIA)
+    q = qh.cuda()
+    out = torch.full_like(q, float("nan"))
+    cache.prefill(0, out, q, [s], [chunk], [kv_len], nh, 128 ** -0.5)
+    cache.check()
+    for _ in range(5):
+        again = torch.full_like(q, float("nan"))
+        cache.prefill(0, again, q, [s], [chunk], [kv_len], nh, 128 ** -0.5)
+        cache.check()
+        assert torch.equal(helpers.tensor_words(again.cpu()), helpers.tensor_words(out.cpu()))
+    out = out.cpu()
+    assert not out.float().isnan().any()
+    expect = attention.self_attention(qh, k, v, 128 ** -0.5)
+    assert helpers.max_abs(out, expect) <= helpers.MAX_ABS["bf16"]
+
+
+@pytest.mark.gpu
 def test_back_to_back_steps_with_launch_overlap_nvidia(cuda_device):
     """Sixteen decode steps queued without any host synchronisation, with programmatic dependent launch enabled: each
     step appends one new row per sequence and attends over the grown context. Every step's output must match the
