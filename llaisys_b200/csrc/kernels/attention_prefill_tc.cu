@@ -297,18 +297,32 @@ __global__ void __launch_bounds__(kThreads, 2)
 
     auto load_q = [&](const Fragment &f, const SeqGeom &g, int first, int stride) {
         // Q rows of the tile, 16 bytes per store, into the K-major 128-byte-swizzled layout
-        // [dims 0-63 | dims 64-127][128 rows][128 B]; rows past the chunk are zero.
+        // [dims 0-63 | dims 64-127][128 rows][128 B]; rows past the chunk are zero. All loads first, then all stores:
+        // the stores are volatile asm, which no load may pass, and one round trip per 16 bytes made a fragment
+        // boundary cost six blocks' time.
         const char *q_base = static_cast<const char *>(p.q);
-#pragma unroll 4
-        for (int idx = first; idx < kBlockM * 16; idx += stride) {
+        constexpr int kMaxIter = kBlockM * 16 / kSoftmaxThreads; // the fewest threads that call this
+        uint4 vals[kMaxIter];
+#pragma unroll
+        for (int it = 0; it < kMaxIter; ++it) {
+            const int idx = first + it * stride;
             const int r = idx >> 4, cc = idx & 15;
             const int t = f.qb * kBlockM + r;
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (t < g.q_len) {
-                val = *reinterpret_cast<const uint4 *>(q_base + ((long long)(g.q_start + t) * p.nh + f.h) * (kD * 2) + cc * 16);
+            vals[it] = make_uint4(0u, 0u, 0u, 0u);
+            if (idx < kBlockM * 16 && t < g.q_len) {
+                vals[it] = *reinterpret_cast<const uint4 *>(q_base + ((long long)(g.q_start + t) * p.nh + f.h) * (kD * 2) + cc * 16);
             }
-            const uint32_t dst = q_u32 + (cc >> 3) * kQHalfBytes + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w) : "memory");
+        }
+#pragma unroll
+        for (int it = 0; it < kMaxIter; ++it) {
+            const int idx = first + it * stride;
+            const int r = idx >> 4, cc = idx & 15;
+            if (idx < kBlockM * 16) {
+                const uint32_t dst = q_u32 + (cc >> 3) * kQHalfBytes + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(vals[it].x), "r"(vals[it].y),
+                             "r"(vals[it].z), "r"(vals[it].w)
+                             : "memory");
+            }
         }
     };
 
