@@ -122,6 +122,7 @@ struct PrefillParams {
     int32_t *error_flag;
     float *partials;   // [2 * gridDim.x][kPartialFloats]
     int32_t *counters; // [gridDim.x], zero between launches
+    int32_t out_wide;  // out is 32-byte aligned: rows are stored 32 bytes (a whole sector) per instruction
 };
 
 // ---- the line of blocks ------------------------------------------------------------------------------------------
@@ -753,7 +754,21 @@ __global__ void __launch_bounds__(kThreads, 2)
                             }
                         }
                     }
-                    if (t < g.q_len) {
+                    if (t < g.q_len && p.out_wide) {
+                        // a thread owns a row: a 16-byte store fills half a 32-byte sector and the other half comes
+                        // with the next instruction; 32-byte stores halve the write transactions of the epilogue
+#pragma unroll
+                        for (int q2 = 0; q2 < 2; ++q2) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                w[e] = pack2<kBf16>(v[q2 * 16 + 2 * e] * inv, v[q2 * 16 + 2 * e + 1] * inv);
+                            }
+                            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"l"(out_row + c4 * 64 + q2 * 32),
+                                         "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                                         : "memory");
+                        }
+                    } else if (t < g.q_len) {
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {
                             uint4 w;
@@ -943,6 +958,7 @@ int attention_prefill_tc(stream_t stream, llaisysDataType_t dtype, const KVView 
         reinterpret_cast<uintptr_t>(scratch.partials) % 16 != 0) {
         return -1;
     }
+    p.out_wide = reinterpret_cast<uintptr_t>(out.out) % 32 == 0 ? 1 : 0;
     p.partials = scratch.partials;
     p.counters = scratch.counters;
     CUtensorMap tmap, tmap_v;
