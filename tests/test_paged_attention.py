@@ -377,6 +377,42 @@ def test_prefill_one_long_sequence_split_over_ctas_nvidia(cuda_device, nh, nkvh,
 
 
 @pytest.mark.gpu
+def test_prefill_many_short_sequences_and_one_long_chunk_nvidia(cuda_device):
+    """More sequences than the kernel has threads per CTA (its prologue sums and scans the sequences' block counts in
+    rounds of one sequence per thread), most with a chunk of one to three rows, some with none, and one whole prompt
+    of 1500 rows without context (12 row blocks of one sequence)."""
+    g = torch.Generator().manual_seed(29)
+    n = 300
+    q_lens = [int(x) for x in torch.randint(0, 4, (n,), generator=g)]
+    ctxs = [int(x) for x in torch.randint(0, 90, (n,), generator=g)]
+    q_lens[137], ctxs[137] = 1500, 0
+    kv_lens = [c + q for c, q in zip(ctxs, q_lens)]
+    pages = sum((l + 15) // 16 for l in kv_lens) + 8
+    cache = llaisys.PagedKVCache(pages, 2, 128, dtype=llaisys.DataType.BF16, device=NVIDIA, max_seqs=n, max_pages_per_seq=96)
+    seqs, ks, vs, qs = [], [], [], []
+    for ql, kl in zip(q_lens, kv_lens):
+        s = cache.add_seq()
+        cache.reserve(s, kl)
+        seqs.append(s)
+        ks.append(workloads.randn((kl, 2, 128), torch.bfloat16, g))
+        vs.append(workloads.randn((kl, 2, 128), torch.bfloat16, g))
+        qs.append(workloads.randn((ql, 12, 128), torch.bfloat16, g))
+    helpers.append_all(cache, 0, seqs, ks, vs, NVIDIA)
+    q = torch.cat(qs).cuda()
+    out = torch.full_like(q, float("nan"))
+    cache.prefill(0, out, q, seqs, q_lens, kv_lens, 12, 128 ** -0.5)
+    cache.check()
+    out = out.cpu()
+    assert not out.float().isnan().any()
+    at = 0
+    for i, ql in enumerate(q_lens):
+        if ql:
+            expect = attention.self_attention(qs[i], ks[i], vs[i], 128 ** -0.5)
+            assert helpers.max_abs(out[at:at + ql], expect) <= helpers.MAX_ABS["bf16"], (i, ql, kv_lens[i])
+        at += ql
+
+
+@pytest.mark.gpu
 def test_back_to_back_steps_with_launch_overlap_nvidia(cuda_device):
     """Sixteen decode steps queued without any host synchronisation, with programmatic dependent launch enabled: each
     step appends one new row per sequence and attends over the grown context. Every step's output must match the
