@@ -184,7 +184,10 @@ LLAISYS_API int llaisysPagedAttentionDecodePartialDev(llaisysPagedKV_t kv, size_
                                                       const int32_t *seq_ids_dev, const int32_t *kv_lens_dev,
                                                       size_t n_seqs, size_t max_kv_len, size_t nh, float scale,
                                                       llaisysStream_t stream);
-/* q_starts_dev is int32 [n_seqs + 1]: row offset of each sequence's chunk in q / out. */
+/* q_starts_dev is int32 [n_seqs + 1]: row offset of each sequence's chunk in q / out. On NVIDIA with 16-bit
+ * data and head_dim 128 the first call allocates the cache's workspace for tiles that are split over CTAs (two
+ * partial results per CTA, about 38 MiB on a 148-SM GPU) and synchronises once; later calls do not allocate.
+ * Calls on one cache share that workspace and must be ordered on one stream. */
 LLAISYS_API int llaisysPagedAttentionPrefillDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
                                                 const int32_t *seq_ids_dev, const int32_t *q_starts_dev,
                                                 const int32_t *kv_lens_dev, size_t n_seqs, size_t total_q,
