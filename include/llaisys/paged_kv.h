@@ -151,7 +151,10 @@ LLAISYS_API int llaisysPagedAttentionDecodePartial(llaisysPagedKV_t kv, size_t l
 /* One decode step from HOST buffers, synchronous -- the call a serving loop without device-resident activations makes.
  * Row i of k_new / v_new (host, [n_seqs, nkvh, head_dim]) becomes token kv_lens[i] - 1 of sequence seq_ids[i]; then
  * out[i] (host, [n_seqs, nh, head_dim]) = attention of q[i] (host) over the sequence's kv_lens[i] tokens. Pinned host
- * buffers make the copies asynchronous; pageable ones work. Returns when out holds the result. */
+ * buffers make the copies asynchronous; pageable ones work. Buffers that are page-locked AND mapped into the device's
+ * address space (cudaHostAlloc / cudaMallocHost, torch's pinned tensors) are read and written by the kernels directly
+ * instead of through separate copies; they must not be touched until the call returns. Returns when out holds the
+ * result. */
 LLAISYS_API int llaisysPagedDecodeStepHost(llaisysPagedKV_t kv, size_t layer, void *out_host, const void *q_host,
                                            const void *k_new_host, const void *v_new_host, const int32_t *seq_ids,
                                            const int32_t *kv_lens, size_t n_seqs, size_t nh, float scale);

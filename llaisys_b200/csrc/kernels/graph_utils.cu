@@ -37,6 +37,15 @@ void advance_decode_state(stream_t stream, int64_t *tokens, const int64_t *next,
     check_launch("advance_decode_state");
 }
 
+const void *mapped_host_alias(const void *host_ptr) {
+    cudaPointerAttributes attr;
+    if (host_ptr == nullptr || cudaPointerGetAttributes(&attr, host_ptr) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+}
+
 void graph_capture_begin(stream_t stream) {
     LLAISYS_CUDA_CHECK(cudaStreamBeginCapture(static_cast<cudaStream_t>(stream), cudaStreamCaptureModeThreadLocal));
 }

@@ -10,6 +10,10 @@ namespace llaisys::kernels {
 
 // Queues a memset of `bytes` zero bytes.
 void fill_zero(stream_t stream, void *ptr, size_t bytes);
+// The address under which kernels of the current device can read a host buffer directly: non-null only for page-locked
+// host memory that is mapped into the device's address space (what cudaHostAlloc / cudaMallocHost and torch's pinned
+// tensors give); null for pageable memory, for device memory and on any error.
+const void *mapped_host_alias(const void *host_ptr);
 
 // c = a + b over n contiguous elements of F32 / F16 / BF16 (arithmetic in f32).
 void add(stream_t stream, llaisysDataType_t dtype, void *c, const void *a, const void *b, size_t n);
@@ -60,10 +64,11 @@ float event_elapsed_ms(void *start, void *stop); // synchronises on `stop`
 void event_destroy(void *event);
 
 // K1: row i of k_rows / v_rows [n_rows, nkvh, d] -> token positions[i] of the sequence in table row seq_ids[i].
-// 16-byte vector copies; a row whose block or page is out of range is skipped and flagged.
+// 16-byte vector copies; a row whose block or page is out of range is skipped and flagged. side_src / side_dst: an
+// optional plain copy of side_bytes (a multiple of 16) done by the same launch.
 void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const void *k_rows, const void *v_rows,
                   const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t max_blocks,
-                  int32_t *error_flag);
+                  int32_t *error_flag, const void *side_src = nullptr, void *side_dst = nullptr, size_t side_bytes = 0);
 
 // K1b: bias + rotary embedding + append in one pass over the packed projection qkv [n_rows, (nh + 2 nkvh) * d]: rotated q
 // -> q_out [n_rows, nh, d]; rotated k and plain v -> their page slots (same addressing and flags as K1).

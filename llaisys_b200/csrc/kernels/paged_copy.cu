@@ -11,6 +11,8 @@
 #include "device_utils.cuh"
 #include "kernels.hpp"
 
+#include <algorithm>
+
 namespace llaisys::kernels {
 
 namespace {
@@ -46,7 +48,8 @@ __global__ void paged_append_kernel(uint4 *__restrict__ k_pool, uint4 *__restric
                                     const uint4 *__restrict__ k_rows, const uint4 *__restrict__ v_rows,
                                     const int32_t *__restrict__ table, const int32_t *__restrict__ seq_ids,
                                     const int32_t *__restrict__ positions, CopyGeom g, int32_t n_rows,
-                                    int32_t max_blocks, int32_t *error_flag) {
+                                    int32_t max_blocks, int32_t *error_flag, const uint4 *__restrict__ side_src,
+                                    uint4 *__restrict__ side_dst, int32_t side_vecs) {
     // Under a programmatic launch this grid may start early: let the next kernel do the same, then wait for the
     // previous one (it may still be reading the pages this grid writes).
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
@@ -68,6 +71,24 @@ __global__ void paged_append_kernel(uint4 *__restrict__ k_pool, uint4 *__restric
             const uint4 kv = k_rows[src], vv = v_rows[src];
             k_pool[dst] = kv;
             v_pool[dst] = vv;
+        }
+    }
+    // An unrelated plain copy riding on this launch (the host step's q rows, read from mapped host memory): four
+    // vectors per thread in flight.
+    const int32_t threads = int32_t(gridDim.x * blockDim.x), me = int32_t(blockIdx.x * blockDim.x + threadIdx.x);
+    for (int32_t i = me; i < side_vecs; i += 4 * threads) {
+        uint4 val[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (i + u * threads < side_vecs) {
+                val[u] = side_src[i + u * threads];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (i + u * threads < side_vecs) {
+                side_dst[i + u * threads] = val[u];
+            }
         }
     }
 }
@@ -278,13 +299,15 @@ void launch_rope_append(cudaStream_t s, const KVView &kv, void *q_out, const voi
 
 void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const void *k_rows, const void *v_rows,
                   const int32_t *seq_ids, const int32_t *positions, int32_t n_rows, int32_t max_blocks,
-                  int32_t *error_flag) {
+                  int32_t *error_flag, const void *side_src, void *side_dst, size_t side_bytes) {
     if (n_rows <= 0) {
         return;
     }
+    CHECK_ARGUMENT(side_bytes % 16 == 0 && side_bytes / 16 < size_t(INT32_MAX), "paged append: side copy size");
     const CopyGeom g = make_geom(kv, elem_size);
     const int block = 256;
-    const int grid = grid_for(int64_t(n_rows) * 32, block); // one warp per row
+    // one warp per row; with a side copy, also enough threads for four of its vectors each
+    const int grid = grid_for(std::max<int64_t>(int64_t(n_rows) * 32, int64_t(side_bytes / 64)), block);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(grid));
     cfg.blockDim = dim3(unsigned(block));
@@ -297,7 +320,8 @@ void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const voi
     LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_append_kernel, static_cast<uint4 *>(kv.k_base),
                                           static_cast<uint4 *>(kv.v_base), static_cast<const uint4 *>(k_rows),
                                           static_cast<const uint4 *>(v_rows), kv.block_table, seq_ids, positions, g, n_rows,
-                                          max_blocks, error_flag));
+                                          max_blocks, error_flag, static_cast<const uint4 *>(side_src),
+                                          static_cast<uint4 *>(side_dst), int32_t(side_bytes / 16)));
     check_launch("paged_append");
 }
 

@@ -769,12 +769,47 @@ void PagedKV::decodeStepHost(size_t layer, void *out_host, const void *q_host, c
     int32_t *idx = stage(arrays, lens, 3);
     const auto *api = rt.api();
     llaisysStream_t stream = rt.stream();
-    api->memcpy_async(k_d, k_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
-    api->memcpy_async(v_d, v_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
-    api->memcpy_async(q_d, q_host, q_bytes, LLAISYS_MEMCPY_H2D, stream);
-    appendDev(layer, k_d, v_d, idx, idx + n_seqs, n_seqs, stream);
-    decodeDev(layer, out_d, nullptr, q_d, idx, idx + 2 * n_seqs, n_seqs, max_kv, nh, scale, stream);
-    api->memcpy_async(out_host, out_d, q_bytes, LLAISYS_MEMCPY_D2H, stream);
+    // The new K/V rows are read exactly once, a row per warp: when the caller's buffers are page-locked and mapped the
+    // append kernel takes them straight from host memory and two of the step's five copies go away (each costs more in
+    // latency than its 32 KiB do in transfer). q is read by every CTA that works on its sequence, so it is copied --
+    // by the append launch as well when it is mapped too.
+    const void *k_src = k_d, *v_src = v_d;
+#ifdef ENABLE_NVIDIA_API
+    const void *k_alias = kernels::mapped_host_alias(k_new_host), *v_alias = kernels::mapped_host_alias(v_new_host);
+    if (k_alias != nullptr && v_alias != nullptr) {
+        k_src = k_alias;
+        v_src = v_alias;
+    }
+#endif
+    if (k_src == k_d) {
+        api->memcpy_async(k_d, k_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
+        api->memcpy_async(v_d, v_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
+    }
+    bool q_rides = false; // q copied by the append launch itself, from mapped host memory
+#ifdef ENABLE_NVIDIA_API
+    const void *q_alias = k_src != k_d ? kernels::mapped_host_alias(q_host) : nullptr;
+    if (q_alias != nullptr && q_bytes % 16 == 0) {
+        kernels::paged_append(stream, _elem, view(layer), k_src, v_src, idx, idx + n_seqs, int32_t(n_seqs),
+                              int32_t(_cfg.max_pages_per_seq), reinterpret_cast<int32_t *>(_error_dev->memory()), q_alias,
+                              q_d, q_bytes);
+        q_rides = true;
+    }
+#endif
+    if (!q_rides) {
+        api->memcpy_async(q_d, q_host, q_bytes, LLAISYS_MEMCPY_H2D, stream);
+        appendDev(layer, k_src, v_src, idx, idx + n_seqs, n_seqs, stream);
+    }
+    // Every output row is written once, 16 bytes per thread: into the caller's buffer directly when it is mapped
+    void *out_dst = out_d;
+#ifdef ENABLE_NVIDIA_API
+    if (const void *out_alias = kernels::mapped_host_alias(out_host)) {
+        out_dst = const_cast<void *>(out_alias);
+    }
+#endif
+    decodeDev(layer, out_dst, nullptr, q_d, idx, idx + 2 * n_seqs, n_seqs, max_kv, nh, scale, stream);
+    if (out_dst == out_d) {
+        api->memcpy_async(out_host, out_d, q_bytes, LLAISYS_MEMCPY_D2H, stream);
+    }
     api->stream_synchronize(stream);
 }
 
