@@ -199,6 +199,37 @@ __device__ __forceinline__ Fragment locate(const PrefillParams &p, Walker &w, in
     return f;
 }
 
+// Blackwell's wider scalar arithmetic for the softmax rows: a three-input maximum and two-wide f32 multiply-add / add
+// (one instruction for two scores: these warps are short of issue slots, not of pipe throughput).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ void fma2(float &x0, float &x1, float a0, float a1, float b, float c) { // x = a * b + c
+    asm("{\n"
+        ".reg .b64 ra, rb, rc, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %4};\n"
+        "mov.b64 rc, {%5, %5};\n"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}\n"
+        : "=f"(x0), "=f"(x1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float &s0, float &s1, float a0, float a1) { // s += a
+    asm("{\n"
+        ".reg .b64 rs, ra;\n"
+        "mov.b64 rs, {%0, %1};\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "add.rn.f32x2 rs, rs, ra;\n"
+        "mov.b64 {%0, %1}, rs;\n"
+        "}\n"
+        : "+f"(s0), "+f"(s1)
+        : "f"(a0), "f"(a1));
+}
+
 template <bool kBf16>
 __global__ void __launch_bounds__(kThreads, 2)
     paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_v,
@@ -538,8 +569,8 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
                     for (int c = 0; c < kBlockN / 32; ++c) {
 #pragma unroll
-                        for (int k = 0; k < 32; ++k) {
-                            mx8[k & 7] = fmaxf(mx8[k & 7], __uint_as_float(sr[c][k]));
+                        for (int k = 0; k < 16; ++k) {
+                            mx8[k & 7] = max3(mx8[k & 7], __uint_as_float(sr[c][k]), __uint_as_float(sr[c][k + 16]));
                         }
                     }
                 } else {
@@ -577,16 +608,14 @@ __global__ void __launch_bounds__(kThreads, 2)
                     for (int c = 0; c < kBlockN / 32; ++c) {
 #pragma unroll
                         for (int k = 0; k < 32; k += 2) {
-                            const float x0 = fmaf(__uint_as_float(sr[c][k]), p.scale_log2, neg_m);
-                            const float x1 = fmaf(__uint_as_float(sr[c][k + 1]), p.scale_log2, neg_m);
+                            float x0, x1;
+                            fma2(x0, x1, __uint_as_float(sr[c][k]), __uint_as_float(sr[c][k + 1]), p.scale_log2, neg_m);
                             const float p0 = fast_exp2(x0);
                             const float p1 = fast_exp2(x1);
                             if (k & 2) {
-                                l2 += p0;
-                                l3 += p1;
+                                add2(l2, l3, p0, p1);
                             } else {
-                                l0 += p0;
-                                l1 += p1;
+                                add2(l0, l1, p0, p1);
                             }
                             packed[c * 16 + (k >> 1)] = pack2<kBf16>(p0, p1);
                         }
