@@ -102,7 +102,8 @@ enum : int {
                                       // earlier, which the MMA thread has waited for)
     kBarPVDone = kBarPFull + 1,       // [2] MMA (commit) -> softmax: O stable; -> producer: V stage is free
     kBarQFull = kBarPVDone + 2,       // softmax (128) -> MMA: Q rows of the next fragment are in shared memory
-    kNumBars = kBarQFull + 1
+    kBarMerge = kBarQFull + 1,        // bulk copy -> softmax: the other half of a split tile is in shared memory
+    kNumBars = kBarMerge + 1
 };
 
 struct PrefillParams {
@@ -361,7 +362,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     // ---- set-up: barriers, TMEM, first Q tile, cleared K/V ring ----------------------------------------------
     if (tid == 0) {
         for (int i = 0; i < kNumBars; ++i) {
-            const bool many = i == kBarPFull || i == kBarQFull;
+            const bool many = i == kBarPFull || i == kBarQFull; // (kBarMerge: one arrival, by the thread that starts the copies)
             mbar_init(bars_u32 + i * 8, many ? kSoftmaxThreads : 1);
         }
         *s_abort = 0;
@@ -686,8 +687,8 @@ __global__ void __launch_bounds__(kThreads, 2)
             tc_fence_after();
             const bool whole = f.b0 == 0 && f.b1 == f.tile_nblk;
             char *out_row = static_cast<char *>(p.out) + ((long long)(g.q_start + t) * p.nh + f.h) * (kD * 2);
-            bool store_rows = whole;
-            float w_own = 1.f, l_all = l, m_all = m_used;
+            bool store_rows = whole, staged = false;
+            float w_own = 1.f, w_other = 0.f, l_all = l, m_all = m_used;
             const int first_slot = f.tile_begin / piece, last_slot = (f.tile_begin + f.tile_nblk - 1) / piece;
             if (!whole) {
                 // unnormalised accumulator + (max, sum) of the rows into this CTA's workspace slot: slot 1 for the
@@ -720,7 +721,38 @@ __global__ void __launch_bounds__(kThreads, 2)
                 }
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");
                 store_rows = s_sched[14] != 0;
-                if (store_rows && !dead) {
+                // The usual merge: the CTA's last fragment begins a tile that the next CTA finished long ago. The
+                // operands and Q are no longer needed, so the other half (64 KiB + maxima and sums) is fetched into
+                // their place by five bulk copies and combined from shared memory: one trip to L2 instead of six
+                // dependent ones. Same arithmetic, in the same order, as the general path below.
+                staged = store_rows && last_slot == first_slot + 1 && slot == first_slot && pos + n == piece_end;
+                if (staged) {
+                    const float *other = p.partials + (long long)((slot + 1) * 2) * kPartialFloats;
+                    if (tid == 0) {
+                        __threadfence();
+                        asm volatile("fence.proxy.async;\n" ::: "memory"); // generic-proxy writes of another SM -> bulk read
+                        mbar_arrive_expect_tx(bar(kBarMerge), uint32_t(kPartialFloats * sizeof(float)));
+                        for (int j = 0; j < 4; ++j) {
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                                             kv_u32 + j * 16384),
+                                         "l"(other + j * 4096), "r"(16384), "r"(bar(kBarMerge))
+                                         : "memory");
+                        }
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(q_u32),
+                                     "l"(other + kBlockM * kD), "r"(2 * kBlockM * 4), "r"(bar(kBarMerge))
+                                     : "memory");
+                    }
+                    if (!dead && !wait_or_abort(bar(kBarMerge), 0u, s_abort)) {
+                        dead = true;
+                    }
+                    float m2, l2;
+                    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(m2) : "r"(q_u32 + row * 4) : "memory");
+                    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(l2) : "r"(q_u32 + (kBlockM + row) * 4) : "memory");
+                    m_all = fmaxf(m_used, m2);
+                    w_own = m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_all);
+                    w_other = m2 == -INFINITY ? 0.f : fast_exp2(m2 - m_all);
+                    l_all = fmaf(l2, w_other, fmaf(l, w_own, 0.f));
+                } else if (store_rows && !dead) {
                     __threadfence();
                     // merge the other fragments' rows into this one's: weights 2^(m_i - m) in the log2 domain
                     for (int s2 = first_slot; s2 <= last_slot; ++s2) {
@@ -753,7 +785,20 @@ __global__ void __launch_bounds__(kThreads, 2)
                 for (int c4 = 0; c4 < 4; ++c4) {
                     float v[32];
                     tmem_ld32(tmem_o + c4 * 32, v);
-                    if (!whole) {
+                    if (staged) {
+#pragma unroll
+                        for (int q8 = 0; q8 < 8; ++q8) {
+                            float4 o;
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                                         : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w)
+                                         : "r"(kv_u32 + ((c4 * 8 + q8) * kBlockM + row) * 16)
+                                         : "memory");
+                            v[q8 * 4] = fmaf(o.x, w_other, fmaf(v[q8 * 4], w_own, 0.f));
+                            v[q8 * 4 + 1] = fmaf(o.y, w_other, fmaf(v[q8 * 4 + 1], w_own, 0.f));
+                            v[q8 * 4 + 2] = fmaf(o.z, w_other, fmaf(v[q8 * 4 + 2], w_own, 0.f));
+                            v[q8 * 4 + 3] = fmaf(o.w, w_other, fmaf(v[q8 * 4 + 3], w_own, 0.f));
+                        }
+                    } else if (!whole) {
                         float own[32];
 #pragma unroll
                         for (int k = 0; k < 32; ++k) {
