@@ -558,7 +558,18 @@ __global__ void __launch_bounds__(kThreads, 2)
                 }
                 tmem_wait_ld();
                 // Most blocks lie wholly below the diagonal: the whole warp then skips the mask (warp-uniform choice).
-                const bool plain = __all_sync(0xffffffffu, n_ok >= kBlockN) && p.scale_log2 > 0.f;
+                // Otherwise the hidden scores become -inf and take the same path: 2^(-inf * scale - m) = 0. (A scale
+                // that is not positive takes the slow path further down.)
+                const bool plain = p.scale_log2 > 0.f;
+                if (plain && !__all_sync(0xffffffffu, n_ok >= kBlockN)) {
+#pragma unroll
+                    for (int c = 0; c < kBlockN / 32; ++c) {
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) {
+                            sr[c][k] = c * 32 + k < n_ok ? sr[c][k] : 0xff800000u;
+                        }
+                    }
+                }
                 // Row maximum as eight independent chains (a single chain of 64 dependent max operations would cost more
                 // than the exponentials that follow).
                 float mx8[8];
