@@ -181,7 +181,7 @@ PROTOTYPES: dict[str, tuple] = {
                                 c_size_t, c_size_t]),
     "llaisysPagedKVAppendDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                         llaisysStream_t]),
-    "llaisysPagedDecodeStepHost": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, _I32P, _I32P, c_size_t,
+    "llaisysPagedDecodeStepHost": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                            c_size_t, c_float]),
     "llaisysPagedKVSeqPublish": (c_int, [_KV, c_int32, POINTER(c_int64), c_size_t]),
     "llaisysPagedKVSeqMatchPrefix": (c_int, [_KV, c_int32, POINTER(c_int64), c_size_t, POINTER(c_size_t)]),

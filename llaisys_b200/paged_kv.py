@@ -35,6 +35,14 @@ def _i32(values) -> tuple[np.ndarray, ctypes.Array]:
     return arr, arr.ctypes.data_as(_I32P)
 
 
+def _i32_address(values) -> tuple[np.ndarray, int]:
+    """The same for the per-step call, where the few microseconds of building a ctypes pointer object count: the
+    array (kept alive by the caller's frame) and its address as a plain integer."""
+    arr = values if (type(values) is np.ndarray and values.dtype == np.int32 and values.flags.c_contiguous) else \
+        np.ascontiguousarray(values, dtype=np.int32)
+    return arr, arr.__array_interface__["data"][0]
+
+
 class PagedKVCache:
     """Fixed pool of pages with a free list and per-sequence block tables.
 
@@ -170,8 +178,8 @@ class PagedKVCache:
         """One decode step from host buffers, synchronous: k_new[i] / v_new[i] become token kv_lens[i] - 1 of sequence
         seq_ids[i], then out[i] = attention of q[i] over kv_lens[i] tokens. out, q, k_new, v_new are HOST tensors
         (pinned ones copy asynchronously); seq_ids / kv_lens may be int32 numpy arrays (used as they are) or lists."""
-        s, sp = _i32(seq_ids)
-        l, lp = _i32(kv_lens)
+        s, sp = _i32_address(seq_ids)
+        l, lp = _i32_address(kv_lens)
         if s.size != l.size:
             raise ValueError("seq_ids and kv_lens must have the same length")
         _check(LIB_LLAISYS.llaisysPagedDecodeStepHost(self._kv, layer, _addr(out), _addr(q), _addr(k_new), _addr(v_new),
