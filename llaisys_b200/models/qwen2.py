@@ -8,6 +8,7 @@ generate() follows the Hugging Face convention the reference's test compares aga
 from __future__ import annotations
 
 import ctypes
+import itertools
 import json
 from ctypes import c_float, c_int, c_int32, c_int64
 from pathlib import Path
@@ -269,9 +270,10 @@ class Qwen2:
         if len(tokens) != n:
             raise ValueError("one token list per sequence")
         ids = np.ascontiguousarray(seq_ids, dtype=np.int32)
-        counts = np.ascontiguousarray([len(t) for t in tokens], dtype=np.int32)
-        flat = np.ascontiguousarray(np.concatenate([np.asarray(t, dtype=np.int64).reshape(-1) for t in tokens])
-                                    if n else np.zeros(0, np.int64))
+        # (one pass over the token lists: building an array per sequence and concatenating them cost more than the
+        # library call's own host work in a 64-sequence decode step)
+        counts = np.fromiter(map(len, tokens), dtype=np.int32, count=n)
+        flat = np.fromiter(itertools.chain.from_iterable(tokens), dtype=np.int64, count=int(counts.sum()))
         nxt = np.zeros(n, dtype=np.int64)
         _check(LIB_LLAISYS.llaisysQwen2ModelStep(
             self._model, ids.ctypes.data_as(ctypes.POINTER(c_int32)), counts.ctypes.data_as(ctypes.POINTER(c_int32)), n,
