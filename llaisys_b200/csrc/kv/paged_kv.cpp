@@ -9,6 +9,7 @@
 #endif
 
 #include <algorithm>
+#include <cstdint>
 #include <cstdlib>
 #include <cstring>
 #include <limits>
@@ -776,7 +777,8 @@ void PagedKV::decodeStepHost(size_t layer, void *out_host, const void *q_host, c
     const void *k_src = k_d, *v_src = v_d;
 #ifdef ENABLE_NVIDIA_API
     const void *k_alias = kernels::mapped_host_alias(k_new_host), *v_alias = kernels::mapped_host_alias(v_new_host);
-    if (k_alias != nullptr && v_alias != nullptr) {
+    if (k_alias != nullptr && v_alias != nullptr && reinterpret_cast<uintptr_t>(k_alias) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(v_alias) % 16 == 0) {
         k_src = k_alias;
         v_src = v_alias;
     }
@@ -788,7 +790,7 @@ void PagedKV::decodeStepHost(size_t layer, void *out_host, const void *q_host, c
     bool q_rides = false; // q copied by the append launch itself, from mapped host memory
 #ifdef ENABLE_NVIDIA_API
     const void *q_alias = k_src != k_d ? kernels::mapped_host_alias(q_host) : nullptr;
-    if (q_alias != nullptr && q_bytes % 16 == 0) {
+    if (q_alias != nullptr && q_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(q_alias) % 16 == 0) {
         kernels::paged_append(stream, _elem, view(layer), k_src, v_src, idx, idx + n_seqs, int32_t(n_seqs),
                               int32_t(_cfg.max_pages_per_seq), reinterpret_cast<int32_t *>(_error_dev->memory()), q_alias,
                               q_d, q_bytes);
@@ -803,7 +805,9 @@ void PagedKV::decodeStepHost(size_t layer, void *out_host, const void *q_host, c
     void *out_dst = out_d;
 #ifdef ENABLE_NVIDIA_API
     if (const void *out_alias = kernels::mapped_host_alias(out_host)) {
-        out_dst = const_cast<void *>(out_alias);
+        if (reinterpret_cast<uintptr_t>(out_alias) % 16 == 0) {
+            out_dst = const_cast<void *>(out_alias);
+        }
     }
 #endif
     decodeDev(layer, out_dst, nullptr, q_d, idx, idx + 2 * n_seqs, n_seqs, max_kv, nh, scale, stream);
