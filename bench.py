@@ -1,7 +1,8 @@
 """Benchmark of the paged KV-cache decode path: one step = append one new K/V row per sequence, then
-flash-decoding attention of one query per sequence over its whole paged context (one layer).
+flash-decoding attention of one query per sequence over its whole paged context (one layer) -- ONE kernel launch
+(llaisysPagedDecodeStepDev).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload north_star|config2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload north_star|config2|...]
 
 Prints ONE JSON line (rank 0). With N > 1 it is launched under torch.distributed.run, one rank per GPU; whole
 sequences are sharded across ranks, each rank owns its page pool, and there is no data-path collective
@@ -12,15 +13,24 @@ random permutation of a 16384-page pool):
   north_star  64 sequences x 4096-token context -- the shape the target "paged decode attention sustaining
               >= 70 % of HBM peak" is quoted on; uses the whole pool (256 MiB per layer)
   config2     32 sequences, context ~ U{128..4096}
+  config3     chunked prefill: 8 sequences, context ~ U{0..8192}, a 512-token chunk appended and attended causally
+  config5     one 131072-token sequence, 28 layers, KV range split over the GPUs, partial results exchanged and merged
+The default run (north_star) also measures config2 and config3 in the same process (N = 1: sub-records "config2",
+"config3") and, with N > 1, the KV-range split of config5 in the same process group (sub-record "kv_split"): the one
+mode of this path in which GPUs exchange data.
 
 Numbers:
-  value      tokens/s of the step with inputs resident in HBM, device-timed (CUDA events on the launch stream),
+  value      tokens/s of the step with inputs resident in HBM, device-timed: a CUDA graph of K steps is replayed R >= 30
+             times with an event pair around every replay; value uses the MEDIAN replay, min and max are reported;
              max over ranks
-  roofline   achieved HBM GB/s of the decode kernel = algorithmic bytes / its mean event-timed duration
-  e2e        same step through the host-array C-ABI calls with host<->device copies of q, k, v, out in the
+  roofline   achieved HBM GB/s of the step kernel = algorithmic bytes / its launch-to-launch period in that graph
+             (consecutive launches overlap by programmatic dependent launch); the same kernel launched without overlap
+             and the decode-only / append-only kernels are timed beside it
+  e2e        same step through the host-buffer C-ABI call with host<->device copies of q, k, v, out in the
              timed region, wall clock bracketed by device synchronisation
   cpu_baseline / --impl reference   the reference's CPU definition of the path (oracle port of its PyTorch
-             torch_self_attention) on a bounded sample of the same workload, all host threads
+             torch_self_attention) on a bounded sample of the same workload, all host threads; the library's own
+             plain-C++ CPU backend of llaisysSelfAttention is timed beside it
 Between timed steps the layer rotates over pools that together exceed L2 several times, so K/V always comes
 from HBM.
 """
@@ -30,7 +40,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -43,9 +52,10 @@ sys.path.insert(0, str(ROOT))
 
 NH, NKVH, D, PAGE, POOL_PAGES = 12, 2, 128, 16, 16384
 METRIC = "decode tokens/s (paged KV append + flash-decoding attention, one layer)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch on the north_star workload, from the ncu
-# capture summarised in profiles/decode_tma_north_star.md; None where no capture exists.
-NCU_TRAFFIC_BYTES = {"north_star": 273_930_000, "config2": None}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the step kernel, from ncu captures of this file's own
+# command line on a 2-layer pool; None where no capture exists.
+NCU_TRAFFIC_BYTES = {"north_star": None, "config2": None}
+MIN_REPEATS = 30
 
 
 def workload_lengths(name: str, seed: int):
@@ -59,19 +69,39 @@ def workload_lengths(name: str, seed: int):
     raise SystemExit(f"unknown workload {name}")
 
 
-def algorithmic_bytes(ctx: list[int]) -> int:
-    """Bytes one decode launch must move: K and V read once, q read, out written, block-table entries."""
+def algorithmic_bytes(ctx: list[int], with_append: bool = False) -> int:
+    """Bytes one decode launch must move: K and V read once, q read, out written, block-table entries; the one-launch
+    step also reads the new K/V rows and writes them into their pages."""
     b = len(ctx)
-    return sum(ctx) * (2 * NKVH * D * 2) + 2 * b * NH * D * 2 + 4 * sum(-(-c // PAGE) for c in ctx)
+    total = sum(ctx) * (2 * NKVH * D * 2) + 2 * b * NH * D * 2 + 4 * sum(-(-c // PAGE) for c in ctx)
+    if with_append:
+        total += 2 * b * (2 * NKVH * D * 2)
+    return total
+
+
+def decode_config(workload: str, ctx: list[int], world: int, layers: int, overlap: bool) -> dict:
+    """The `config` object of the decode workloads; both arms (this library and --impl reference) print the same one."""
+    return {"workload": workload, "batch_per_gpu": len(ctx), "context": f"{min(ctx)}..{max(ctx)}",
+            "heads": "12q/2kv", "head_dim": D, "page_size": PAGE, "pool_pages": POOL_PAGES,
+            "parallelism": f"sequences sharded over {world} GPU(s), no collective",
+            "l2": f"inputs larger than L2: layer pool rotates over {layers} x {POOL_PAGES * PAGE * 1024 >> 20} MiB between steps",
+            "launch": ("programmatic dependent launch: a kernel's set-up and first K/V copies overlap the previous "
+                       "kernel's tail") if overlap else "plain"}
+
+
+def spread(samples: list[float], scale: float = 1.0) -> dict:
+    """median / min / max of a list of timings (already divided by `scale` units each)."""
+    xs = [x / scale for x in samples]
+    return {"median": statistics.median(xs), "min": min(xs), "max": max(xs), "n": len(xs)}
 
 
 class ClockSampler:
-    """Samples the SM clock and the throttle reasons through NVML (read-only queries) every few milliseconds
+    """Samples the SM clock and the throttle reasons through NVML (read-only queries) about once a millisecond
     while the timed region runs."""
 
     REASONS = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
-    def __init__(self, index: int, period_s: float = 0.002):
+    def __init__(self, index: int, period_s: float = 0.001):
         self.index, self.period, self.sm, self.bits, self.max_mhz = index, period_s, [], 0, None
         self.stop = threading.Event()
         self.thread = None
@@ -130,19 +160,33 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.sm)}
 
 
-def reference_cpu_rate(ctx: list[int], seed: int, min_seconds: float, max_seqs: int):
-    """Times the oracle port of the reference's torch_self_attention (reference: test/ops/self_attention.py:11-28),
-    one call per sequence on contiguous bf16 K/V, on a bounded sample of the workload. -> tokens/s, description"""
+def host_threads() -> int:
+    return len(os.sched_getaffinity(0))
+
+
+def cpu_sample(ctx: list[int], seed: int, max_seqs: int):
+    """The bounded CPU sample of a decode workload: the first max_seqs sequences, contiguous bf16 K/V, one query each."""
     import torch
 
-    from oracle import attention, workloads
+    from oracle import workloads
 
-    torch.set_num_threads(len(os.sched_getaffinity(0)))
     g = torch.Generator().manual_seed(seed)
     sample = ctx[:max_seqs]
     qs = [workloads.randn((1, NH, D), torch.bfloat16, g) for _ in sample]
     ks = [workloads.randn((c, NKVH, D), torch.bfloat16, g) for c in sample]
     vs = [workloads.randn((c, NKVH, D), torch.bfloat16, g) for c in sample]
+    return sample, qs, ks, vs
+
+
+def reference_cpu_rate(ctx: list[int], seed: int, min_seconds: float, max_seqs: int):
+    """Times the oracle port of the reference's torch_self_attention (reference: test/ops/self_attention.py:11-28),
+    one call per sequence on contiguous bf16 K/V, on a bounded sample of the workload. -> tokens/s, seconds, description, threads"""
+    import torch
+
+    from oracle import attention
+
+    torch.set_num_threads(host_threads())
+    sample, qs, ks, vs = cpu_sample(ctx, seed, max_seqs)
     scale = 1.0 / D ** 0.5
     attention.self_attention(qs[0], ks[0], vs[0], scale)  # warm-up
     done, t0 = 0, time.perf_counter()
@@ -158,11 +202,38 @@ def reference_cpu_rate(ctx: list[int], seed: int, min_seconds: float, max_seqs: 
     return done / dt, dt, desc, torch.get_num_threads()
 
 
+def cpp_backend_cpu_rate(ctx: list[int], seed: int, min_seconds: float, max_seqs: int) -> dict:
+    """The same sample through the library's own CPU backend of llaisysSelfAttention (plain C++ loops, OpenMP over
+    query heads): what a CPU-only build of the reference's operator interface runs. -> record for cpu_baseline"""
+    import llaisys_b200 as llaisys
+    from tests import helpers
+
+    cpu = llaisys.DeviceType.CPU
+    sample, qs, ks, vs = cpu_sample(ctx, seed, max_seqs)
+    scale = 1.0 / D ** 0.5
+    tensors = [tuple(helpers.to_llaisys(t, cpu, "bf16") for t in (q, k, v)) for q, k, v in zip(qs, ks, vs)]
+    outs = [llaisys.Tensor((1, NH, D), dtype=llaisys.DataType.BF16, device=cpu) for _ in sample]
+    llaisys.Ops.self_attention(outs[0], *tensors[0], scale)
+    done, t0 = 0, time.perf_counter()
+    while True:
+        for o, (q, k, v) in zip(outs, tensors):
+            llaisys.Ops.self_attention(o, q, k, v, scale)
+        done += len(sample)
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds:
+            break
+    threads = int(os.environ.get("OMP_NUM_THREADS") or host_threads())
+    return {"value": done / dt, "unit": "tokens/s", "cores": threads, "kind": "llaisys_b200 CPU backend (C++, OpenMP)",
+            "sample": f"{len(sample)} of {len(ctx)} sequences, {done // len(sample)} passes, {dt:.1f} s"}
+
+
 def run_reference_arm(args) -> None:
     """--impl reference: the reference's own CPU definition of the path on the host cores, rank 0 only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # launchers such as torch.distributed.run export OMP_NUM_THREADS=1; the CPU arm is meant to use the whole host
+    os.environ["OMP_NUM_THREADS"] = str(host_threads())
     if args.workload == "config4":
         rate, threads, sample = model_cpu_rate(QWEN2_1P5B, 20.0)
         print(json.dumps({
@@ -179,23 +250,19 @@ def run_reference_arm(args) -> None:
                           f"the CPU arm covers north_star, config2 and config4; {args.workload} has no bounded CPU sample"}),
               flush=True)
         return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     ctx = workload_lengths(args.workload, seed=2)
     per_step = max(1, min(4, len(ctx)))
     args.steps = min(args.steps, 200)  # bounded: the CPU arm needs seconds per step, not microseconds
-    times, threads, desc = [], 1, ""
     import torch
 
-    from oracle import attention, workloads
+    from oracle import attention
 
-    # launchers such as torch.distributed.run export OMP_NUM_THREADS=1; the CPU arm is meant to use the whole host
-    torch.set_num_threads(len(os.sched_getaffinity(0)))
-    g = torch.Generator().manual_seed(2)
-    sample = ctx[:per_step]
-    qs = [workloads.randn((1, NH, D), torch.bfloat16, g) for _ in sample]
-    ks = [workloads.randn((c, NKVH, D), torch.bfloat16, g) for c in sample]
-    vs = [workloads.randn((c, NKVH, D), torch.bfloat16, g) for c in sample]
+    torch.set_num_threads(host_threads())
+    sample, qs, ks, vs = cpu_sample(ctx, 2, per_step)
     scale = 1.0 / D ** 0.5
     threads = torch.get_num_threads()
+    times = []
     for step in range(args.warmup + args.steps):
         t0 = time.perf_counter()
         for q, k, v in zip(qs, ks, vs):
@@ -204,12 +271,14 @@ def run_reference_arm(args) -> None:
             times.append(time.perf_counter() - t0)
     total = sum(times)
     value = per_step * len(times) / total
-    desc = f"each step = {per_step} of the workload's {len(ctx)} sequences (ctx {sample}), bf16, contiguous K/V"
+    desc = (f"each step = the first {per_step} of the workload's {len(ctx)} sequences (ctx {sample}), bf16, contiguous K/V, "
+            f"oracle port of torch_self_attention, torch {torch.__version__}; tokens/s does not depend on how many of the "
+            "equal-length sequences a step holds")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "batch": len(ctx), "heads": "12q/2kv", "head_dim": D},
+        "config": decode_config(args.workload, ctx, world, args.layers, not args.no_overlap),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -239,17 +308,207 @@ def _init_device():
 
 
 def _peaks():
+    """-> HBM GB/s, bf16 TFLOP/s burst, bf16 TFLOP/s sustained, "measured" | "fallback" """
     peaks_file = ROOT / "MEASURED_PEAKS.json"
     if peaks_file.exists():
         d = json.loads(peaks_file.read_text())
-        return float(d["hbm_gbs"]), float(d["bf16_tflops_sustained"]), "measured"
-    return 6650.0, 1400.0, "fallback"
+        return float(d["hbm_gbs"]), float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
 
 
-def run_prefill_workload(args) -> None:
-    """--workload config3: chunked prefill. 8 sequences per GPU, existing context ~ U{0..8192}, a 512-token chunk
-    appended and then attended causally. A step = append of the chunk rows + the tcgen05 prefill kernel."""
-    torch, llaisys, rank, local_rank, world, dist = _init_device()
+def replay_times(torch, stream, graph, repeats: int) -> list[float]:
+    """Replays a captured graph `repeats` times with an event pair around every replay -> milliseconds per replay."""
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(repeats + 1)]
+    with torch.cuda.stream(stream):
+        graph.replay()  # untimed: the first replay uploads the graph
+        events[0].record(stream)
+        for r in range(repeats):
+            graph.replay()
+            events[r + 1].record(stream)
+    stream.synchronize()
+    return [events[r].elapsed_time(events[r + 1]) for r in range(repeats)]
+
+
+def reduce_max(torch, dist, values: list[float]) -> list[float]:
+    if dist is None:
+        return values
+    t = torch.tensor(values, device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t]
+
+
+def measure_decode(env, workload: str, args, *, steps: int, repeats: int, with_e2e: bool, sampler=None) -> dict:
+    """One decode workload on this rank's GPU -> record (timings already reduced to the max over ranks).
+
+    The timed loops are CUDA graphs (a step is shorter than the Python time to queue it): `steps` consecutive steps with
+    the layer rotating over pools larger than L2, replayed `repeats` times. Graphs: the one-launch step (the product
+    path), the same without launch overlap, decode only, append only, and the two-launch step (append, then decode)."""
+    torch, llaisys, rank, local_rank, world, dist = env
+    dev = llaisys.DeviceType.NVIDIA
+    ctx = workload_lengths(workload, seed=2 + rank)
+    B, layers = len(ctx), args.layers
+    max_pages = max(-(-c // PAGE) for c in ctx)
+    cache = llaisys.PagedKVCache(POOL_PAGES, NKVH, D, nlayer=layers, dtype=llaisys.DataType.BF16, device=dev,
+                                 device_id=local_rank, max_seqs=B, max_pages_per_seq=max_pages)
+    g = torch.Generator().manual_seed(100 + rank)
+    perm = torch.randperm(POOL_PAGES, generator=g).tolist()
+    seqs, at = [], 0
+    for c in ctx:
+        s = cache.add_seq()
+        n = -(-c // PAGE)
+        cache.assign_pages(s, perm[at:at + n])
+        at += n
+        seqs.append(s)
+    cache.flush()
+    stream = torch.cuda.Stream()
+    cs = stream.cuda_stream
+    cg = torch.Generator(device="cuda").manual_seed(200 + rank)
+    seq_ids_dev = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    kv_lens_dev = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+    last_pos_dev = kv_lens_dev - 1
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        # fill every layer's pages: all rows but the last of each sequence (the timed step appends the last)
+        row_seq = torch.repeat_interleave(seq_ids_dev, (kv_lens_dev - 1).long())
+        starts = torch.cumsum(kv_lens_dev - 1, 0) - (kv_lens_dev - 1)
+        row_pos = (torch.arange(row_seq.numel(), device="cuda", dtype=torch.int32)
+                   - torch.repeat_interleave(starts, (kv_lens_dev - 1).long()).int())
+        n_rows = row_seq.numel()
+        for layer in range(layers):
+            k_rows = torch.randn((n_rows, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+            v_rows = torch.randn((n_rows, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+            cache.append_dev(layer, k_rows, v_rows, row_seq, row_pos, n_rows, cs)
+            stream.synchronize()
+            del k_rows, v_rows
+        q = torch.randn((B, NH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+        k_new = torch.randn((B, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+        v_new = torch.randn((B, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
+        out = torch.empty_like(q)
+    stream.synchronize()
+    cache.check()
+    scale, max_kv = 1.0 / D ** 0.5, max(ctx)
+    overlap = not args.no_overlap
+
+    def step_one_launch(i):
+        cache.decode_step_dev(i % layers, out, q, k_new, v_new, seq_ids_dev, kv_lens_dev, B, max_kv, NH, scale, cs)
+
+    def only_decode(i):
+        cache.decode_dev(i % layers, out, q, seq_ids_dev, kv_lens_dev, B, max_kv, NH, scale, cs)
+
+    def only_append(i):
+        cache.append_dev(i % layers, k_new, v_new, seq_ids_dev, last_pos_dev, B, cs)
+
+    def step_two_launches(i):
+        only_append(i)
+        only_decode(i)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cache.set_launch_overlap(overlap)
+    for i in range(max(3, args.warmup)):
+        step_one_launch(i)
+    stream.synchronize()
+    assert cache.last_kernel() == llaisys.Kernel.DECODE_TMA_FUSED, "the step did not run on the TMA decode kernel"
+
+    def capture(body, with_overlap):
+        cache.set_launch_overlap(with_overlap)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(steps):
+                body(i)
+        cache.set_launch_overlap(overlap)
+        return graph
+
+    g_step = capture(step_one_launch, overlap)
+    g_step_plain = capture(step_one_launch, False)
+    g_decode = capture(only_decode, overlap)
+    g_append = capture(only_append, overlap)
+    g_two = capture(step_two_launches, overlap)
+
+    barrier()
+    if sampler is not None:
+        sampler.__enter__()
+    step_ms = replay_times(torch, stream, g_step, repeats)
+    barrier()
+    plain_ms = replay_times(torch, stream, g_step_plain, repeats)
+    decode_ms = replay_times(torch, stream, g_decode, repeats)
+    append_ms = replay_times(torch, stream, g_append, repeats)
+    two_ms = replay_times(torch, stream, g_two, repeats)
+    if sampler is not None:
+        sampler.__exit__()
+    cache.check()
+
+    # ---- end to end through the host-buffer call: host buffers, copies inside the timed region ---------------------
+    e2e = None
+    if with_e2e:
+        q_h, k_h, v_h = (t.cpu().pin_memory() for t in (q, k_new, v_new))
+        out_h = torch.empty_like(q_h).pin_memory()
+        seqs_np, ctx_np = np.asarray(seqs, dtype=np.int32), np.asarray(ctx, dtype=np.int32)
+
+        def step_e2e(i: int):
+            # the library's host-buffer step: pinned q / new K,V rows in, the step kernel, attention output back, one
+            # synchronise -- one call per decode step, as a serving loop without device-resident activations makes it
+            cache.decode_step_host(i % layers, out_h, q_h, k_h, v_h, seqs_np, ctx_np, NH, scale)
+
+        e2e_steps = max(10, min(steps * repeats, 1000))
+        for i in range(3):
+            step_e2e(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            step_e2e(i)
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        cache.check()
+        step_e2e(0)  # both legs on the same layer must give the same bits
+        step_one_launch(0)
+        stream.synchronize()
+        same = bool(torch.equal(out_h.view(torch.int16), out.cpu().view(torch.int16)))
+        e2e_s = reduce_max(torch, dist, [e2e_s])[0]
+        e2e = {"value": B * world * e2e_steps / e2e_s, "unit": "tokens/s",
+               "h2d_bytes_per_step": (q_h.numel() + k_h.numel() + v_h.numel()) * 2 + 2 * B * 4,  # + two index arrays
+               "d2h_bytes_per_step": out_h.numel() * 2, "steps": e2e_steps, "ms_per_step": 1e3 * e2e_s / e2e_steps,
+               "matches_device_path": same,
+               "what": "PagedKVCache.decode_step_host(): pinned host q / K,V rows in, attention out, one synchronise"}
+
+    med = [statistics.median(x) for x in (step_ms, plain_ms, decode_ms, append_ms, two_ms)]
+    med = reduce_max(torch, dist, med)
+    lo_hi = reduce_max(torch, dist, [max(step_ms), -min(step_ms)])
+    bytes_step = algorithmic_bytes(ctx, with_append=True)
+    hbm, _, _, kind = _peaks()
+    period_ms = med[0] / steps
+    achieved = bytes_step / (period_ms * 1e-3) / 1e9
+    record = {
+        "workload": workload,
+        "value": B * world * steps / (med[0] * 1e-3), "unit": "tokens/s",
+        "ms_per_step": period_ms, "ms_per_step_min": -lo_hi[1] / steps, "ms_per_step_max": lo_hi[0] / steps,
+        "steps": steps, "repeats": repeats,
+        "config": decode_config(workload, ctx, world, layers, overlap),
+        "roofline": {"bound": "hbm", "kernel": "paged_decode_tma_kernel (one launch per step: append + decode)",
+                     "achieved": achieved, "peak": hbm, "peak_kind": f"of {kind}", "unit": "GB/s", "frac": achieved / hbm,
+                     "frac_of_nominal_8000": achieved / 8000.0, "traffic": NCU_TRAFFIC_BYTES.get(workload),
+                     "algorithmic_bytes_per_launch": bytes_step,
+                     "kernel_ms": period_ms, "kernel_ms_spread": spread(step_ms, steps),
+                     "kernel_ms_without_launch_overlap": med[1] / steps,
+                     "frac_without_launch_overlap": bytes_step / (med[1] / steps * 1e-3) / 1e9 / hbm,
+                     "decode_only_kernel_ms": med[2] / steps, "append_only_kernel_ms": med[3] / steps,
+                     "two_launch_step_ms": med[4] / steps},
+        "e2e": e2e,
+        "gpu_launches": steps * repeats,
+        "timing": f"CUDA graph of {steps} steps, {repeats} replays, event pair per replay, median (min/max beside it)",
+    }
+    del g_step, g_step_plain, g_decode, g_append, g_two
+    cache.close()
+    return record
+
+
+def measure_prefill(env, args, *, repeats: int) -> dict:
+    """Configuration 3: chunked prefill. 8 sequences, existing context ~ U{0..8192}, a 512-token chunk appended and then
+    attended causally. A step = append of the chunk rows + the tcgen05 chunk kernel; graphs of `layers` steps."""
+    torch, llaisys, rank, local_rank, world, dist = env
     dev = llaisys.DeviceType.NVIDIA
     g = torch.Generator().manual_seed(3 + rank)
     B, chunk, layers = 8, 512, max(2, args.layers)
@@ -268,6 +527,7 @@ def run_prefill_workload(args) -> None:
         seqs.append(s)
     cache.flush()
     stream = torch.cuda.Stream()
+    cs = stream.cuda_stream
     cg = torch.Generator(device="cuda").manual_seed(300 + rank)
     ids = torch.tensor(seqs, dtype=torch.int32, device="cuda")
     lens = torch.tensor(kv_lens, dtype=torch.int32, device="cuda")
@@ -284,7 +544,7 @@ def run_prefill_workload(args) -> None:
     for layer in range(layers):
         k_rows = torch.randn((n_old, NKVH, D), generator=cg, device="cuda").bfloat16()
         v_rows = torch.randn((n_old, NKVH, D), generator=cg, device="cuda").bfloat16()
-        cache.append_dev(layer, k_rows, v_rows, old_seq, old_pos, n_old, stream.cuda_stream)
+        cache.append_dev(layer, k_rows, v_rows, old_seq, old_pos, n_old, cs)
         stream.synchronize()
     q = torch.randn((B * chunk, NH, D), generator=cg, device="cuda").bfloat16()
     k_new = torch.randn((B * chunk, NKVH, D), generator=cg, device="cuda").bfloat16()
@@ -294,11 +554,10 @@ def run_prefill_workload(args) -> None:
     torch.cuda.synchronize()
 
     def do_append(i):
-        cache.append_dev(i % layers, k_new, v_new, new_seq, new_pos, B * chunk, stream.cuda_stream)
+        cache.append_dev(i % layers, k_new, v_new, new_seq, new_pos, B * chunk, cs)
 
     def do_attend(i):
-        cache.prefill_dev(i % layers, out, q, ids, starts, lens, B, B * chunk, chunk, max_kv, NH, scale,
-                          stream.cuda_stream)
+        cache.prefill_dev(i % layers, out, q, ids, starts, lens, B, B * chunk, chunk, max_kv, NH, scale, cs)
 
     def do_step(i):
         do_append(i)
@@ -308,41 +567,29 @@ def run_prefill_workload(args) -> None:
         do_step(i)
     stream.synchronize()
     cache.check()
-    chunk_steps = max(layers, min(args.steps, 40) // layers * layers)
-    reps = max(1, min(args.steps, 400) // chunk_steps)
-    steps = chunk_steps * reps
+    assert cache.last_kernel() == llaisys.Kernel.PREFILL_TC, "the chunk attention did not run on the tcgen05 kernel"
+    steps = layers
 
     def capture(body):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            for i in range(chunk_steps):
+            for i in range(steps):
                 body(i)
         return graph
-
-    def timed(graph):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(stream):
-            graph.replay()
-            e0.record(stream)
-            for _ in range(reps):
-                graph.replay()
-            e1.record(stream)
-        stream.synchronize()
-        return e0.elapsed_time(e1)
 
     g_step, g_att, g_app = capture(do_step), capture(do_attend), capture(do_append)
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    with ClockSampler(local_rank) as clocks:
-        elapsed_ms = timed(g_step)
-    attend_ms, append_ms = timed(g_att) / steps, timed(g_app) / steps
+    step_ms = replay_times(torch, stream, g_step, repeats)
+    attend_ms = replay_times(torch, stream, g_att, repeats)
+    append_ms = replay_times(torch, stream, g_app, repeats)
     cache.check()
 
     # end to end: host index arrays, pinned host q / k / v / out, copies and a synchronise per step
     e2e = None
     if not args.no_e2e:
-        api, cs = llaisys.RuntimeAPI(dev), llaisys.context_stream()
+        api, lib_stream = llaisys.RuntimeAPI(dev), llaisys.context_stream()
         q_h, k_h, v_h = (t.cpu().pin_memory() for t in (q, k_new, v_new))
         out_h = torch.empty_like(q_h).pin_memory()
         q_d, k_d, v_d, out_d = (torch.empty_like(t) for t in (q, k_new, v_new, out))
@@ -351,13 +598,13 @@ def run_prefill_workload(args) -> None:
 
         def step_e2e(i):
             for dst, src in ((q_d, q_h), (k_d, k_h), (v_d, v_h)):
-                api.memcpy_async(dst, src, src.numel() * 2, H2D, cs)
+                api.memcpy_async(dst, src, src.numel() * 2, H2D, lib_stream)
             cache.append(i % layers, k_d, v_d, new_seq_h, new_pos_h)
             cache.prefill(i % layers, out_d, q_d, seqs, [chunk] * B, kv_lens, NH, scale)
-            api.memcpy_async(out_h, out_d, out_h.numel() * 2, D2H, cs)
-            api.stream_synchronize(cs)
+            api.memcpy_async(out_h, out_d, out_h.numel() * 2, D2H, lib_stream)
+            api.stream_synchronize(lib_stream)
 
-        n_e2e = max(10, min(args.steps, 100))
+        n_e2e = 30
         for i in range(2):
             step_e2e(i)
         torch.cuda.synchronize()
@@ -374,35 +621,32 @@ def run_prefill_workload(args) -> None:
                "d2h_bytes_per_step": out_h.numel() * 2, "steps": n_e2e,
                "matches_device_path": bool(torch.equal(out_h.view(torch.int16), out.cpu().view(torch.int16)))}
 
-    stats = torch.tensor([elapsed_ms, attend_ms, append_ms], device="cuda", dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        elapsed_ms, attend_ms, append_ms = (float(x) for x in stats)
-    if rank == 0:
-        hbm_peak, tensor_peak, kind = _peaks()
-        flops = sum(4 * NH * D * (chunk * c + chunk * (chunk + 1) // 2) for c in context)
-        achieved = flops / (attend_ms * 1e-3) / 1e12
-        line = {
-            "metric": "prefill tokens/s (paged KV append of a 512-token chunk + causal chunk attention, one layer)",
-            "value": world * B * chunk * steps / (elapsed_ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": elapsed_ms / steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "config3", "batch_per_gpu": B, "context": context, "chunk": chunk,
-                       "heads": "12q/2kv", "head_dim": D, "page_size": PAGE, "pool_pages": POOL_PAGES,
-                       "parallelism": f"sequences sharded over {world} GPU(s), no collective",
-                       "l2": f"layer pool rotates over {layers} x {cache.layer_bytes() >> 20} MiB between steps"},
-            "roofline": {"bound": "tensor", "kernel": "paged_prefill_tc_kernel", "achieved": achieved,
-                         "peak": tensor_peak, "peak_kind": f"sustained bf16, of {kind}", "unit": "TFLOP/s",
-                         "frac": achieved / tensor_peak, "frac_of_nominal_2250": achieved / 2250.0, "traffic": None,
-                         "algorithmic_flops_per_launch": flops, "kernel_ms_mean": attend_ms,
-                         "append_kernel_ms_mean": append_ms},
-            "e2e": e2e, "gpu_launches": 2 * steps, "timing": f"CUDA graphs of {chunk_steps} steps x {reps} replays",
-            "clocks": clocks.summary(),
-        }
-        print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    med = reduce_max(torch, dist, [statistics.median(x) for x in (step_ms, attend_ms, append_ms)])
+    _, burst, sustained, kind = _peaks()
+    flops = sum(4 * NH * D * (chunk * c + chunk * (chunk + 1) // 2) for c in context)
+    kernel_ms = med[1] / steps
+    achieved = flops / (kernel_ms * 1e-3) / 1e12
+    record = {
+        "workload": "config3",
+        "metric": "prefill tokens/s (paged KV append of a 512-token chunk + causal chunk attention, one layer)",
+        "value": world * B * chunk * steps / (med[0] * 1e-3), "unit": "tokens/s", "ms_per_step": med[0] / steps,
+        "steps": steps, "repeats": repeats,
+        "config": {"workload": "config3", "batch_per_gpu": B, "context": context, "chunk": chunk,
+                   "heads": "12q/2kv", "head_dim": D, "page_size": PAGE, "pool_pages": POOL_PAGES,
+                   "parallelism": f"sequences sharded over {world} GPU(s), no collective",
+                   "l2": f"layer pool rotates over {layers} x {cache.layer_bytes() >> 20} MiB between steps"},
+        "roofline": {"bound": "tensor", "kernel": "paged_prefill_tc_kernel", "achieved": achieved,
+                     "peak": burst, "peak_kind": f"burst bf16 (a kernel timed alone), of {kind}", "unit": "TFLOP/s",
+                     "frac": achieved / burst, "frac_of_sustained": achieved / sustained, "peak_sustained": sustained,
+                     "frac_of_nominal_2250": achieved / 2250.0, "traffic": None,
+                     "algorithmic_flops_per_launch": flops, "kernel_ms": kernel_ms,
+                     "kernel_ms_spread": spread(attend_ms, steps), "append_kernel_ms": med[2] / steps},
+        "e2e": e2e, "gpu_launches": 2 * steps * repeats,
+        "timing": f"CUDA graphs of {steps} steps, {repeats} replays, event pair per replay, median",
+    }
+    del g_step, g_att, g_app
+    cache.close()
+    return record
 
 
 QWEN2_1P5B = dict(hidden_size=1536, num_hidden_layers=28, num_attention_heads=12, num_key_value_heads=2, head_dim=128,
@@ -539,7 +783,7 @@ def run_model_workload(args) -> None:
             dist.all_reduce(rate, op=dist.ReduceOp.MIN)
             e2e["value"] = float(rate)
     if rank == 0:
-        hbm_peak, _, kind = _peaks()
+        hbm_peak, _, _, kind = _peaks()
         kv_bytes = cfg["num_hidden_layers"] * B * ctx_mid * (2 * (NKVH // world if tp else NKVH) * D * 2)
         achieved = (weight_bytes + kv_bytes) / (step_ms * 1e-3) / 1e9
         # per layer: 2 norms, bias+rope+append, decode attention, activation; per step: embedding, norm, argmax, 2 x advance
@@ -644,7 +888,7 @@ def run_copy_workload(args) -> None:
     gather_ms = e0.elapsed_time(e1) / reps
     cache.check()
     if rank == 0:
-        hbm_peak, _, kind = _peaks()
+        hbm_peak, _, _, kind = _peaks()
         row_kv = 2 * NKVH * D * 2
         append_bytes = rows * (2 * row_kv + 8)
         fused_bytes = rows * ((NH + 2 * NKVH) * D * 2 + NH * D * 2 + row_kv + 8)
@@ -675,16 +919,16 @@ def run_copy_workload(args) -> None:
         dist.destroy_process_group()
 
 
-def run_longctx_workload(args) -> None:
-    """--workload config5: ONE 131072-token sequence, 28 layers, KV range split across the N GPUs (strong scaling).
+def measure_kv_split(env, args, *, steps: int, one_gpu_reference: bool) -> dict:
+    """Configuration 5: ONE 131072-token sequence, 28 layers, KV range split across the N GPUs (strong scaling).
 
     Each rank holds its page-aligned slice of every layer (28 per-layer "sequences" in one pool). A step is one decode
-    token's attention through all 28 layers in batched mode -- the synthetic workload supplies every layer's query up
-    front, so it is one partial-decode launch over 28 sequences, ONE all-gather of the (o, m, l) partials (174 720 B per
-    rank) and one log-sum-exp merge. The per-layer mode (28 dependent launch + all-gather + merge rounds, what a real
-    model needs) is timed too and reported under "per_layer".
-    """
-    torch, llaisys, rank, local_rank, world, dist = _init_device()
+    token's attention through all 28 layers. Batched mode: the synthetic workload supplies every layer's query up front,
+    so it is one partial-decode launch over 28 sequences whose rows the kernel itself stores into every rank's exchange
+    slots, and one merge. Per-layer mode: 28 dependent rounds of the same two launches (what a real model needs). Both
+    are replayed as CUDA graphs; the NCCL path (partial decode, all_gather_into_tensor, merge, host-driven) is timed
+    beside them and must give the same bits. Layer 0 is also checked against the float64 oracle on the full sequence."""
+    torch, llaisys, rank, local_rank, world, dist = env
     from llaisys_b200 import sharding
 
     dev = llaisys.DeviceType.NVIDIA
@@ -704,19 +948,22 @@ def run_longctx_workload(args) -> None:
     cache.flush()
     cs = llaisys.context_stream()
     ext = torch.cuda.ExternalStream(cs)
+    api = llaisys.RuntimeAPI(dev)
     cg = torch.Generator(device="cuda").manual_seed(500 + rank)
     pos = torch.arange(local, dtype=torch.int32, device="cuda")
-    for s in seqs:  # N(0,1) K/V rows of this rank's slice of each layer
+    k0 = v0 = None
+    for i, s in enumerate(seqs):  # N(0,1) K/V rows of this rank's slice of each layer
         k_rows = torch.randn((local, NKVH, D), generator=cg, device="cuda").bfloat16()
         v_rows = torch.randn((local, NKVH, D), generator=cg, device="cuda").bfloat16()
         torch.cuda.synchronize()
         cache.append_dev(0, k_rows, v_rows, torch.full((local,), s, dtype=torch.int32, device="cuda"), pos, local, cs)
-        llaisys.RuntimeAPI(dev).stream_synchronize(cs)
+        api.stream_synchronize(cs)
+        if i == 0:
+            k0, v0 = k_rows, v_rows  # layer 0's slice, for the oracle check
     qg = torch.Generator(device="cuda").manual_seed(999)  # the same queries on every rank
     q = torch.randn((n_layers, NH, D), generator=qg, device="cuda").bfloat16()
     out = torch.empty_like(q)
     part = torch.empty((n_layers, NH, D + 2), dtype=torch.float32, device="cuda")
-    gathered = torch.empty((world * n_layers, NH, D + 2), dtype=torch.float32, device="cuda")
     lens = [local] * n_layers
     scale = 1.0 / D ** 0.5
     torch.cuda.synchronize()
@@ -724,14 +971,14 @@ def run_longctx_workload(args) -> None:
     def merge(parts, n_parts, rows, dst):
         llaisys.lse_merge(dst, parts, n_parts, rows, D, dtype=llaisys.DataType.BF16, device=dev, device_id=local_rank)
 
-    def step_batched():
+    def nccl_batched():
         if world > 1:
             sharding.split_decode(cache, 0, out, q, seqs, lens, NH, scale)
         else:
             cache.decode_partial(0, part, q, seqs, lens, NH, scale)
             merge(part, 1, n_layers * NH, out)
 
-    def step_per_layer():
+    def nccl_per_layer():
         for layer in range(n_layers):
             if world > 1:
                 sharding.split_decode(cache, 0, out[layer:layer + 1], q[layer:layer + 1], seqs[layer:layer + 1], [local],
@@ -746,112 +993,201 @@ def run_longctx_workload(args) -> None:
     def only_decode_one_layer():
         cache.decode_partial(0, part[:1], q[:1], seqs[:1], [local], NH, scale)
 
-    # ---- the same step through peer memory: partial decode, NVLink stores into every rank's slots, flags, merge --
-    # (no collective library, no host work between the kernels: captured once, replayed)
-    peer = None
-    if world > 1:
-        peer = sharding.PeerExchange(n_layers * NH, D, device_id=local_rank)
-        seq_dev = torch.tensor(seqs, dtype=torch.int32, device="cuda")
-        len_dev = torch.full((n_layers,), local, dtype=torch.int32, device="cuda")
-        out_p = torch.empty_like(q)
+    # ---- the same step through peer memory: no collective library, no host work between the kernels ----------------
+    peer = sharding.PeerExchange(n_layers * NH, D, device_id=local_rank)
+    seq_dev = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    len_dev = torch.full((n_layers,), local, dtype=torch.int32, device="cuda")
+    out_p = torch.empty_like(q)
 
-        def peer_batched():
-            peer.split_decode(cache, 0, out_p, q, seq_dev, len_dev, n_layers, local, NH, scale, cs)
+    def peer_batched():
+        peer.split_decode(cache, 0, out_p, q, seq_dev, len_dev, n_layers, local, NH, scale, cs)
 
-        def peer_per_layer():
-            for layer in range(n_layers):
-                peer.split_decode(cache, 0, out_p[layer:layer + 1], q[layer:layer + 1], seq_dev[layer:layer + 1],
-                                  len_dev[layer:layer + 1], 1, local, NH, scale, cs)
+    def peer_per_layer():
+        for layer in range(n_layers):
+            peer.split_decode(cache, 0, out_p[layer:layer + 1], q[layer:layer + 1], seq_dev[layer:layer + 1],
+                              len_dev[layer:layer + 1], 1, local, NH, scale, cs)
 
-        def graphed(body):
-            body()  # eager once: sizes scratch before the capture
-            peer.check(cs)
+    def sync_all():
+        if dist is not None:
             dist.barrier()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=ext):
-                body()
+        torch.cuda.synchronize()
 
-            def replay():
-                with torch.cuda.stream(ext):
-                    graph.replay()
-            return replay
+    def graphed(body):
+        body()  # eager once
+        peer.check(cs)
+        sync_all()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=ext):
+            body()
+
+        def replay():
+            with torch.cuda.stream(ext):
+                graph.replay()
+        return replay
 
     def timed(body, n):
+        """-> milliseconds per call, one event pair per call (median taken by the caller)."""
         for _ in range(3):
             body()
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(ext)
-        for _ in range(n):
+        sync_all()
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        events[0].record(ext)
+        for i in range(n):
             body()
-        e1.record(ext)
+            events[i + 1].record(ext)
         torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
-        return e0.elapsed_time(e1) / n
+        sync_all()
+        return [events[i].elapsed_time(events[i + 1]) for i in range(n)]
 
-    steps = max(10, min(args.steps, 200))
-    with ClockSampler(local_rank) as clocks:
-        batched_ms = timed(step_batched, steps)
-    per_layer_ms = timed(step_per_layer, max(5, steps // 10))
-    decode_ms = timed(only_decode, steps)
-    decode_layer_ms = timed(only_decode_one_layer, steps)
+    n_rep = max(MIN_REPEATS, min(steps, 200))
+    nccl_ms = timed(nccl_batched, n_rep)
+    nccl_layer_ms = timed(nccl_per_layer, max(10, n_rep // 5))
+    decode_ms = timed(only_decode, n_rep)
+    decode_layer_ms = timed(only_decode_one_layer, n_rep)
     cache.check()
-    peer_ms = peer_layer_ms = float("nan")
-    peer_same = None
-    if peer is not None:
-        step_batched()
-        torch.cuda.synchronize()
-        expect = out.clone()
-        peer_ms = timed(graphed(peer_batched), steps)
-        peer.check(cs)
-        peer_same = bool(torch.equal(out_p.view(torch.int16), expect.view(torch.int16)))  # same partials, same merge order
-        peer_layer_ms = timed(graphed(peer_per_layer), max(5, steps // 10))
-        peer.check(cs)
-    stats = torch.tensor([batched_ms, per_layer_ms, decode_ms, peer_ms, peer_layer_ms], device="cuda", dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        batched_ms, per_layer_ms, decode_ms, peer_ms, peer_layer_ms = (float(x) for x in stats)
-    nccl_ms, nccl_layer_ms = batched_ms, per_layer_ms
-    if peer is not None:  # the headline is the peer-memory path; the NCCL path is reported beside it
-        batched_ms, per_layer_ms = peer_ms, peer_layer_ms
+    nccl_batched()
+    torch.cuda.synchronize()
+    expect = out.clone()
+    peer_ms = timed(graphed(peer_batched), n_rep)
+    peer.check(cs)
+    assert cache.last_kernel() == llaisys.Kernel.DECODE_TMA, "the partial decode did not run on the TMA decode kernel"
+    peer_same = bool(torch.equal(out_p.view(torch.int16), expect.view(torch.int16)))  # same partials, same merge order
+    peer_layer_ms = timed(graphed(peer_per_layer), max(10, n_rep // 5))
+    peer.check(cs)
+    peer_layer_same = bool(torch.equal(out_p.view(torch.int16), expect.view(torch.int16)))
+
+    # ---- layer 0 against the float64 oracle on the FULL sequence (rank 0 collects the slices) -----------------------
+    if world > 1:
+        k_all = torch.empty((world * local, NKVH, D), dtype=torch.bfloat16, device="cuda")
+        v_all = torch.empty_like(k_all)
+        dist.all_gather_into_tensor(k_all, k0)
+        dist.all_gather_into_tensor(v_all, v0)
+    else:
+        k_all, v_all = k0, v0
+    max_abs = None
     if rank == 0:
-        hbm_peak, _, kind = _peaks()
-        bytes_per_launch = n_layers * local * (2 * NKVH * D * 2) + 2 * n_layers * NH * D * 2 + 4 * n_layers * pages_per
-        achieved = bytes_per_launch / (decode_ms * 1e-3) / 1e9
-        line = {
-            "metric": "decode tokens/s (one 131072-token sequence, attention of 28 layers, KV range split across GPUs)",
-            "value": 1e3 / batched_ms, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": 3,
-            "ms_per_step": batched_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "config5", "context": total_tokens, "layers": n_layers, "tokens_per_gpu": local,
-                       "heads": "12q/2kv", "head_dim": D, "page_size": PAGE,
-                       "mode": ("batched: one partial-decode launch, partials stored into every rank's exchange slots over "
-                                "NVLink (peer memory), flags, one merge; replayed as a CUDA graph") if peer is not None
-                       else "batched: one launch, one merge",
-                       "parallelism": f"KV range split over {world} GPU(s), (o, m, l) partials exchanged through peer memory",
-                       "l2": f"{bytes_per_launch >> 20} MiB of K/V per GPU per step, larger than L2" if bytes_per_launch > 2e8
-                       else f"{bytes_per_launch >> 20} MiB of K/V per GPU per step (fits L2 at this GPU count)"},
-            "roofline": {"bound": "hbm", "kernel": "paged_decode_tma_kernel", "achieved": achieved, "peak": hbm_peak,
-                         "peak_kind": f"of {kind}", "unit": "GB/s", "frac": achieved / hbm_peak,
-                         "frac_of_nominal_8000": achieved / 8000.0, "traffic": None,
-                         "algorithmic_bytes_per_launch": bytes_per_launch, "kernel_ms_mean": decode_ms},
-            "per_layer": {"ms_per_step": per_layer_ms, "value": 1e3 / per_layer_ms,
-                          "note": "28 dependent rounds of partial decode + exchange + merge",
-                          "decode_kernel_ms_one_layer_host_driven": decode_layer_ms},
-            "nccl_all_gather": None if peer is None else {
-                "ms_per_step": nccl_ms, "per_layer_ms_per_step": nccl_layer_ms, "peer_path_matches": peer_same,
-                "note": "the same step with torch.distributed all_gather_into_tensor (NCCL) between the library calls, "
-                        "driven from the host"},
-            "e2e": None, "gpu_launches": (5 if peer is not None else 2) * steps,
-            "timing": "CUDA events on the library stream, max over ranks",
-            "clocks": clocks.summary(),
-        }
+        from oracle import attention
+
+        f64 = attention.decode_attention_f64_chunked(q[:1].cpu(), k_all.cpu(), v_all.cpu(), scale)
+        max_abs = float((out_p[:1].cpu().double() - f64).abs().max())
+    del k_all, v_all, k0, v0
+
+    # ---- the whole sequence on ONE GPU, for the speed-up (rank 0 alone; the others wait) -----------------------------
+    one_gpu_ms = None
+    if one_gpu_reference and world > 1:
+        if rank == 0:
+            full_pages = total_tokens // PAGE
+            big = llaisys.PagedKVCache(n_layers * full_pages, NKVH, D, nlayer=1, dtype=llaisys.DataType.BF16, device=dev,
+                                       device_id=local_rank, max_seqs=n_layers, max_pages_per_seq=full_pages)
+            bperm = torch.randperm(n_layers * full_pages, generator=g).tolist()
+            bseqs = []
+            for layer in range(n_layers):
+                s = big.add_seq()
+                big.assign_pages(s, bperm[layer * full_pages:(layer + 1) * full_pages])
+                bseqs.append(s)
+            big.flush()
+            bpos = torch.arange(total_tokens, dtype=torch.int32, device="cuda")
+            for s in bseqs:
+                k_rows = torch.randn((total_tokens, NKVH, D), generator=cg, device="cuda").bfloat16()
+                v_rows = torch.randn((total_tokens, NKVH, D), generator=cg, device="cuda").bfloat16()
+                torch.cuda.synchronize()
+                big.append_dev(0, k_rows, v_rows, torch.full((total_tokens,), s, dtype=torch.int32, device="cuda"), bpos,
+                               total_tokens, cs)
+                api.stream_synchronize(cs)
+                del k_rows, v_rows
+            blens = [total_tokens] * n_layers
+
+            def one_gpu():
+                big.decode(0, out, q, bseqs, blens, NH, scale)
+
+            for _ in range(3):
+                one_gpu()
+            torch.cuda.synchronize()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(n_rep + 1)]
+            ev[0].record(ext)
+            for i in range(n_rep):
+                one_gpu()
+                ev[i + 1].record(ext)
+            torch.cuda.synchronize()
+            one_gpu_ms = statistics.median(ev[i].elapsed_time(ev[i + 1]) for i in range(n_rep))
+            big.close()
+        sync_all()
+
+    med = reduce_max(torch, dist, [statistics.median(x) for x in
+                                   (peer_ms, peer_layer_ms, nccl_ms, nccl_layer_ms, decode_ms, decode_layer_ms)])
+    hbm, _, _, kind = _peaks()
+    bytes_per_launch = n_layers * local * (2 * NKVH * D * 2) + 2 * n_layers * NH * D * 2 + 4 * n_layers * pages_per
+    achieved = bytes_per_launch / (med[4] * 1e-3) / 1e9
+    record = {
+        "workload": "config5",
+        "metric": "decode tokens/s (one 131072-token sequence, attention of 28 layers, KV range split across GPUs)",
+        "value": 1e3 / med[0], "unit": "tokens/s", "n_gpus": world,
+        "ms_per_step": med[0], "ms_per_step_spread": spread(peer_ms),
+        "per_layer_ms": med[1], "per_layer_round_ms": med[1] / n_layers,
+        "nccl_ms": med[2], "nccl_per_layer_ms": med[3],
+        "speedup_vs_1gpu": (one_gpu_ms / med[0]) if one_gpu_ms else None, "one_gpu_ms": one_gpu_ms,
+        "max_abs_vs_oracle": max_abs,
+        "peer_path_matches_nccl_path": peer_same and peer_layer_same,
+        "decode_kernel_ms": med[4], "decode_kernel_ms_one_layer_host_driven": med[5],
+        "config": {"workload": "config5", "context": total_tokens, "layers": n_layers, "tokens_per_gpu": local,
+                   "heads": "12q/2kv", "head_dim": D, "page_size": PAGE,
+                   "mode": "batched: one partial-decode launch that stores its rows into every rank's exchange slots over "
+                           "NVLink (peer memory) and stamps the flags, one merge; per-layer: 28 dependent rounds of the "
+                           "same two launches; both replayed as CUDA graphs",
+                   "parallelism": f"KV range split over {world} GPU(s), (o, m, l) partials exchanged through peer memory",
+                   "l2": f"{bytes_per_launch >> 20} MiB of K/V per GPU per step" +
+                         (", larger than L2" if bytes_per_launch > 2e8 else " (fits L2 at this GPU count)")},
+        "roofline": {"bound": "hbm", "kernel": "paged_decode_tma_kernel", "achieved": achieved, "peak": hbm,
+                     "peak_kind": f"of {kind}", "unit": "GB/s", "frac": achieved / hbm,
+                     "frac_of_nominal_8000": achieved / 8000.0, "traffic": None,
+                     "algorithmic_bytes_per_launch": bytes_per_launch, "kernel_ms": med[4]},
+        "oracle": "layer 0 of the batched peer-memory step against the float64 statement of the reference's attention over "
+                  "all 131072 tokens (max-abs; one bf16 ulp of the output is 8e-3)",
+        "timing": f"CUDA events on the library stream, one pair per step, median of {n_rep}, max over ranks",
+        "gpu_launches": 2 * n_rep,
+    }
+    peer.close()
+    cache.close()
+    return record
+
+
+def run_longctx_workload(args) -> None:
+    """--workload config5 as its own line."""
+    env = _init_device()
+    torch, llaisys, rank, local_rank, world, dist = env
+    with ClockSampler(local_rank) as clocks:
+        rec = measure_kv_split(env, args, steps=args.steps, one_gpu_reference=False)
+    if rank == 0:
+        line = {"metric": rec["metric"], "value": rec["value"], "unit": "tokens/s", "n_gpus": world, "steps": rec["ms_per_step_spread"]["n"],
+                "warmup": 3, "ms_per_step": rec["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": rec["config"],
+                "roofline": rec["roofline"],
+                "per_layer": {"ms_per_step": rec["per_layer_ms"], "ms_per_round": rec["per_layer_round_ms"],
+                              "note": "28 dependent rounds of partial decode (+ exchange in the kernel) + merge",
+                              "decode_kernel_ms_one_layer_host_driven": rec["decode_kernel_ms_one_layer_host_driven"]},
+                "nccl_all_gather": {"ms_per_step": rec["nccl_ms"], "per_layer_ms_per_step": rec["nccl_per_layer_ms"],
+                                    "peer_path_matches": rec["peer_path_matches_nccl_path"]},
+                "max_abs_vs_oracle": rec["max_abs_vs_oracle"], "e2e": None, "gpu_launches": rec["gpu_launches"],
+                "timing": rec["timing"], "clocks": clocks.summary()}
         print(json.dumps(line), flush=True)
-    if peer is not None:
-        peer.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_prefill_workload(args) -> None:
+    """--workload config3 as its own line."""
+    env = _init_device()
+    torch, llaisys, rank, local_rank, world, dist = env
+    with ClockSampler(local_rank) as clocks:
+        rec = measure_prefill(env, args, repeats=max(MIN_REPEATS, min(args.steps, 200)))
+    if rank == 0:
+        line = {"metric": rec["metric"], "value": rec["value"], "unit": "tokens/s", "n_gpus": world, "steps": rec["steps"],
+                "repeats": rec["repeats"], "warmup": max(3, args.warmup), "ms_per_step": rec["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": rec["config"], "roofline": rec["roofline"], "e2e": rec["e2e"], "gpu_launches": rec["gpu_launches"],
+                "timing": rec["timing"], "clocks": clocks.summary()}
+        print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -860,14 +1196,17 @@ def run_longctx_workload(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=100, help="steps per timed graph replay (the graph is replayed >= 30 times)")
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="north_star", choices=["north_star", "config2", "config3", "config4", "config5", "copy"])
     ap.add_argument("--layers", type=int, default=4, help="pools to rotate over between steps (L2 flush)")
+    ap.add_argument("--repeats", type=int, default=100, help="replays of the timed graph (at least 30)")
     ap.add_argument("--tp", action="store_true", help="config4 on several GPUs: tensor parallelism instead of sequence sharding")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-API leg (profiling runs)")
+    ap.add_argument("--no-sub-records", action="store_true",
+                    help="north_star only: skip the config2 / config3 (N = 1) and kv_split (N > 1) sub-records")
     ap.add_argument("--no-overlap", action="store_true",
                     help="launch kernels without programmatic stream serialisation (on by default for decode workloads)")
     args = ap.parse_args()
@@ -884,224 +1223,53 @@ def main() -> None:
         run_longctx_workload(args)
         return
     if args.workload == "config4":
+        if args.steps == 100:
+            args.steps = 2000  # run_model_workload's marker for "the configuration's own 256 steps"
         run_model_workload(args)
         return
     if args.workload == "copy":
         run_copy_workload(args)
         return
 
-    import torch
-
-    import llaisys_b200 as llaisys
-
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU stand-in")
-    torch.cuda.set_device(local_rank)
-    dev = llaisys.DeviceType.NVIDIA
-    llaisys.set_context_runtime(dev, local_rank)
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-
-    # ---- build the workload on this rank's GPU -----------------------------------------------------------
-    ctx = workload_lengths(args.workload, seed=2 + rank)
-    B, layers = len(ctx), args.layers
-    max_pages = max(-(-c // PAGE) for c in ctx)
-    cache = llaisys.PagedKVCache(POOL_PAGES, NKVH, D, nlayer=layers, dtype=llaisys.DataType.BF16, device=dev,
-                                 device_id=local_rank, max_seqs=B, max_pages_per_seq=max_pages)
-    g = torch.Generator().manual_seed(100 + rank)
-    perm = torch.randperm(POOL_PAGES, generator=g).tolist()
-    seqs, at = [], 0
-    for c in ctx:
-        s = cache.add_seq()
-        n = -(-c // PAGE)
-        cache.assign_pages(s, perm[at:at + n])
-        at += n
-        seqs.append(s)
-    cache.flush()
-    cache.set_launch_overlap(not args.no_overlap)
-    stream = torch.cuda.Stream()
-    cg = torch.Generator(device="cuda").manual_seed(200 + rank)
-    seq_ids_dev = torch.tensor(seqs, dtype=torch.int32, device="cuda")
-    kv_lens_dev = torch.tensor(ctx, dtype=torch.int32, device="cuda")
-    last_pos_dev = kv_lens_dev - 1
-    torch.cuda.synchronize()
-    with torch.cuda.stream(stream):
-        # fill every layer's pages: all rows but the last of each sequence (the timed step appends the last)
-        row_seq = torch.repeat_interleave(seq_ids_dev, (kv_lens_dev - 1).long())
-        starts = torch.cumsum(kv_lens_dev - 1, 0) - (kv_lens_dev - 1)
-        row_pos = (torch.arange(row_seq.numel(), device="cuda", dtype=torch.int32)
-                   - torch.repeat_interleave(starts, (kv_lens_dev - 1).long()).int())
-        n_rows = row_seq.numel()
-        for layer in range(layers):
-            k_rows = torch.randn((n_rows, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
-            v_rows = torch.randn((n_rows, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
-            cache.append_dev(layer, k_rows, v_rows, row_seq, row_pos, n_rows, stream.cuda_stream)
-            stream.synchronize()
-            del k_rows, v_rows
-        q = torch.randn((B, NH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
-        k_new = torch.randn((B, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
-        v_new = torch.randn((B, NKVH, D), generator=cg, device="cuda", dtype=torch.float32).bfloat16()
-        out = torch.empty_like(q)
-    stream.synchronize()
-    cache.check()
-    scale = 1.0 / D ** 0.5
-    max_kv = max(ctx)
-
-    def step_device(i: int, ev=None):
-        layer = i % layers
-        if ev is not None:
-            ev[0].record(stream)
-        cache.append_dev(layer, k_new, v_new, seq_ids_dev, last_pos_dev, B, stream.cuda_stream)
-        if ev is not None:
-            ev[1].record(stream)
-        cache.decode_dev(layer, out, q, seq_ids_dev, kv_lens_dev, B, max_kv, NH, scale, stream.cuda_stream)
-        if ev is not None:
-            ev[2].record(stream)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-timed region ----------------------------------------------------------------------------------
-    # A step takes tens of microseconds, less than the host needs to queue it through Python, so the timed loops
-    # are CUDA graphs: `chunk` consecutive steps (layers rotating) captured once, replayed back to back. The
-    # whole-step graph gives `value`; graphs holding only the decode launches / only the append launches of the
-    # same steps give each kernel's mean duration (events bracket the replays on the launch stream).
-    for i in range(args.warmup):
-        step_device(i)
-    stream.synchronize()
-    chunk = max(layers, min(args.steps, 100) // layers * layers)
-    reps = max(1, args.steps // chunk)
-    steps = chunk * reps
-
-    def capture(body):
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            for i in range(chunk):
-                body(i)
-        return graph
-
-    def only_decode(i):
-        cache.decode_dev(i % layers, out, q, seq_ids_dev, kv_lens_dev, B, max_kv, NH, scale, stream.cuda_stream)
-
-    def only_append(i):
-        cache.append_dev(i % layers, k_new, v_new, seq_ids_dev, last_pos_dev, B, stream.cuda_stream)
-
-    g_step, g_decode, g_append = capture(step_device), capture(only_decode), capture(only_append)
-
-    def timed(graph, n_reps):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(stream):
-            graph.replay()  # untimed: first replay uploads the graph
-            e0.record(stream)
-            for _ in range(n_reps):
-                graph.replay()
-            e1.record(stream)
-        stream.synchronize()
-        return e0.elapsed_time(e1)
-
-    barrier()
-    with ClockSampler(local_rank) as clocks:
-        elapsed_ms = timed(g_step, reps)
-        barrier()
-    decode_ms = timed(g_decode, reps) / steps
-    append_ms = timed(g_append, reps) / steps
-    decode_ms_median = decode_ms
-    cache.check()
-    args.steps = steps
-
-    # ---- end to end through the host-array API, host buffers, copies inside the timed region ---------------------
-    q_h, k_h, v_h = (t.cpu().pin_memory() for t in (q, k_new, v_new))
-    out_h = torch.empty_like(q_h).pin_memory()
-    seqs_np, ctx_np = np.asarray(seqs, dtype=np.int32), np.asarray(ctx, dtype=np.int32)
-
-    def step_e2e(i: int):
-        # the library's host-buffer step: pinned q / new K,V rows in, both kernels, attention output back, one
-        # synchronise -- one call per decode step, as a serving loop without device-resident activations makes it
-        cache.decode_step_host(i % layers, out_h, q_h, k_h, v_h, seqs_np, ctx_np, NH, scale)
-
-    e2e_steps, e2e_s, same = 0, float("nan"), None
-    if not args.no_e2e:
-        e2e_steps = max(10, min(args.steps, 1000))
-        for i in range(3):
-            step_e2e(i)
-        barrier()
-        t0 = time.perf_counter()
-        for i in range(e2e_steps):
-            step_e2e(i)
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-        cache.check()
-        # both legs on the same layer must give the same bits
-        step_e2e(0)
-        step_device(0)
-        stream.synchronize()
-        same = torch.equal(out_h.view(torch.int16), out.cpu().view(torch.int16))
-
-    # ---- reduce over ranks ------------------------------------------------------------------------------
-    stats = torch.tensor([elapsed_ms, e2e_s, decode_ms, append_ms, float(sum(ctx))], device="cuda",
-                         dtype=torch.float64)
-    if world > 1:
-        mx = stats.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stats.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        elapsed_ms, e2e_s, decode_ms, append_ms = (float(x) for x in mx[:4])
-    total_tokens = B * world
-
-    if rank == 0:
-        peaks_file = ROOT / "MEASURED_PEAKS.json"
-        if peaks_file.exists():
-            peak, peak_kind = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
+    env = _init_device()
+    torch, llaisys, rank, local_rank, world, dist = env
+    steps = max(args.layers, min(args.steps, 400) // args.layers * args.layers)  # whole rotations of the layer pools
+    repeats = max(MIN_REPEATS, args.repeats)
+    clocks = ClockSampler(local_rank)
+    rec = measure_decode(env, args.workload, args, steps=steps, repeats=repeats, with_e2e=not args.no_e2e, sampler=clocks)
+    subs = {}
+    if args.workload == "north_star" and not args.no_sub_records:
+        if world == 1:
+            sub_args = argparse.Namespace(**vars(args))
+            c2 = measure_decode(env, "config2", sub_args, steps=steps, repeats=repeats, with_e2e=False)
+            subs["config2"] = {k: c2[k] for k in ("value", "unit", "ms_per_step", "ms_per_step_min", "ms_per_step_max", "steps",
+                                                  "repeats", "config", "roofline", "timing")}
+            c3 = measure_prefill(env, sub_args, repeats=repeats)
+            subs["config3"] = {k: c3[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "repeats", "config",
+                                                  "roofline", "timing")}
         else:
-            peak, peak_kind = 6650.0, "fallback"
-        bytes_per_launch = algorithmic_bytes(ctx)
-        achieved = bytes_per_launch / (decode_ms * 1e-3) / 1e9
+            kv = measure_kv_split(env, args, steps=repeats, one_gpu_reference=True)
+            subs["kv_split"] = {k: kv[k] for k in ("metric", "value", "unit", "n_gpus", "ms_per_step", "ms_per_step_spread",
+                                                   "per_layer_ms", "per_layer_round_ms", "speedup_vs_1gpu", "one_gpu_ms",
+                                                   "max_abs_vs_oracle", "nccl_ms", "nccl_per_layer_ms",
+                                                   "peer_path_matches_nccl_path", "decode_kernel_ms", "config", "oracle",
+                                                   "timing")}
+    if rank == 0:
         line = {
-            "metric": METRIC,
-            "value": total_tokens * args.steps / (elapsed_ms * 1e-3),
-            "unit": "tokens/s",
-            "n_gpus": world,
-            "steps": args.steps,
-            "warmup": args.warmup,
-            "ms_per_step": elapsed_ms / args.steps,
-            "higher_is_better": True,
-            "scaling": "weak",
-            "vs_baseline": None,
-            "dtype": "bf16",
-            "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": B, "context": f"{min(ctx)}..{max(ctx)}",
-                       "heads": "12q/2kv", "head_dim": D, "page_size": PAGE, "pool_pages": POOL_PAGES,
-                       "parallelism": f"sequences sharded over {world} GPU(s), no collective",
-                       "l2": f"inputs larger than L2: layer pool rotates over {layers} x "
-                             f"{cache.layer_bytes() >> 20} MiB between steps",
-                       "launch": "plain" if args.no_overlap else "programmatic dependent launch: a kernel's set-up and "
-                                 "first K/V copies overlap the previous kernel's tail"},
-            "roofline": {"bound": "hbm", "kernel": "paged_decode_tma_kernel", "achieved": achieved, "peak": peak,
-                         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                         "frac_of_nominal_8000": achieved / 8000.0, "traffic": NCU_TRAFFIC_BYTES[args.workload],
-                         "algorithmic_bytes_per_launch": bytes_per_launch, "kernel_ms_mean": decode_ms,
-                         "append_kernel_ms_mean": append_ms},
-            "e2e": None if args.no_e2e else {
-                "value": total_tokens * e2e_steps / e2e_s, "unit": "tokens/s",
-                "h2d_bytes_per_step": (q_h.numel() + k_h.numel() + v_h.numel()) * 2 + 3 * B * 4,  # + three index arrays
-                "d2h_bytes_per_step": out_h.numel() * 2, "steps": e2e_steps, "matches_device_path": same,
-                "what": "PagedKVCache.decode_step_host(): pinned host q / K,V rows in, attention out, one synchronise"},
-            "gpu_launches": 2 * args.steps, "timing": f"CUDA graphs of {chunk} steps x {reps} replays",
-            "clocks": clocks.summary(),
+            "metric": METRIC, "value": rec["value"], "unit": "tokens/s", "n_gpus": world, "steps": steps, "repeats": repeats,
+            "warmup": max(3, args.warmup), "ms_per_step": rec["ms_per_step"], "ms_per_step_min": rec["ms_per_step_min"],
+            "ms_per_step_max": rec["ms_per_step_max"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": rec["config"], "roofline": rec["roofline"], "e2e": rec["e2e"],
+            "gpu_launches": rec["gpu_launches"], "timing": rec["timing"], "clocks": clocks.summary(),
         }
+        line.update(subs)
         if world == 1 and not args.no_cpu_baseline:
+            ctx = workload_lengths(args.workload, seed=2)
             rate, dt, desc, threads = reference_cpu_rate(ctx, seed=2, min_seconds=10.0, max_seqs=4)
-            line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                    "sample": desc}
+            line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": desc,
+                                    "cpp_backend": cpp_backend_cpu_rate(ctx, seed=2, min_seconds=5.0, max_seqs=4)}
         print(json.dumps(line), flush=True)
-    if world > 1:
+    if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
 

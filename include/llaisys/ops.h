@@ -24,6 +24,11 @@ LLAISYS_EXTERN_C LLAISYS_API void llaisysLinear(llaisysTensor_t out, llaisysTens
 /* New (no counterpart in the reference): out += in . weight^T, the sum rounded once -- the residual add of a decoder
  * block folded into its projection. Same shape rules and error behaviour as llaisysLinear. */
 LLAISYS_EXTERN_C LLAISYS_API void llaisysLinearAccumulate(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight);
+/* New: which kernel serves decode-sized projections (at most 128 rows of 16-bit activations) on NVIDIA, process-wide.
+ * 0 (default) = the hand-written tcgen05 weight-streaming kernel where it measured faster than cuBLAS (at most 16 rows
+ * with K >= 4096), cuBLAS elsewhere; 1 = that kernel wherever its shape rules allow; 2 = always cuBLAS. Returns 0, or 1
+ * for an unknown value (nothing changes). */
+LLAISYS_EXTERN_C LLAISYS_API int llaisysSetLinearPolicy(int policy);
 LLAISYS_EXTERN_C LLAISYS_API void llaisysRearrange(llaisysTensor_t out, llaisysTensor_t in);
 LLAISYS_EXTERN_C LLAISYS_API void llaisysRmsNorm(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight,
                                                  float eps);

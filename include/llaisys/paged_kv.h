@@ -45,11 +45,28 @@ extern "C" {
 /* Text of the calling thread's most recent non-OK status ("" if none). */
 LLAISYS_API const char *llaisysGetLastError(void);
 
+/* ---- which kernel served an attention call ------------------------------------------------ */
+/* The library picks the kernel from the call's shape alone and says which one it queued. Pools of 16-bit data with
+ * head_dim 128, 16-token pages and at most 8 query heads per kv head are served by the TMA decode kernel and the
+ * tcgen05 chunk kernel and by nothing else: a call of that shape they cannot take (misaligned buffers, ...) returns
+ * LLAISYS_E_UNSUPPORTED with the reason in llaisysGetLastError; it is never re-routed to the generic kernel. */
+#define LLAISYS_KERNEL_NONE 0
+#define LLAISYS_KERNEL_CPU 1              /* the host loops of a CPU cache / CPU tensors                          */
+#define LLAISYS_KERNEL_GENERIC 2          /* CUDA, any dtype / head_dim / page size: one CTA per (query, head)    */
+#define LLAISYS_KERNEL_DECODE_TMA 3       /* split-KV flash decoding over a page pool, TMA copy pipeline          */
+#define LLAISYS_KERNEL_DECODE_TMA_FUSED 4 /* the same launch also appends the step's new K/V rows                 */
+#define LLAISYS_KERNEL_DECODE_CP_ASYNC 5  /* split-KV flash decoding over plain K/V tensors (legacy operator)     */
+#define LLAISYS_KERNEL_PREFILL_TC 6       /* causal chunk attention on tcgen05 tensor cores                       */
+/* Kernel of the calling thread's most recent attention call: any cache, or llaisysSelfAttention. */
+LLAISYS_API int llaisysLastAttentionKernel(void);
+
 typedef struct LlaisysPagedKV *llaisysPagedKV_t;
 
 /* ---- lifetime ------------------------------------------------------------------------ */
 
-/* Allocates the page pool, block tables and split-KV scratch on (device_type, device_id).
+/* Allocates the page pool, block tables and the attention kernels' workspace on (device_type, device_id): everything
+ * a data-path call with device index arrays will ever need (for 16-bit, head_dim 128, page 16 pools on NVIDIA about
+ * 40 MiB beside the pool), so those calls never allocate and CUDA graphs captured over them stay valid.
  * max_seqs bounds live sequences; max_pages_per_seq bounds one sequence's block table.
  * dtype is F32, F16 or BF16. */
 LLAISYS_API int llaisysPagedKVCreate(llaisysPagedKV_t *kv_out, llaisysDeviceType_t device_type, int device_id,
@@ -110,12 +127,15 @@ LLAISYS_API int llaisysPagedKVFlush(llaisysPagedKV_t kv);
  * pages overlap the tail of the kernels before it on the stream. A decode kernel touches q, each sequence's LAST
  * page, scratch and outputs only after the kernel directly before it has completed, and lets its own successor start
  * only after that; the append kernel waits for its predecessor before doing anything. Contract while overlap is on:
- *   - the kernel directly before a decode call on the stream writes K/V only into each sequence's last page (by the
- *     kv_lens of that decode call) -- true for a one-row-per-sequence append; after a multi-page append (a prefill
+ *   - the kernel directly before a decode call on the stream writes K/V only into the last two token slots of each
+ *     sequence (positions kv_len - 2 and kv_len - 1 by the kv_lens of that decode call) -- true for a one-row-per-
+ *     sequence append and for the one-launch decode step of the token before; after a multi-page append (a prefill
  *     chunk) put any non-overlapping kernel, a copy or a synchronisation before the first decode call;
  *   - index arrays and block-table rows passed to a call were written before that directly preceding kernel started
  *     (true for host-array calls, whose staging copies break the chain, and for device arrays prepared per batch). */
 LLAISYS_API int llaisysPagedKVSetLaunchOverlap(llaisysPagedKV_t kv, int enable);
+/* LLAISYS_KERNEL_* of this cache's most recent attention call (-1 for a null handle). */
+LLAISYS_API int llaisysPagedKVLastKernel(llaisysPagedKV_t kv);
 /* Synchronises the cache's stream and reports LLAISYS_E_KERNEL if any kernel since the last
  * check met an out-of-range page or position (the kernel skips such an access). */
 LLAISYS_API int llaisysPagedKVCheck(llaisysPagedKV_t kv);
@@ -183,14 +203,20 @@ LLAISYS_API int llaisysPagedKVRopeAppendDev(llaisysPagedKV_t kv, size_t layer, v
 LLAISYS_API int llaisysPagedAttentionDecodeDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
                                                const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
                                                size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream);
+/* One decode step in ONE launch: row i of k_new / v_new ([n_seqs, nkvh, head_dim], device, 16-byte aligned) becomes
+ * token kv_lens_dev[i] - 1 of sequence seq_ids_dev[i] -- the same bits llaisysPagedKVAppendDev would write -- and out[i]
+ * is the attention of q[i] over the sequence's kv_lens_dev[i] tokens, the new one included. A sequence may appear once
+ * per call. NVIDIA: pools of 16-bit data, head_dim 128, 16-token pages, nh / nkvh <= 8 (LLAISYS_E_UNSUPPORTED otherwise:
+ * call AppendDev then DecodeDev). Takes part in launch overlap like the decode call. */
+LLAISYS_API int llaisysPagedDecodeStepDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q, const void *k_new,
+                                          const void *v_new, const int32_t *seq_ids_dev, const int32_t *kv_lens_dev,
+                                          size_t n_seqs, size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream);
 LLAISYS_API int llaisysPagedAttentionDecodePartialDev(llaisysPagedKV_t kv, size_t layer, float *part, const void *q,
                                                       const int32_t *seq_ids_dev, const int32_t *kv_lens_dev,
                                                       size_t n_seqs, size_t max_kv_len, size_t nh, float scale,
                                                       llaisysStream_t stream);
-/* q_starts_dev is int32 [n_seqs + 1]: row offset of each sequence's chunk in q / out. On NVIDIA with 16-bit
- * data and head_dim 128 the first call allocates the cache's workspace for tiles that are split over CTAs (two
- * partial results per CTA, about 38 MiB on a 148-SM GPU) and synchronises once; later calls do not allocate.
- * Calls on one cache share that workspace and must be ordered on one stream. */
+/* q_starts_dev is int32 [n_seqs + 1]: row offset of each sequence's chunk in q / out. Attention calls on one cache
+ * share its workspace (partial results of work that is split over CTAs) and must be ordered on one stream. */
 LLAISYS_API int llaisysPagedAttentionPrefillDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
                                                 const int32_t *seq_ids_dev, const int32_t *q_starts_dev,
                                                 const int32_t *kv_lens_dev, size_t n_seqs, size_t total_q,
@@ -210,21 +236,29 @@ LLAISYS_API int llaisysPagedAttentionPrefillDev(llaisysPagedKV_t kv, size_t laye
  *           that loads the library, for the life of the process.
  *   Sharing: every call on a device uses the same array. What has to start at zero is cleared at the start of
  *           each call; calls that overlap on the GPU (unordered streams) race on it -- keep them ordered.
- *   First call on a device looks up the array's device address; make that call before any stream capture.
+ *   First call on a device looks up the array's device address; make that call before any stream capture. A failed
+ *           look-up is reported (LLAISYS_E_DEVICE) and tried again by the next call.
+ *   Device: the call makes device_id current while it runs and restores the caller's current device before returning.
  * error_flag_dev (optional, device int32, caller-zeroed): receives the kErr bits if the kernel had to skip an
- * out-of-range page; NULL keeps the word inside the library. */
+ * out-of-range page. NULL collects them in a word inside the library instead, which stays set until
+ * llaisysPagedAttentionDecodeNoAllocStatus reads it -- a caller that passes NULL should poll that call. */
 LLAISYS_API int llaisysPagedAttentionDecodeNoAlloc(int device_id, void *out, const void *q, void *pool_layer,
                                                    const int32_t *block_table_dev, size_t table_stride,
                                                    size_t num_pages, const int32_t *seq_ids_dev,
                                                    const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len,
                                                    size_t nh, size_t nkvh, llaisysDataType_t dtype, float scale,
                                                    int32_t *error_flag_dev, llaisysStream_t stream);
+/* Synchronises `stream`, writes to *flags_out the error bits collected on device_id by no-alloc calls that passed no
+ * error word of their own (0 = none; 1 = a page index was out of range and its page was skipped) and clears them.
+ * Allocates nothing. No counterpart in the reference. */
+LLAISYS_API int llaisysPagedAttentionDecodeNoAllocStatus(int device_id, llaisysStream_t stream, int32_t *flags_out);
 
 /* ---- split-KV decode across the GPUs of one node through peer memory --------------------------------------------- */
 /* For ONE long sequence whose KV range is cut across ranks (one process per GPU): instead of an all-gather through a
- * collective library, every rank writes its partial (o, m, l) rows straight into slots of all the other ranks' exchange
- * buffers over NVLink (buffers mapped with CUDA IPC), stamps a flag, and merges once the flags of all writers carry the
- * step. Everything is queued on the given stream and can be captured in a CUDA graph. Waits for peers are bounded
+ * collective library, every rank's decode kernel stores its partial (o, m, l) rows straight into slots of all the ranks'
+ * exchange buffers over NVLink (buffers mapped with CUDA IPC; plain stores, nothing reads remote memory), the thread
+ * that finishes the rank's last row stamps a flag in every buffer, and a merge kernel combines the slots once the flags
+ * of all writers carry the step: two launches per step. Everything is queued on the given stream and can be captured in a CUDA graph. Waits for peers are bounded
  * (about a second): a wait that runs out flags an error (llaisysPeerExchangeStatus) instead of hanging. */
 typedef struct LlaisysPeerExchange *llaisysPeerExchange_t;
 
@@ -237,12 +271,19 @@ LLAISYS_API void llaisysPeerExchangeDestroy(llaisysPeerExchange_t ex);
 LLAISYS_API int llaisysPeerExchangeHandle(llaisysPeerExchange_t ex, void *out_64_bytes);
 /* handles: world * 64 bytes, entry i from rank i. Every rank must call it once before the first step. */
 LLAISYS_API int llaisysPeerExchangeConnect(llaisysPeerExchange_t ex, const void *handles);
+/* Unmaps the other ranks' buffers (synchronises the device first). Shutting down: every rank disconnects, the ranks
+ * meet on the host, then every rank destroys -- a buffer is released only when nobody maps it any more. */
+LLAISYS_API int llaisysPeerExchangeDisconnect(llaisysPeerExchange_t ex);
 /* Partial decode of this rank's slice (as llaisysPagedAttentionDecodePartialDev) + exchange + merge into out
  * [n_seqs, nh, head_dim]. Every rank passes the same q and its LOCAL sequences / lengths. */
 LLAISYS_API int llaisysPagedAttentionDecodeSplitDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q,
                                                     const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
                                                     size_t max_kv_len, size_t nh, float scale, llaisysPeerExchange_t ex,
                                                     llaisysStream_t stream);
+/* Polls (about 0.2 us each) after which the merge's wait for a peer's rows gives up; the default is about a second
+ * (4 << 20). Set it before the first step. After a wait has run out the step's output is undefined and the ranks' step
+ * counters have diverged: every rank destroys its exchange and creates a new one before the next step. */
+LLAISYS_API int llaisysPeerExchangeSetWaitLimit(llaisysPeerExchange_t ex, uint32_t polls);
 /* Synchronises the stream; 0, or 1 when a wait for a peer ran out since the last call (cleared by the call). */
 LLAISYS_API int llaisysPeerExchangeStatus(llaisysPeerExchange_t ex, llaisysStream_t stream);
 

@@ -10,11 +10,13 @@ from .libllaisys import llaisysStream_t as Stream
 from .runtime import RuntimeAPI, context_stream, set_context_runtime
 from .tensor import Tensor
 from .ops import Ops
-from .paged_kv import LlaisysError, PagedKVCache, decode_no_alloc, lse_merge
+from .paged_kv import (Kernel, LlaisysError, PagedKVCache, decode_no_alloc, decode_no_alloc_status, last_attention_kernel,
+                       lse_merge)
 from . import models
 from .serving import Engine
 
 __all__ = [
     "RuntimeAPI", "DeviceType", "DataType", "MemcpyKind", "Stream", "Tensor", "Ops", "models", "Engine",
-    "PagedKVCache", "lse_merge", "decode_no_alloc", "LlaisysError", "Status", "context_stream", "set_context_runtime",
+    "PagedKVCache", "lse_merge", "decode_no_alloc", "decode_no_alloc_status", "LlaisysError", "Status", "Kernel",
+    "last_attention_kernel", "context_stream", "set_context_runtime",
 ]

@@ -8,6 +8,9 @@
 #include "../device/runtime_api.hpp"
 #include "handles.hpp"
 #include "../ops/ops.hpp"
+#ifdef ENABLE_NVIDIA_API
+#include "../kernels/kernels.hpp"
+#endif
 
 #include <algorithm>
 
@@ -67,6 +70,13 @@ void llaisysLinear(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weig
 }
 void llaisysLinearAccumulate(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight) {
     llaisys::ops::linear_ex(out->tensor, in->tensor, weight->tensor, nullptr, true);
+}
+int llaisysSetLinearPolicy(int policy) {
+#ifdef ENABLE_NVIDIA_API
+    return llaisys::kernels::set_linear_policy(policy) ? 0 : 1;
+#else
+    return policy >= 0 && policy <= 2 ? 0 : 1; // CPU-only build: one kernel, nothing to choose
+#endif
 }
 void llaisysRearrange(llaisysTensor_t out, llaisysTensor_t in) { llaisys::ops::rearrange(out->tensor, in->tensor); }
 void llaisysRmsNorm(llaisysTensor_t out, llaisysTensor_t in, llaisysTensor_t weight, float eps) {

@@ -282,10 +282,31 @@ int llaisysPagedAttentionDecodeSplitDev(llaisysPagedKV_t kv, size_t layer, void 
         if (rows * (cfg.head_dim + 2) > ex->impl.slotFloats()) {
             throw llaisys::kv::StatusError(LLAISYS_E_INVALID, "split decode: the exchange's slots are too small for this batch");
         }
-        kv->impl.decodeDev(layer, nullptr, ex->impl.localPartial(), q, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale,
-                           stream);
-        ex->impl.exchangeAndMerge(stream, cfg.dtype, out, int(rows), int(cfg.head_dim));
+        if (kv->impl.canPushPartials(nh)) {
+            // the decode kernel stores its rows at every rank and stamps the flags itself
+            const llaisys::kernels::PeerSink sink = ex->impl.sink();
+            kv->impl.decodeSplitDev(layer, q, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale, sink, stream);
+        } else {
+            kv->impl.decodeDev(layer, nullptr, ex->impl.localPartial(), q, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh,
+                               scale, stream);
+            ex->impl.push(stream, int(rows), int(cfg.head_dim));
+        }
+        ex->impl.merge(stream, cfg.dtype, out, int(rows), int(cfg.head_dim));
     });
+}
+int llaisysPeerExchangeDisconnect(llaisysPeerExchange_t ex) {
+    if (ex == nullptr) {
+        g_last_error = "peer exchange: null handle";
+        return LLAISYS_E_INVALID;
+    }
+    return guarded([&] { ex->impl.disconnect(); });
+}
+int llaisysPeerExchangeSetWaitLimit(llaisysPeerExchange_t ex, uint32_t polls) {
+    if (ex == nullptr) {
+        g_last_error = "peer exchange: null handle";
+        return LLAISYS_E_INVALID;
+    }
+    return guarded([&] { ex->impl.setWaitLimit(polls); });
 }
 int llaisysPeerExchangeStatus(llaisysPeerExchange_t ex, llaisysStream_t stream) {
     if (ex == nullptr) {
@@ -302,6 +323,8 @@ int llaisysPagedAttentionDecodeSplitDev(llaisysPagedKV_t, size_t, void *, const 
                                         size_t, size_t, float, llaisysPeerExchange_t, llaisysStream_t) {
     return LLAISYS_E_UNSUPPORTED;
 }
+int llaisysPeerExchangeDisconnect(llaisysPeerExchange_t) { return LLAISYS_E_UNSUPPORTED; }
+int llaisysPeerExchangeSetWaitLimit(llaisysPeerExchange_t, uint32_t) { return LLAISYS_E_UNSUPPORTED; }
 int llaisysPeerExchangeStatus(llaisysPeerExchange_t, llaisysStream_t) { return -1; }
 #endif
 
@@ -350,6 +373,16 @@ int llaisysPagedAttentionDecodeDev(llaisysPagedKV_t kv, size_t layer, void *out,
         kv->impl.decodeDev(layer, out, nullptr, q, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale, stream);
     });
 }
+int llaisysPagedDecodeStepDev(llaisysPagedKV_t kv, size_t layer, void *out, const void *q, const void *k_new,
+                              const void *v_new, const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
+                              size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream) {
+    KV_OR_FAIL(kv);
+    return guarded([&] {
+        kv->impl.decodeStepDev(layer, out, q, k_new, v_new, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale, stream);
+    });
+}
+int llaisysPagedKVLastKernel(llaisysPagedKV_t kv) { return kv ? kv->impl.lastKernel() : -1; }
+int llaisysLastAttentionKernel(void) { return llaisys::kv::lastAttentionKernel(); }
 int llaisysPagedAttentionDecodePartialDev(llaisysPagedKV_t kv, size_t layer, float *part, const void *q,
                                           const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
                                           size_t max_kv_len, size_t nh, float scale, llaisysStream_t stream) {

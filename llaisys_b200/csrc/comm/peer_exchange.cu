@@ -21,7 +21,6 @@ void cuda_ok(cudaError_t rc, const char *what) {
     }
 }
 
-constexpr uint32_t kSpinLimit = 4u << 20; // polls of ~0.2 us each: gives up after about a second
 constexpr int kErrPeerTimeout = 1;
 
 struct PeerTable {
@@ -58,14 +57,14 @@ __global__ void peer_push_kernel(PeerTable t, const float4 *__restrict__ src, si
 // (the same arithmetic as the library's LSE merge; one warp per row).
 template <typename T>
 __global__ void peer_merge_kernel(T *__restrict__ out, unsigned char *local_base, size_t slot_floats, int world, int n_rows,
-                                  int d, size_t flags_offset, size_t epoch_offset, size_t error_offset) {
+                                  int d, size_t flags_offset, size_t epoch_offset, size_t error_offset, uint32_t spin_limit) {
     const uint32_t step = *reinterpret_cast<const uint32_t *>(local_base + epoch_offset) + 1;
     if (int(threadIdx.x) < world) {
         const uint32_t *flag = reinterpret_cast<const uint32_t *>(local_base + flags_offset) + threadIdx.x;
         uint32_t spins = 0;
         // flags only grow; a value ahead of the step means the writer is already one step further (allowed)
         while (int32_t(load_acquire_sys(flag) - step) < 0) {
-            if (++spins > kSpinLimit) {
+            if (++spins > spin_limit) {
                 atomicOr(reinterpret_cast<int *>(local_base + error_offset), kErrPeerTimeout);
                 break;
             }
@@ -128,7 +127,8 @@ PeerExchange::PeerExchange(int rank, int world, size_t slot_floats) : _rank(rank
     _flags_offset = align_up(slots_bytes, 256);
     _epoch_offset = _flags_offset + align_up(size_t(world) * sizeof(uint32_t), 256);
     _error_offset = _epoch_offset + 256;
-    _bytes = _error_offset + 256;
+    _done_offset = _error_offset + 256;
+    _bytes = _done_offset + 256;
     cuda_ok(cudaMalloc(&_base, _bytes), "peer exchange: cudaMalloc");
     cuda_ok(cudaMemset(_base, 0, _bytes), "peer exchange: cudaMemset");
     cuda_ok(cudaMalloc(&_local_part, slot_floats * sizeof(float)), "peer exchange: cudaMalloc");
@@ -139,13 +139,20 @@ PeerExchange::PeerExchange(int rank, int world, size_t slot_floats) : _rank(rank
     _connected = world == 1;
 }
 
-PeerExchange::~PeerExchange() {
+void PeerExchange::disconnect() {
     (void)cudaDeviceSynchronize();
     for (int p = 0; p < _world; ++p) {
         if (p != _rank && _peer[size_t(p)] != nullptr) {
             (void)cudaIpcCloseMemHandle(_peer[size_t(p)]);
+            _peer[size_t(p)] = nullptr;
         }
     }
+    (void)cudaGetLastError();
+    _connected = false;
+}
+
+PeerExchange::~PeerExchange() {
+    disconnect();
     (void)cudaFree(_local_part);
     (void)cudaFree(_base);
     (void)cudaGetLastError();
@@ -181,40 +188,73 @@ void PeerExchange::connect(const void *handles) {
     _connected = true;
 }
 
-void PeerExchange::exchangeAndMerge(llaisysStream_t stream, llaisysDataType_t dtype, void *out, int n_rows, int d) {
+kernels::PeerSink PeerExchange::sink() const {
     if (!_connected) {
         fail(LLAISYS_E_INVALID, "peer exchange: connect() has not been called");
     }
-    if (n_rows <= 0 || d <= 0 || out == nullptr || size_t(n_rows) * size_t(d + 2) > _slot_floats ||
-        (size_t(n_rows) * size_t(d + 2)) % 4 != 0) {
+    kernels::PeerSink k;
+    for (int p = 0; p < _world; ++p) {
+        k.base[p] = _peer[size_t(p)];
+    }
+    k.world = _world;
+    k.rank = _rank;
+    k.slot_floats = _slot_floats;
+    k.flags_offset = _flags_offset;
+    k.epoch_offset = _epoch_offset;
+    k.done_offset = _done_offset;
+    return k;
+}
+
+void PeerExchange::setWaitLimit(uint32_t polls) {
+    if (polls == 0) {
+        fail(LLAISYS_E_INVALID, "peer exchange: the wait limit must be at least one poll");
+    }
+    _spin_limit = polls;
+}
+
+void PeerExchange::push(llaisysStream_t stream, int n_rows, int d) {
+    if (!_connected) {
+        fail(LLAISYS_E_INVALID, "peer exchange: connect() has not been called");
+    }
+    if (n_rows <= 0 || d <= 0 || size_t(n_rows) * size_t(d + 2) > _slot_floats || (size_t(n_rows) * size_t(d + 2)) % 4 != 0) {
         fail(LLAISYS_E_INVALID, "peer exchange: rows do not fit the slot (or are not a multiple of 16 bytes)");
     }
-    auto s = static_cast<cudaStream_t>(stream);
     PeerTable t{};
     for (int p = 0; p < _world; ++p) {
         t.base[p] = _peer[size_t(p)];
     }
     const size_t n_vec = size_t(n_rows) * size_t(d + 2) / 4;
-    peer_push_kernel<<<unsigned(_world), 512, 0, s>>>(t, reinterpret_cast<const float4 *>(_local_part), n_vec, _slot_floats,
-                                                      _rank, _world, _flags_offset, _epoch_offset);
+    peer_push_kernel<<<unsigned(_world), 512, 0, static_cast<cudaStream_t>(stream)>>>(
+        t, reinterpret_cast<const float4 *>(_local_part), n_vec, _slot_floats, _rank, _world, _flags_offset, _epoch_offset);
+    kernels::check_launch("peer_exchange push");
+}
+
+void PeerExchange::merge(llaisysStream_t stream, llaisysDataType_t dtype, void *out, int n_rows, int d) {
+    if (!_connected) {
+        fail(LLAISYS_E_INVALID, "peer exchange: connect() has not been called");
+    }
+    if (n_rows <= 0 || d <= 0 || out == nullptr || size_t(n_rows) * size_t(d + 2) > _slot_floats) {
+        fail(LLAISYS_E_INVALID, "peer exchange: rows do not fit the slot");
+    }
+    auto s = static_cast<cudaStream_t>(stream);
     const int block = 128, grid = (n_rows + 3) / 4;
     switch (dtype) {
     case LLAISYS_DTYPE_F32:
         peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<float *>(out), _base, _slot_floats, _world, n_rows, d,
-                                                 _flags_offset, _epoch_offset, _error_offset);
+                                                 _flags_offset, _epoch_offset, _error_offset, _spin_limit);
         break;
     case LLAISYS_DTYPE_F16:
         peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<__half *>(out), _base, _slot_floats, _world, n_rows, d,
-                                                 _flags_offset, _epoch_offset, _error_offset);
+                                                 _flags_offset, _epoch_offset, _error_offset, _spin_limit);
         break;
     case LLAISYS_DTYPE_BF16:
         peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<__nv_bfloat16 *>(out), _base, _slot_floats, _world, n_rows, d,
-                                                 _flags_offset, _epoch_offset, _error_offset);
+                                                 _flags_offset, _epoch_offset, _error_offset, _spin_limit);
         break;
     default:
         fail(LLAISYS_E_INVALID, "peer exchange: unsupported output type");
     }
-    kernels::check_launch("peer_exchange");
+    kernels::check_launch("peer_exchange merge");
 }
 
 int PeerExchange::status(llaisysStream_t stream) {

@@ -58,6 +58,17 @@ struct AttnBatch {
 struct AttnOut {
     void *out = nullptr;
     float *part = nullptr;
+    const struct PeerSink *peers = nullptr; // decode over a page pool only: partial rows go to exchange slots instead
+};
+
+// Exchange buffers of a KV-range split across the GPUs of a node, as rank `rank` sees them: base[r] is rank r's buffer
+// (peer memory for r != rank). A buffer holds 2 (step parity) x world slots of slot_floats floats -- slot s of parity p
+// is written by rank s -- then, at the byte offsets below, one uint32 flag per writer (the last step whose rows are
+// complete), the step counter (merges completed) and a counter of this rank's finished (sequence, kv-head) pairs.
+struct PeerSink {
+    unsigned char *base[16] = {};
+    int32_t world = 0, rank = 0;
+    size_t slot_floats = 0, flags_offset = 0, epoch_offset = 0, done_offset = 0;
 };
 
 // Device-side scratch a launch may use (split-KV partials and arrival counters); owned by the caller.

@@ -11,12 +11,14 @@
 //   * the array has a fixed size: n_seqs * nkvh <= kMaxPairs and a GPU of at most kMaxCtas / 2 SMs; anything larger
 //     is refused with LLAISYS_E_INVALID before any work is queued;
 //   * every GPU that loads the library carries the array (about 3.5 MiB) until the process exits;
-//   * all calls on a device share it. The counters and the error word are cleared at the start of every call;
-//     the partials need no clearing (each launch writes a slot before reading it). Two calls that overlap on the
-//     GPU -- different streams, no ordering between them -- race on it and give garbage: keep calls on one
-//     device ordered;
+//   * all calls on a device share it. The arrival counters are cleared at the start of every call; the partials need
+//     no clearing (each launch writes a slot before reading it). Two calls that overlap on the GPU -- different
+//     streams, no ordering between them -- race on it and give garbage: keep calls on one device ordered;
 //   * the first call on each device resolves the array's device address (cudaGetSymbolAddress). Make that first
-//     call outside any stream capture.
+//     call outside any stream capture; a call whose look-up fails reports it and the next call tries again;
+//   * a caller that passes no error word of its own gets the kernel's "skipped a bad page" bits collected in a word
+//     inside the array, which stays set until llaisysPagedAttentionDecodeNoAllocStatus reads and clears it;
+//   * the call runs with device_id current and puts the caller's current device back before it returns.
 #include "kernels.hpp"
 #include "device_utils.cuh"
 
@@ -44,11 +46,40 @@ struct StaticScratch {
 static __device__ __align__(256) StaticScratch g_decode_scratch;
 
 struct DeviceSlot {
-    std::once_flag once;
-    StaticScratch *ptr = nullptr;
-    cudaError_t status = cudaSuccess;
+    std::mutex lock;
+    StaticScratch *ptr = nullptr; // set once the look-up has succeeded; a failed look-up is retried by the next call
 };
 DeviceSlot g_slots[kMaxDevices];
+
+// Makes `device` current for the life of the object and the previous device current again afterwards.
+struct DeviceScope {
+    int previous = -1;
+    explicit DeviceScope(int device) {
+        LLAISYS_CUDA_CHECK(cudaGetDevice(&previous));
+        if (previous != device) {
+            LLAISYS_CUDA_CHECK(cudaSetDevice(device));
+        } else {
+            previous = -1;
+        }
+    }
+    ~DeviceScope() {
+        if (previous >= 0 && cudaSetDevice(previous) != cudaSuccess) {
+            (void)cudaGetLastError();
+        }
+    }
+};
+
+// Device address of the static array on the CURRENT device; throws if the runtime cannot give it (nothing is cached then).
+StaticScratch *scratch_of(int device_id) {
+    DeviceSlot &slot = g_slots[device_id];
+    std::lock_guard<std::mutex> guard(slot.lock);
+    if (slot.ptr == nullptr) {
+        void *p = nullptr;
+        LLAISYS_CUDA_CHECK(cudaGetSymbolAddress(&p, g_decode_scratch));
+        slot.ptr = static_cast<StaticScratch *>(p);
+    }
+    return slot.ptr;
+}
 
 } // namespace
 
@@ -91,29 +122,16 @@ extern "C" LLAISYS_API int llaisysPagedAttentionDecodeNoAlloc(
         return report(LLAISYS_E_INVALID, "decode (no-alloc): device id out of range");
     }
     try {
-        int current = -1;
-        LLAISYS_CUDA_CHECK(cudaGetDevice(&current));
-        if (current != device_id) {
-            LLAISYS_CUDA_CHECK(cudaSetDevice(device_id));
-        }
+        DeviceScope scope(device_id);
         // set-up, once per device, with that device current: the device address of the static array
-        DeviceSlot &slot = g_slots[device_id];
-        std::call_once(slot.once, [&slot] {
-            void *p = nullptr;
-            slot.status = cudaGetSymbolAddress(&p, g_decode_scratch);
-            slot.ptr = static_cast<StaticScratch *>(p);
-        });
-        if (slot.status != cudaSuccess || slot.ptr == nullptr) {
-            return report(LLAISYS_E_DEVICE, std::string("decode (no-alloc): cudaGetSymbolAddress failed: ") +
-                                                cudaGetErrorString(slot.status));
-        }
+        StaticScratch *scratch = scratch_of(device_id);
         const int grid = decode_grid_size(int32_t(n_seqs), int32_t(nkvh), int32_t(max_kv_len));
         if (grid > kMaxCtas) {
             return report(LLAISYS_E_INVALID, "decode (no-alloc): this GPU has more SMs than the static scratch was sized for");
         }
         auto s = static_cast<cudaStream_t>(stream);
-        // counters and the error word must start at zero; a call that was cut short may have left them set
-        LLAISYS_CUDA_CHECK(cudaMemsetAsync(slot.ptr->counters, 0, sizeof(int32_t) * (kMaxPairs + 1), s));
+        // the arrival counters must start at zero; a call that was cut short may have left some set
+        LLAISYS_CUDA_CHECK(cudaMemsetAsync(scratch->counters, 0, sizeof(scratch->counters), s));
 
         KVView kv;
         const size_t tile = 16 * 128; // elements of one (page, K|V, kv-head) tile
@@ -140,11 +158,11 @@ extern "C" LLAISYS_API int llaisysPagedAttentionDecodeNoAlloc(
         AttnOut o;
         o.out = out;
         AttnScratch sc;
-        sc.partials = slot.ptr->partials;
+        sc.partials = scratch->partials;
         sc.partials_floats = kPartialFloats;
-        sc.counters = slot.ptr->counters;
+        sc.counters = scratch->counters;
         sc.counters_len = kMaxPairs;
-        sc.error_flag = error_flag_dev != nullptr ? error_flag_dev : &slot.ptr->error_word;
+        sc.error_flag = error_flag_dev != nullptr ? error_flag_dev : &scratch->error_word;
         if (attention_decode_split(stream, dtype, kv, batch, q, scale, o, sc) != 0) {
             return report(LLAISYS_E_UNSUPPORTED, "decode (no-alloc): shape not covered by the split-KV kernel "
                                                  "(needs 16-byte aligned pool and q, n_seqs <= 1024)");
@@ -152,5 +170,30 @@ extern "C" LLAISYS_API int llaisysPagedAttentionDecodeNoAlloc(
         return LLAISYS_OK;
     } catch (const std::exception &e) {
         return report(LLAISYS_E_DEVICE, e.what());
+    }
+}
+
+// Reads (and clears) the error bits that calls WITHOUT an error word of their own have collected on the device since
+// the last read. Synchronises `stream` first; allocates nothing.
+extern "C" LLAISYS_API int llaisysPagedAttentionDecodeNoAllocStatus(int device_id, llaisysStream_t stream,
+                                                                    int32_t *flags_out) {
+    using namespace llaisys::kernels;
+    if (flags_out == nullptr || device_id < 0 || device_id >= kMaxDevices) {
+        set_last_error("decode (no-alloc) status: bad device id or null output");
+        return LLAISYS_E_INVALID;
+    }
+    try {
+        DeviceScope scope(device_id);
+        StaticScratch *scratch = scratch_of(device_id);
+        auto s = static_cast<cudaStream_t>(stream);
+        LLAISYS_CUDA_CHECK(cudaMemcpyAsync(flags_out, &scratch->error_word, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+        LLAISYS_CUDA_CHECK(cudaStreamSynchronize(s));
+        if (*flags_out != 0) {
+            LLAISYS_CUDA_CHECK(cudaMemsetAsync(&scratch->error_word, 0, sizeof(int32_t), s));
+        }
+        return LLAISYS_OK;
+    } catch (const std::exception &e) {
+        set_last_error(e.what());
+        return LLAISYS_E_DEVICE;
     }
 }

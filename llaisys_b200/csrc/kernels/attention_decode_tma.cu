@@ -16,6 +16,12 @@
 // Measured motivation: the cp.async version spent its issue slots on address arithmetic and its time in
 // long-scoreboard stalls behind block-table loads, reaching 45 % of DRAM throughput with 8 warps per SM.
 //
+// Fused step (k_new / v_new given): the call also appends one new K/V row per sequence, at position kv_len - 1, so a
+// decode step is ONE launch. The consumer warp that takes a pair's last page fetches the pair's new row with cp.async
+// while it loads q, writes it over its slot of the tile in shared memory once the page has landed (whatever the TMA copy
+// read of that slot, old bytes or a torn new row, is replaced) and stores it into the page in global memory for later
+// calls. Nobody else reads that row in this launch: a (page, kv-head) tile is copied by exactly one CTA.
+//
 // Every mbarrier wait is bounded; a wait that runs out sets bit 8 of the error word, the CTA stops touching the
 // ring (its warps still meet at their named barriers) and the launch ends with wrong output and a flagged error
 // instead of a hang. No cluster multicast is used anywhere.
@@ -32,10 +38,7 @@ namespace llaisys::kernels {
 
 namespace {
 
-#ifndef LLAISYS_DECODE_CONSUMER_WARPS
-#define LLAISYS_DECODE_CONSUMER_WARPS 4
-#endif
-constexpr int kConsumerWarps = LLAISYS_DECODE_CONSUMER_WARPS; // 4 (two CTAs per SM) or 8 (one CTA per SM)
+constexpr int kConsumerWarps = 4; // two CTAs per SM
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kProducerWarp = kConsumerWarps;      // warp 4 issues the copies
 constexpr int kEpilogueWarp = kConsumerWarps + 1;  // warp 5 counts arrivals and merges cut pairs
@@ -55,6 +58,7 @@ constexpr int kMaxSeqs = 1024;
 constexpr int kCtasPerSm = 8 / kConsumerWarps;
 constexpr uint32_t kWaitLimit = 1u << 20; // polls before a wait gives up (about a second at worst)
 constexpr int kErrTimeout = 8;
+constexpr int kStageBytes = 512 + 16; // per consumer warp: a new K row and V row (256 B each) and their page index
 constexpr int kDimGroups = kConsumerThreads / kD; // the pair epilogue maps a consumer thread to one output
 static_assert(kConsumerThreads % kD == 0, "dimension and to every kDimGroups-th head of the group");
 
@@ -72,7 +76,54 @@ struct TmaDecodeParams {
     float *partials;
     int32_t *counters;
     int32_t *error_flag;
+    // fused step: row i of k_new / v_new [n_seqs, nkvh, 128] becomes token kv_lens[i] - 1 of sequence i (null: plain decode)
+    const char *k_new;
+    const char *v_new;
+    char *pool_k;                           // K tile of (page 0, kv-head 0) of this layer
+    long long page_stride_b, head_stride_b; // bytes between pages / kv-heads
+    long long v_offset_b;                   // V tile - K tile of the same (page, kv-head)
+    // KV-range split across GPUs (xchg_world > 0, out and part null): every partial row (o, m, l) is stored into slot
+    // xchg_rank of EVERY rank's exchange buffer (plain stores into peer memory), and the thread that completes the
+    // launch's last pair stamps this rank's flag in every buffer with the step number.
+    PeerSink xchg;
 };
+
+constexpr int kMaxXchg = int(sizeof(PeerSink::base) / sizeof(PeerSink::base[0]));
+
+__device__ __forceinline__ void store_release_sys_u32(uint32_t *addr, uint32_t value) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(addr), "r"(value) : "memory");
+}
+
+// The device-side step counter of the exchange: the number of merges completed so far. This launch belongs to the next.
+__device__ __forceinline__ uint32_t xchg_step(const TmaDecodeParams &p) {
+    return __ldcg(reinterpret_cast<const uint32_t *>(p.xchg.base[p.xchg.rank] + p.xchg.epoch_offset)) + 1u;
+}
+
+// One float of a partial row: into the plain array, or into this rank's slot of every rank's buffer.
+__device__ __forceinline__ void put_part(const TmaDecodeParams &p, uint32_t step, long long idx, float v) {
+    if (p.xchg.world == 0) {
+        p.part[idx] = v;
+        return;
+    }
+    const long long at = ((long long)(step & 1u) * p.xchg.world + p.xchg.rank) * (long long)p.xchg.slot_floats + idx;
+    for (int pe = 0; pe < p.xchg.world; ++pe) {
+        reinterpret_cast<float *>(p.xchg.base[pe])[at] = v;
+    }
+}
+
+// Called by ONE thread after `n` more pairs of this launch are complete and their rows fenced at system scope by the
+// threads that stored them. The caller that completes the last pair publishes the step to every rank.
+__device__ __forceinline__ void xchg_pairs_done(const TmaDecodeParams &p, uint32_t step, int n, int n_pairs) {
+    int *done = reinterpret_cast<int *>(p.xchg.base[p.xchg.rank] + p.xchg.done_offset);
+    __threadfence();
+    if (atomicAdd(done, n) + n == n_pairs) {
+        *done = 0; // for the next launch (ordered behind this one by the stream)
+        __threadfence_system();
+        for (int pe = 0; pe < p.xchg.world; ++pe) {
+            store_release_sys_u32(reinterpret_cast<uint32_t *>(p.xchg.base[pe] + p.xchg.flags_offset) + p.xchg.rank, step);
+        }
+    }
+}
 
 struct Cursor {
     int s, kvh, j, np, kv_len, remaining;
@@ -134,7 +185,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     float *red_ml = red_o + kConsumerWarps * p.group * kD;                                // [warps][kMaxGroup][2]
     uint64_t *bars = reinterpret_cast<uint64_t *>(red_ml + kConsumerWarps * kMaxGroup * 2); // full[], empty[], epi_ready, epi_done
     int *cum = reinterpret_cast<int *>(bars + 2 * kSlots + 2);                                // [n_seqs + 1]
+    int *rows = cum + p.n_seqs + 1;                                                           // [n_seqs] block-table rows
+    // new-row staging, 16-byte aligned, one block per consumer warp
+    const uint32_t stage_u32 = (smem_u32(rows + p.n_seqs) + 15u) & ~15u;
     __shared__ int s_abort;
+    __shared__ uint32_t s_step; // exchange mode: the step this launch belongs to (written by consumer thread 0)
     const uint32_t bars_u32 = smem_u32(bars);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -173,6 +228,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             }
             running += __shfl_sync(0xffffffffu, incl, 31);
         }
+    } else {
+        // the sequences' block-table rows, fetched by the other warps in the same round trip as the lengths
+        for (int s = tid - 32; s < p.n_seqs; s += kThreads - 32) {
+            rows[s] = p.seq_ids ? p.seq_ids[s] : s;
+        }
+        if (warp == kProducerWarp && lane == 0) {
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
+        }
     }
     __syncthreads();
 
@@ -182,32 +245,45 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const long long x0 = (long long)blockIdx.x * span;
     const long long x1 = min(total, x0 + span);
 
-    auto write_empty_pairs = [&]() {
-        // -- sequences without any token: the output row is zero (partial: o = 0, m = -inf, l = 0) ----------
-        if (tid < kD) {
-            for (int pair = blockIdx.x; pair < n_pairs; pair += gridDim.x) {
-                const int s = pair / p.nkvh, kvh = pair - s * p.nkvh;
-                if (cum[s + 1] - cum[s] != 0) {
-                    continue;
-                }
-                for (int h = 0; h < p.group; ++h) {
-                    const long long row = (long long)s * p.nh + kvh * p.group + h;
-                    if (p.part != nullptr) {
-                        p.part[row * (kD + 2) + tid] = 0.f;
-                        if (tid == 0) {
-                            p.part[row * (kD + 2) + kD] = -INFINITY;
-                            p.part[row * (kD + 2) + kD + 1] = 0.f;
-                        }
-                    } else {
-                        store_out<kBf16>(p.out, row * kD + tid, 0.f);
+    const bool partial = p.part != nullptr || p.xchg.world > 0;
+    // -- sequences without any token: the output row is zero (partial: o = 0, m = -inf, l = 0). Called by threads
+    //    0..127 at least, after their grid_dependency_wait; `sync` is a barrier over the calling threads.
+    auto write_empty_pairs = [&](auto sync) {
+        int n_empty = 0;
+        const uint32_t step = p.xchg.world > 0 ? xchg_step(p) : 0u;
+        for (int pair = blockIdx.x; pair < n_pairs; pair += gridDim.x) {
+            const int s = pair / p.nkvh, kvh = pair - s * p.nkvh;
+            if (cum[s + 1] - cum[s] != 0) {
+                continue;
+            }
+            ++n_empty;
+            if (tid >= kD) {
+                continue;
+            }
+            for (int h = 0; h < p.group; ++h) {
+                const long long row = (long long)s * p.nh + kvh * p.group + h;
+                if (partial) {
+                    put_part(p, step, row * (kD + 2) + tid, 0.f);
+                    if (tid == 0) {
+                        put_part(p, step, row * (kD + 2) + kD, -INFINITY);
+                        put_part(p, step, row * (kD + 2) + kD + 1, 0.f);
                     }
+                } else {
+                    store_out<kBf16>(p.out, row * kD + tid, 0.f);
                 }
+            }
+        }
+        if (p.xchg.world > 0 && n_empty > 0) { // uniform over the CTA
+            __threadfence_system();
+            sync();
+            if (tid == 0) {
+                xchg_pairs_done(p, step, n_empty, n_pairs);
             }
         }
     };
     if (x0 >= x1) {
         grid_dependency_wait(); // outputs may still be in use by the previous kernel on the stream
-        write_empty_pairs();
+        write_empty_pairs([] { __syncthreads(); });
         return; // exiting counts as this CTA's launch_dependents
     }
 
@@ -241,9 +317,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             if (sg.n <= 0) {
                 break; // inconsistent lengths: the consumers flag it
             }
-            const int seq_row = p.seq_ids ? p.seq_ids[sg.s] : sg.s;
-            const long long tbase = (long long)seq_row * p.table_stride + sg.j0;
-            const int pair_np = cum[sg.s + 1] - cum[sg.s];
+            const long long tbase = (long long)rows[sg.s] * p.table_stride + sg.j0;
+            // first page the kernel before this one on the stream may still be writing: the one holding token kv_len - 2
+            const int guard_page = (max(sg.kv_len, 2) - 2) / kPage;
             for (int base = 0; base < sg.n && !dead; base += kIssueLanes) {
                 // One page per lane: kIssueLanes lanes fetch their table entries in one coalesced read and each lane
                 // issues the copies of its own page, so the per-instruction latency of TMA issue is paid once
@@ -252,8 +328,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 // page order, so every wait ends. No more lanes than ring slots take part in a round: two lanes
                 // on one slot would wait for consecutive phases of the same barrier, and a parity wait cannot tell
                 // phase k + 1 from phase k - 1.
-                if (!waited && sg.j0 + min(base + kIssueLanes, sg.n) == pair_np) {
-                    grid_dependency_wait(); // this round reaches the sequence's last page: its newest rows come from the
+                if (!waited && sg.j0 + min(base + kIssueLanes, sg.n) > guard_page) {
+                    grid_dependency_wait(); // this round reaches the sequence's newest rows: they may come from the
                     waited = true;          // previous kernel on the stream (everything before it was there long ago)
                 }
                 const bool active = lane < kIssueLanes && base + lane < sg.n;
@@ -303,6 +379,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const uint32_t epi_ready = bars_u32 + 2 * kSlots * 8, epi_done = bars_u32 + (2 * kSlots + 1) * 8;
     if (warp == kEpilogueWarp) {
         grid_dependency_wait(); // counters and partials are shared with the previous launch
+        const uint32_t step = p.xchg.world > 0 ? xchg_step(p) : 0u;
         int k = 0; // cut segments handled so far
         while (cur.remaining > 0) {
             const Segment sg = next_segment(cur, cum, p);
@@ -333,10 +410,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             if (last) {
                 __threadfence(); // the other CTAs' partials are visible to the reads below
                 const float *first = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
-                warp_combine_partials<kBf16>(first, expected, p.group, lane, p.out, p.part,
-                                             (long long)sg.s * p.nh + sg.kvh * p.group);
+                warp_combine_partials<kBf16>(
+                    first, expected, p.group, lane, p.out, partial, [&](long long idx, float v) { put_part(p, step, idx, v); },
+                    (long long)sg.s * p.nh + sg.kvh * p.group);
+                if (p.xchg.world > 0) {
+                    __threadfence_system(); // every lane: its rows are at the peers before the pair is counted
+                    __syncwarp();
+                }
                 if (lane == 0) {
                     p.counters[pair] = 0; // ready for the next launch
+                    if (p.xchg.world > 0) {
+                        xchg_pairs_done(p, step, 1, n_pairs);
+                    }
                 }
             }
             __syncwarp();
@@ -363,7 +448,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     // Only now may the successor on the stream be scheduled: whatever starts early behind this grid can then rely on
     // everything BEFORE this grid's predecessor being complete (see the overlap contract in paged_kv.h).
     grid_launch_dependents();
-    write_empty_pairs();
+    if (p.xchg.world > 0 && tid == 0) {
+        s_step = xchg_step(p); // read by the others after the first barrier of the consumer warps
+    }
+    write_empty_pairs([] { named_barrier_sync(1, kConsumerThreads); });
     float m2[2], l[2], o_acc[8][4];
     uint32_t qf[8][2];
     auto reset_state = [&]() {
@@ -396,6 +484,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 qf[ks][1] = g < p.group ? q_row[ks * 8 + 4 + q4] : 0u;
             }
         }
+        // fused step: index in this segment of the pair's last page, which receives the new row; the warp that will
+        // take that page fetches the row (K: lanes 0-15, V: lanes 16-31, 16 bytes each) and the page index now
+        const int new_i = p.k_new != nullptr ? (cum[sg.s + 1] - cum[sg.s]) - 1 - sg.j0 : -1;
+        const bool brings_new = new_i >= 0 && new_i < sg.n && new_i % kConsumerWarps == warp;
+        const uint32_t my_stage = stage_u32 + warp * kStageBytes;
+        if (brings_new) {
+            const char *src = (lane < 16 ? p.k_new : p.v_new) + ((long long)sg.s * p.nkvh + sg.kvh) * (kD * 2) + (lane & 15) * 16;
+            cp_async_16(my_stage + lane * 16, src, 16);
+            if (lane == 0) {
+                const int32_t *entry = p.block_table + (long long)rows[sg.s] * p.table_stride + sg.j0 + new_i;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(my_stage + 512), "l"(entry) : "memory");
+            }
+            cp_async_commit();
+        }
 
         for (int i = warp; i < sg.n && !dead; i += kConsumerWarps) {
             const int n = n_base + i;
@@ -411,6 +513,28 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             }
             const uint32_t tile = ring_u32 + slot * kSlotBytes;
             const int n_valid = min(kPage, sg.kv_len - (sg.j0 + i) * kPage);
+            const bool patch = brings_new && i == new_i;
+            if (patch) {
+                // the new row: over slot n_valid - 1 of the tile (swizzled like the TMA copy) and into the page itself
+                cp_async_wait<0>();
+                __syncwarp();
+                const int r = n_valid - 1, cc = lane & 15;
+                uint32_t w0, w1, w2, w3;
+                int page;
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                             : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                             : "r"(my_stage + lane * 16));
+                asm volatile("ld.shared.s32 %0, [%1];\n" : "=r"(page) : "r"(my_stage + 512));
+                const uint32_t a = tile + (lane < 16 ? 0 : kQuarterBytes) + (cc >> 3) * kHalfBytes + r * 128 +
+                                   (((cc & 7) ^ (r & 7)) << 4);
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(a), "r"(w0), "r"(w1), "r"(w2), "r"(w3) : "memory");
+                if (page >= 0 && page < p.num_pages) { // (the producer has flagged a bad entry already)
+                    char *dst = p.pool_k + (long long)page * p.page_stride_b + (long long)sg.kvh * p.head_stride_b +
+                                (lane < 16 ? 0 : p.v_offset_b) + r * (kD * 2) + cc * 16;
+                    *reinterpret_cast<uint4 *>(dst) = make_uint4(w0, w1, w2, w3);
+                }
+                __syncwarp();
+            }
             if (n_valid < kPage) {
                 // Rows past the sequence's end hold whatever the page held before. K rows are neutralised by the
                 // score mask; V rows are cleared here so that 0 * garbage cannot make a NaN.
@@ -473,8 +597,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 mma_16816<kBf16>(o_acc[mt], a, b0, b1);
             }
             // hand the slot back: every lane's reads are done once the warp has converged here
-            if (n_valid < kPage) {
-                fence_proxy_async_smem(); // the cleared rows were ordinary stores; the next writer is the TMA unit
+            if (n_valid < kPage || patch) {
+                fence_proxy_async_smem(); // the cleared / new rows were ordinary stores; the next writer is the TMA unit
             }
             __syncwarp();
             if (lane == 0) {
@@ -540,11 +664,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             if (expected == 1) {
                 const long long row = row0 + h;
                 const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-                if (p.part != nullptr) {
-                    p.part[row * (kD + 2) + dim] = o * inv;
+                if (partial) {
+                    const uint32_t step = p.xchg.world > 0 ? s_step : 0u;
+                    put_part(p, step, row * (kD + 2) + dim, o * inv);
                     if (dim == 0) {
-                        p.part[row * (kD + 2) + kD] = m_all * 0.6931471805599453f; // log2 units -> natural log
-                        p.part[row * (kD + 2) + kD + 1] = l_all;
+                        put_part(p, step, row * (kD + 2) + kD, m_all * 0.6931471805599453f); // log2 units -> natural log
+                        put_part(p, step, row * (kD + 2) + kD + 1, l_all);
                     }
                 } else {
                     store_out<kBf16>(p.out, row * kD + dim, o * inv);
@@ -573,8 +698,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             ++n_cut;
         }
         reset_state();
+        const bool whole_pair_sent = p.xchg.world > 0 && expected == 1;
+        if (whole_pair_sent) {
+            __threadfence_system(); // this thread's rows are at the peers before the pair is counted
+        }
         // red_o / red_ml are next written after this pair's readers have passed the barrier below
         named_barrier_sync(1, kConsumerThreads);
+        if (whole_pair_sent && tid == 0) {
+            xchg_pairs_done(p, s_step, 1, n_pairs);
+        }
     }
 }
 
@@ -601,7 +733,7 @@ EncodeTiledFn encode_tiled_fn() {
 size_t smem_bytes(int group, int n_seqs) {
     return 1024 + size_t(kRingBytes) + size_t(kConsumerWarps) * group * kD * sizeof(float) +
            size_t(kConsumerWarps) * kMaxGroup * 2 * sizeof(float) + (2 * kSlots + 2) * sizeof(uint64_t) +
-           size_t(n_seqs + 1) * sizeof(int);
+           size_t(2 * n_seqs + 1) * sizeof(int) + 16 + size_t(kConsumerWarps) * kStageBytes;
 }
 
 template <bool kBf16>
@@ -669,21 +801,50 @@ int make_kv_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows
 }
 
 int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
-                         const void *q, float scale, const AttnOut &out, const AttnScratch &scratch) {
+                         const void *q, float scale, const AttnOut &out, const AttnScratch &scratch, const void *k_new,
+                         const void *v_new, const char **why) {
+    const char *dummy = nullptr;
+    const char *&reason = why != nullptr ? *why : dummy;
     const bool bf16 = dtype == LLAISYS_DTYPE_BF16;
-    if (kv.tma_desc == nullptr || !(bf16 || dtype == LLAISYS_DTYPE_F16) || kv.d != kD || kv.page_size != kPage ||
-        kv.nkvh <= 0 || kv.block_table == nullptr || batch.kv_lens == nullptr || batch.nh % kv.nkvh != 0 ||
-        batch.nh / kv.nkvh > kMaxGroup || batch.q_starts != nullptr || batch.const_q_len != 1 || batch.n_seqs <= 0 ||
-        batch.n_seqs > kMaxSeqs || reinterpret_cast<uintptr_t>(q) % 4 != 0) {
+    if (!(bf16 || dtype == LLAISYS_DTYPE_F16) || kv.d != kD || kv.page_size != kPage || kv.nkvh <= 0 ||
+        batch.nh % kv.nkvh != 0 || batch.nh / kv.nkvh > kMaxGroup || batch.q_starts != nullptr || batch.const_q_len != 1) {
+        reason = "needs 16-bit K/V, head_dim 128, 16-token pages, at most 8 query heads per kv head, one query per sequence";
+        return -1;
+    }
+    if (kv.tma_desc == nullptr || kv.block_table == nullptr || batch.kv_lens == nullptr) {
+        reason = "the pool carries no tensor map (the driver could not encode one), or block table / lengths are missing";
+        return -1;
+    }
+    if (batch.n_seqs <= 0 || batch.n_seqs > kMaxSeqs) {
+        reason = "more than 1024 sequences in one call: split the batch";
+        return -1;
+    }
+    if (reinterpret_cast<uintptr_t>(q) % 4 != 0) {
+        reason = "q is not 4-byte aligned";
+        return -1;
+    }
+    if ((k_new == nullptr) != (v_new == nullptr) || reinterpret_cast<uintptr_t>(k_new) % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(v_new) % 16 != 0) {
+        reason = "the new K/V rows of a fused step must both be given and be 16-byte aligned";
         return -1;
     }
     const int group = batch.nh / kv.nkvh;
-    // decode_grid_size caps at two CTAs per SM; this kernel may be built with one
-    const int two_per_sm = decode_grid_size(1 << 20, 1, 1 << 20);
-    const int grid = min(decode_grid_size(batch.n_seqs, kv.nkvh, batch.max_kv_len), two_per_sm / 2 * kCtasPerSm);
+    const int grid = decode_grid_size(batch.n_seqs, kv.nkvh, batch.max_kv_len);
     const size_t n_pairs = size_t(batch.n_seqs) * kv.nkvh;
     if (scratch.partials == nullptr || scratch.counters == nullptr || scratch.error_flag == nullptr ||
         scratch.partials_floats < (size_t(grid) + n_pairs) * group * kPartStride || scratch.counters_len < n_pairs) {
+        reason = "split-KV scratch missing or too small for this batch";
+        return -1;
+    }
+    if (out.peers != nullptr) {
+        const PeerSink &x = *out.peers;
+        if (out.out != nullptr || out.part != nullptr || x.world < 1 || x.world > kMaxXchg || x.rank < 0 || x.rank >= x.world ||
+            size_t(batch.n_seqs) * batch.nh * (kD + 2) > x.slot_floats) {
+            reason = "exchange slots: bad rank / world size, rows do not fit a slot, or another output was given too";
+            return -1;
+        }
+    } else if ((out.out != nullptr) == (out.part != nullptr)) {
+        reason = "exactly one of out and part must be given";
         return -1;
     }
     TmaDecodeParams p;
@@ -705,6 +866,16 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
     p.partials = scratch.partials;
     p.counters = scratch.counters;
     p.error_flag = scratch.error_flag;
+    p.k_new = static_cast<const char *>(k_new);
+    p.v_new = static_cast<const char *>(v_new);
+    p.pool_k = static_cast<char *>(kv.k_base);
+    p.page_stride_b = kv.page_stride * 2;
+    p.head_stride_b = kv.head_stride * 2;
+    p.v_offset_b = static_cast<char *>(kv.v_base) - static_cast<char *>(kv.k_base);
+    p.xchg = PeerSink{};
+    if (out.peers != nullptr) {
+        p.xchg = *out.peers;
+    }
     CUtensorMap tmap;
     memcpy(&tmap, kv.tma_desc, sizeof(tmap));
     const size_t smem = smem_bytes(group, batch.n_seqs);

@@ -105,9 +105,11 @@ __device__ __forceinline__ void combine_partials(const float *first, int expecte
 // a microsecond, so a round keeps kParts parts x kHeads heads of 16-byte loads in flight per lane (the common cut,
 // 2-4 pieces per pair, merges in ONE round trip); the (m, l) scalars of a round are loaded one per lane and
 // broadcast with shuffles instead of occupying kParts * kHeads more registers.
-template <bool kBf16, int kHeads, int kParts>
+// The result goes to `out` (rows of the K/V dtype) or, when partial is set, through put_part(index, value) into rows of
+// d + 2 floats (o, m, l): a plain array, or the exchange slots of a KV-range split.
+template <bool kBf16, int kHeads, int kParts, typename PutPart>
 __device__ __forceinline__ void warp_combine_impl(const float *first, int expected, int group, int lane, void *out,
-                                                  float *part, long long out_row0) {
+                                                  bool partial, PutPart put_part, long long out_row0) {
     constexpr int kD = 128, kStride = kD + 4, kOutStride = kD + 2;
     static_assert(kHeads * kParts <= 32, "one (m, l) pair per lane per round");
     float m_run[kHeads], l_run[kHeads];
@@ -172,14 +174,14 @@ __device__ __forceinline__ void warp_combine_impl(const float *first, int expect
             const long long row = out_row0 + h;
             const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
             const float r[4] = {o_run[h].x * inv, o_run[h].y * inv, o_run[h].z * inv, o_run[h].w * inv};
-            if (part != nullptr) {
+            if (partial) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    part[row * kOutStride + lane * 4 + e] = r[e];
+                    put_part(row * kOutStride + lane * 4 + e, r[e]);
                 }
                 if (lane == 0) {
-                    part[row * kOutStride + kD] = m_run[h] * 0.6931471805599453f; // log2 units -> natural log
-                    part[row * kOutStride + kD + 1] = l_run[h];
+                    put_part(row * kOutStride + kD, m_run[h] * 0.6931471805599453f); // log2 units -> natural log
+                    put_part(row * kOutStride + kD + 1, l_run[h]);
                 }
             } else {
 #pragma unroll
@@ -191,15 +193,15 @@ __device__ __forceinline__ void warp_combine_impl(const float *first, int expect
     }
 }
 
-template <bool kBf16>
+template <bool kBf16, typename PutPart>
 __device__ __forceinline__ void warp_combine_partials(const float *first, int expected, int group, int lane, void *out,
-                                                      float *part, long long out_row0) {
+                                                      bool partial, PutPart put_part, long long out_row0) {
     if (group <= 4) {
-        warp_combine_impl<kBf16, 4, 4>(first, expected, group, lane, out, part, out_row0);
+        warp_combine_impl<kBf16, 4, 4>(first, expected, group, lane, out, partial, put_part, out_row0);
     } else if (group <= 6) {
-        warp_combine_impl<kBf16, 6, 4>(first, expected, group, lane, out, part, out_row0);
+        warp_combine_impl<kBf16, 6, 4>(first, expected, group, lane, out, partial, put_part, out_row0);
     } else {
-        warp_combine_impl<kBf16, 8, 2>(first, expected, group, lane, out, part, out_row0);
+        warp_combine_impl<kBf16, 8, 2>(first, expected, group, lane, out, partial, put_part, out_row0);
     }
 }
 

@@ -3,6 +3,8 @@
 #include "device_utils.cuh"
 #include "kernels.hpp"
 
+#include <cuda.h>
+
 namespace llaisys::kernels {
 
 namespace {
@@ -37,13 +39,44 @@ void advance_decode_state(stream_t stream, int64_t *tokens, const int64_t *next,
     check_launch("advance_decode_state");
 }
 
-const void *mapped_host_alias(const void *host_ptr) {
-    cudaPointerAttributes attr;
-    if (host_ptr == nullptr || cudaPointerGetAttributes(&attr, host_ptr) != cudaSuccess) {
+const void *mapped_host_alias(const void *host_ptr, size_t bytes) {
+    cudaPointerAttributes first, last;
+    if (host_ptr == nullptr || bytes == 0 || cudaPointerGetAttributes(&first, host_ptr) != cudaSuccess ||
+        first.type != cudaMemoryTypeHost || first.devicePointer == nullptr) {
         (void)cudaGetLastError();
         return nullptr;
     }
-    return attr.type == cudaMemoryTypeHost ? attr.devicePointer : nullptr;
+    // the end of the buffer must be mapped too, at the matching device address
+    const char *end = static_cast<const char *>(host_ptr) + (bytes - 1);
+    if (cudaPointerGetAttributes(&last, end) != cudaSuccess || last.type != cudaMemoryTypeHost ||
+        static_cast<const char *>(last.devicePointer) - static_cast<const char *>(first.devicePointer) !=
+            ptrdiff_t(bytes - 1)) {
+        (void)cudaGetLastError();
+        return nullptr;
+    }
+    // and both ends must belong to ONE allocation: a buffer that starts in one pinned block and runs on into another
+    // would cross whatever lies between them
+    using RangeFn = CUresult (*)(CUdeviceptr *, size_t *, CUdeviceptr);
+    static const RangeFn range = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &res) != cudaSuccess ||
+            res != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            return RangeFn(nullptr);
+        }
+        return reinterpret_cast<RangeFn>(sym);
+    }();
+    if (range == nullptr) {
+        return nullptr;
+    }
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    const CUdeviceptr dptr = reinterpret_cast<CUdeviceptr>(first.devicePointer);
+    if (range(&base, &size, dptr) != CUDA_SUCCESS || dptr < base || dptr - base + bytes > size) {
+        return nullptr;
+    }
+    return first.devicePointer;
 }
 
 void graph_capture_begin(stream_t stream) {

@@ -13,7 +13,11 @@ void fill_zero(stream_t stream, void *ptr, size_t bytes);
 // The address under which kernels of the current device can read a host buffer directly: non-null only for page-locked
 // host memory that is mapped into the device's address space (what cudaHostAlloc / cudaMallocHost and torch's pinned
 // tensors give); null for pageable memory, for device memory and on any error.
-const void *mapped_host_alias(const void *host_ptr);
+// All `bytes` bytes from host_ptr on must lie inside one such allocation.
+const void *mapped_host_alias(const void *host_ptr, size_t bytes);
+// Up to three plain copies (each a 16-byte aligned multiple of 16 bytes) done by ONE kernel launch: for small blocks in
+// mapped host memory, where a kernel's loads start sooner than a copy-engine transfer is set up.
+void small_copies(stream_t stream, const void *const *src, void *const *dst, const size_t *bytes, int n);
 
 // c = a + b over n contiguous elements of F32 / F16 / BF16 (arithmetic in f32).
 void add(stream_t stream, llaisysDataType_t dtype, void *c, const void *a, const void *b, size_t n);
@@ -35,6 +39,8 @@ void linear(stream_t stream, llaisysDataType_t dtype, void *out, const void *in,
 // N a multiple of 64, not vocabulary-sized). False = shape not covered, nothing launched. overlap: programmatic launch
 // (the weight stream starts under the previous kernel's tail). linear_tc_status synchronises the stream and returns (and
 // clears) the kernel's error word: 0, or 16 when a bounded wait ran out.
+// 0 = the streaming kernel where it measured faster (default), 1 = wherever it applies, 2 = never. False: unknown value.
+bool set_linear_policy(int policy);
 bool linear_tc(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, size_t m, size_t n,
                size_t k, bool accumulate, bool overlap);
 int linear_tc_status(stream_t stream);
@@ -98,9 +104,12 @@ void attention_decode_split_scratch(int32_t n_seqs, int32_t nh, int32_t nkvh, in
 int decode_grid_size(int32_t n_seqs, int32_t nkvh, int32_t max_kv_len);
 
 // TMA edition of K2 + K3 for page pools that carry a tensor map (KVView::tma_desc). Same contract and scratch
-// as attention_decode_split; returns -1 if the view or shape is not covered.
+// as attention_decode_split. k_new / v_new (both or neither; [n_seqs, nkvh, 128], 16-byte aligned): fused step -- row i
+// is also appended as token kv_lens[i] - 1 of sequence i by the same launch. Returns -1 and sets *why (a static string)
+// if the view or shape is not covered; nothing is queued then.
 int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
-                         const void *q, float scale, const AttnOut &out, const AttnScratch &scratch);
+                         const void *q, float scale, const AttnOut &out, const AttnScratch &scratch,
+                         const void *k_new = nullptr, const void *v_new = nullptr, const char **why = nullptr);
 // Encodes the tensor map over a 16-bit page pool (head_dim 128, page 16) starting at pool_base into out_128_bytes
 // (host memory): total_rows rows of 128 elements, nkvh of them per (page, K|V) block of 16 slots each. Returns -1
 // when the driver cannot provide one (the cp.async kernel is used then).

@@ -7,6 +7,7 @@
 #include "device_utils.cuh"
 #include "kernels.hpp"
 
+#include <atomic>
 #include <cstdlib>
 #include <string>
 
@@ -67,7 +68,17 @@ cublasHandle_t handle_for_current_device() {
     return h;
 }
 
+std::atomic<int> g_linear_policy{0};
+
 } // namespace
+
+bool set_linear_policy(int policy) {
+    if (policy < 0 || policy > 2) {
+        return false;
+    }
+    g_linear_policy.store(policy, std::memory_order_relaxed);
+    return true;
+}
 
 void linear(stream_t stream, llaisysDataType_t dtype, void *out, const void *in, const void *weight, const void *bias,
             size_t m, size_t n, size_t k, bool accumulate) {
@@ -78,10 +89,9 @@ void linear(stream_t stream, llaisysDataType_t dtype, void *out, const void *in,
     // (graph replays, weights rotated beyond L2): it wins where the activations are a small fraction of the traffic and K is
     // long enough to split over a cluster (8 x 8960 -> 1536: 12.5 vs 17.2 us); at 64 rows every CTA re-reads the
     // activations from L2 and cuBLAS's paired-CTA kernels are faster (64 x 1536 -> 17920: 16.5 vs 11.8 us), so those stay
-    // with the library. LLAISYS_LINEAR_PATH=tc forces the kernel wherever it applies, =cublas never uses it.
-    const char *path = std::getenv("LLAISYS_LINEAR_PATH");
-    const bool force_tc = path != nullptr && std::string(path) == "tc";
-    const bool never_tc = path != nullptr && std::string(path) == "cublas";
+    // with the library. set_linear_policy(1) takes the kernel wherever it applies, (2) never.
+    const int policy = g_linear_policy.load(std::memory_order_relaxed);
+    const bool force_tc = policy == 1, never_tc = policy == 2;
     const bool prefer_tc = m <= 16 && k >= 4096;
     if (!never_tc && (force_tc || prefer_tc) && m <= 128 &&
         linear_tc(stream, dtype, out, in, weight, m, n, k, accumulate, false)) {

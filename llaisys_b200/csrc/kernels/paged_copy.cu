@@ -41,36 +41,69 @@ __device__ __forceinline__ bool resolve_slot(const int32_t *__restrict__ table, 
     return true;
 }
 
-// One warp per new row. The row's slot is resolved once (the three dependent loads -- sequence id, position, table
-// entry -- are the same for the whole row), then lane l moves 16-byte piece l of the K row and of the V row: with 2
-// kv-heads of 128 16-bit dims a row of K is 512 B, one coalesced warp-wide read, written as two 256 B head-rows.
-__global__ void paged_append_kernel(uint4 *__restrict__ k_pool, uint4 *__restrict__ v_pool,
-                                    const uint4 *__restrict__ k_rows, const uint4 *__restrict__ v_rows,
-                                    const int32_t *__restrict__ table, const int32_t *__restrict__ seq_ids,
-                                    const int32_t *__restrict__ positions, CopyGeom g, int32_t n_rows,
-                                    int32_t max_blocks, int32_t *error_flag, const uint4 *__restrict__ side_src,
-                                    uint4 *__restrict__ side_dst, int32_t side_vecs) {
+// One warp per new row, kRows rows per warp and pass. A row is moved by lane l as 16-byte piece l (+ 32, ...) of the K
+// row and of the V row: with 2 kv-heads of 128 16-bit dims a row of K is 512 B, one coalesced warp-wide read, written as
+// two 256 B head-rows. What bounds the kernel is latency, not bytes: a row's slot takes three dependent loads (sequence
+// id and position, then the table entry), and with one row per warp in flight that chain -- not the 2 KiB moved -- set
+// the pace (63 % of the copy rate). So a pass first issues the index loads AND the data loads of all its rows, which do
+// not depend on the slots, then resolves the slots, then stores: kRows KiB of reads in flight per warp while the index
+// chain runs underneath.
+template <int kRows, int kIters>
+__global__ void __launch_bounds__(256)
+    paged_append_kernel(uint4 *__restrict__ k_pool, uint4 *__restrict__ v_pool, const uint4 *__restrict__ k_rows,
+                        const uint4 *__restrict__ v_rows, const int32_t *__restrict__ table,
+                        const int32_t *__restrict__ seq_ids, const int32_t *__restrict__ positions, CopyGeom g,
+                        int32_t n_rows, int32_t max_blocks, int32_t *error_flag, const uint4 *__restrict__ side_src,
+                        uint4 *__restrict__ side_dst, int32_t side_vecs) {
     // Under a programmatic launch this grid may start early: let the next kernel do the same, then wait for the
     // previous one (it may still be reading the pages this grid writes).
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
-    const int32_t vecs_per_row = g.vecs_per_head_row * g.nkvh; // per K (or V) row
+    const int32_t vecs_per_row = g.vecs_per_head_row * g.nkvh; // per K (or V) row; at most 32 * kIters
     const int lane = threadIdx.x & 31;
     const int32_t warps = int32_t((gridDim.x * blockDim.x) >> 5);
-    for (int32_t row = int32_t((blockIdx.x * blockDim.x + threadIdx.x) >> 5); row < n_rows; row += warps) {
-        int32_t page, slot;
-        if (!resolve_slot(table, g, seq_ids[row], positions[row], max_blocks, error_flag, page, slot)) {
-            continue;
+    const int32_t warp_id = int32_t((blockIdx.x * blockDim.x + threadIdx.x) >> 5);
+    for (int32_t row0 = warp_id; row0 < n_rows; row0 += kRows * warps) {
+        int32_t seq[kRows], pos[kRows];
+        uint4 kd[kRows][kIters], vd[kRows][kIters];
+#pragma unroll
+        for (int u = 0; u < kRows; ++u) {
+            const int32_t row = row0 + u * warps;
+            seq[u] = row < n_rows ? seq_ids[row] : -1;
+            pos[u] = row < n_rows ? positions[row] : 0;
         }
-        const int64_t slot_vec = (int64_t(page) * g.page_stride_b + int64_t(slot) * g.token_stride_b) / 16;
-        for (int32_t in_row = lane; in_row < vecs_per_row; in_row += 32) {
-            const int32_t kvh = in_row / g.vecs_per_head_row;
-            const int32_t vec = in_row - kvh * g.vecs_per_head_row;
-            const int64_t dst = slot_vec + int64_t(kvh) * (g.head_stride_b / 16) + vec;
-            const int64_t src = int64_t(row) * vecs_per_row + in_row;
-            const uint4 kv = k_rows[src], vv = v_rows[src];
-            k_pool[dst] = kv;
-            v_pool[dst] = vv;
+#pragma unroll
+        for (int u = 0; u < kRows; ++u) {
+            const int32_t row = row0 + u * warps;
+#pragma unroll
+            for (int it = 0; it < kIters; ++it) {
+                const int32_t in_row = lane + 32 * it;
+                if (row < n_rows && in_row < vecs_per_row) {
+                    const int64_t src = int64_t(row) * vecs_per_row + in_row;
+                    kd[u][it] = __ldcs(k_rows + src); // read once: do not keep in cache
+                    vd[u][it] = __ldcs(v_rows + src);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kRows; ++u) {
+            const int32_t row = row0 + u * warps;
+            int32_t page, slot;
+            if (row >= n_rows || !resolve_slot(table, g, seq[u], pos[u], max_blocks, error_flag, page, slot)) {
+                continue;
+            }
+            const int64_t slot_vec = (int64_t(page) * g.page_stride_b + int64_t(slot) * g.token_stride_b) / 16;
+#pragma unroll
+            for (int it = 0; it < kIters; ++it) {
+                const int32_t in_row = lane + 32 * it;
+                if (in_row < vecs_per_row) {
+                    const int32_t kvh = in_row / g.vecs_per_head_row;
+                    const int32_t vec = in_row - kvh * g.vecs_per_head_row;
+                    const int64_t dst = slot_vec + int64_t(kvh) * (g.head_stride_b / 16) + vec;
+                    k_pool[dst] = kd[u][it];
+                    v_pool[dst] = vd[u][it];
+                }
+            }
         }
     }
     // An unrelated plain copy riding on this launch (the host step's q rows, read from mapped host memory): four
@@ -89,6 +122,23 @@ __global__ void paged_append_kernel(uint4 *__restrict__ k_pool, uint4 *__restric
             if (i + u * threads < side_vecs) {
                 side_dst[i + u * threads] = val[u];
             }
+        }
+    }
+}
+
+// Plain copies of up to three small blocks (multiples of 16 bytes) in one launch: the host step's index arrays and q
+// rows, read from mapped host memory -- a kernel's loads start sooner than a copy-engine transfer is set up.
+struct CopyList {
+    const uint4 *src[3];
+    uint4 *dst[3];
+    int32_t vecs[3];
+};
+__global__ void small_copies_kernel(CopyList l) {
+    const int32_t threads = int32_t(gridDim.x * blockDim.x), me = int32_t(blockIdx.x * blockDim.x + threadIdx.x);
+#pragma unroll
+    for (int b = 0; b < 3; ++b) {
+        for (int32_t i = me; i < l.vecs[b]; i += threads) {
+            l.dst[b][i] = l.src[b][i];
         }
     }
 }
@@ -305,9 +355,13 @@ void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const voi
     }
     CHECK_ARGUMENT(side_bytes % 16 == 0 && side_bytes / 16 < size_t(INT32_MAX), "paged append: side copy size");
     const CopyGeom g = make_geom(kv, elem_size);
+    const int32_t vecs_per_row = g.vecs_per_head_row * g.nkvh;
+    CHECK_ARGUMENT(vecs_per_row <= 256, "paged append: a K row of more than 4 KiB is not supported");
     const int block = 256;
-    // one warp per row; with a side copy, also enough threads for four of its vectors each
-    const int grid = grid_for(std::max<int64_t>(int64_t(n_rows) * 32, int64_t(side_bytes / 64)), block);
+    // a warp per row while that fills the GPU; from there on 2, then 4 rows per warp and pass
+    const int64_t full = int64_t(148) * 8 * (block / 32);
+    const int rows_per_warp = n_rows >= 4 * full ? 4 : (n_rows >= 2 * full ? 2 : 1);
+    const int grid = grid_for(std::max<int64_t>(int64_t(n_rows + rows_per_warp - 1) / rows_per_warp * 32, int64_t(side_bytes / 64)), block);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(grid));
     cfg.blockDim = dim3(unsigned(block));
@@ -317,12 +371,43 @@ void paged_append(stream_t stream, size_t elem_size, const KVView &kv, const voi
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = kv.overlap_launch ? 1 : 0;
-    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_append_kernel, static_cast<uint4 *>(kv.k_base),
-                                          static_cast<uint4 *>(kv.v_base), static_cast<const uint4 *>(k_rows),
-                                          static_cast<const uint4 *>(v_rows), kv.block_table, seq_ids, positions, g, n_rows,
-                                          max_blocks, error_flag, static_cast<const uint4 *>(side_src),
-                                          static_cast<uint4 *>(side_dst), int32_t(side_bytes / 16)));
+    auto go = [&](auto kernel) {
+        LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, static_cast<uint4 *>(kv.k_base), static_cast<uint4 *>(kv.v_base),
+                                              static_cast<const uint4 *>(k_rows), static_cast<const uint4 *>(v_rows),
+                                              kv.block_table, seq_ids, positions, g, n_rows, max_blocks, error_flag,
+                                              static_cast<const uint4 *>(side_src), static_cast<uint4 *>(side_dst),
+                                              int32_t(side_bytes / 16)));
+    };
+    if (vecs_per_row <= 32) {
+        rows_per_warp == 4 ? go(paged_append_kernel<4, 1>) : rows_per_warp == 2 ? go(paged_append_kernel<2, 1>)
+                                                                               : go(paged_append_kernel<1, 1>);
+    } else if (vecs_per_row <= 64) {
+        rows_per_warp >= 2 ? go(paged_append_kernel<2, 2>) : go(paged_append_kernel<1, 2>);
+    } else {
+        go(paged_append_kernel<1, 8>);
+    }
     check_launch("paged_append");
+}
+
+void small_copies(stream_t stream, const void *const *src, void *const *dst, const size_t *bytes, int n) {
+    CHECK_ARGUMENT(n >= 0 && n <= 3, "small_copies: at most three blocks");
+    CopyList l{};
+    size_t most = 0;
+    for (int i = 0; i < n; ++i) {
+        CHECK_ARGUMENT(bytes[i] % 16 == 0 && bytes[i] / 16 < size_t(INT32_MAX) &&
+                           reinterpret_cast<uintptr_t>(src[i]) % 16 == 0 && reinterpret_cast<uintptr_t>(dst[i]) % 16 == 0,
+                       "small_copies: blocks must be 16-byte aligned multiples of 16 bytes");
+        l.src[i] = static_cast<const uint4 *>(src[i]);
+        l.dst[i] = static_cast<uint4 *>(dst[i]);
+        l.vecs[i] = int32_t(bytes[i] / 16);
+        most = std::max(most, bytes[i] / 16);
+    }
+    if (most == 0) {
+        return;
+    }
+    const int block = 256;
+    small_copies_kernel<<<grid_for(int64_t(most), block), block, 0, static_cast<cudaStream_t>(stream)>>>(l);
+    check_launch("small_copies");
 }
 
 void paged_gather(stream_t stream, size_t elem_size, const KVView &kv, int32_t seq_row, int32_t n_tokens,

@@ -414,13 +414,8 @@ bool linear_tc(stream_t stream, llaisysDataType_t dtype, void *out, const void *
     }
     // few feature tiles: split K over a cluster until the grid fills the GPU
     const int chunks = int(k / kBK);
-    static const int max_split = [] {
-        const char *e = std::getenv("LLAISYS_GEMM_MAX_SPLIT"); // experiments: cap the cluster size
-        const int v = e ? std::atoi(e) : kMaxSplit;
-        return v < 1 ? 1 : (v > kMaxSplit ? kMaxSplit : v);
-    }();
     int split = sms / tiles;
-    split = split < 1 ? 1 : (split > max_split ? max_split : split);
+    split = split < 1 ? 1 : (split > kMaxSplit ? kMaxSplit : split);
     split = split > chunks ? chunks : split;
     GemmParams p;
     p.out = out;

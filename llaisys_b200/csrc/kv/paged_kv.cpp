@@ -34,6 +34,7 @@ template <typename... Args>
     } while (0)
 
 constexpr size_t kMaxInt32 = size_t(std::numeric_limits<int32_t>::max());
+constexpr size_t kMaxDecodeSeqs = 1024; // sequences per launch of the TMA decode kernel
 
 } // namespace
 
@@ -80,7 +81,27 @@ PagedKV::PagedKV(const PagedKVConfig &cfg) : _cfg(cfg) {
             _has_tma = kernels::make_kv_tensor_map(_tma_desc, _pool->memory(), rows, uint32_t(cfg.nkvh), cfg.dtype) == 0;
             _has_tma_tile =
                 kernels::make_kv_tile_tensor_map(_tma_tile_desc, _pool->memory(), rows, uint32_t(cfg.nkvh), cfg.dtype) == 0;
+            // These pools are served by the TMA decode kernel and the tcgen05 chunk kernel and by nothing else: a pool
+            // they cannot address is refused here, not quietly handed to a slower kernel later.
+            KV_REQUIRE(_has_tma && _has_tma_tile, LLAISYS_E_DEVICE,
+                       "paged KV: no TMA tensor map for this pool (cuTensorMapEncodeTiled unavailable, or more than 2^31 "
+                       "rows of 128 elements)");
+            // Workspace of both kernels, for the largest call this cache can take (a decode call is cut into launches
+            // of at most kMaxDecodeSeqs sequences; the chunk kernel's need does not depend on the batch).
+            size_t floats = 0, counters = 0, f2 = 0, c2 = 0;
+            const size_t seqs = std::min(cfg.max_seqs, kMaxDecodeSeqs);
+            kernels::attention_decode_split_scratch(int32_t(seqs), int32_t(8 * cfg.nkvh), int32_t(cfg.nkvh), 128,
+                                                    int32_t(cfg.page_size * cfg.max_pages_per_seq), &floats, &counters);
+            kernels::attention_prefill_tc_scratch(&f2, &c2);
+            _partials_floats = std::max(floats, f2);
+            _counters_len = std::max(counters, c2);
+            _partials = rt.allocateDeviceStorage(_partials_floats * sizeof(float));
+            _counters = rt.allocateDeviceStorage(_counters_len * sizeof(int32_t));
+            kernels::fill_zero(rt.stream(), _counters->memory(), _counters->size());
+            rt.synchronize();
         }
+        // index arrays of the host-buffer step are written here and read by a kernel: page-locked, mapped memory
+        _host_stage = rt.allocateHostStorage((3 * cfg.max_seqs * sizeof(int32_t) + 15) / 16 * 16);
 #endif
     } else {
         std::memset(_pool->memory(), 0, _pool->size());
@@ -481,42 +502,13 @@ int32_t *PagedKV::stage(const int32_t *const *arrays, const size_t *lens, size_t
     return dev;
 }
 
-kernels::AttnScratch PagedKV::scratchFor(size_t n_seqs, size_t nh, size_t max_kv_len, bool chunks) {
+kernels::AttnScratch PagedKV::scratch() const {
     kernels::AttnScratch sc;
     sc.error_flag = reinterpret_cast<int32_t *>(_error_dev->memory());
-#ifdef ENABLE_NVIDIA_API
-    if (onDevice()) {
-        size_t floats = 0, counters = 0;
-        if (chunks) {
-            // the tensor-core chunk kernel splits long tiles over CTAs: fixed workspace, whatever the batch
-            if (_cfg.head_dim == 128 && _elem == 2) {
-                kernels::attention_prefill_tc_scratch(&floats, &counters);
-            }
-        } else {
-            kernels::attention_decode_split_scratch(int32_t(n_seqs), int32_t(nh), int32_t(_cfg.nkvh),
-                                                    int32_t(_cfg.head_dim), int32_t(max_kv_len), &floats, &counters);
-        }
-        auto &rt = enter();
-        if (floats > _partials_floats) {
-            _partials_floats = floats;
-            _partials = rt.allocateDeviceStorage(floats * sizeof(float));
-        }
-        if (counters > _counters_len) {
-            _counters_len = counters;
-            _counters = rt.allocateDeviceStorage(counters * sizeof(int32_t));
-            kernels::fill_zero(rt.stream(), _counters->memory(), _counters->size());
-            rt.synchronize(); // the next launch may be on a caller's stream
-        }
-        sc.partials = _partials ? reinterpret_cast<float *>(_partials->memory()) : nullptr;
-        sc.partials_floats = _partials_floats;
-        sc.counters = _counters ? reinterpret_cast<int32_t *>(_counters->memory()) : nullptr;
-        sc.counters_len = _counters_len;
-    }
-#else
-    (void)n_seqs;
-    (void)nh;
-    (void)max_kv_len;
-#endif
+    sc.partials = _partials ? reinterpret_cast<float *>(_partials->memory()) : nullptr;
+    sc.partials_floats = _partials_floats;
+    sc.counters = _counters ? reinterpret_cast<int32_t *>(_counters->memory()) : nullptr;
+    sc.counters_len = _counters_len;
     return sc;
 }
 
@@ -587,31 +579,107 @@ void PagedKV::decodeDev(size_t layer, void *out, float *part, const void *q, con
     }
     KV_REQUIRE((out != nullptr) != (part != nullptr), LLAISYS_E_INVALID, "paged attention: exactly one output");
     KV_REQUIRE(q && seq_ids_dev && kv_lens_dev, LLAISYS_E_INVALID, "paged attention: null argument");
-    const kernels::KVView v = view(layer);
-    kernels::AttnBatch b;
-    b.seq_ids = seq_ids_dev;
-    b.kv_lens = kv_lens_dev;
-    b.const_q_len = 1;
-    b.n_seqs = int32_t(n_seqs);
-    b.total_q = int32_t(n_seqs);
-    b.max_q_len = 1;
-    b.max_kv_len = int32_t(max_kv_len);
-    b.nh = int32_t(nh);
-    kernels::AttnOut o;
-    o.out = out;
-    o.part = part;
-    if (!onDevice()) {
-        const int err = cpu::attention(_cfg.dtype, v, b, q, scale, o);
-        *reinterpret_cast<int32_t *>(_error_dev->memory()) |= err;
+    launchDecode(layer, out, part, q, nullptr, nullptr, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale, stream,
+                 _overlap);
+}
+
+void PagedKV::decodeStepDev(size_t layer, void *out, const void *q, const void *k_new, const void *v_new,
+                            const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len,
+                            size_t nh, float scale, llaisysStream_t stream) {
+    checkLayer(layer);
+    KV_REQUIRE(nh > 0 && nh % _cfg.nkvh == 0, LLAISYS_E_INVALID, "paged decode step: nh = ", nh,
+               " is not a multiple of nkvh = ", _cfg.nkvh);
+    KV_REQUIRE(n_seqs <= kMaxInt32 && max_kv_len <= _cfg.page_size * _cfg.max_pages_per_seq, LLAISYS_E_INVALID,
+               "paged decode step: batch or context too large for this cache");
+    if (n_seqs == 0) {
         return;
     }
+    KV_REQUIRE(out && q && k_new && v_new && seq_ids_dev && kv_lens_dev, LLAISYS_E_INVALID,
+               "paged decode step: null argument");
+    if (!onDevice()) {
+        // host memory: the arrays can be read here
+        std::vector<int32_t> pos(n_seqs);
+        for (size_t i = 0; i < n_seqs; ++i) {
+            pos[i] = kv_lens_dev[i] - 1;
+        }
+        appendDev(layer, k_new, v_new, seq_ids_dev, pos.data(), n_seqs, nullptr);
+        decodeDev(layer, out, nullptr, q, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale, nullptr);
+        return;
+    }
+    KV_REQUIRE(fastShape() && nh / _cfg.nkvh <= 8, LLAISYS_E_UNSUPPORTED,
+               "paged decode step: the one-launch step needs a 16-bit pool with head_dim 128, 16-token pages and at most 8 "
+               "query heads per kv head; use llaisysPagedKVAppendDev + llaisysPagedAttentionDecodeDev");
+    launchDecode(layer, out, nullptr, q, k_new, v_new, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale, stream,
+                 _overlap);
+}
+
+void PagedKV::decodeSplitDev(size_t layer, const void *q, const int32_t *seq_ids_dev, const int32_t *kv_lens_dev,
+                             size_t n_seqs, size_t max_kv_len, size_t nh, float scale, const kernels::PeerSink &peers,
+                             llaisysStream_t stream) {
+    checkLayer(layer);
+    KV_REQUIRE(nh > 0 && nh % _cfg.nkvh == 0, LLAISYS_E_INVALID, "split decode: nh = ", nh, " is not a multiple of nkvh = ",
+               _cfg.nkvh);
+    KV_REQUIRE(n_seqs >= 1 && n_seqs <= kMaxDecodeSeqs && max_kv_len <= _cfg.page_size * _cfg.max_pages_per_seq,
+               LLAISYS_E_INVALID, "split decode: 1 to 1024 sequences per call, context within the cache's tables");
+    KV_REQUIRE(q && seq_ids_dev && kv_lens_dev, LLAISYS_E_INVALID, "split decode: null argument");
+    KV_REQUIRE(onDevice() && fastShape() && nh / _cfg.nkvh <= 8, LLAISYS_E_UNSUPPORTED,
+               "split decode with the exchange in the kernel needs a 16-bit device pool, head_dim 128, 16-token pages");
+    launchDecode(layer, nullptr, nullptr, q, nullptr, nullptr, seq_ids_dev, kv_lens_dev, n_seqs, max_kv_len, nh, scale, stream,
+                 _overlap, &peers);
+}
+
+// The decode kernel for one call, cut into launches of at most kMaxDecodeSeqs sequences (they share the workspace and
+// run in stream order). k_new / v_new non-null: fused step.
+void PagedKV::launchDecode(size_t layer, void *out, float *part, const void *q, const void *k_new, const void *v_new,
+                           const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len,
+                           size_t nh, float scale, llaisysStream_t stream, bool overlap, const kernels::PeerSink *peers) {
+    kernels::KVView v = view(layer);
+    v.overlap_launch = overlap;
+    const size_t d = _cfg.head_dim;
+    for (size_t at = 0; at < n_seqs; at += kMaxDecodeSeqs) {
+        kernels::AttnBatch b;
+        b.seq_ids = seq_ids_dev + at;
+        b.kv_lens = kv_lens_dev + at;
+        b.const_q_len = 1;
+        b.n_seqs = int32_t(std::min(kMaxDecodeSeqs, n_seqs - at));
+        b.total_q = b.n_seqs;
+        b.max_q_len = 1;
+        b.max_kv_len = int32_t(max_kv_len);
+        b.nh = int32_t(nh);
+        kernels::AttnOut o;
+        o.out = out ? static_cast<std::byte *>(out) + at * nh * d * _elem : nullptr;
+        o.part = part ? part + at * nh * (d + 2) : nullptr;
+        o.peers = peers;
+        const std::byte *q_at = static_cast<const std::byte *>(q) + at * nh * d * _elem;
+        if (!onDevice()) {
+            const int err = cpu::attention(_cfg.dtype, v, b, q_at, scale, o);
+            *reinterpret_cast<int32_t *>(_error_dev->memory()) |= err;
+            _last_kernel = LLAISYS_KERNEL_CPU;
+            noteAttentionKernel(_last_kernel);
+            continue;
+        }
 #ifdef ENABLE_NVIDIA_API
-    const kernels::AttnScratch sc = scratchFor(n_seqs, nh, max_kv_len);
-    run_attention_nvidia(stream, _cfg.dtype, v, b, q, scale, o, sc);
+        enter();
+        if (k_new != nullptr) {
+            const size_t row_bytes = _cfg.nkvh * d * _elem;
+            const char *why = nullptr;
+            if (kernels::attention_decode_tma(stream, _cfg.dtype, v, b, q_at, scale, o, scratch(),
+                                              static_cast<const std::byte *>(k_new) + at * row_bytes,
+                                              static_cast<const std::byte *>(v_new) + at * row_bytes, &why) != 0) {
+                fail(LLAISYS_E_UNSUPPORTED, "paged decode step (TMA kernel): ", why ? why : "call not covered");
+            }
+            _last_kernel = LLAISYS_KERNEL_DECODE_TMA_FUSED;
+            noteAttentionKernel(_last_kernel);
+        } else {
+            _last_kernel = run_attention_nvidia(stream, _cfg.dtype, v, b, q_at, scale, o, scratch());
+        }
 #else
-    (void)stream;
-    fail(LLAISYS_E_UNSUPPORTED, "this build has no NVIDIA backend");
+        (void)stream;
+        (void)k_new;
+        (void)v_new;
+        fail(LLAISYS_E_UNSUPPORTED, "this build has no NVIDIA backend");
 #endif
+    }
 }
 
 void PagedKV::prefillDev(size_t layer, void *out, const void *q, const int32_t *seq_ids_dev,
@@ -642,11 +710,13 @@ void PagedKV::prefillDev(size_t layer, void *out, const void *q, const int32_t *
     if (!onDevice()) {
         const int err = cpu::attention(_cfg.dtype, v, b, q, scale, o);
         *reinterpret_cast<int32_t *>(_error_dev->memory()) |= err;
+        _last_kernel = LLAISYS_KERNEL_CPU;
+        noteAttentionKernel(_last_kernel);
         return;
     }
 #ifdef ENABLE_NVIDIA_API
-    const kernels::AttnScratch sc = scratchFor(n_seqs, nh, max_kv_len, true);
-    run_attention_nvidia(stream, _cfg.dtype, v, b, q, scale, o, sc);
+    enter();
+    _last_kernel = run_attention_nvidia(stream, _cfg.dtype, v, b, q, scale, o, scratch());
 #else
     (void)stream;
     fail(LLAISYS_E_UNSUPPORTED, "this build has no NVIDIA backend");
@@ -739,15 +809,24 @@ void PagedKV::decodeStepHost(size_t layer, void *out_host, const void *q_host, c
                "paged decode step: null argument");
     KV_REQUIRE(nh > 0 && nh % _cfg.nkvh == 0, LLAISYS_E_INVALID, "paged attention: nh = ", nh,
                " is not a multiple of nkvh = ", _cfg.nkvh);
-    KV_REQUIRE(n_seqs <= kMaxInt32, LLAISYS_E_INVALID, "paged decode step: too many sequences");
+    KV_REQUIRE(n_seqs <= _cfg.max_seqs, LLAISYS_E_INVALID, "paged decode step: more rows than the cache has sequences");
     size_t max_kv = 0;
     std::vector<int32_t> &pos = _step_positions;
     pos.resize(n_seqs);
+    _seen_mark.resize(_cfg.max_seqs, 0);
+    if (++_seen_epoch == 0) { // wrapped: forget every mark
+        std::fill(_seen_mark.begin(), _seen_mark.end(), 0u);
+        _seen_epoch = 1;
+    }
     for (size_t i = 0; i < n_seqs; ++i) {
         const Seq &s = liveSeq(seq_ids[i]);
         KV_REQUIRE(kv_lens[i] >= 1 && size_t(kv_lens[i]) <= size_t(s.n_pages) * _cfg.page_size, LLAISYS_E_INVALID,
                    "paged decode step: kv_len ", kv_lens[i], " is outside the ", s.n_pages,
                    " page(s) reserved for sequence ", seq_ids[i]);
+        // two rows of one sequence would be written to the same slot by different warps
+        KV_REQUIRE(_seen_mark[size_t(seq_ids[i])] != _seen_epoch, LLAISYS_E_INVALID, "paged decode step: sequence ",
+                   seq_ids[i], " appears twice in one step");
+        _seen_mark[size_t(seq_ids[i])] = _seen_epoch;
         pos[i] = kv_lens[i] - 1;
         max_kv = std::max(max_kv, size_t(kv_lens[i]));
     }
@@ -765,55 +844,67 @@ void PagedKV::decodeStepHost(size_t layer, void *out_host, const void *q_host, c
         _step_dev = rt.allocateDeviceStorage(_step_cap);
     }
     std::byte *q_d = _step_dev->memory(), *out_d = q_d + q_bytes, *k_d = out_d + q_bytes, *v_d = k_d + kv_bytes;
+    const auto *api = rt.api();
+    llaisysStream_t stream = rt.stream();
+#ifdef ENABLE_NVIDIA_API
+    if (fastShape() && nh / _cfg.nkvh <= 8) {
+        // Two launches and no copy-engine transfer when the caller's buffers are page-locked and mapped (each small
+        // copy costs more in set-up than in transfer): a copy kernel brings the index arrays and q to the device --
+        // q is read by every CTA that works on its sequence, so it is not left in host memory -- then the one-launch
+        // step reads each new K/V row once, straight from the caller's memory, and stores each output row once,
+        // straight into it.
+        const size_t idx_bytes = (2 * n_seqs * sizeof(int32_t) + 15) / 16 * 16;
+        if (idx_bytes / sizeof(int32_t) > _meta_cap) {
+            _meta_cap = std::max<size_t>(idx_bytes / sizeof(int32_t) * 2, 1024);
+            _meta_dev = rt.allocateDeviceStorage(_meta_cap * sizeof(int32_t));
+        }
+        auto *idx_host = reinterpret_cast<int32_t *>(_host_stage->memory()); // free: the previous step has synchronised
+        std::memcpy(idx_host, seq_ids, n_seqs * sizeof(int32_t));
+        std::memcpy(idx_host + n_seqs, kv_lens, n_seqs * sizeof(int32_t));
+        auto *idx = reinterpret_cast<int32_t *>(_meta_dev->memory());
+        const void *q_alias = kernels::mapped_host_alias(q_host, q_bytes);
+        const void *k_alias = kernels::mapped_host_alias(k_new_host, kv_bytes);
+        const void *v_alias = kernels::mapped_host_alias(v_new_host, kv_bytes);
+        const void *out_alias = kernels::mapped_host_alias(out_host, q_bytes);
+        const void *idx_alias = kernels::mapped_host_alias(idx_host, idx_bytes);
+        auto aligned = [](const void *p) { return p != nullptr && reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+        const void *k_src = k_d, *v_src = v_d;
+        if (aligned(k_alias) && aligned(v_alias)) {
+            k_src = k_alias;
+            v_src = v_alias;
+        } else {
+            api->memcpy_async(k_d, k_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
+            api->memcpy_async(v_d, v_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
+        }
+        if (aligned(q_alias) && aligned(idx_alias) && q_bytes % 16 == 0) {
+            const void *src[2] = {idx_alias, q_alias};
+            void *dst[2] = {idx, q_d};
+            const size_t bytes[2] = {idx_bytes, q_bytes};
+            kernels::small_copies(stream, src, dst, bytes, 2);
+        } else {
+            api->memcpy_async(idx, idx_host, idx_bytes, LLAISYS_MEMCPY_H2D, stream);
+            api->memcpy_async(q_d, q_host, q_bytes, LLAISYS_MEMCPY_H2D, stream);
+        }
+        void *out_dst = aligned(out_alias) ? const_cast<void *>(out_alias) : out_d;
+        // a plain launch: the kernel reads the index arrays before any wait, and they come from the launch just before it
+        launchDecode(layer, out_dst, nullptr, q_d, k_src, v_src, idx, idx + n_seqs, n_seqs, max_kv, nh, scale, stream, false);
+        if (out_dst == out_d) {
+            api->memcpy_async(out_host, out_d, q_bytes, LLAISYS_MEMCPY_D2H, stream);
+        }
+        api->stream_synchronize(stream);
+        return;
+    }
+#endif
+    // every other pool (f32, other head dims or page sizes): plain copies, the append kernel, the generic attention kernel
     const int32_t *arrays[3] = {seq_ids, pos.data(), kv_lens};
     const size_t lens[3] = {n_seqs, n_seqs, n_seqs};
     int32_t *idx = stage(arrays, lens, 3);
-    const auto *api = rt.api();
-    llaisysStream_t stream = rt.stream();
-    // The new K/V rows are read exactly once, a row per warp: when the caller's buffers are page-locked and mapped the
-    // append kernel takes them straight from host memory and two of the step's five copies go away (each costs more in
-    // latency than its 32 KiB do in transfer). q is read by every CTA that works on its sequence, so it is copied --
-    // by the append launch as well when it is mapped too.
-    const void *k_src = k_d, *v_src = v_d;
-#ifdef ENABLE_NVIDIA_API
-    const void *k_alias = kernels::mapped_host_alias(k_new_host), *v_alias = kernels::mapped_host_alias(v_new_host);
-    if (k_alias != nullptr && v_alias != nullptr && reinterpret_cast<uintptr_t>(k_alias) % 16 == 0 &&
-        reinterpret_cast<uintptr_t>(v_alias) % 16 == 0) {
-        k_src = k_alias;
-        v_src = v_alias;
-    }
-#endif
-    if (k_src == k_d) {
-        api->memcpy_async(k_d, k_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
-        api->memcpy_async(v_d, v_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
-    }
-    bool q_rides = false; // q copied by the append launch itself, from mapped host memory
-#ifdef ENABLE_NVIDIA_API
-    const void *q_alias = k_src != k_d ? kernels::mapped_host_alias(q_host) : nullptr;
-    if (q_alias != nullptr && q_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(q_alias) % 16 == 0) {
-        kernels::paged_append(stream, _elem, view(layer), k_src, v_src, idx, idx + n_seqs, int32_t(n_seqs),
-                              int32_t(_cfg.max_pages_per_seq), reinterpret_cast<int32_t *>(_error_dev->memory()), q_alias,
-                              q_d, q_bytes);
-        q_rides = true;
-    }
-#endif
-    if (!q_rides) {
-        api->memcpy_async(q_d, q_host, q_bytes, LLAISYS_MEMCPY_H2D, stream);
-        appendDev(layer, k_src, v_src, idx, idx + n_seqs, n_seqs, stream);
-    }
-    // Every output row is written once, 16 bytes per thread: into the caller's buffer directly when it is mapped
-    void *out_dst = out_d;
-#ifdef ENABLE_NVIDIA_API
-    if (const void *out_alias = kernels::mapped_host_alias(out_host)) {
-        if (reinterpret_cast<uintptr_t>(out_alias) % 16 == 0) {
-            out_dst = const_cast<void *>(out_alias);
-        }
-    }
-#endif
-    decodeDev(layer, out_dst, nullptr, q_d, idx, idx + 2 * n_seqs, n_seqs, max_kv, nh, scale, stream);
-    if (out_dst == out_d) {
-        api->memcpy_async(out_host, out_d, q_bytes, LLAISYS_MEMCPY_D2H, stream);
-    }
+    api->memcpy_async(k_d, k_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
+    api->memcpy_async(v_d, v_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
+    api->memcpy_async(q_d, q_host, q_bytes, LLAISYS_MEMCPY_H2D, stream);
+    appendDev(layer, k_d, v_d, idx, idx + n_seqs, n_seqs, stream);
+    decodeDev(layer, out_d, nullptr, q_d, idx, idx + 2 * n_seqs, n_seqs, max_kv, nh, scale, stream);
+    api->memcpy_async(out_host, out_d, q_bytes, LLAISYS_MEMCPY_D2H, stream);
     api->stream_synchronize(stream);
 }
 
@@ -853,37 +944,59 @@ void PagedKV::prefill(size_t layer, void *out, const void *q, const int32_t *seq
 
 // ---- kernel choice on NVIDIA ------------------------------------------------------------------------
 
+namespace {
+thread_local int g_last_attention_kernel = LLAISYS_KERNEL_NONE;
+} // namespace
+
+int lastAttentionKernel() { return g_last_attention_kernel; }
+void noteAttentionKernel(int id) { g_last_attention_kernel = id; }
+
 #ifdef ENABLE_NVIDIA_API
-void run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const kernels::KVView &view,
-                          const kernels::AttnBatch &batch, const void *q, float scale, const kernels::AttnOut &out,
-                          const kernels::AttnScratch &scratch) {
+namespace {
+// The shapes the specialised kernels are written for: 16-bit K/V, head_dim 128, 16-token pages, at most 8 query
+// heads per kv head. Inside this domain a kernel that cannot take a call makes the call fail; it never hands the
+// call to the generic kernel behind the caller's back.
+bool fast_shape(llaisysDataType_t dtype, const kernels::KVView &view, const kernels::AttnBatch &batch) {
+    return (dtype == LLAISYS_DTYPE_BF16 || dtype == LLAISYS_DTYPE_F16) && view.d == 128 && view.page_size == 16 &&
+           view.nkvh > 0 && batch.nh % view.nkvh == 0 && batch.nh / view.nkvh <= 8;
+}
+} // namespace
+
+int run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const kernels::KVView &view,
+                         const kernels::AttnBatch &batch, const void *q, float scale, const kernels::AttnOut &out,
+                         const kernels::AttnScratch &scratch) {
     const bool one_query_each = batch.q_starts == nullptr && batch.const_q_len == 1;
-    if (one_query_each && scratch.counters != nullptr) {
-        // LLAISYS_DECODE_PATH=cp_async keeps page pools on the cp.async kernel (for A/B measurements)
-        static const bool allow_tma = [] {
-            const char *e = std::getenv("LLAISYS_DECODE_PATH");
-            return !(e != nullptr && std::string(e) == "cp_async");
-        }();
-        if (allow_tma && kernels::attention_decode_tma(stream, dtype, view, batch, q, scale, out, scratch) == 0) {
-            return;
+    const bool fast = fast_shape(dtype, view, batch);
+    int used = LLAISYS_KERNEL_GENERIC;
+    if (fast && one_query_each && view.block_table != nullptr && batch.kv_lens != nullptr) {
+        // a page pool: the TMA kernel, or nothing
+        const char *why = nullptr;
+        if (kernels::attention_decode_tma(stream, dtype, view, batch, q, scale, out, scratch, nullptr, nullptr, &why) != 0) {
+            fail(LLAISYS_E_UNSUPPORTED, "paged decode attention (TMA kernel): ", why ? why : "call not covered");
         }
-        if (kernels::attention_decode_split(stream, dtype, view, batch, q, scale, out, scratch) == 0) {
-            return;
+        used = LLAISYS_KERNEL_DECODE_TMA;
+    } else if (fast && one_query_each) {
+        // one query over plain K/V tensors (the legacy operator): the cp.async split-KV kernel
+        if (kernels::attention_decode_split(stream, dtype, view, batch, q, scale, out, scratch) != 0) {
+            fail(LLAISYS_E_UNSUPPORTED, "decode attention (cp.async kernel): K/V, q or the scratch are not 16-byte aligned, "
+                                        "or more than 1024 sequences");
         }
-    }
-    if (batch.q_starts != nullptr || (view.block_table == nullptr && batch.const_q_len >= 16)) {
+        used = LLAISYS_KERNEL_DECODE_CP_ASYNC;
+    } else if (fast && out.part == nullptr &&
+               (batch.q_starts != nullptr || (view.block_table == nullptr && batch.const_q_len >= 16))) {
         // chunks over a page pool, or the legacy operator's multi-token query over plain K/V tensors (from 16 rows on:
-        // below that the 128-row tensor-core tile is mostly padding). LLAISYS_PREFILL_PATH=generic keeps both on the
-        // generic kernel (for A/B measurements)
-        static const bool allow_tc = [] {
-            const char *e = std::getenv("LLAISYS_PREFILL_PATH");
-            return !(e != nullptr && std::string(e) == "generic");
-        }();
-        if (allow_tc && kernels::attention_prefill_tc(stream, dtype, view, batch, q, scale, out, scratch) == 0) {
-            return;
+        // below that the 128-row tensor-core tile is mostly padding and the generic kernel serves the call)
+        if (kernels::attention_prefill_tc(stream, dtype, view, batch, q, scale, out, scratch) != 0) {
+            fail(LLAISYS_E_UNSUPPORTED, "chunk attention (tcgen05 kernel): q, out or K/V are not 16-byte aligned, the pool "
+                                        "has no tensor map, or the workspace is missing");
         }
+        used = LLAISYS_KERNEL_PREFILL_TC;
+    } else {
+        // f32 data, other head dims, page sizes or group widths, and short multi-token queries of the legacy operator
+        kernels::attention_generic(stream, dtype, view, batch, q, scale, out, scratch.error_flag);
     }
-    kernels::attention_generic(stream, dtype, view, batch, q, scale, out, scratch.error_flag);
+    g_last_attention_kernel = used;
+    return used;
 }
 #endif
 

@@ -72,6 +72,8 @@ public:
     size_t layerBytes() const { return _layer_bytes; }
     const int32_t *blockTableData() const { return reinterpret_cast<const int32_t *>(_table_dev->memory()); }
     void setLaunchOverlap(bool enable) { _overlap = enable; }
+    // LLAISYS_KERNEL_* id of the kernel that served this cache's most recent attention call
+    int lastKernel() const { return _last_kernel; }
     void flush(); // queue uploads of the table rows that changed since the last flush
     void check(); // synchronise, throw LLAISYS_E_KERNEL if a kernel flagged bad metadata
 
@@ -98,6 +100,16 @@ public:
     void decodeDev(size_t layer, void *out, float *part, const void *q, const int32_t *seq_ids_dev,
                    const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len, size_t nh, float scale,
                    llaisysStream_t stream);
+    // One decode step in one launch: row i of k_new / v_new becomes token kv_lens[i] - 1 of sequence i, then attention of
+    // q[i] over the kv_lens[i] tokens. Device caches: 16-bit, head_dim 128, page 16 pools only (the TMA decode kernel).
+    void decodeStepDev(size_t layer, void *out, const void *q, const void *k_new, const void *v_new,
+                       const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len, size_t nh,
+                       float scale, llaisysStream_t stream);
+    // Partial decode of this cache's slice of a KV-range split, its rows stored by the decode kernel itself into slot
+    // `rank` of every rank's exchange buffer and this rank's flag stamped there when the last row is out. TMA pools only.
+    bool canPushPartials(size_t nh) const { return onDevice() && fastShape() && nh % _cfg.nkvh == 0 && nh / _cfg.nkvh <= 8; }
+    void decodeSplitDev(size_t layer, const void *q, const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
+                        size_t max_kv_len, size_t nh, float scale, const kernels::PeerSink &peers, llaisysStream_t stream);
     void prefillDev(size_t layer, void *out, const void *q, const int32_t *seq_ids_dev, const int32_t *q_starts_dev,
                     const int32_t *kv_lens_dev, size_t n_seqs, size_t total_q, size_t max_q_len, size_t max_kv_len,
                     size_t nh, float scale, llaisysStream_t stream);
@@ -130,7 +142,12 @@ private:
     kernels::KVView view(size_t layer) const;
     core::Runtime &enter() const;                   // make the cache's device current on this thread
     int32_t *stage(const int32_t *const *arrays, const size_t *lens, size_t n_arrays); // host arrays -> device
-    kernels::AttnScratch scratchFor(size_t n_seqs, size_t nh, size_t max_kv_len, bool chunks = false);
+    kernels::AttnScratch scratch() const;
+    // 16-bit, head_dim 128, 16-token pages on a device: the shapes the TMA decode and tcgen05 chunk kernels serve
+    bool fastShape() const { return _has_tma; }
+    void launchDecode(size_t layer, void *out, float *part, const void *q, const void *k_new, const void *v_new,
+                      const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len, size_t nh,
+                      float scale, llaisysStream_t stream, bool overlap, const kernels::PeerSink *peers = nullptr);
     bool onDevice() const { return _cfg.device_type != LLAISYS_DEVICE_CPU; }
 
     PagedKVConfig _cfg;
@@ -150,22 +167,33 @@ private:
     size_t _n_live = 0;
 
     // device memory (host memory for a CPU cache)
-    core::storage_t _pool, _table_dev, _error_dev, _meta_dev, _partials, _counters, _step_dev;
+    // _partials / _counters: split-KV and split-tile workspace of the attention kernels, sized for the largest call the
+    // cache can take and allocated ONCE, at construction: captured graphs keep pointing at it, and no data-path call with
+    // device index arrays ever allocates
+    core::storage_t _pool, _table_dev, _error_dev, _meta_dev, _partials, _counters, _step_dev, _host_stage;
     size_t _step_cap = 0;
     size_t _meta_cap = 0, _partials_floats = 0, _counters_len = 0;
     std::vector<int32_t> _stage_buf, _step_positions;
+    std::vector<uint32_t> _seen_mark; // per sequence: the step that last named it (duplicate check of the host step)
+    uint32_t _seen_epoch = 0;
 
     // TMA view of the pool (NVIDIA, 16-bit, head_dim 128, page 16 only); _has_tma is false otherwise
     alignas(64) unsigned char _tma_desc[128] = {};      // decode: box = K and V of a page
     alignas(64) unsigned char _tma_tile_desc[128] = {}; // prefill: box = one half-tile
     bool _has_tma = false, _has_tma_tile = false;
     bool _overlap = false; // launch append / decode with programmatic stream serialisation
+    int _last_kernel = 0;
 };
 
 // Picks the kernel for a batch on an NVIDIA device and queues it: split-KV decode or tensor-core prefill where
 // the shape allows, the generic kernel otherwise. `scratch` may be empty when the shape cannot use it.
-void run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const kernels::KVView &view,
-                          const kernels::AttnBatch &batch, const void *q, float scale, const kernels::AttnOut &out,
-                          const kernels::AttnScratch &scratch);
+// -> the LLAISYS_KERNEL_* id of the kernel queued. Inside the specialised kernels' domain (16-bit, head_dim 128, page 16,
+// group <= 8) a call the kernel cannot take throws LLAISYS_E_UNSUPPORTED with the reason; it is never re-routed.
+int run_attention_nvidia(llaisysStream_t stream, llaisysDataType_t dtype, const kernels::KVView &view,
+                         const kernels::AttnBatch &batch, const void *q, float scale, const kernels::AttnOut &out,
+                         const kernels::AttnScratch &scratch);
+// Kernel id of the calling thread's most recent attention call (any cache, or the legacy operator).
+int lastAttentionKernel();
+void noteAttentionKernel(int id);
 
 } // namespace llaisys::kv

@@ -170,7 +170,7 @@ void Qwen2::configureCache(size_t max_seqs, size_t max_tokens) {
     _cache = std::make_unique<kv::PagedKV>(cfg);
     // [bias + rope + append] -> decode attention run as a programmatic pair: the attention kernel's set-up and its copies
     // of older pages overlap the append (which writes each sequence's last page only, as the overlap contract asks)
-    _cache->setLaunchOverlap(_on_gpu && std::getenv("LLAISYS_MODEL_NO_OVERLAP") == nullptr);
+    _cache->setLaunchOverlap(_on_gpu);
     _max_tokens_per_seq = cfg.max_pages_per_seq * kPageSize;
     _seq_len.assign(max_seqs, kNotLive);
     _seq_tokens.assign(max_seqs, {});

@@ -9,6 +9,7 @@
 #ifdef ENABLE_NVIDIA_API
 #include "../kernels/kernels.hpp"
 #include "../kv/paged_kv.hpp"
+#include "llaisys/paged_kv.h"
 
 #include <map>
 #endif
@@ -160,6 +161,7 @@ void self_attention(tensor_t attn_val, tensor_t q, tensor_t k, tensor_t v, float
     switch (attn_val->deviceType()) {
     case LLAISYS_DEVICE_CPU:
         cpu::attention(q->dtype(), view, batch, q->data(), scale, out);
+        kv::noteAttentionKernel(LLAISYS_KERNEL_CPU);
         return;
 #ifdef ENABLE_NVIDIA_API
     case LLAISYS_DEVICE_NVIDIA: {

@@ -144,10 +144,22 @@ size_t Engine::step(Event *events, size_t cap) {
     _n_tokens.clear();
     _owner.clear();
     _tokens.clear();
+    // Both scans start one request further on every step: with a budget smaller than the number of running requests
+    // the ones that go without a token change from step to step, so every request keeps making progress.
+    // While a prompt is still being fed, a share of the budget (a chunk, at most half) is kept back for it: decoding
+    // requests alone can never take all of a small budget step after step.
     size_t budget = _cfg.max_tokens_per_step;
-    for (size_t i = 0; i < _running.size() && budget > 0; ++i) {
+    const size_t n_run = _running.size(), first = _steps % n_run;
+    const bool prompts_pending =
+        std::any_of(_running.begin(), _running.end(), [](const Request &r) { return r.fed < r.prompt.size(); });
+    const size_t kept_back = prompts_pending ? std::max<size_t>(1, std::min(_cfg.prefill_chunk, budget / 2)) : 0;
+    const size_t decode_budget = budget > kept_back ? budget - kept_back : (prompts_pending ? 0 : budget);
+    size_t decoded = 0;
+    for (size_t k = 0; k < n_run && decoded < decode_budget; ++k) {
+        const size_t i = (first + k) % n_run;
         Request &r = _running[i];
         if (r.fed == r.prompt.size()) {
+            ++decoded;
             _seq_ids.push_back(r.seq);
             _n_tokens.push_back(1);
             _owner.push_back(int32_t(i));
@@ -155,7 +167,8 @@ size_t Engine::step(Event *events, size_t cap) {
             --budget;
         }
     }
-    for (size_t i = 0; i < _running.size() && budget > 0; ++i) {
+    for (size_t k = 0; k < n_run && budget > 0; ++k) {
+        const size_t i = (first + k) % n_run;
         Request &r = _running[i];
         if (r.fed < r.prompt.size()) {
             const size_t n = std::min({_cfg.prefill_chunk, r.prompt.size() - r.fed, budget});

@@ -207,6 +207,14 @@ PROTOTYPES: dict[str, tuple] = {
     "llaisysPagedAttentionDecodeSplitDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                                     c_size_t, c_size_t, c_float, c_void_p, llaisysStream_t]),
     "llaisysPeerExchangeStatus": (c_int, [c_void_p, llaisysStream_t]),
+    "llaisysPeerExchangeSetWaitLimit": (c_int, [c_void_p, ctypes.c_uint32]),
+    "llaisysPeerExchangeDisconnect": (c_int, [c_void_p]),
+    "llaisysPagedDecodeStepDev": (c_int, [_KV, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_size_t, c_size_t, c_size_t, c_float, llaisysStream_t]),
+    "llaisysPagedKVLastKernel": (c_int, [_KV]),
+    "llaisysLastAttentionKernel": (c_int, []),
+    "llaisysPagedAttentionDecodeNoAllocStatus": (c_int, [c_int, llaisysStream_t, _I32P]),
+    "llaisysSetLinearPolicy": (c_int, [c_int]),
     # include/llaisys/models/qwen2.h
     "llaisysQwen2ModelCreate": (_MODEL, [POINTER(LlaisysQwen2Meta), llaisysDeviceType_t, POINTER(c_int), c_int]),
     "llaisysQwen2ModelDestroy": (None, [_MODEL]),

@@ -34,6 +34,13 @@ class Ops:
         LIB_LLAISYS.llaisysLinearAccumulate(_h(out), _h(inp), _h(weight))
 
     @staticmethod
+    def set_linear_policy(policy: int) -> None:
+        """Which kernel serves decode-sized projections on NVIDIA, process-wide: 0 = hand-written tcgen05 kernel where it
+        measured faster than cuBLAS (default), 1 = wherever its shape rules allow, 2 = always cuBLAS."""
+        if LIB_LLAISYS.llaisysSetLinearPolicy(policy) != 0:
+            raise ValueError(f"unknown linear policy {policy}")
+
+    @staticmethod
     def rearrange(out: Tensor, inp: Tensor) -> None:
         LIB_LLAISYS.llaisysRearrange(_h(out), _h(inp))
 

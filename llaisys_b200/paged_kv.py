@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import byref, c_int32
+from enum import IntEnum
 from typing import Sequence
 
 import numpy as np
@@ -17,6 +18,22 @@ from .libllaisys import LIB_LLAISYS, DataType, DeviceType, Status, llaisysPagedK
 from .runtime import _addr
 
 _I32P = ctypes.POINTER(c_int32)
+
+
+class Kernel(IntEnum):
+    """LLAISYS_KERNEL_* of include/llaisys/paged_kv.h: the kernel that served an attention call."""
+    NONE = 0
+    CPU = 1
+    GENERIC = 2
+    DECODE_TMA = 3
+    DECODE_TMA_FUSED = 4
+    DECODE_CP_ASYNC = 5
+    PREFILL_TC = 6
+
+
+def last_attention_kernel() -> Kernel:
+    """Kernel of the calling thread's most recent attention call (any cache, or Ops.self_attention)."""
+    return Kernel(LIB_LLAISYS.llaisysLastAttentionKernel())
 
 
 class LlaisysError(RuntimeError):
@@ -148,6 +165,10 @@ class PagedKVCache:
         """Opt in to programmatic dependent launch of append / decode (see llaisysPagedKVSetLaunchOverlap)."""
         _check(LIB_LLAISYS.llaisysPagedKVSetLaunchOverlap(self._kv, 1 if enable else 0))
 
+    def last_kernel(self) -> "Kernel":
+        """Which kernel served this cache's most recent attention call."""
+        return Kernel(LIB_LLAISYS.llaisysPagedKVLastKernel(self._kv))
+
     def flush(self) -> None:
         _check(LIB_LLAISYS.llaisysPagedKVFlush(self._kv))
 
@@ -219,6 +240,14 @@ class PagedKVCache:
         _check(LIB_LLAISYS.llaisysPagedAttentionDecodeDev(self._kv, layer, _addr(out), _addr(q), _addr(seq_ids_dev),
                                                           _addr(kv_lens_dev), n_seqs, max_kv_len, nh, scale, stream))
 
+    def decode_step_dev(self, layer: int, out, q, k_new, v_new, seq_ids_dev, kv_lens_dev, n_seqs: int, max_kv_len: int,
+                        nh: int, scale: float, stream) -> None:
+        """One decode step in one launch: k_new[i] / v_new[i] become token kv_lens[i] - 1 of sequence i, then attention of
+        q[i] over its kv_lens[i] tokens (device index arrays, explicit stream)."""
+        _check(LIB_LLAISYS.llaisysPagedDecodeStepDev(self._kv, layer, _addr(out), _addr(q), _addr(k_new), _addr(v_new),
+                                                     _addr(seq_ids_dev), _addr(kv_lens_dev), n_seqs, max_kv_len, nh, scale,
+                                                     stream))
+
     def decode_partial_dev(self, layer: int, part, q, seq_ids_dev, kv_lens_dev, n_seqs: int, max_kv_len: int,
                            nh: int, scale: float, stream) -> None:
         _check(LIB_LLAISYS.llaisysPagedAttentionDecodePartialDev(self._kv, layer, _addr(part), _addr(q),
@@ -253,3 +282,11 @@ def decode_no_alloc(out, q, pool_layer, block_table_dev, table_stride: int, num_
         device_id, _addr(out), _addr(q), _addr(pool_layer), _addr(block_table_dev), table_stride, num_pages,
         _addr(seq_ids_dev), _addr(kv_lens_dev), n_seqs, max_kv_len, nh, nkvh, int(dtype), scale,
         _addr(error_flag_dev), stream))
+
+
+def decode_no_alloc_status(device_id: int = 0, stream=None) -> int:
+    """Synchronises the stream and returns (and clears) the error bits that decode_no_alloc calls WITHOUT an error word
+    of their own have collected on the device: 0 = none, 1 = an out-of-range page index was skipped."""
+    flags = c_int32(0)
+    _check(LIB_LLAISYS.llaisysPagedAttentionDecodeNoAllocStatus(device_id, stream, byref(flags)))
+    return int(flags.value)

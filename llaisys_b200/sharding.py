@@ -79,12 +79,16 @@ class PeerExchange:
         from .paged_kv import _check
 
         self.group = group
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        # without a process group: a single rank exchanging with itself (the same kernels, one GPU)
+        self._solo = not (dist.is_available() and dist.is_initialized())
+        self.rank, self.world = (0, 1) if self._solo else (dist.get_rank(group), dist.get_world_size(group))
         slot = -(-max_rows * (head_dim + 2) // 4) * 4
         self._ex = ctypes.c_void_p()
         _check(LIB_LLAISYS.llaisysPeerExchangeCreate(ctypes.byref(self._ex), device_id, self.rank, self.world, slot))
         mine = ctypes.create_string_buffer(64)
         _check(LIB_LLAISYS.llaisysPeerExchangeHandle(self._ex, mine))
+        if self._solo:
+            return
         handles: list = [None] * self.world
         dist.all_gather_object(handles, mine.raw, group=group)
         _check(LIB_LLAISYS.llaisysPeerExchangeConnect(self._ex, ctypes.create_string_buffer(b"".join(handles), 64 * self.world)))
@@ -101,6 +105,19 @@ class PeerExchange:
                                                                _addr(kv_lens_dev), n_seqs, max_kv_len, nh, scale,
                                                                self._ex, stream))
 
+    def set_wait_limit(self, polls: int) -> None:
+        """Polls (about 0.2 us each) after which a merge stops waiting for a peer's rows; the default is about a second."""
+        from .libllaisys import LIB_LLAISYS
+        from .paged_kv import _check
+
+        _check(LIB_LLAISYS.llaisysPeerExchangeSetWaitLimit(self._ex, polls))
+
+    def status(self, stream) -> int:
+        """Synchronises the stream; 0, or 1 when a wait for a peer ran out since the last call (which clears it)."""
+        from .libllaisys import LIB_LLAISYS
+
+        return int(LIB_LLAISYS.llaisysPeerExchangeStatus(self._ex, stream))
+
     def check(self, stream) -> None:
         """Synchronises the stream and raises if a wait for a peer ran out."""
         from .libllaisys import LIB_LLAISYS
@@ -113,7 +130,10 @@ class PeerExchange:
         from .libllaisys import LIB_LLAISYS
 
         if getattr(self, "_ex", None):
-            dist.barrier(group=self.group)  # nobody unmaps while a peer may still write
+            if not self._solo:
+                dist.barrier(group=self.group)  # nobody unmaps while a peer may still write
+                LIB_LLAISYS.llaisysPeerExchangeDisconnect(self._ex)
+                dist.barrier(group=self.group)  # nobody releases its buffer while a peer still maps it
             LIB_LLAISYS.llaisysPeerExchangeDestroy(self._ex)
             self._ex = None
 

@@ -83,3 +83,19 @@ def lse_merge_f64(o: torch.Tensor, m: torch.Tensor, l: torch.Tensor) -> torch.Te
     tot = w.sum(dim=0)
     num = (w.unsqueeze(-1) * o).sum(dim=0)
     return torch.where(tot.unsqueeze(-1) > 0, num / tot.clamp_min(1e-300).unsqueeze(-1), torch.zeros_like(num))
+
+
+def decode_attention_f64_chunked(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                                 chunk: int = 16384) -> torch.Tensor:
+    """self_attention_f64 for ONE query over a very long context, in bounded memory: the keys are walked in ranges of
+    `chunk` tokens (partial_attention_f64) and the ranges merged (lse_merge_f64). q [1, nh, d] -> float64 [1, nh, d].
+    Equal to self_attention_f64 up to float64 rounding; the whole-context version would repeat K and V per query head
+    in float64 (3 GB at 131072 tokens)."""
+    assert q.size(0) == 1
+    os_, ms, ls = [], [], []
+    for lo in range(0, k.size(0), chunk):
+        o, m, l = partial_attention_f64(q, k[lo:lo + chunk], v[lo:lo + chunk], scale)
+        os_.append(o)
+        ms.append(m)
+        ls.append(l)
+    return lse_merge_f64(torch.stack(os_), torch.stack(ms), torch.stack(ls)).unsqueeze(0)

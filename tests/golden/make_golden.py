@@ -1,7 +1,7 @@
 """Generates tests/golden/self_attention_golden.npz from the REFERENCE's own oracle function.
 
 Run in a checkout that has the reference tree mounted:
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py <root of the reference tree>
 
 The reference defines the operator only as a PyTorch function inside its test file
 (test/ops/self_attention.py:11-28, `torch_self_attention`); that file imports the compiled llaisys package at
@@ -84,7 +84,9 @@ def cases():
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <root of the reference project's tree>")
+    ref_root = Path(sys.argv[1])
     reference = load_reference_function(ref_root)
     out: dict[str, np.ndarray] = {}
     names = []

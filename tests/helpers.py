@@ -10,6 +10,18 @@ import llaisys_b200 as llaisys
 
 GOLDEN = Path(__file__).with_name("golden") / "self_attention_golden.npz"
 
+
+def reference_root() -> Path | None:
+    """Where the reference project's tree is, if it is available: the directory named by LLAISYS_REFERENCE_ROOT, else a
+    checkout called `reference` beside this repository. None (the tests that need it are skipped) otherwise."""
+    import os
+
+    cands = [os.environ.get("LLAISYS_REFERENCE_ROOT"), Path(__file__).resolve().parents[2] / "reference"]
+    for c in cands:
+        if c and (Path(c) / "test" / "ops" / "self_attention.py").is_file():
+            return Path(c)
+    return None
+
 TORCH_DTYPE = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 LL_DTYPE = {"f32": llaisys.DataType.F32, "f16": llaisys.DataType.F16, "bf16": llaisys.DataType.BF16,
             "i64": llaisys.DataType.I64, "i32": llaisys.DataType.I32}

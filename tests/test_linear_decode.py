@@ -50,20 +50,20 @@ def test_decode_projections_cpu(dname):
 @pytest.mark.parametrize("path", ["tc", "default"])
 @pytest.mark.parametrize("dname", ["bf16", "f16", "f32"])
 @pytest.mark.parametrize("shape", MODEL_SHAPES + EDGE_SHAPES, ids=lambda s: "x".join(map(str, s)))
-def test_decode_projections_nvidia(cuda_device, monkeypatch, dname, shape, path):
-    """path "tc" forces the hand-written kernel wherever its shape rules allow (the library otherwise picks it only
+def test_decode_projections_nvidia(cuda_device, dname, shape, path):
+    """path "tc" takes the hand-written kernel wherever its shape rules allow (the library otherwise picks it only
     where it measured faster than cuBLAS); "default" is the routing a user gets."""
-    if path == "tc":
-        monkeypatch.setenv("LLAISYS_LINEAR_PATH", "tc")
-    else:
-        monkeypatch.delenv("LLAISYS_LINEAR_PATH", raising=False)
-    run_case(NVIDIA, dname, *shape)
+    llaisys.Ops.set_linear_policy(1 if path == "tc" else 0)
+    try:
+        run_case(NVIDIA, dname, *shape)
+    finally:
+        llaisys.Ops.set_linear_policy(0)
 
 
 @pytest.mark.gpu
-def test_decode_projection_is_deterministic_nvidia(cuda_device, monkeypatch):
+def test_decode_projection_is_deterministic_nvidia(cuda_device):
     """The cluster reduction adds the K splits in rank order: the same call twice gives the same bits."""
-    monkeypatch.setenv("LLAISYS_LINEAR_PATH", "tc")
+    llaisys.Ops.set_linear_policy(1)
     g = torch.Generator().manual_seed(3)
     x = torch.randn((64, 8960), generator=g).to(torch.bfloat16)
     w = (torch.randn((1536, 8960), generator=g) * 0.05).to(torch.bfloat16)
@@ -73,4 +73,5 @@ def test_decode_projection_is_deterministic_nvidia(cuda_device, monkeypatch):
         out = llaisys.Tensor((64, 1536), dtype=llaisys.DataType.BF16, device=NVIDIA)
         llaisys.Ops.linear(out, x_, w_, None)
         outs.append(helpers.tensor_words(helpers.from_llaisys(out, "bf16")))
+    llaisys.Ops.set_linear_policy(0)
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])

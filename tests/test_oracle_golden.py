@@ -9,7 +9,7 @@ from oracle import attention, workloads
 from tests import helpers
 from tests.golden import make_golden
 
-REFERENCE = Path("/root/reference")
+REFERENCE = helpers.reference_root()
 
 
 @pytest.mark.parametrize("name", helpers.golden_cases())
@@ -30,7 +30,7 @@ def test_oracle_matches_golden(name):
     assert helpers.max_abs(f64, expect) <= {"f32": 2e-6, "f16": 2e-3, "bf16": 1.6e-2}[dname]
 
 
-@pytest.mark.skipif(not REFERENCE.exists(), reason="reference tree not mounted")
+@pytest.mark.skipif(REFERENCE is None, reason="reference tree not available (set LLAISYS_REFERENCE_ROOT)")
 @pytest.mark.parametrize("dname", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("shape", [(2, 2, 1, 1, 4), (5, 11, 4, 2, 8), (1, 130, 12, 2, 128), (33, 70, 12, 2, 128)])
 def test_oracle_bit_equal_to_reference_function(shape, dname):

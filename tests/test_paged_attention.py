@@ -233,6 +233,187 @@ def test_decode_step_host_nvidia(cuda_device, pinned):
     check_decode_step_host(NVIDIA, pinned)
 
 
+def check_one_launch_step(device, lens, pool_pages=256, dname="bf16", nh=12, nkvh=2):
+    """llaisysPagedDecodeStepDev (append the step's row and attend, one launch on NVIDIA) must leave the pool and the
+    output exactly as llaisysPagedKVAppendDev + llaisysPagedAttentionDecodeDev do, and match the oracle."""
+    dev = helpers.torch_device(device)
+    dt = helpers.TORCH_DTYPE[dname]
+    g = torch.Generator().manual_seed(sum(lens) + len(lens))
+    perm = torch.randperm(pool_pages, generator=g).tolist()
+    pages, at = [], 0
+    for c in lens:
+        n = -(-c // 16)
+        pages.append(perm[at:at + n])
+        at += n
+    ks = [workloads.randn((c, nkvh, 128), dt, g) for c in lens]
+    vs = [workloads.randn((c, nkvh, 128), dt, g) for c in lens]
+    q = workloads.randn((len(lens), nh, 128), dt, g)
+    k_new = torch.stack([k[-1] for k in ks]).contiguous().to(dev)
+    v_new = torch.stack([v[-1] for v in vs]).contiguous().to(dev)
+    scale = 128 ** -0.5
+    results = []
+    for one_launch in (False, True):
+        cache, seqs = helpers.build_cache(device, dname, pages, num_pages=pool_pages, nkvh=nkvh, d=128)
+        helpers.append_all(cache, 0, seqs, ks, vs, device, hi=[c - 1 for c in lens])
+        cache.flush()
+        ids = torch.tensor(seqs, dtype=torch.int32, device=dev)
+        kv = torch.tensor(lens, dtype=torch.int32, device=dev)
+        out = torch.full(q.shape, float("nan"), dtype=dt, device=dev)
+        stream = llaisys.context_stream() if device == NVIDIA else None
+        if one_launch:
+            cache.decode_step_dev(0, out, q.to(dev), k_new, v_new, ids, kv, len(lens), max(lens), nh, scale, stream)
+            if device == NVIDIA:
+                assert cache.last_kernel() == llaisys.Kernel.DECODE_TMA_FUSED
+        else:
+            cache.append_dev(0, k_new, v_new, ids, kv - 1, len(lens), stream)
+            cache.decode_dev(0, out, q.to(dev), ids, kv, len(lens), max(lens), nh, scale, stream)
+        cache.check()
+        pool = torch.empty(cache.layer_bytes(), dtype=torch.uint8)
+        kind = llaisys.MemcpyKind.H2H if device == CPU else llaisys.MemcpyKind.D2H
+        llaisys.RuntimeAPI(device).memcpy_sync(pool.data_ptr(), cache.pool_ptr(0), pool.numel(), kind)
+        results.append((out.cpu(), pool))
+    assert torch.equal(results[0][1], results[1][1]), "the pool differs from append + decode"
+    assert torch.equal(helpers.tensor_words(results[0][0]), helpers.tensor_words(results[1][0]))
+    out = results[1][0]
+    for i, c in enumerate(lens):
+        expect = attention.self_attention(q[i:i + 1], ks[i], vs[i], scale)
+        assert helpers.max_abs(out[i:i + 1], expect) <= helpers.MAX_ABS[dname], (i, c)
+
+
+def test_one_launch_step_cpu():
+    check_one_launch_step(CPU, [1, 2, 16, 17, 40], pool_pages=32)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dname", ["bf16", "f16"])
+def test_one_launch_step_nvidia(cuda_device, dname):
+    """New rows in every slot position: the only token of a sequence, the last slot of a page, the first slot of a fresh
+    page; short and long sequences in one batch, so that several pairs end inside one CTA's span and long ones are cut."""
+    check_one_launch_step(NVIDIA, [1, 2, 15, 16, 17, 31, 32, 33, 300, 1000, 48, 1, 64, 65], dname=dname)
+    check_one_launch_step(NVIDIA, [2000, 5, 777], pool_pages=256, dname=dname, nh=16)
+    check_one_launch_step(NVIDIA, [33] * 40, pool_pages=256, dname=dname, nh=4, nkvh=4)
+
+
+@pytest.mark.gpu
+def test_one_launch_step_north_star_shape_nvidia(cuda_device):
+    """The shape the headline number is quoted on -- 64 sequences x 4096 tokens, 12/2 heads, bf16, all 16384 pages of the
+    pool in a random permutation -- through the one-launch step, against the oracle: every output row within 2e-2 and
+    one output ulp of the float64 result, the appended rows bit-exact, and the kernel the TMA decode kernel."""
+    g = torch.Generator().manual_seed(64)
+    n, ctx = 64, 4096
+    perm = torch.randperm(workloads.POOL_PAGES, generator=g).tolist()
+    pages = [perm[i * 256:(i + 1) * 256] for i in range(n)]
+    ks = [workloads.randn((ctx, 2, 128), torch.bfloat16, g) for _ in range(n)]
+    vs = [workloads.randn((ctx, 2, 128), torch.bfloat16, g) for _ in range(n)]
+    q = workloads.randn((n, 12, 128), torch.bfloat16, g)
+    cache, seqs = helpers.build_cache(NVIDIA, "bf16", pages, num_pages=workloads.POOL_PAGES, nkvh=2, d=128)
+    helpers.append_all(cache, 0, seqs, ks, vs, NVIDIA, hi=[ctx - 1] * n)
+    cache.flush()
+    ids = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    kv = torch.full((n,), ctx, dtype=torch.int32, device="cuda")
+    out = torch.full(q.shape, float("nan"), dtype=torch.bfloat16, device="cuda")
+    k_new = torch.stack([k[-1] for k in ks]).cuda()
+    v_new = torch.stack([v[-1] for v in vs]).cuda()
+    scale = 128 ** -0.5
+    cache.decode_step_dev(0, out, q.cuda(), k_new, v_new, ids, kv, n, ctx, 12, scale, llaisys.context_stream())
+    cache.check()
+    assert cache.last_kernel() == llaisys.Kernel.DECODE_TMA_FUSED
+    out = out.cpu()
+    for i in range(n):
+        expect = attention.self_attention(q[i:i + 1], ks[i], vs[i], scale)
+        assert helpers.max_abs(out[i:i + 1], expect) <= helpers.MAX_ABS["bf16"], i
+        f64 = attention.self_attention_f64(q[i:i + 1], ks[i], vs[i], scale)
+        assert helpers.max_abs(out[i:i + 1], f64) <= 8e-3 * max(1.0, f64.abs().max().item()), i
+    for i in (0, 31, 63):
+        k_out = torch.empty_like(ks[i], device="cuda")
+        v_out = torch.empty_like(vs[i], device="cuda")
+        cache.gather(0, seqs[i], ctx, k_out, v_out)
+        cache.check()
+        assert torch.equal(helpers.tensor_words(k_out.cpu()), helpers.tensor_words(ks[i]))
+        assert torch.equal(helpers.tensor_words(v_out.cpu()), helpers.tensor_words(vs[i]))
+    # the plain decode call on the same cache: same kernel without the append, same bits
+    again = torch.empty_like(q, device="cuda")
+    cache.decode_dev(0, again, q.cuda(), ids, kv, n, ctx, 12, scale, llaisys.context_stream())
+    cache.check()
+    assert cache.last_kernel() == llaisys.Kernel.DECODE_TMA
+    assert torch.equal(helpers.tensor_words(again.cpu()), helpers.tensor_words(out))
+
+
+@pytest.mark.gpu
+def test_one_long_sequence_131072_tokens_nvidia(cuda_device):
+    """One layer of the long-context configuration on one GPU: a single 131072-token sequence (8192 pages), decode and
+    partial decode against the float64 oracle (walked in key ranges to bound its memory)."""
+    g = torch.Generator().manual_seed(131072)
+    total = 131072
+    k = workloads.randn((total, 2, 128), torch.bfloat16, g)
+    v = workloads.randn((total, 2, 128), torch.bfloat16, g)
+    q = workloads.randn((1, 12, 128), torch.bfloat16, g)
+    cache = llaisys.PagedKVCache(total // 16, 2, 128, dtype=llaisys.DataType.BF16, device=NVIDIA, max_seqs=1,
+                                 max_pages_per_seq=total // 16)
+    s = cache.add_seq()
+    cache.assign_pages(s, torch.randperm(total // 16, generator=g).tolist())
+    helpers.append_all(cache, 0, [s], [k], [v], NVIDIA)
+    out = torch.empty_like(q, device="cuda")
+    scale = 128 ** -0.5
+    cache.decode(0, out, q.cuda(), [s], [total], 12, scale)
+    cache.check()
+    assert cache.last_kernel() == llaisys.Kernel.DECODE_TMA
+    f64 = attention.decode_attention_f64_chunked(q, k, v, scale)
+    assert helpers.max_abs(out.cpu(), f64) <= 8e-3 * max(1.0, f64.abs().max().item())
+
+
+@pytest.mark.gpu
+def test_back_to_back_one_launch_steps_with_launch_overlap_nvidia(cuda_device):
+    """Twenty one-launch steps queued without any host synchronisation, programmatic dependent launch on, on ONE layer:
+    step t + 1 reads the row step t wrote, sometimes in the same page and sometimes (lengths cross several page
+    boundaries) in the page before its own last one. Every step must match the oracle."""
+    steps, nseq = 20, 6
+    batch = workloads.decode_batch(nseq, 60, 900, seed=71, pool_pages=512)
+    cache, seqs = helpers.build_cache(NVIDIA, "bf16", [p for p in batch.pages], num_pages=512, nkvh=2, d=128)
+    cache.set_launch_overlap(True)
+    start = [c - steps for c in batch.ctx]
+    helpers.append_all(cache, 0, seqs, batch.k, batch.v, NVIDIA, hi=start)
+    cache.flush()
+    stream = llaisys.context_stream()
+    ids = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    g = torch.Generator().manual_seed(72)
+    qs = [workloads.randn((nseq, 12, 128), torch.bfloat16, g) for _ in range(steps)]
+    len_dev = [torch.tensor([st + t + 1 for st in start], dtype=torch.int32, device="cuda") for t in range(steps)]
+    k_new = [torch.stack([batch.k[i][start[i] + t] for i in range(nseq)]).cuda() for t in range(steps)]
+    v_new = [torch.stack([batch.v[i][start[i] + t] for i in range(nseq)]).cuda() for t in range(steps)]
+    q_dev = [q.cuda() for q in qs]
+    outs = [torch.full((nseq, 12, 128), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(steps)]
+    torch.cuda.synchronize()
+    for t in range(steps):
+        cache.decode_step_dev(0, outs[t], q_dev[t], k_new[t], v_new[t], ids, len_dev[t], nseq, max(batch.ctx), 12,
+                              batch.scale, stream)
+    cache.check()
+    for t in range(steps):
+        got = outs[t].cpu()
+        for i in range(nseq):
+            n = start[i] + t + 1
+            expect = attention.self_attention(qs[t][i:i + 1], batch.k[i][:n], batch.v[i][:n], batch.scale)
+            assert helpers.max_abs(got[i:i + 1], expect) <= helpers.MAX_ABS["bf16"], (t, i)
+    for i in range(nseq):
+        k_out = torch.empty_like(batch.k[i], device="cuda")
+        v_out = torch.empty_like(batch.v[i], device="cuda")
+        cache.gather(0, seqs[i], batch.ctx[i], k_out, v_out)
+        assert torch.equal(helpers.tensor_words(k_out.cpu()), helpers.tensor_words(batch.k[i]))
+        assert torch.equal(helpers.tensor_words(v_out.cpu()), helpers.tensor_words(batch.v[i]))
+
+
+def test_host_step_rejects_a_sequence_named_twice_cpu():
+    cache = llaisys.PagedKVCache(8, 2, 128, dtype=llaisys.DataType.BF16, max_seqs=2)
+    s = cache.add_seq()
+    cache.reserve(s, 16)
+    rows = torch.zeros((2, 2, 128), dtype=torch.bfloat16)
+    q = torch.zeros((2, 12, 128), dtype=torch.bfloat16)
+    with pytest.raises(LlaisysError) as e:
+        cache.decode_step_host(0, q.clone(), q, rows, rows, np.asarray([s, s], np.int32), np.asarray([3, 3], np.int32), 12, 1.0)
+    assert e.value.status == Status.INVALID and "twice" in str(e.value)
+    cache.decode_step_host(0, q[:1].clone(), q[:1], rows[:1], rows[:1], np.asarray([s], np.int32), np.asarray([3], np.int32), 12, 1.0)
+
+
 def test_lse_merge_cpu():
     g = torch.Generator().manual_seed(9)
     q = workloads.randn((1, 12, 128), torch.float32, g)

@@ -210,3 +210,41 @@ def test_model_on_gpu_matches_hugging_face(dtype_name):
     for s in range(n_steps):
         cur = ours.step(seqs, [[t] for t in cur])
         assert cur == loop[s].tolist(), f"step {s}"
+
+
+@pytest.mark.gpu
+def test_cached_step_graph_survives_a_first_prefill_nvidia():
+    """Eight sequences decode from one-token prompts until their step is replayed from its cached CUDA graph; then the
+    cache serves its FIRST prompt chunk (another sequence, fewer rows than the workspace holds) and a decode step of
+    another batch size, and the eight are stepped again through the old graph. Everything the captured kernels point at --
+    the attention workspace of the cache included -- must still be where it was: every token of every step has to be
+    (near-)optimal under Hugging Face's logits for the tokens fed so far."""
+    tol = 0.05
+    cfg, hf32 = hf_model(seed=8, std=0.02, num_attention_heads=12, num_key_value_heads=2, hidden_size=1536, intermediate_size=1024)
+    hf = hf32.to(torch.bfloat16).float()
+    ours = llaisys.models.Qwen2(config=cfg, state_dict=hf.state_dict(), device=llaisys.DeviceType.NVIDIA,
+                                dtype=llaisys.DataType.BF16)
+    ours.configure_cache(10, 64)
+    rng = np.random.default_rng(4)
+    seqs = [ours.add_seq() for _ in range(8)]
+    history = [[int(t)] for t in rng.integers(0, 318, 8)]
+
+    def step_eight():
+        nxt = ours.step(seqs, [[h[-1]] for h in history])
+        for h, t in zip(history, nxt):
+            h.append(t)
+
+    for _ in range(4):  # step 1 eager, step 2 captures the graph, steps 3-4 replay it
+        step_eight()
+    other = ours.add_seq()
+    prompt = rng.integers(0, 318, 5).tolist()
+    first = ours.step([other], [prompt])[0]  # the cache's first chunk call
+    more = ours.add_seq()
+    ours.step([other, more], [[first], [7]])  # a decode step of another batch size
+    for _ in range(3):  # the eight again, through the graph captured before all that
+        step_eight()
+    for h in history:
+        rows = hf_logits(hf, h[:-1])
+        for pos in range(len(h) - 1):
+            row = rows[pos]
+            assert (row.max() - row[h[pos + 1]]).item() <= 2 * tol * max(1.0, row.abs().max().item()), (h, pos)

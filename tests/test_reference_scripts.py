@@ -10,7 +10,9 @@ from pathlib import Path
 
 import pytest
 
-REFERENCE = Path("/root/reference")
+from tests import helpers
+
+REFERENCE = helpers.reference_root()
 ROOT = Path(__file__).resolve().parents[1]
 
 SHIM = "import sys, llaisys_b200; sys.modules['llaisys'] = llaisys_b200; import runpy; " \
@@ -29,7 +31,7 @@ def run_script(script: str, device: str):
     return subprocess.run(args, env=env, capture_output=True, text=True, timeout=600)
 
 
-@pytest.mark.skipif(not REFERENCE.exists(), reason="reference tree not mounted")
+@pytest.mark.skipif(REFERENCE is None, reason="reference tree not available (set LLAISYS_REFERENCE_ROOT)")
 @pytest.mark.parametrize("script", SCRIPTS)
 def test_reference_script_passes_on_cpu(script):
     res = run_script(script, "cpu")
@@ -37,7 +39,7 @@ def test_reference_script_passes_on_cpu(script):
     assert "Test passed!" in res.stdout
 
 
-@pytest.mark.skipif(not REFERENCE.exists(), reason="reference tree not mounted")
+@pytest.mark.skipif(REFERENCE is None, reason="reference tree not available (set LLAISYS_REFERENCE_ROOT)")
 def test_reference_runtime_script_skips_nvidia_without_a_gpu():
     res = run_script("test/test_runtime.py", "nvidia")
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]

@@ -36,6 +36,34 @@ def test_engine_matches_single_sequence_generation_cpu():
     assert model.add_seq() >= 0  # every sequence slot came back
 
 
+def test_budget_below_running_requests_starves_nobody_cpu():
+    """A step budget smaller than the number of decoding requests: the requests that go without a token rotate, so all of
+    them advance together instead of the last ones waiting for the first to finish, and every token is still the one
+    the request gets alone."""
+    cfg, hf = hf_model(seed=23)
+    model = make(cfg, hf)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, 318, 3).tolist() for _ in range(4)]
+    max_new = [8, 8, 8, 8]
+    want = expected(hf, prompts, max_new)
+    model.configure_cache(4, 32)
+    engine = llaisys.Engine(model, max_batch=4, max_tokens_per_step=2, prefill_chunk=2)
+    ids = [engine.submit(p, n) for p, n in zip(prompts, max_new)]
+    got = {rid: [] for rid in ids}
+    progress_when_first_finished = None
+    while engine.num_waiting or engine.num_running:
+        for rid, token, finished in engine.step():
+            got[rid].append(token)
+            if finished and progress_when_first_finished is None:
+                progress_when_first_finished = [len(got[r]) for r in ids]
+    for rid, w in zip(ids, want):
+        assert got[rid] == w
+    # when the first request finished, the slowest one was at most a couple of tokens behind (without the rotation the
+    # last two requests had not produced anything yet)
+    assert min(progress_when_first_finished) >= max(progress_when_first_finished) - 3, progress_when_first_finished
+    engine.close()
+
+
 def test_prefix_reuse_gives_the_same_tokens_and_skips_work_cpu():
     cfg, hf = hf_model(seed=22)
     model = make(cfg, hf)

@@ -65,3 +65,70 @@ def test_no_alloc_decode_rejects_sizes_beyond_the_static_scratch(cuda_device):
         llaisys.decode_no_alloc(q, q, pool, table, 4, 8, ids, ids, 4, 64, 12, 2, 0.1, dtype=llaisys.DataType.F32,
                                 stream=llaisys.context_stream())
     assert e.value.status == Status.UNSUPPORTED
+
+
+@pytest.mark.gpu
+def test_no_alloc_decode_without_sequence_ids_and_without_an_error_word(cuda_device):
+    """seq_ids_dev = NULL (row i of the block table is sequence i) and error_flag_dev = NULL: the kernel's error bits
+    are then collected inside the library and llaisysPagedAttentionDecodeNoAllocStatus is how a caller sees them -- a
+    page index out of range must show up there (once), not vanish, and a clean call must leave it at zero."""
+    nseq, pages_per, pool_pages = 3, 4, 32
+    g = torch.Generator().manual_seed(7)
+    ctx = [64, 37, 1]
+    table = torch.zeros((nseq, pages_per), dtype=torch.int32)
+    perm = torch.randperm(pool_pages, generator=g).tolist()
+    pool = torch.zeros((pool_pages, 2, 2, 16, 128), dtype=torch.bfloat16)  # [page][K|V][kvh][slot][d]
+    ks = [workloads.randn((c, 2, 128), torch.bfloat16, g) for c in ctx]
+    vs = [workloads.randn((c, 2, 128), torch.bfloat16, g) for c in ctx]
+    for s in range(nseq):
+        for j in range(pages_per):
+            table[s, j] = perm[s * pages_per + j]
+        for t in range(ctx[s]):
+            page = int(table[s, t // 16])
+            pool[page, 0, :, t % 16] = ks[s][t]
+            pool[page, 1, :, t % 16] = vs[s][t]
+    q_host = workloads.randn((nseq, 12, 128), torch.bfloat16, g)
+    pool_d, table_d, q = pool.cuda(), table.cuda(), q_host.cuda()
+    lens = torch.tensor(ctx, dtype=torch.int32, device="cuda")
+    stream = llaisys.context_stream()
+    assert llaisys.decode_no_alloc_status(0, stream) == 0
+    got = torch.full_like(q, float("nan"))
+    llaisys.decode_no_alloc(got, q, pool_d, table_d, pages_per, pool_pages, None, lens, nseq, max(ctx), 12, 2, 128 ** -0.5,
+                            error_flag_dev=None, stream=stream)
+    assert llaisys.decode_no_alloc_status(0, stream) == 0
+    got = got.cpu()
+    for i in range(nseq):
+        ref = attention.self_attention(q_host[i:i + 1], ks[i], vs[i], 128 ** -0.5)
+        assert helpers.max_abs(got[i:i + 1], ref) <= helpers.MAX_ABS["bf16"], i
+    # a block-table entry outside the pool: skipped, flagged, reported once
+    bad = table.clone()
+    bad[0, 1] = pool_pages + 5
+    llaisys.decode_no_alloc(torch.empty_like(q), q, pool_d, bad.cuda(), pages_per, pool_pages, None, lens, nseq, max(ctx), 12, 2,
+                            128 ** -0.5, error_flag_dev=None, stream=stream)
+    assert llaisys.decode_no_alloc_status(0, stream) == 1
+    assert llaisys.decode_no_alloc_status(0, stream) == 0
+
+
+@pytest.mark.gpu
+def test_no_alloc_decode_on_a_device_that_is_not_current(cuda_device):
+    """The call makes its device current while it runs and puts the caller's device back."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with torch.cuda.device(1):
+        q = torch.randn((2, 12, 128), device="cuda:1").bfloat16()
+        pool = torch.randn((8, 2, 2, 16, 128), device="cuda:1").bfloat16()
+        table = torch.tensor([[0, 1], [2, 3]], dtype=torch.int32, device="cuda:1")
+        lens = torch.tensor([20, 32], dtype=torch.int32, device="cuda:1")
+        got = torch.full_like(q, float("nan"))
+        torch.cuda.synchronize()
+    torch.cuda.set_device(0)
+    llaisys.decode_no_alloc(got, q, pool, table, 2, 8, None, lens, 2, 32, 12, 2, 128 ** -0.5, device_id=1, stream=None)
+    assert torch.cuda.current_device() == 0
+    with torch.cuda.device(1):
+        torch.cuda.synchronize()
+    qh, ph = q.cpu(), pool.cpu()
+    for i, n in enumerate((20, 32)):
+        k = torch.cat([ph[int(table[i, j]), 0].transpose(0, 1) for j in range(2)])[:n].contiguous()
+        v = torch.cat([ph[int(table[i, j]), 1].transpose(0, 1) for j in range(2)])[:n].contiguous()
+        ref = attention.self_attention(qh[i:i + 1], k, v, 128 ** -0.5)
+        assert helpers.max_abs(got[i:i + 1].cpu(), ref) <= helpers.MAX_ABS["bf16"]
