@@ -100,8 +100,9 @@ __device__ __forceinline__ uint32_t xchg_step(const TmaDecodeParams &p) {
 }
 
 // One float of a partial row: into the plain array, or into this rank's slot of every rank's buffer.
+template <bool kXchg>
 __device__ __forceinline__ void put_part(const TmaDecodeParams &p, uint32_t step, long long idx, float v) {
-    if (p.xchg.world == 0) {
+    if constexpr (!kXchg) {
         p.part[idx] = v;
         return;
     }
@@ -173,7 +174,10 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
     return false;
 }
 
-template <bool kBf16>
+// kXchg: the exchange mode of a KV-range split (PeerSink) -- a separate instantiation, so that the ordinary decode
+// kernel carries none of its code (with a run-time switch the system-scope fences and peer stores, although never
+// executed, cost the ordinary kernel 2 us of 47).
+template <bool kBf16, bool kXchg>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, TmaDecodeParams p) {
     extern __shared__ unsigned char smem_raw[];
@@ -245,12 +249,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const long long x0 = (long long)blockIdx.x * span;
     const long long x1 = min(total, x0 + span);
 
-    const bool partial = p.part != nullptr || p.xchg.world > 0;
+    const bool partial = kXchg || p.part != nullptr;
     // -- sequences without any token: the output row is zero (partial: o = 0, m = -inf, l = 0). Called by threads
     //    0..127 at least, after their grid_dependency_wait; `sync` is a barrier over the calling threads.
     auto write_empty_pairs = [&](auto sync) {
         int n_empty = 0;
-        const uint32_t step = p.xchg.world > 0 ? xchg_step(p) : 0u;
+        const uint32_t step = kXchg ? xchg_step(p) : 0u;
         for (int pair = blockIdx.x; pair < n_pairs; pair += gridDim.x) {
             const int s = pair / p.nkvh, kvh = pair - s * p.nkvh;
             if (cum[s + 1] - cum[s] != 0) {
@@ -263,17 +267,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             for (int h = 0; h < p.group; ++h) {
                 const long long row = (long long)s * p.nh + kvh * p.group + h;
                 if (partial) {
-                    put_part(p, step, row * (kD + 2) + tid, 0.f);
+                    put_part<kXchg>(p, step, row * (kD + 2) + tid, 0.f);
                     if (tid == 0) {
-                        put_part(p, step, row * (kD + 2) + kD, -INFINITY);
-                        put_part(p, step, row * (kD + 2) + kD + 1, 0.f);
+                        put_part<kXchg>(p, step, row * (kD + 2) + kD, -INFINITY);
+                        put_part<kXchg>(p, step, row * (kD + 2) + kD + 1, 0.f);
                     }
                 } else {
                     store_out<kBf16>(p.out, row * kD + tid, 0.f);
                 }
             }
         }
-        if (p.xchg.world > 0 && n_empty > 0) { // uniform over the CTA
+        if (kXchg && n_empty > 0) { // uniform over the CTA
             __threadfence_system();
             sync();
             if (tid == 0) {
@@ -379,7 +383,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const uint32_t epi_ready = bars_u32 + 2 * kSlots * 8, epi_done = bars_u32 + (2 * kSlots + 1) * 8;
     if (warp == kEpilogueWarp) {
         grid_dependency_wait(); // counters and partials are shared with the previous launch
-        const uint32_t step = p.xchg.world > 0 ? xchg_step(p) : 0u;
+        const uint32_t step = kXchg ? xchg_step(p) : 0u;
         int k = 0; // cut segments handled so far
         while (cur.remaining > 0) {
             const Segment sg = next_segment(cur, cum, p);
@@ -411,15 +415,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 __threadfence(); // the other CTAs' partials are visible to the reads below
                 const float *first = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
                 warp_combine_partials<kBf16>(
-                    first, expected, p.group, lane, p.out, partial, [&](long long idx, float v) { put_part(p, step, idx, v); },
+                    first, expected, p.group, lane, p.out, partial, [&](long long idx, float v) { put_part<kXchg>(p, step, idx, v); },
                     (long long)sg.s * p.nh + sg.kvh * p.group);
-                if (p.xchg.world > 0) {
+                if (kXchg) {
                     __threadfence_system(); // every lane: its rows are at the peers before the pair is counted
                     __syncwarp();
                 }
                 if (lane == 0) {
                     p.counters[pair] = 0; // ready for the next launch
-                    if (p.xchg.world > 0) {
+                    if (kXchg) {
                         xchg_pairs_done(p, step, 1, n_pairs);
                     }
                 }
@@ -448,7 +452,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     // Only now may the successor on the stream be scheduled: whatever starts early behind this grid can then rely on
     // everything BEFORE this grid's predecessor being complete (see the overlap contract in paged_kv.h).
     grid_launch_dependents();
-    if (p.xchg.world > 0 && tid == 0) {
+    if (kXchg && tid == 0) {
         s_step = xchg_step(p); // read by the others after the first barrier of the consumer warps
     }
     write_empty_pairs([] { named_barrier_sync(1, kConsumerThreads); });
@@ -665,11 +669,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 const long long row = row0 + h;
                 const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
                 if (partial) {
-                    const uint32_t step = p.xchg.world > 0 ? s_step : 0u;
-                    put_part(p, step, row * (kD + 2) + dim, o * inv);
+                    const uint32_t step = kXchg ? s_step : 0u;
+                    put_part<kXchg>(p, step, row * (kD + 2) + dim, o * inv);
                     if (dim == 0) {
-                        put_part(p, step, row * (kD + 2) + kD, m_all * 0.6931471805599453f); // log2 units -> natural log
-                        put_part(p, step, row * (kD + 2) + kD + 1, l_all);
+                        put_part<kXchg>(p, step, row * (kD + 2) + kD, m_all * 0.6931471805599453f); // log2 units -> natural log
+                        put_part<kXchg>(p, step, row * (kD + 2) + kD + 1, l_all);
                     }
                 } else {
                     store_out<kBf16>(p.out, row * kD + dim, o * inv);
@@ -698,7 +702,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             ++n_cut;
         }
         reset_state();
-        const bool whole_pair_sent = p.xchg.world > 0 && expected == 1;
+        const bool whole_pair_sent = kXchg && expected == 1;
         if (whole_pair_sent) {
             __threadfence_system(); // this thread's rows are at the peers before the pair is counted
         }
@@ -736,7 +740,7 @@ size_t smem_bytes(int group, int n_seqs) {
            size_t(2 * n_seqs + 1) * sizeof(int) + 16 + size_t(kConsumerWarps) * kStageBytes;
 }
 
-template <bool kBf16>
+template <bool kBf16, bool kXchg>
 void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, int grid, size_t smem, bool overlap) {
     static std::once_flag once[64];
     int dev = 0;
@@ -745,8 +749,8 @@ void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, i
         int optin = 0;
         LLAISYS_CUDA_CHECK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
         cudaFuncAttributes attr{};
-        LLAISYS_CUDA_CHECK(cudaFuncGetAttributes(&attr, paged_decode_tma_kernel<kBf16>));
-        LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tma_kernel<kBf16>,
+        LLAISYS_CUDA_CHECK(cudaFuncGetAttributes(&attr, paged_decode_tma_kernel<kBf16, kXchg>));
+        LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tma_kernel<kBf16, kXchg>,
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 optin - int(attr.sharedSizeBytes)));
     });
@@ -760,7 +764,7 @@ void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, i
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<kBf16>, tmap, p));
+    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<kBf16, kXchg>, tmap, p));
 }
 
 } // namespace
@@ -880,10 +884,13 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
     memcpy(&tmap, kv.tma_desc, sizeof(tmap));
     const size_t smem = smem_bytes(group, batch.n_seqs);
     auto s = static_cast<cudaStream_t>(stream);
+    const bool xchg = out.peers != nullptr;
     if (bf16) {
-        launch<true>(s, tmap, p, grid, smem, kv.overlap_launch);
+        xchg ? launch<true, true>(s, tmap, p, grid, smem, kv.overlap_launch)
+             : launch<true, false>(s, tmap, p, grid, smem, kv.overlap_launch);
     } else {
-        launch<false>(s, tmap, p, grid, smem, kv.overlap_launch);
+        xchg ? launch<false, true>(s, tmap, p, grid, smem, kv.overlap_launch)
+             : launch<false, false>(s, tmap, p, grid, smem, kv.overlap_launch);
     }
     check_launch("paged_decode_tma");
     return 0;
