@@ -52,9 +52,10 @@ sys.path.insert(0, str(ROOT))
 
 NH, NKVH, D, PAGE, POOL_PAGES = 12, 2, 128, 16, 16384
 METRIC = "decode tokens/s (paged KV append + flash-decoding attention, one layer)"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the step kernel, from ncu captures of this file's own
-# command line on a 2-layer pool; None where no capture exists.
-NCU_TRAFFIC_BYTES = {"north_star": None, "config2": None}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the step kernel (mean of two captured launches), from
+# `ncu --set full -k regex:paged_decode_tma -s 4 -c 2` over `bench.py --quick --steps 3 --warmup 3 --layers 2
+# [--workload config2]`: a profiler reading, taken once per kernel change, not measured by this run.
+NCU_TRAFFIC_BYTES = {"north_star": 274_092_928, "config2": 72_993_920}
 MIN_REPEATS = 30
 
 
@@ -412,6 +413,16 @@ def measure_decode(env, workload: str, args, *, steps: int, repeats: int, with_e
         step_one_launch(i)
     stream.synchronize()
     assert cache.last_kernel() == llaisys.Kernel.DECODE_TMA_FUSED, "the step did not run on the TMA decode kernel"
+    if args.quick:  # profiler runs: a few eager launches of each kernel of the step, no graphs, no timing
+        for i in range(steps):
+            step_one_launch(i)
+        for i in range(steps):
+            step_two_launches(i)
+        stream.synchronize()
+        cache.check()
+        cache.close()
+        return {"workload": workload, "quick": True, "launches": {"paged_decode_tma_kernel": max(3, args.warmup) + 2 * steps,
+                                                                    "paged_append_kernel": layers + steps}}
 
     def capture(body, with_overlap):
         cache.set_launch_overlap(with_overlap)
@@ -569,6 +580,13 @@ def measure_prefill(env, args, *, repeats: int) -> dict:
     cache.check()
     assert cache.last_kernel() == llaisys.Kernel.PREFILL_TC, "the chunk attention did not run on the tcgen05 kernel"
     steps = layers
+    if args.quick:  # profiler runs: eager launches only
+        for i in range(steps):
+            do_step(i)
+        stream.synchronize()
+        cache.check()
+        cache.close()
+        return {"workload": "config3", "quick": True, "launches": {"paged_prefill_tc_kernel": max(3, args.warmup) + steps}}
 
     def capture(body):
         graph = torch.cuda.CUDAGraph()
@@ -869,6 +887,12 @@ def run_copy_workload(args) -> None:
     with ClockSampler(local_rank) as clocks:
         append_ms = timed(lambda i: cache.append_dev(i % layers, k_rows, v_rows, seq_of_row, pos_of_row, rows, cs))
     fused_ms = timed(lambda i: cache.rope_append_dev(i % layers, q_out, qkv, bias, seq_of_row, pos_of_row, rows, NH, 10000.0, cs))
+    # A plain device-to-device copy that moves the same bytes as the append (K and V rows read once, written once), timed
+    # the same way: what a copy of THIS size reaches (the measured peak is taken on a 4 GB copy). Four destinations rotate.
+    copy_src = torch.cat([k_rows.view(-1), v_rows.view(-1)])
+    copy_dst = [torch.empty_like(copy_src) for _ in range(4)]
+    plain_copy_ms = timed(lambda i: copy_dst[i % 4].copy_(copy_src, non_blocking=True))
+    del copy_dst
 
     def gather_all(i):  # the gather entry point takes one sequence: 64 launches move the same 64 MiB back out
         with torch.cuda.stream(stream):
@@ -903,7 +927,9 @@ def run_copy_workload(args) -> None:
             "roofline": {"bound": "hbm", "kernel": "paged_append_kernel", "achieved": append_bytes / (append_ms * 1e-3) / 1e9,
                          "peak": hbm_peak, "peak_kind": f"of {kind}", "unit": "GB/s",
                          "frac": append_bytes / (append_ms * 1e-3) / 1e9 / hbm_peak, "traffic": None,
-                         "algorithmic_bytes_per_launch": append_bytes, "kernel_ms_mean": append_ms},
+                         "algorithmic_bytes_per_launch": append_bytes, "kernel_ms_mean": append_ms,
+                         "plain_copy_of_the_same_bytes": {"ms": plain_copy_ms, "GB/s": 2 * rows * row_kv / (plain_copy_ms * 1e-3) / 1e9,
+                                                          "append_vs_copy": plain_copy_ms / append_ms}},
             "rope_append": {"kernel": "paged_rope_append_kernel", "ms": fused_ms, "algorithmic_bytes_per_launch": fused_bytes,
                             "GB/s": fused_bytes / (fused_ms * 1e-3) / 1e9,
                             "frac": fused_bytes / (fused_ms * 1e-3) / 1e9 / hbm_peak},
@@ -1179,6 +1205,9 @@ def run_prefill_workload(args) -> None:
     """--workload config3 as its own line."""
     env = _init_device()
     torch, llaisys, rank, local_rank, world, dist = env
+    if args.quick:
+        print(json.dumps(measure_prefill(env, args, repeats=1)), flush=True)
+        return
     with ClockSampler(local_rank) as clocks:
         rec = measure_prefill(env, args, repeats=max(MIN_REPEATS, min(args.steps, 200)))
     if rank == 0:
@@ -1207,6 +1236,8 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-API leg (profiling runs)")
     ap.add_argument("--no-sub-records", action="store_true",
                     help="north_star only: skip the config2 / config3 (N = 1) and kv_split (N > 1) sub-records")
+    ap.add_argument("--quick", action="store_true",
+                    help="profiler runs (north_star, config2, config3): warm-up plus --steps eager launches, no graphs or timing")
     ap.add_argument("--no-overlap", action="store_true",
                     help="launch kernels without programmatic stream serialisation (on by default for decode workloads)")
     args = ap.parse_args()
@@ -1233,6 +1264,10 @@ def main() -> None:
 
     env = _init_device()
     torch, llaisys, rank, local_rank, world, dist = env
+    if args.quick:
+        print(json.dumps(measure_decode(env, args.workload, args, steps=max(1, min(args.steps, 8)), repeats=1, with_e2e=False)),
+              flush=True)
+        return
     steps = max(args.layers, min(args.steps, 400) // args.layers * args.layers)  # whole rotations of the layer pools
     repeats = max(MIN_REPEATS, args.repeats)
     clocks = ClockSampler(local_rank)
