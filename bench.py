@@ -1068,6 +1068,8 @@ def measure_kv_split(env, args, *, steps: int, one_gpu_reference: bool) -> dict:
     n_rep = max(MIN_REPEATS, min(steps, 200))
     nccl_ms = timed(nccl_batched, n_rep)
     nccl_layer_ms = timed(nccl_per_layer, max(10, n_rep // 5))
+    torch.cuda.synchronize()
+    expect_layer = out.clone()  # per-layer launches cut the pairs differently from the batched one: their own reference
     decode_ms = timed(only_decode, n_rep)
     decode_layer_ms = timed(only_decode_one_layer, n_rep)
     cache.check()
@@ -1080,7 +1082,7 @@ def measure_kv_split(env, args, *, steps: int, one_gpu_reference: bool) -> dict:
     peer_same = bool(torch.equal(out_p.view(torch.int16), expect.view(torch.int16)))  # same partials, same merge order
     peer_layer_ms = timed(graphed(peer_per_layer), max(10, n_rep // 5))
     peer.check(cs)
-    peer_layer_same = bool(torch.equal(out_p.view(torch.int16), expect.view(torch.int16)))
+    peer_layer_same = bool(torch.equal(out_p.view(torch.int16), expect_layer.view(torch.int16)))
 
     # ---- layer 0 against the float64 oracle on the FULL sequence (rank 0 collects the slices) -----------------------
     if world > 1:

@@ -255,11 +255,12 @@ LLAISYS_API int llaisysPagedAttentionDecodeNoAllocStatus(int device_id, llaisysS
 
 /* ---- split-KV decode across the GPUs of one node through peer memory --------------------------------------------- */
 /* For ONE long sequence whose KV range is cut across ranks (one process per GPU): instead of an all-gather through a
- * collective library, every rank's decode kernel stores its partial (o, m, l) rows straight into slots of all the ranks'
- * exchange buffers over NVLink (buffers mapped with CUDA IPC; plain stores, nothing reads remote memory), the thread
- * that finishes the rank's last row stamps a flag in every buffer, and a merge kernel combines the slots once the flags
- * of all writers carry the step: two launches per step. Everything is queued on the given stream and can be captured in a CUDA graph. Waits for peers are bounded
- * (about a second): a wait that runs out flags an error (llaisysPeerExchangeStatus) instead of hanging. */
+ * collective library, every rank's decode kernel stores the values of its partial (o, m, l) rows straight into slots of
+ * all the ranks' exchange buffers over NVLink (buffers mapped with CUDA IPC; plain stores, nothing reads remote memory).
+ * Every value travels as one 8-byte word together with the number of the step it belongs to, so a merge kernel can take
+ * each value the moment it is current: no flag, no fence, two launches per step. Everything is queued on the given
+ * stream and can be captured in a CUDA graph (the step counter lives on the device). Waits for peers are bounded: a
+ * wait that runs out flags an error (llaisysPeerExchangeStatus) instead of hanging. */
 typedef struct LlaisysPeerExchange *llaisysPeerExchange_t;
 
 /* slot_floats: capacity for one rank's partial = rows * (head_dim + 2) floats, a multiple of 4. world <= 16. The
@@ -280,8 +281,8 @@ LLAISYS_API int llaisysPagedAttentionDecodeSplitDev(llaisysPagedKV_t kv, size_t 
                                                     const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs,
                                                     size_t max_kv_len, size_t nh, float scale, llaisysPeerExchange_t ex,
                                                     llaisysStream_t stream);
-/* Polls (about 0.2 us each) after which the merge's wait for a peer's rows gives up; the default is about a second
- * (4 << 20). Set it before the first step. After a wait has run out the step's output is undefined and the ranks' step
+/* Polls (about half a microsecond each) after which the merge's wait for a peer's values gives up; the default is
+ * about a second (2 << 20). Set it before the first step. After a wait has run out the step's output is undefined and the ranks' step
  * counters have diverged: every rank destroys its exchange and creates a new one before the next step. */
 LLAISYS_API int llaisysPeerExchangeSetWaitLimit(llaisysPeerExchange_t ex, uint32_t polls);
 /* Synchronises the stream; 0, or 1 when a wait for a peer ran out since the last call (cleared by the call). */

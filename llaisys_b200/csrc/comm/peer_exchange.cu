@@ -27,80 +27,93 @@ struct PeerTable {
     unsigned char *base[kMaxPeers]; // every rank's buffer as this rank sees it
 };
 
-__device__ __forceinline__ void store_release_sys(uint32_t *addr, uint32_t value) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(addr), "r"(value) : "memory");
+// A slot word: a float and the step it belongs to, written and read as ONE aligned 8-byte access, so the two always
+// travel together. The step is the word's own flag (the scheme of low-latency collectives): no fence orders anything.
+__device__ __forceinline__ void store_word(uint2 *addr, float value, uint32_t step) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};\n" ::"l"(addr), "r"(__float_as_uint(value)), "r"(step) : "memory");
 }
-__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t *addr) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(addr) : "memory");
+__device__ __forceinline__ uint2 load_word(const uint2 *addr) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(addr) : "memory");
     return v;
 }
 
-// One CTA per destination rank: copy the local partial into slot `rank` (of the step's parity) of that rank's buffer,
-// then -- all of the CTA's stores done and fenced at system scope -- stamp this rank's flag there with the step.
-__global__ void peer_push_kernel(PeerTable t, const float4 *__restrict__ src, size_t n_vec, size_t slot_floats, int rank,
-                                 int world, size_t flags_offset, size_t epoch_offset) {
+// For pools the TMA decode kernel does not serve: the partial was written locally as plain floats; one CTA per
+// destination rank forwards it as slot words into slot `rank` (of the step's parity) of that rank's buffer.
+__global__ void peer_push_kernel(PeerTable t, const float *__restrict__ src, size_t n_floats, size_t slot_floats, int rank,
+                                 int world, size_t epoch_offset) {
     const uint32_t step = *reinterpret_cast<const uint32_t *>(t.base[rank] + epoch_offset) + 1;
-    unsigned char *peer = t.base[blockIdx.x];
-    float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(peer) + (size_t(step & 1u) * world + rank) * slot_floats);
-    for (size_t i = threadIdx.x; i < n_vec; i += blockDim.x) {
-        dst[i] = src[i];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        store_release_sys(reinterpret_cast<uint32_t *>(peer + flags_offset) + rank, step);
+    uint2 *dst = reinterpret_cast<uint2 *>(t.base[blockIdx.x]) + (size_t(step & 1u) * world + rank) * slot_floats;
+    for (size_t i = threadIdx.x; i < n_floats; i += blockDim.x) {
+        store_word(dst + i, src[i], step);
     }
 }
 
-// Waits for every writer's flag, then merges: out[r] = sum_p w_p o_p[r] / sum_p w_p with w_p = l_p exp(m_p - M)
-// (the same arithmetic as the library's LSE merge; one warp per row).
+// The value of a slot word once it carries `step`; polls (bounded) until it does. After one wait has run out the lane
+// stops waiting: the step is lost anyway, and the kernel must end.
+__device__ __forceinline__ float wait_word(const uint2 *addr, uint32_t step, uint32_t limit, bool &gave_up, int *error_word) {
+    uint2 w = load_word(addr);
+    uint32_t spins = 0;
+    while (w.y != step && !gave_up) {
+        if (++spins > limit) {
+            gave_up = true;
+            atomicOr(error_word, kErrPeerTimeout);
+            break;
+        }
+        __nanosleep(100);
+        w = load_word(addr);
+    }
+    return __uint_as_float(w.x);
+}
+
+// Merges every rank's slot: out[r] = sum_p w_p o_p[r] / sum_p w_p with w_p = l_p exp(m_p - M) (the same arithmetic, in
+// the same order, as the library's LSE merge; one warp per row). Each value is taken when its word carries the step.
 template <typename T>
 __global__ void peer_merge_kernel(T *__restrict__ out, unsigned char *local_base, size_t slot_floats, int world, int n_rows,
-                                  int d, size_t flags_offset, size_t epoch_offset, size_t error_offset, uint32_t spin_limit) {
+                                  int d, size_t epoch_offset, size_t error_offset, uint32_t spin_limit) {
     const uint32_t step = *reinterpret_cast<const uint32_t *>(local_base + epoch_offset) + 1;
-    if (int(threadIdx.x) < world) {
-        const uint32_t *flag = reinterpret_cast<const uint32_t *>(local_base + flags_offset) + threadIdx.x;
-        uint32_t spins = 0;
-        // flags only grow; a value ahead of the step means the writer is already one step further (allowed)
-        while (int32_t(load_acquire_sys(flag) - step) < 0) {
-            if (++spins > spin_limit) {
-                atomicOr(reinterpret_cast<int *>(local_base + error_offset), kErrPeerTimeout);
-                break;
-            }
-            __nanosleep(100);
-        }
-    }
-    __syncthreads();
+    int *error_word = reinterpret_cast<int *>(local_base + error_offset);
     const int warps_per_block = blockDim.x >> 5;
     const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    bool gave_up = false;
     if (row < n_rows) {
-        const float *parts = reinterpret_cast<const float *>(local_base) + size_t(step & 1u) * world * slot_floats;
-        const float *base = parts + size_t(row) * (d + 2);
+        const uint2 *parts = reinterpret_cast<const uint2 *>(local_base) + size_t(step & 1u) * world * slot_floats;
+        const uint2 *base = parts + size_t(row) * (d + 2);
+        // (m, l) of every rank: lane p fetches rank p's pair, the warp shares them
+        float m_mine = -INFINITY, l_mine = 0.f;
+        if (lane < world) {
+            m_mine = wait_word(base + size_t(lane) * slot_floats + d, step, spin_limit, gave_up, error_word);
+            l_mine = wait_word(base + size_t(lane) * slot_floats + d + 1, step, spin_limit, gave_up, error_word);
+        }
         float m_all = -INFINITY;
         for (int p = 0; p < world; ++p) {
-            if (base[p * slot_floats + d + 1] > 0.f) {
-                m_all = fmaxf(m_all, base[p * slot_floats + d]);
+            const float l = __shfl_sync(0xffffffffu, l_mine, p), m = __shfl_sync(0xffffffffu, m_mine, p);
+            if (l > 0.f) {
+                m_all = fmaxf(m_all, m);
             }
         }
         float l_all = 0.f;
         for (int p = 0; p < world; ++p) {
-            const float l = base[p * slot_floats + d + 1];
+            const float l = __shfl_sync(0xffffffffu, l_mine, p), m = __shfl_sync(0xffffffffu, m_mine, p);
             if (l > 0.f) {
-                l_all += l * expf(base[p * slot_floats + d] - m_all);
+                l_all += l * expf(m - m_all);
             }
         }
         const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-        for (int dim = lane; dim < d; dim += 32) {
+        for (int dim0 = 0; dim0 < d; dim0 += 32) { // uniform trip count: the shuffles below need the whole warp
+            const int dim = dim0 + lane;
             float o = 0.f;
             for (int p = 0; p < world; ++p) {
-                const float l = base[p * slot_floats + d + 1];
-                if (l > 0.f) {
-                    o = fmaf(l * expf(base[p * slot_floats + d] - m_all), base[p * slot_floats + dim], o);
+                const float l = __shfl_sync(0xffffffffu, l_mine, p), m = __shfl_sync(0xffffffffu, m_mine, p);
+                if (l > 0.f && dim < d) {
+                    const float v = wait_word(base + size_t(p) * slot_floats + dim, step, spin_limit, gave_up, error_word);
+                    o = fmaf(l * expf(m - m_all), v, o);
                 }
             }
-            out[size_t(row) * d + dim] = kernels::from_f32<T>(o * inv);
+            if (dim < d) {
+                out[size_t(row) * d + dim] = kernels::from_f32<T>(o * inv);
+            }
         }
     }
     // The CTA that finishes last moves the step counter on (every CTA read it at its start, before it could finish).
@@ -123,12 +136,10 @@ PeerExchange::PeerExchange(int rank, int world, size_t slot_floats) : _rank(rank
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || slot_floats == 0 || slot_floats % 4 != 0) {
         fail(LLAISYS_E_INVALID, "peer exchange: bad rank, world size (at most 16) or slot size (a multiple of 4 floats)");
     }
-    const size_t slots_bytes = 2 * size_t(world) * slot_floats * sizeof(float);
-    _flags_offset = align_up(slots_bytes, 256);
-    _epoch_offset = _flags_offset + align_up(size_t(world) * sizeof(uint32_t), 256);
+    const size_t slots_bytes = 2 * size_t(world) * slot_floats * sizeof(uint2); // a word per float: value and step
+    _epoch_offset = align_up(slots_bytes, 256);
     _error_offset = _epoch_offset + 256;
-    _done_offset = _error_offset + 256;
-    _bytes = _done_offset + 256;
+    _bytes = _error_offset + 256;
     cuda_ok(cudaMalloc(&_base, _bytes), "peer exchange: cudaMalloc");
     cuda_ok(cudaMemset(_base, 0, _bytes), "peer exchange: cudaMemset");
     cuda_ok(cudaMalloc(&_local_part, slot_floats * sizeof(float)), "peer exchange: cudaMalloc");
@@ -199,9 +210,7 @@ kernels::PeerSink PeerExchange::sink() const {
     k.world = _world;
     k.rank = _rank;
     k.slot_floats = _slot_floats;
-    k.flags_offset = _flags_offset;
     k.epoch_offset = _epoch_offset;
-    k.done_offset = _done_offset;
     return k;
 }
 
@@ -223,9 +232,8 @@ void PeerExchange::push(llaisysStream_t stream, int n_rows, int d) {
     for (int p = 0; p < _world; ++p) {
         t.base[p] = _peer[size_t(p)];
     }
-    const size_t n_vec = size_t(n_rows) * size_t(d + 2) / 4;
     peer_push_kernel<<<unsigned(_world), 512, 0, static_cast<cudaStream_t>(stream)>>>(
-        t, reinterpret_cast<const float4 *>(_local_part), n_vec, _slot_floats, _rank, _world, _flags_offset, _epoch_offset);
+        t, _local_part, size_t(n_rows) * size_t(d + 2), _slot_floats, _rank, _world, _epoch_offset);
     kernels::check_launch("peer_exchange push");
 }
 
@@ -241,15 +249,15 @@ void PeerExchange::merge(llaisysStream_t stream, llaisysDataType_t dtype, void *
     switch (dtype) {
     case LLAISYS_DTYPE_F32:
         peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<float *>(out), _base, _slot_floats, _world, n_rows, d,
-                                                 _flags_offset, _epoch_offset, _error_offset, _spin_limit);
+                                                 _epoch_offset, _error_offset, _spin_limit);
         break;
     case LLAISYS_DTYPE_F16:
         peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<__half *>(out), _base, _slot_floats, _world, n_rows, d,
-                                                 _flags_offset, _epoch_offset, _error_offset, _spin_limit);
+                                                 _epoch_offset, _error_offset, _spin_limit);
         break;
     case LLAISYS_DTYPE_BF16:
         peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<__nv_bfloat16 *>(out), _base, _slot_floats, _world, n_rows, d,
-                                                 _flags_offset, _epoch_offset, _error_offset, _spin_limit);
+                                                 _epoch_offset, _error_offset, _spin_limit);
         break;
     default:
         fail(LLAISYS_E_INVALID, "peer exchange: unsupported output type");

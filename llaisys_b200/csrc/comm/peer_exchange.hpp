@@ -1,19 +1,20 @@
 // Exchange of split-KV attention partials between the GPUs of one node through peer memory instead of a collective
 // library: every rank owns a buffer of per-rank slots that all the others map (CUDA IPC) and write straight into over
-// NVLink; a flag per writer, stamped with the step number, tells the owner when a slot is complete.
+// NVLink. A slot is made of 8-byte words, each a float and, beside it, the number of the step it belongs to: written and
+// read as one aligned access, the word is its own flag, so nothing in the exchange needs a fence, a separate flag or a
+// count of finished rows (system-scope fences cost this GPU about 20 us apiece).
 //
 // One step on rank r (all on the caller's stream, capturable in a CUDA graph):
-//   push    done by the TMA decode kernel itself (attention_decode_tma.cu, PeerSink): whichever thread finishes a partial
-//           row stores it into slot r of EVERY rank's buffer (plain peer stores) and fences it at system scope; the thread
-//           that completes the launch's last (sequence, kv-head) pair then stamps flag[r] = step in every buffer. Pools the
-//           TMA kernel does not serve write the partial locally and a push kernel (one CTA per destination) forwards it;
-//   merge   wait (bounded) until all of this rank's flags carry the step, log-sum-exp merge the slots; the last CTA to
-//           finish moves the device-side step counter on.
-// Slots are double-buffered by the step's parity: a rank can run at most one step ahead of the slowest (its next wait
-// needs that rank's next push), so a writer never overwrites a slot that is still being merged. No kernel waits
-// without a limit: a wait that runs out sets the error word and the merge runs on what is there -- the output of such
-// a step is undefined, and because the ranks' step counters have then diverged the exchange must be destroyed and
-// created again (by every rank) before the next step.
+//   push    done by the TMA decode kernel itself (attention_decode_tma.cu, PeerSink): whichever thread finishes a value
+//           of a partial row stores its word into slot r of EVERY rank's buffer (plain peer stores). Pools the TMA kernel
+//           does not serve write the partial locally and a push kernel (one CTA per destination) forwards it;
+//   merge   takes each value as soon as its word carries the step (bounded wait), log-sum-exp merges the slots; the last
+//           CTA to finish moves the device-side step counter on.
+// Slots are double-buffered by the step's parity: a rank can run at most one step ahead of the slowest (its next merge
+// needs that rank's next values), so a writer never overwrites a slot that is still being merged, and a word left from
+// two steps ago carries the wrong step. No kernel waits without a limit: a wait that runs out sets the error word and
+// the merge runs on what is there -- the output of such a step is undefined, and because the ranks' step counters have
+// then diverged the exchange must be destroyed and created again (by every rank) before the next step.
 // New code: the reference has no multi-GPU path (README.md:426-427 names it as future work).
 #pragma once
 
@@ -51,11 +52,12 @@ public:
     float *localPartial() const { return _local_part; }
     // The buffers as the decode kernel needs them to store its partial rows at every rank itself.
     kernels::PeerSink sink() const;
-    // Forwards n_rows rows of localPartial() to every rank and stamps the flags (for kernels that cannot do it themselves).
+    // Forwards n_rows rows of localPartial() to every rank (for kernels that cannot store there themselves).
     void push(llaisysStream_t stream, int n_rows, int d);
-    // Waits (bounded) for every rank's rows of this step, merges them into out [n_rows, d] of dtype, moves the step on.
+    // Takes every rank's values of this step as they arrive (bounded waits), merges them into out [n_rows, d] of dtype,
+    // moves the step on.
     void merge(llaisysStream_t stream, llaisysDataType_t dtype, void *out, int n_rows, int d);
-    // Polls (about 0.2 us each) after which a wait for a peer gives up; the default is about a second.
+    // Polls (about half a microsecond each) after which a wait for a peer gives up; the default is about a second.
     void setWaitLimit(uint32_t polls);
     // Synchronises the stream, returns and clears the error word (0 = fine, 1 = a wait for a peer ran out).
     int status(llaisysStream_t stream);
@@ -67,8 +69,8 @@ private:
     unsigned char *_base = nullptr;      // this rank's allocation
     float *_local_part = nullptr;        // separate allocation: the decode kernel's output
     std::vector<unsigned char *> _peer;  // mapped bases, [_rank] = _base
-    size_t _flags_offset = 0, _epoch_offset = 0, _error_offset = 0, _done_offset = 0, _bytes = 0;
-    uint32_t _spin_limit = 4u << 20;
+    size_t _epoch_offset = 0, _error_offset = 0, _bytes = 0;
+    uint32_t _spin_limit = 2u << 20;
 };
 
 } // namespace llaisys::comm

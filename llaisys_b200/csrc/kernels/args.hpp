@@ -62,13 +62,14 @@ struct AttnOut {
 };
 
 // Exchange buffers of a KV-range split across the GPUs of a node, as rank `rank` sees them: base[r] is rank r's buffer
-// (peer memory for r != rank). A buffer holds 2 (step parity) x world slots of slot_floats floats -- slot s of parity p
-// is written by rank s -- then, at the byte offsets below, one uint32 flag per writer (the last step whose rows are
-// complete), the step counter (merges completed) and a counter of this rank's finished (sequence, kv-head) pairs.
+// (peer memory for r != rank). A buffer holds 2 (step parity) x world slots of slot_floats 8-byte words -- slot s of
+// parity p is written by rank s; a word is a float and, beside it, the number of the step it belongs to, so that a
+// reader can tell a current value from a stale one without any flag or fence -- then, at epoch_offset bytes, the step
+// counter (merges completed).
 struct PeerSink {
     unsigned char *base[16] = {};
     int32_t world = 0, rank = 0;
-    size_t slot_floats = 0, flags_offset = 0, epoch_offset = 0, done_offset = 0;
+    size_t slot_floats = 0, epoch_offset = 0;
 };
 
 // Device-side scratch a launch may use (split-KV partials and arrival counters); owned by the caller.

@@ -82,24 +82,23 @@ struct TmaDecodeParams {
     char *pool_k;                           // K tile of (page 0, kv-head 0) of this layer
     long long page_stride_b, head_stride_b; // bytes between pages / kv-heads
     long long v_offset_b;                   // V tile - K tile of the same (page, kv-head)
-    // KV-range split across GPUs (xchg_world > 0, out and part null): every partial row (o, m, l) is stored into slot
-    // xchg_rank of EVERY rank's exchange buffer (plain stores into peer memory), and the thread that completes the
-    // launch's last pair stamps this rank's flag in every buffer with the step number.
+    // KV-range split across GPUs (exchange instantiation; out and part null): every value of a partial row (o, m, l) is
+    // stored, together with the step number, as one 8-byte word into slot `rank` of EVERY rank's exchange buffer (plain
+    // stores into peer memory). The word is its own flag: the reader takes a value once the step beside it is the
+    // current one, so no fence, no flag and no count of finished pairs is needed (a system-scope fence costs this
+    // GPU about 20 us: two per launch doubled the single-sequence kernel's time).
     PeerSink xchg;
 };
 
 constexpr int kMaxXchg = int(sizeof(PeerSink::base) / sizeof(PeerSink::base[0]));
-
-__device__ __forceinline__ void store_release_sys_u32(uint32_t *addr, uint32_t value) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(addr), "r"(value) : "memory");
-}
 
 // The device-side step counter of the exchange: the number of merges completed so far. This launch belongs to the next.
 __device__ __forceinline__ uint32_t xchg_step(const TmaDecodeParams &p) {
     return __ldcg(reinterpret_cast<const uint32_t *>(p.xchg.base[p.xchg.rank] + p.xchg.epoch_offset)) + 1u;
 }
 
-// One float of a partial row: into the plain array, or into this rank's slot of every rank's buffer.
+// One float of a partial row: into the plain array, or -- with the step beside it -- into this rank's slot of every
+// rank's buffer (an aligned 8-byte store is one transaction: value and step arrive together).
 template <bool kXchg>
 __device__ __forceinline__ void put_part(const TmaDecodeParams &p, uint32_t step, long long idx, float v) {
     if constexpr (!kXchg) {
@@ -108,21 +107,9 @@ __device__ __forceinline__ void put_part(const TmaDecodeParams &p, uint32_t step
     }
     const long long at = ((long long)(step & 1u) * p.xchg.world + p.xchg.rank) * (long long)p.xchg.slot_floats + idx;
     for (int pe = 0; pe < p.xchg.world; ++pe) {
-        reinterpret_cast<float *>(p.xchg.base[pe])[at] = v;
-    }
-}
-
-// Called by ONE thread after `n` more pairs of this launch are complete and their rows fenced at system scope by the
-// threads that stored them. The caller that completes the last pair publishes the step to every rank.
-__device__ __forceinline__ void xchg_pairs_done(const TmaDecodeParams &p, uint32_t step, int n, int n_pairs) {
-    int *done = reinterpret_cast<int *>(p.xchg.base[p.xchg.rank] + p.xchg.done_offset);
-    __threadfence();
-    if (atomicAdd(done, n) + n == n_pairs) {
-        *done = 0; // for the next launch (ordered behind this one by the stream)
-        __threadfence_system();
-        for (int pe = 0; pe < p.xchg.world; ++pe) {
-            store_release_sys_u32(reinterpret_cast<uint32_t *>(p.xchg.base[pe] + p.xchg.flags_offset) + p.xchg.rank, step);
-        }
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};\n" ::"l"(reinterpret_cast<uint2 *>(p.xchg.base[pe]) + at),
+                     "r"(__float_as_uint(v)), "r"(step)
+                     : "memory");
     }
 }
 
@@ -248,16 +235,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 
     const bool partial = kXchg || p.part != nullptr;
     // -- sequences without any token: the output row is zero (partial: o = 0, m = -inf, l = 0). Called by threads
-    //    0..127 at least, after their grid_dependency_wait; `sync` is a barrier over the calling threads.
-    auto write_empty_pairs = [&](auto sync) {
-        int n_empty = 0;
+    //    0..127 at least, after their grid_dependency_wait.
+    auto write_empty_pairs = [&]() {
         const uint32_t step = kXchg ? xchg_step(p) : 0u;
         for (int pair = blockIdx.x; pair < n_pairs; pair += gridDim.x) {
             const int s = pair / p.nkvh, kvh = pair - s * p.nkvh;
             if (cum[s + 1] - cum[s] != 0) {
                 continue;
             }
-            ++n_empty;
             if (tid >= kD) {
                 continue;
             }
@@ -274,17 +259,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 }
             }
         }
-        if (kXchg && n_empty > 0) { // uniform over the CTA
-            __threadfence_system();
-            sync();
-            if (tid == 0) {
-                xchg_pairs_done(p, step, n_empty, n_pairs);
-            }
-        }
     };
     if (x0 >= x1) {
         grid_dependency_wait(); // outputs may still be in use by the previous kernel on the stream
-        write_empty_pairs([] { __syncthreads(); });
+        write_empty_pairs();
         return; // exiting counts as this CTA's launch_dependents
     }
 
@@ -415,18 +393,21 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             last = __shfl_sync(0xffffffffu, last, 0);
             if (last) {
                 const float *first = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
-                warp_combine_partials<kBf16>(
-                    first, expected, p.group, lane, p.out, partial, [&](long long idx, float v) { put_part<kXchg>(p, step, idx, v); },
-                    (long long)sg.s * p.nh + sg.kvh * p.group);
-                if (kXchg) {
-                    __threadfence_system(); // every lane: its rows are at the peers before the pair is counted
+                const long long row0 = (long long)sg.s * p.nh + sg.kvh * p.group;
+                if constexpr (kXchg) {
+                    // merged rows first into the pair's own first partial slot (every piece has been read by then; a
+                    // slot holds group x 132 floats, the rows need group x 130), then from there to every rank
+                    float *staged = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
+                    warp_combine_partials_call<kBf16>(first, expected, p.group, lane, nullptr, staged - row0 * (kD + 2), row0);
                     __syncwarp();
+                    for (int i = lane; i < p.group * (kD + 2); i += 32) {
+                        put_part<true>(p, step, row0 * (kD + 2) + i, __ldcg(staged + i));
+                    }
+                } else {
+                    warp_combine_partials<kBf16>(first, expected, p.group, lane, p.out, p.part, row0);
                 }
                 if (lane == 0) {
                     p.counters[pair] = 0; // ready for the next launch
-                    if (kXchg) {
-                        xchg_pairs_done(p, step, 1, n_pairs);
-                    }
                 }
             }
             __syncwarp();
@@ -456,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     if (kXchg && tid == 0) {
         s_step = xchg_step(p); // read by the others after the first barrier of the consumer warps
     }
-    write_empty_pairs([] { named_barrier_sync(1, kConsumerThreads); });
+    write_empty_pairs();
     float m2[2], l[2], o_acc[8][4];
     uint32_t qf[8][2];
     auto reset_state = [&]() {
@@ -703,15 +684,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             ++n_cut;
         }
         reset_state();
-        const bool whole_pair_sent = kXchg && expected == 1;
-        if (whole_pair_sent) {
-            __threadfence_system(); // this thread's rows are at the peers before the pair is counted
-        }
         // red_o / red_ml are next written after this pair's readers have passed the barrier below
         named_barrier_sync(1, kConsumerThreads);
-        if (whole_pair_sent && tid == 0) {
-            xchg_pairs_done(p, s_step, 1, n_pairs);
-        }
     }
 }
 

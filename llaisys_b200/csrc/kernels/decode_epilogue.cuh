@@ -105,11 +105,9 @@ __device__ __forceinline__ void combine_partials(const float *first, int expecte
 // a microsecond, so a round keeps kParts parts x kHeads heads of 16-byte loads in flight per lane (the common cut,
 // 2-4 pieces per pair, merges in ONE round trip); the (m, l) scalars of a round are loaded one per lane and
 // broadcast with shuffles instead of occupying kParts * kHeads more registers.
-// The result goes to `out` (rows of the K/V dtype) or, when partial is set, through put_part(index, value) into rows of
-// d + 2 floats (o, m, l): a plain array, or the exchange slots of a KV-range split.
-template <bool kBf16, int kHeads, int kParts, typename PutPart>
+template <bool kBf16, int kHeads, int kParts>
 __device__ __forceinline__ void warp_combine_impl(const float *first, int expected, int group, int lane, void *out,
-                                                  bool partial, PutPart put_part, long long out_row0) {
+                                                  float *part, long long out_row0) {
     constexpr int kD = 128, kStride = kD + 4, kOutStride = kD + 2;
     static_assert(kHeads * kParts <= 32, "one (m, l) pair per lane per round");
     float m_run[kHeads], l_run[kHeads];
@@ -168,20 +166,21 @@ __device__ __forceinline__ void warp_combine_impl(const float *first, int expect
             m_run[h] = nm;
         }
     }
+    __syncwarp(); // every lane has consumed its loads: `part` may lie over the partials just read
 #pragma unroll
     for (int h = 0; h < kHeads; ++h) {
         if (h < group) {
             const long long row = out_row0 + h;
             const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
             const float r[4] = {o_run[h].x * inv, o_run[h].y * inv, o_run[h].z * inv, o_run[h].w * inv};
-            if (partial) {
+            if (part != nullptr) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    put_part(row * kOutStride + lane * 4 + e, r[e]);
+                    part[row * kOutStride + lane * 4 + e] = r[e];
                 }
                 if (lane == 0) {
-                    put_part(row * kOutStride + kD, m_run[h] * 0.6931471805599453f); // log2 units -> natural log
-                    put_part(row * kOutStride + kD + 1, l_run[h]);
+                    part[row * kOutStride + kD] = m_run[h] * 0.6931471805599453f; // log2 units -> natural log
+                    part[row * kOutStride + kD + 1] = l_run[h];
                 }
             } else {
 #pragma unroll
@@ -193,16 +192,26 @@ __device__ __forceinline__ void warp_combine_impl(const float *first, int expect
     }
 }
 
-template <bool kBf16, typename PutPart>
+template <bool kBf16>
 __device__ __forceinline__ void warp_combine_partials(const float *first, int expected, int group, int lane, void *out,
-                                                      bool partial, PutPart put_part, long long out_row0) {
+                                                      float *part, long long out_row0) {
     if (group <= 4) {
-        warp_combine_impl<kBf16, 4, 4>(first, expected, group, lane, out, partial, put_part, out_row0);
+        warp_combine_impl<kBf16, 4, 4>(first, expected, group, lane, out, part, out_row0);
     } else if (group <= 6) {
-        warp_combine_impl<kBf16, 6, 4>(first, expected, group, lane, out, partial, put_part, out_row0);
+        warp_combine_impl<kBf16, 6, 4>(first, expected, group, lane, out, part, out_row0);
     } else {
-        warp_combine_impl<kBf16, 8, 2>(first, expected, group, lane, out, partial, put_part, out_row0);
+        warp_combine_impl<kBf16, 8, 2>(first, expected, group, lane, out, part, out_row0);
     }
+}
+
+// The same merge as a function of its own, for kernels in which the inlined loop does not come out well: it keeps up
+// to 96 registers of loads in flight, and inlined into the exchange instantiation of the TMA decode kernel (whose other
+// warps sit at the register limit) it ran 2.3 times slower than in the ordinary one. Compiled by itself it does not
+// depend on its surroundings; the call costs about a microsecond, which is why the ordinary kernel keeps the inlined one.
+template <bool kBf16>
+__device__ __noinline__ void warp_combine_partials_call(const float *first, int expected, int group, int lane, void *out,
+                                                        float *part, long long out_row0) {
+    warp_combine_partials<kBf16>(first, expected, group, lane, out, part, out_row0);
 }
 
 } // namespace llaisys::kernels

@@ -106,7 +106,7 @@ class PeerExchange:
                                                                self._ex, stream))
 
     def set_wait_limit(self, polls: int) -> None:
-        """Polls (about 0.2 us each) after which a merge stops waiting for a peer's rows; the default is about a second."""
+        """Polls (about half a microsecond each) after which a merge stops waiting for a peer's values; the default is about a second."""
         from .libllaisys import LIB_LLAISYS
         from .paged_kv import _check
 

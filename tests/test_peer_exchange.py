@@ -210,7 +210,7 @@ def _timeout_worker(rank: int, world: int, port: int, results):
             return out
 
         ex = sharding.PeerExchange(12, 128, device_id=rank)
-        ex.set_wait_limit(1 << 21)  # about half a second instead of a second
+        ex.set_wait_limit(1 << 19)  # about a quarter of a second instead of a second
         first = step(ex)
         assert ex.status(stream) == 0
         ok_first = helpers.max_abs(first.cpu(), full) <= 8e-3
