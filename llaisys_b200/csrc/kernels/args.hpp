@@ -44,6 +44,10 @@ struct AttnBatch {
     const int32_t *seq_ids = nullptr;  // [n_seqs] row of block_table per sequence; null: row i for sequence i
     const int32_t *kv_lens = nullptr;  // [n_seqs]; null: every sequence has const_kv_len tokens
     const int32_t *q_starts = nullptr; // [n_seqs + 1] first query row of each sequence; null: const_q_len each
+    // The same seq_ids / kv_lens in HOST memory, for a caller that has them there anyway: the TMA decode kernel then takes
+    // them by value with the launch (batches of at most 256 sequences) and the device arrays above may be null.
+    const int32_t *host_seq_ids = nullptr;
+    const int32_t *host_kv_lens = nullptr;
     int32_t const_kv_len = 0;
     int32_t const_q_len = 1;
     int32_t n_seqs = 0;

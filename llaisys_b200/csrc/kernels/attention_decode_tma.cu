@@ -121,11 +121,19 @@ struct Segment {
     int s, kvh, j0, n, kv_len; // pages [j0, j0 + n) of pair (s, kvh): the piece of the pair inside this span
 };
 
-__device__ __forceinline__ int seq_kv_len(const TmaDecodeParams &p, int s) {
-    return min(max(p.kv_lens[s], 0), p.max_tokens);
+// Index arrays passed BY VALUE with the launch (at most kInlineSeqs sequences): for a caller whose arrays are in host
+// memory this saves the upload and lets the kernel start before whatever upload precedes it on the stream.
+constexpr int kInlineSeqs = 256;
+struct InlineIndex {
+    int32_t n;                   // 0: the arrays are in device memory (TmaDecodeParams::seq_ids / kv_lens)
+    int32_t v[2 * kInlineSeqs];  // seq_ids[n], then kv_lens[n]
+};
+
+__device__ __forceinline__ int seq_kv_len(const int32_t *kv_lens, int max_tokens, int s) {
+    return min(max(kv_lens[s], 0), max_tokens);
 }
 
-__device__ __forceinline__ Segment next_segment(Cursor &c, const int *cum, const TmaDecodeParams &p) {
+__device__ __forceinline__ Segment next_segment(Cursor &c, const int *cum, const TmaDecodeParams &p, const int32_t *kv_lens) {
     Segment sg;
     sg.s = c.s;
     sg.kvh = c.kvh;
@@ -142,7 +150,7 @@ __device__ __forceinline__ Segment next_segment(Cursor &c, const int *cum, const
                 ++c.s;
                 c.np = cum[c.s + 1] - cum[c.s];
             } while (c.np == 0 && c.s + 1 < p.n_seqs);
-            c.kv_len = seq_kv_len(p, c.s);
+            c.kv_len = seq_kv_len(kv_lens, p.max_tokens, c.s);
         }
     }
     return sg;
@@ -166,7 +174,8 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 // executed, cost the ordinary kernel 2 us of 47).
 template <bool kBf16, bool kXchg>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
-    paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, TmaDecodeParams p) {
+    paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ InlineIndex ix,
+                            TmaDecodeParams p) {
     extern __shared__ unsigned char smem_raw[];
     // the 128-byte swizzle is a function of the shared-memory address: slots must start on 1 KiB boundaries
     const uint32_t raw_u32 = smem_u32(smem_raw);
@@ -184,6 +193,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const uint32_t bars_u32 = smem_u32(bars);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int32_t *seq_ids = ix.n > 0 ? ix.v : p.seq_ids;
+    const int32_t *kv_lens = ix.n > 0 ? ix.v + ix.n : p.kv_lens;
 
     if (tid == 0) {
         for (int i = 0; i < 2 * kSlots; ++i) {
@@ -197,8 +208,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     // -- page counts and block-table rows of all sequences: ONE round trip to global memory by all threads, then the
     //    prefix sums (warp 0, in place) --------------------------------------------------------------------------
     for (int s = tid; s < p.n_seqs; s += kThreads) {
-        cum[s + 1] = (seq_kv_len(p, s) + kPage - 1) / kPage;
-        rows[s] = p.seq_ids ? p.seq_ids[s] : s;
+        cum[s + 1] = (seq_kv_len(kv_lens, p.max_tokens, s) + kPage - 1) / kPage;
+        rows[s] = seq_ids ? seq_ids[s] : s;
     }
     if (warp == kProducerWarp && lane == 0) {
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tmap)) : "memory");
@@ -283,7 +294,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         const int r = int(x0 - (long long)cum[lo] * p.nkvh);
         cur.kvh = r / cur.np;
         cur.j = r - cur.kvh * cur.np;
-        cur.kv_len = seq_kv_len(p, lo);
+        cur.kv_len = seq_kv_len(kv_lens, p.max_tokens, lo);
         cur.remaining = int(x1 - x0);
     }
 
@@ -292,7 +303,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         int n = 0; // pages issued so far; page n uses slot n % kSlots for the (n / kSlots)-th time
         bool dead = false, waited = false;
         while (cur.remaining > 0 && !dead) {
-            const Segment sg = next_segment(cur, cum, p);
+            const Segment sg = next_segment(cur, cum, p, kv_lens);
             if (sg.n <= 0) {
                 break; // inconsistent lengths: the consumers flag it
             }
@@ -361,7 +372,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         const uint32_t step = kXchg ? xchg_step(p) : 0u;
         int k = 0; // cut segments handled so far
         while (cur.remaining > 0) {
-            const Segment sg = next_segment(cur, cum, p);
+            const Segment sg = next_segment(cur, cum, p, kv_lens);
             if (sg.n <= 0) {
                 break;
             }
@@ -453,7 +464,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     int n_base = 0, n_cut = 0; // pages consumed so far; cut segments handed to the epilogue warp so far
     bool dead = false;
     while (cur.remaining > 0) {
-        const Segment sg = next_segment(cur, cum, p);
+        const Segment sg = next_segment(cur, cum, p, kv_lens);
         if (sg.n <= 0) { // cannot happen with consistent lengths; leave rather than spin (uniform over the CTA)
             if (tid == 0) {
                 atomicOr(p.error_flag, kErrBadSeq);
@@ -716,7 +727,8 @@ size_t smem_bytes(int group, int n_seqs) {
 }
 
 template <bool kBf16, bool kXchg>
-void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, int grid, size_t smem, bool overlap) {
+void launch(cudaStream_t s, const CUtensorMap &tmap, const InlineIndex &ix, const TmaDecodeParams &p, int grid, size_t smem,
+            bool overlap) {
     static std::once_flag once[64];
     int dev = 0;
     LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
@@ -739,7 +751,7 @@ void launch(cudaStream_t s, const CUtensorMap &tmap, const TmaDecodeParams &p, i
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<kBf16, kXchg>, tmap, p));
+    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<kBf16, kXchg>, tmap, ix, p));
 }
 
 } // namespace
@@ -790,7 +802,8 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
         reason = "needs 16-bit K/V, head_dim 128, 16-token pages, at most 8 query heads per kv head, one query per sequence";
         return -1;
     }
-    if (kv.tma_desc == nullptr || kv.block_table == nullptr || batch.kv_lens == nullptr) {
+    const bool inline_index = batch.host_seq_ids != nullptr && batch.host_kv_lens != nullptr && batch.n_seqs <= kInlineSeqs;
+    if (kv.tma_desc == nullptr || kv.block_table == nullptr || (batch.kv_lens == nullptr && !inline_index)) {
         reason = "the pool carries no tensor map (the driver could not encode one), or block table / lengths are missing";
         return -1;
     }
@@ -859,13 +872,20 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
     memcpy(&tmap, kv.tma_desc, sizeof(tmap));
     const size_t smem = smem_bytes(group, batch.n_seqs);
     auto s = static_cast<cudaStream_t>(stream);
+    static thread_local InlineIndex ix; // 2 KB: kept off the stack, filled only when the caller has host arrays
+    ix.n = 0;
+    if (batch.host_seq_ids != nullptr && batch.host_kv_lens != nullptr && batch.n_seqs <= kInlineSeqs) {
+        ix.n = batch.n_seqs;
+        memcpy(ix.v, batch.host_seq_ids, size_t(batch.n_seqs) * sizeof(int32_t));
+        memcpy(ix.v + batch.n_seqs, batch.host_kv_lens, size_t(batch.n_seqs) * sizeof(int32_t));
+    }
     const bool xchg = out.peers != nullptr;
     if (bf16) {
-        xchg ? launch<true, true>(s, tmap, p, grid, smem, kv.overlap_launch)
-             : launch<true, false>(s, tmap, p, grid, smem, kv.overlap_launch);
+        xchg ? launch<true, true>(s, tmap, ix, p, grid, smem, kv.overlap_launch)
+             : launch<true, false>(s, tmap, ix, p, grid, smem, kv.overlap_launch);
     } else {
-        xchg ? launch<false, true>(s, tmap, p, grid, smem, kv.overlap_launch)
-             : launch<false, false>(s, tmap, p, grid, smem, kv.overlap_launch);
+        xchg ? launch<false, true>(s, tmap, ix, p, grid, smem, kv.overlap_launch)
+             : launch<false, false>(s, tmap, ix, p, grid, smem, kv.overlap_launch);
     }
     check_launch("paged_decode_tma");
     return 0;

@@ -40,22 +40,14 @@ void advance_decode_state(stream_t stream, int64_t *tokens, const int64_t *next,
 }
 
 const void *mapped_host_alias(const void *host_ptr, size_t bytes) {
-    cudaPointerAttributes first, last;
+    cudaPointerAttributes first;
     if (host_ptr == nullptr || bytes == 0 || cudaPointerGetAttributes(&first, host_ptr) != cudaSuccess ||
         first.type != cudaMemoryTypeHost || first.devicePointer == nullptr) {
         (void)cudaGetLastError();
         return nullptr;
     }
-    // the end of the buffer must be mapped too, at the matching device address
-    const char *end = static_cast<const char *>(host_ptr) + (bytes - 1);
-    if (cudaPointerGetAttributes(&last, end) != cudaSuccess || last.type != cudaMemoryTypeHost ||
-        static_cast<const char *>(last.devicePointer) - static_cast<const char *>(first.devicePointer) !=
-            ptrdiff_t(bytes - 1)) {
-        (void)cudaGetLastError();
-        return nullptr;
-    }
-    // and both ends must belong to ONE allocation: a buffer that starts in one pinned block and runs on into another
-    // would cross whatever lies between them
+    // The whole buffer must lie in ONE mapped allocation: a buffer that starts in a page-locked block and runs past its
+    // end would have the kernel read or write whatever lies behind it.
     using RangeFn = CUresult (*)(CUdeviceptr *, size_t *, CUdeviceptr);
     static const RangeFn range = [] {
         void *sym = nullptr;

@@ -134,6 +134,9 @@ struct CopyList {
     int32_t vecs[3];
 };
 __global__ void small_copies_kernel(CopyList l) {
+    // lets a kernel launched behind this one with programmatic stream serialisation begin at once (it waits for these
+    // copies where it needs them); no effect on an ordinary successor
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int32_t threads = int32_t(gridDim.x * blockDim.x), me = int32_t(blockIdx.x * blockDim.x + threadIdx.x);
 #pragma unroll
     for (int b = 0; b < 3; ++b) {

@@ -632,14 +632,17 @@ void PagedKV::decodeSplitDev(size_t layer, const void *q, const int32_t *seq_ids
 // run in stream order). k_new / v_new non-null: fused step.
 void PagedKV::launchDecode(size_t layer, void *out, float *part, const void *q, const void *k_new, const void *v_new,
                            const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len,
-                           size_t nh, float scale, llaisysStream_t stream, bool overlap, const kernels::PeerSink *peers) {
+                           size_t nh, float scale, llaisysStream_t stream, bool overlap, const kernels::PeerSink *peers,
+                           const int32_t *host_seq_ids, const int32_t *host_kv_lens) {
     kernels::KVView v = view(layer);
     v.overlap_launch = overlap;
     const size_t d = _cfg.head_dim;
     for (size_t at = 0; at < n_seqs; at += kMaxDecodeSeqs) {
         kernels::AttnBatch b;
-        b.seq_ids = seq_ids_dev + at;
-        b.kv_lens = kv_lens_dev + at;
+        b.seq_ids = seq_ids_dev ? seq_ids_dev + at : nullptr;
+        b.kv_lens = kv_lens_dev ? kv_lens_dev + at : nullptr;
+        b.host_seq_ids = host_seq_ids ? host_seq_ids + at : nullptr;
+        b.host_kv_lens = host_kv_lens ? host_kv_lens + at : nullptr;
         b.const_q_len = 1;
         b.n_seqs = int32_t(std::min(kMaxDecodeSeqs, n_seqs - at));
         b.total_q = b.n_seqs;
@@ -849,24 +852,16 @@ void PagedKV::decodeStepHost(size_t layer, void *out_host, const void *q_host, c
 #ifdef ENABLE_NVIDIA_API
     if (fastShape() && nh / _cfg.nkvh <= 8) {
         // Two launches and no copy-engine transfer when the caller's buffers are page-locked and mapped (each small
-        // copy costs more in set-up than in transfer): a copy kernel brings the index arrays and q to the device --
-        // q is read by every CTA that works on its sequence, so it is not left in host memory -- then the one-launch
-        // step reads each new K/V row once, straight from the caller's memory, and stores each output row once,
-        // straight into it.
-        const size_t idx_bytes = (2 * n_seqs * sizeof(int32_t) + 15) / 16 * 16;
-        if (idx_bytes / sizeof(int32_t) > _meta_cap) {
-            _meta_cap = std::max<size_t>(idx_bytes / sizeof(int32_t) * 2, 1024);
-            _meta_dev = rt.allocateDeviceStorage(_meta_cap * sizeof(int32_t));
-        }
-        auto *idx_host = reinterpret_cast<int32_t *>(_host_stage->memory()); // free: the previous step has synchronised
-        std::memcpy(idx_host, seq_ids, n_seqs * sizeof(int32_t));
-        std::memcpy(idx_host + n_seqs, kv_lens, n_seqs * sizeof(int32_t));
-        auto *idx = reinterpret_cast<int32_t *>(_meta_dev->memory());
+        // copy costs more in set-up than in transfer): a copy kernel brings q to the device -- q is read by every CTA
+        // that works on its sequence, so it is not left in host memory -- and the one-launch step reads each new K/V row
+        // once, straight from the caller's memory, and stores each output row once, straight into it. Batches of up to
+        // 256 sequences hand their index arrays to the step kernel by value, with the launch: nothing of them is
+        // uploaded, and the kernel (launched to overlap the copy kernel) starts its page copies at once and waits for
+        // q only where it needs it.
         const void *q_alias = kernels::mapped_host_alias(q_host, q_bytes);
         const void *k_alias = kernels::mapped_host_alias(k_new_host, kv_bytes);
         const void *v_alias = kernels::mapped_host_alias(v_new_host, kv_bytes);
         const void *out_alias = kernels::mapped_host_alias(out_host, q_bytes);
-        const void *idx_alias = kernels::mapped_host_alias(idx_host, idx_bytes);
         auto aligned = [](const void *p) { return p != nullptr && reinterpret_cast<uintptr_t>(p) % 16 == 0; };
         const void *k_src = k_d, *v_src = v_d;
         if (aligned(k_alias) && aligned(v_alias)) {
@@ -876,18 +871,44 @@ void PagedKV::decodeStepHost(size_t layer, void *out_host, const void *q_host, c
             api->memcpy_async(k_d, k_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
             api->memcpy_async(v_d, v_new_host, kv_bytes, LLAISYS_MEMCPY_H2D, stream);
         }
-        if (aligned(q_alias) && aligned(idx_alias) && q_bytes % 16 == 0) {
-            const void *src[2] = {idx_alias, q_alias};
-            void *dst[2] = {idx, q_d};
-            const size_t bytes[2] = {idx_bytes, q_bytes};
-            kernels::small_copies(stream, src, dst, bytes, 2);
-        } else {
-            api->memcpy_async(idx, idx_host, idx_bytes, LLAISYS_MEMCPY_H2D, stream);
-            api->memcpy_async(q_d, q_host, q_bytes, LLAISYS_MEMCPY_H2D, stream);
-        }
         void *out_dst = aligned(out_alias) ? const_cast<void *>(out_alias) : out_d;
-        // a plain launch: the kernel reads the index arrays before any wait, and they come from the launch just before it
-        launchDecode(layer, out_dst, nullptr, q_d, k_src, v_src, idx, idx + n_seqs, n_seqs, max_kv, nh, scale, stream, false);
+        const bool q_by_kernel = aligned(q_alias) && q_bytes % 16 == 0;
+        if (n_seqs <= 256) {
+            if (q_by_kernel) {
+                const void *src[1] = {q_alias};
+                void *dst[1] = {q_d};
+                const size_t bytes[1] = {q_bytes};
+                kernels::small_copies(stream, src, dst, bytes, 1);
+            } else {
+                api->memcpy_async(q_d, q_host, q_bytes, LLAISYS_MEMCPY_H2D, stream);
+            }
+            launchDecode(layer, out_dst, nullptr, q_d, k_src, v_src, nullptr, nullptr, n_seqs, max_kv, nh, scale, stream,
+                         /*overlap=*/q_by_kernel, nullptr, seq_ids, kv_lens);
+        } else {
+            const size_t idx_bytes = (2 * n_seqs * sizeof(int32_t) + 15) / 16 * 16;
+            if (idx_bytes / sizeof(int32_t) > _meta_cap) {
+                _meta_cap = std::max<size_t>(idx_bytes / sizeof(int32_t) * 2, 1024);
+                _meta_dev = rt.allocateDeviceStorage(_meta_cap * sizeof(int32_t));
+            }
+            auto *idx_host = reinterpret_cast<int32_t *>(_host_stage->memory()); // free: the previous step has synchronised
+            std::memcpy(idx_host, seq_ids, n_seqs * sizeof(int32_t));
+            std::memcpy(idx_host + n_seqs, kv_lens, n_seqs * sizeof(int32_t));
+            auto *idx = reinterpret_cast<int32_t *>(_meta_dev->memory());
+            if (_host_stage_alias == nullptr) { // the cache's own buffer: looked up once
+                _host_stage_alias = kernels::mapped_host_alias(_host_stage->memory(), _host_stage->size());
+            }
+            if (q_by_kernel && aligned(_host_stage_alias)) {
+                const void *src[2] = {_host_stage_alias, q_alias};
+                void *dst[2] = {idx, q_d};
+                const size_t bytes[2] = {idx_bytes, q_bytes};
+                kernels::small_copies(stream, src, dst, bytes, 2);
+            } else {
+                api->memcpy_async(idx, idx_host, idx_bytes, LLAISYS_MEMCPY_H2D, stream);
+                api->memcpy_async(q_d, q_host, q_bytes, LLAISYS_MEMCPY_H2D, stream);
+            }
+            // a plain launch: the kernel reads the index arrays before any wait, and they come from the launch before it
+            launchDecode(layer, out_dst, nullptr, q_d, k_src, v_src, idx, idx + n_seqs, n_seqs, max_kv, nh, scale, stream, false);
+        }
         if (out_dst == out_d) {
             api->memcpy_async(out_host, out_d, q_bytes, LLAISYS_MEMCPY_D2H, stream);
         }

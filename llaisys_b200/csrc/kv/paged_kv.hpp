@@ -147,7 +147,8 @@ private:
     bool fastShape() const { return _has_tma; }
     void launchDecode(size_t layer, void *out, float *part, const void *q, const void *k_new, const void *v_new,
                       const int32_t *seq_ids_dev, const int32_t *kv_lens_dev, size_t n_seqs, size_t max_kv_len, size_t nh,
-                      float scale, llaisysStream_t stream, bool overlap, const kernels::PeerSink *peers = nullptr);
+                      float scale, llaisysStream_t stream, bool overlap, const kernels::PeerSink *peers = nullptr,
+                      const int32_t *host_seq_ids = nullptr, const int32_t *host_kv_lens = nullptr);
     bool onDevice() const { return _cfg.device_type != LLAISYS_DEVICE_CPU; }
 
     PagedKVConfig _cfg;
@@ -176,6 +177,7 @@ private:
     std::vector<int32_t> _stage_buf, _step_positions;
     std::vector<uint32_t> _seen_mark; // per sequence: the step that last named it (duplicate check of the host step)
     uint32_t _seen_epoch = 0;
+    const void *_host_stage_alias = nullptr; // device-side address of _host_stage (mapped page-locked memory)
 
     // TMA view of the pool (NVIDIA, 16-bit, head_dim 128, page 16 only); _has_tma is false otherwise
     alignas(64) unsigned char _tma_desc[128] = {};      // decode: box = K and V of a page

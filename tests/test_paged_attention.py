@@ -223,6 +223,39 @@ def check_decode_step_host(device, pinned=False):
                                np.zeros(len(seqs), np.int32), nh, batch.scale)
 
 
+@pytest.mark.gpu
+def test_decode_step_host_many_sequences_nvidia(cuda_device):
+    """300 sequences: beyond the 256 whose index arrays travel with the launch, so the step uploads them; page-locked
+    buffers. Output against the oracle, appended rows bit-exact."""
+    n = 300
+    g = torch.Generator().manual_seed(33)
+    ctx = torch.randint(1, 40, (n,), generator=g).tolist()
+    cache = llaisys.PagedKVCache(3 * n, 2, 128, dtype=llaisys.DataType.BF16, device=NVIDIA, max_seqs=n, max_pages_per_seq=3)
+    seqs, ks, vs = [], [], []
+    for c in ctx:
+        s = cache.add_seq()
+        cache.reserve(s, c)
+        seqs.append(s)
+        ks.append(workloads.randn((c, 2, 128), torch.bfloat16, g))
+        vs.append(workloads.randn((c, 2, 128), torch.bfloat16, g))
+    helpers.append_all(cache, 0, seqs, ks, vs, NVIDIA, hi=[c - 1 for c in ctx])
+    q = workloads.randn((n, 12, 128), torch.bfloat16, g).pin_memory()
+    k_new = torch.stack([k[-1] for k in ks]).contiguous().pin_memory()
+    v_new = torch.stack([v[-1] for v in vs]).contiguous().pin_memory()
+    out = torch.empty_like(q).pin_memory()
+    cache.decode_step_host(0, out, q, k_new, v_new, np.asarray(seqs, np.int32), np.asarray(ctx, np.int32), 12, 128 ** -0.5)
+    cache.check()
+    assert cache.last_kernel() == llaisys.Kernel.DECODE_TMA_FUSED
+    for i in (0, 7, 255, 256, 299):
+        expect = attention.self_attention(q[i:i + 1], ks[i], vs[i], 128 ** -0.5)
+        assert helpers.max_abs(out[i:i + 1], expect) <= helpers.MAX_ABS["bf16"], i
+        k_out = torch.empty_like(ks[i], device="cuda")
+        v_out = torch.empty_like(vs[i], device="cuda")
+        cache.gather(0, seqs[i], ctx[i], k_out, v_out)
+        assert torch.equal(helpers.tensor_words(k_out.cpu()), helpers.tensor_words(ks[i]))
+        assert torch.equal(helpers.tensor_words(v_out.cpu()), helpers.tensor_words(vs[i]))
+
+
 def test_decode_step_host_cpu():
     check_decode_step_host(CPU)
 
