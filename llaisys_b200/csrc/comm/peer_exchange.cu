@@ -71,6 +71,10 @@ __device__ __forceinline__ float wait_word(const uint2 *addr, uint32_t step, uin
 template <typename T>
 __global__ void peer_merge_kernel(T *__restrict__ out, unsigned char *local_base, size_t slot_floats, int world, int n_rows,
                                   int d, size_t epoch_offset, size_t error_offset, uint32_t spin_limit) {
+    // Launched with programmatic stream serialisation behind the decode kernel that feeds it: it starts while that kernel
+    // still runs (its CTAs take SM slots the decode grid leaves free), takes values as they arrive, and lets its own
+    // successor -- the next round's decode kernel -- start its page copies in turn.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const uint32_t step = *reinterpret_cast<const uint32_t *>(local_base + epoch_offset) + 1;
     int *error_word = reinterpret_cast<int *>(local_base + error_offset);
     const int warps_per_block = blockDim.x >> 5;
@@ -116,6 +120,9 @@ __global__ void peer_merge_kernel(T *__restrict__ out, unsigned char *local_base
             }
         }
     }
+    // Completion of this kernel must imply completion of the decode kernel before it (its successor relies on that for
+    // the scratch the two decode launches share): wait for it here, where nearly always it has long finished.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     // The CTA that finishes last moves the step counter on (every CTA read it at its start, before it could finish).
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -244,20 +251,30 @@ void PeerExchange::merge(llaisysStream_t stream, llaisysDataType_t dtype, void *
     if (n_rows <= 0 || d <= 0 || out == nullptr || size_t(n_rows) * size_t(d + 2) > _slot_floats) {
         fail(LLAISYS_E_INVALID, "peer exchange: rows do not fit the slot");
     }
-    auto s = static_cast<cudaStream_t>(stream);
     const int block = 128, grid = (n_rows + 3) / 4;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(unsigned(block));
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    auto go = [&](auto kernel, auto *typed_out) {
+        cuda_ok(cudaLaunchKernelEx(&cfg, kernel, typed_out, _base, _slot_floats, _world, n_rows, d, _epoch_offset, _error_offset,
+                                   _spin_limit),
+                "peer exchange: merge launch");
+    };
     switch (dtype) {
     case LLAISYS_DTYPE_F32:
-        peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<float *>(out), _base, _slot_floats, _world, n_rows, d,
-                                                 _epoch_offset, _error_offset, _spin_limit);
+        go(peer_merge_kernel<float>, static_cast<float *>(out));
         break;
     case LLAISYS_DTYPE_F16:
-        peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<__half *>(out), _base, _slot_floats, _world, n_rows, d,
-                                                 _epoch_offset, _error_offset, _spin_limit);
+        go(peer_merge_kernel<__half>, static_cast<__half *>(out));
         break;
     case LLAISYS_DTYPE_BF16:
-        peer_merge_kernel<<<grid, block, 0, s>>>(static_cast<__nv_bfloat16 *>(out), _base, _slot_floats, _world, n_rows, d,
-                                                 _epoch_offset, _error_offset, _spin_limit);
+        go(peer_merge_kernel<__nv_bfloat16>, static_cast<__nv_bfloat16 *>(out));
         break;
     default:
         fail(LLAISYS_E_INVALID, "peer exchange: unsupported output type");
