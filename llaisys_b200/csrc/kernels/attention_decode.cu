@@ -530,7 +530,8 @@ void attention_decode_split_scratch(int32_t n_seqs, int32_t nh, int32_t nkvh, in
     }
     const int grid = decode_grid_size(n_seqs, nkvh, max_kv_len);
     const size_t n_pairs = size_t(n_seqs) * nkvh;
-    *partials_floats = (size_t(grid) + n_pairs) * size_t(nh / nkvh) * (kD + 4); // the TMA kernel pads rows to 132
+    // the TMA kernel pads rows to 132 floats and keeps five more slots per CTA for merges that its warps share
+    *partials_floats = (size_t(grid) * 6 + n_pairs) * size_t(nh / nkvh) * (kD + 4);
     *counters_len = n_pairs;
 }
 

@@ -33,6 +33,7 @@
 
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 namespace llaisys::kernels {
 
@@ -58,6 +59,8 @@ constexpr int kMaxSeqs = 1024;
 constexpr int kCtasPerSm = 8 / kConsumerWarps;
 constexpr uint32_t kWaitLimit = 1u << 20; // polls before a wait gives up (about a second at worst)
 constexpr int kErrTimeout = 8;
+constexpr int kSharedMergeFrom = 9; // a pair cut into this many pieces or more is merged by all five warps of the CTA
+constexpr int kMergeWarps = kConsumerWarps + 1; // that arrives last, if the pair ends the CTA's span (consumers + epilogue)
 constexpr int kStageBytes = 512 + 16; // per consumer warp: a new K row and V row (256 B each) and their page index
 constexpr int kDimGroups = kConsumerThreads / kD; // the pair epilogue maps a consumer thread to one output
 static_assert(kConsumerThreads % kD == 0, "dimension and to every kDimGroups-th head of the group");
@@ -172,7 +175,10 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 // kXchg: the exchange mode of a KV-range split (PeerSink) -- a separate instantiation, so that the ordinary decode
 // kernel carries none of its code (with a run-time switch the system-scope fences and peer stores, although never
 // executed, cost the ordinary kernel 2 us of 47).
-template <bool kBf16, bool kXchg>
+// kShare: launches with few pairs for their grid, whose pairs can be in many pieces, carry the shared merge (all five
+// warps of the last-arriving CTA); the others do not even contain its code -- this kernel's timing moves by a
+// microsecond with what is compiled around its hot loop.
+template <bool kBf16, bool kXchg, bool kShare>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ InlineIndex ix,
                             TmaDecodeParams p) {
@@ -183,12 +189,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     unsigned char *aligned = smem_raw + (ring_u32 - raw_u32);
     float *red_o = reinterpret_cast<float *>(aligned + kRingBytes);                       // [warps][group][kD]
     float *red_ml = red_o + kConsumerWarps * p.group * kD;                                // [warps][kMaxGroup][2]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(red_ml + kConsumerWarps * kMaxGroup * 2); // full[], empty[], epi_ready, epi_done
-    int *cum = reinterpret_cast<int *>(bars + 2 * kSlots + 2);                                // [n_seqs + 1]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(red_ml + kConsumerWarps * kMaxGroup * 2); // full[], empty[], epi_ready, epi_done, verdict
+    int *cum = reinterpret_cast<int *>(bars + 2 * kSlots + 3);                                // [n_seqs + 1]
     int *rows = cum + p.n_seqs + 1;                                                           // [n_seqs] block-table rows
     // new-row staging, 16-byte aligned, one block per consumer warp
     const uint32_t stage_u32 = (smem_u32(rows + p.n_seqs) + 15u) & ~15u;
     __shared__ int s_abort;
+    __shared__ int s_verdict; // shared merge: 1 = this CTA arrived last at its final pair and every warp takes a share
     __shared__ uint32_t s_step; // exchange mode: the step this launch belongs to (written by consumer thread 0)
     const uint32_t bars_u32 = smem_u32(bars);
 
@@ -202,6 +209,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         }
         mbar_init(bars_u32 + 2 * kSlots * 8, kConsumerThreads); // epi_ready: every consumer thread arrives
         mbar_init(bars_u32 + (2 * kSlots + 1) * 8, 1);          // epi_done: the epilogue warp's lane 0
+        mbar_init(bars_u32 + (2 * kSlots + 2) * 8, 1);          // verdict: the epilogue warp's lane 0, once
         s_abort = 0;
         mbar_init_fence();
     }
@@ -367,6 +375,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     // have written this CTA's partial, publishes it (fence + arrival count) and, if this was the last arrival,
     // merges all partials of the pair -- off the consumers' critical path, so the ring keeps draining meanwhile.
     const uint32_t epi_ready = bars_u32 + 2 * kSlots * 8, epi_done = bars_u32 + (2 * kSlots + 1) * 8;
+    const uint32_t verdict_bar = bars_u32 + (2 * kSlots + 2) * 8;
+    // The shared merge keeps its warps' unfinished states in this CTA's own five slots behind the partial results.
+    float *stash = p.partials + ((long long)gridDim.x + n_pairs + (long long)blockIdx.x * kMergeWarps) * p.group * kPartStride;
     if (warp == kEpilogueWarp) {
         grid_dependency_wait(); // counters and partials are shared with the previous launch
         const uint32_t step = kXchg ? xchg_step(p) : 0u;
@@ -402,20 +413,52 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             }
             __syncwarp(); // the other lanes' reads below come after lane 0's acquire
             last = __shfl_sync(0xffffffffu, last, 0);
+            // A pair in many pieces is merged in five shares (share w = parts w, w + 5, ...) whose unfinished states are
+            // then folded: by all five warps of the CTA where the pair ends the CTA's span (the consumers have nothing
+            // left to do and wait for the verdict), by this warp alone, share after share, where the consumers are still
+            // streaming. The arithmetic and its order are the same either way: the bits do not depend on who arrived last.
+            const bool shared_merge = kShare && expected >= kSharedMergeFrom;
+            const bool helpers = shared_merge && cur.remaining == 0;
+            if (helpers && lane == 0) {
+                s_verdict = last;
+                mbar_arrive(verdict_bar); // release: the consumers read s_verdict after their wait
+            }
             if (last) {
                 const float *first = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
                 const long long row0 = (long long)sg.s * p.nh + sg.kvh * p.group;
-                if constexpr (kXchg) {
+                float *staged = p.partials + (long long)(c_first + pair) * p.group * kPartStride; // exchange mode only
+                if constexpr (kShare) {
+                  if (shared_merge) {
+                    if (helpers) {
+                        warp_merge_share<kBf16>(first, expected, kConsumerWarps, kMergeWarps, p.group, lane, stash);
+                        named_barrier_sync(2, kMergeWarps * 32); // every share is stashed; all parts have been read
+                    } else {
+                        for (int w = 0; w < kMergeWarps; ++w) {
+                            warp_merge_share<kBf16>(first, expected, w, kMergeWarps, p.group, lane, stash);
+                        }
+                        __syncwarp();
+                    }
+                    if constexpr (kXchg) {
+                        warp_merge_finish<kBf16>(stash, kMergeWarps, p.group, lane, nullptr, staged - row0 * (kD + 2), row0);
+                    } else {
+                        warp_merge_finish<kBf16>(stash, kMergeWarps, p.group, lane, p.out, p.part, row0);
+                    }
+                  }
+                }
+                if (shared_merge) {
+                    // done above
+                } else if constexpr (kXchg) {
                     // merged rows first into the pair's own first partial slot (every piece has been read by then; a
                     // slot holds group x 132 floats, the rows need group x 130), then from there to every rank
-                    float *staged = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
                     warp_combine_partials_call<kBf16>(first, expected, p.group, lane, nullptr, staged - row0 * (kD + 2), row0);
+                } else {
+                    warp_combine_partials<kBf16>(first, expected, p.group, lane, p.out, p.part, row0);
+                }
+                if constexpr (kXchg) {
                     __syncwarp();
                     for (int i = lane; i < p.group * (kD + 2); i += 32) {
                         put_part<true>(p, step, row0 * (kD + 2) + i, __ldcg(staged + i));
                     }
-                } else {
-                    warp_combine_partials<kBf16>(first, expected, p.group, lane, p.out, p.part, row0);
                 }
                 if (lane == 0) {
                     p.counters[pair] = 0; // ready for the next launch
@@ -697,6 +740,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
         reset_state();
         // red_o / red_ml are next written after this pair's readers have passed the barrier below
         named_barrier_sync(1, kConsumerThreads);
+        if (kShare && cur.remaining == 0 && expected >= kSharedMergeFrom && !dead) {
+            // the span ended inside a pair in many pieces: if this CTA is the one that merges it (the epilogue warp says),
+            // take a share of the parts -- warp w folds parts w, w + 5, ... -- and meet the others
+            if (wait_or_abort(verdict_bar, 0u, &s_abort) && s_verdict != 0) {
+                const float *first = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
+                warp_merge_share<kBf16>(first, expected, warp, kMergeWarps, p.group, lane, stash);
+                named_barrier_sync(2, kMergeWarps * 32);
+            }
+        }
     }
 }
 
@@ -722,11 +774,11 @@ EncodeTiledFn encode_tiled_fn() {
 
 size_t smem_bytes(int group, int n_seqs) {
     return 1024 + size_t(kRingBytes) + size_t(kConsumerWarps) * group * kD * sizeof(float) +
-           size_t(kConsumerWarps) * kMaxGroup * 2 * sizeof(float) + (2 * kSlots + 2) * sizeof(uint64_t) +
+           size_t(kConsumerWarps) * kMaxGroup * 2 * sizeof(float) + (2 * kSlots + 3) * sizeof(uint64_t) +
            size_t(2 * n_seqs + 1) * sizeof(int) + 16 + size_t(kConsumerWarps) * kStageBytes;
 }
 
-template <bool kBf16, bool kXchg>
+template <bool kBf16, bool kXchg, bool kShare>
 void launch(cudaStream_t s, const CUtensorMap &tmap, const InlineIndex &ix, const TmaDecodeParams &p, int grid, size_t smem,
             bool overlap) {
     static std::once_flag once[64];
@@ -736,8 +788,8 @@ void launch(cudaStream_t s, const CUtensorMap &tmap, const InlineIndex &ix, cons
         int optin = 0;
         LLAISYS_CUDA_CHECK(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
         cudaFuncAttributes attr{};
-        LLAISYS_CUDA_CHECK(cudaFuncGetAttributes(&attr, paged_decode_tma_kernel<kBf16, kXchg>));
-        LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tma_kernel<kBf16, kXchg>,
+        LLAISYS_CUDA_CHECK(cudaFuncGetAttributes(&attr, paged_decode_tma_kernel<kBf16, kXchg, kShare>));
+        LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_decode_tma_kernel<kBf16, kXchg, kShare>,
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 optin - int(attr.sharedSizeBytes)));
     });
@@ -751,7 +803,7 @@ void launch(cudaStream_t s, const CUtensorMap &tmap, const InlineIndex &ix, cons
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = overlap ? 1 : 0;
-    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<kBf16, kXchg>, tmap, ix, p));
+    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_decode_tma_kernel<kBf16, kXchg, kShare>, tmap, ix, p));
 }
 
 } // namespace
@@ -824,7 +876,8 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
     const int grid = decode_grid_size(batch.n_seqs, kv.nkvh, batch.max_kv_len);
     const size_t n_pairs = size_t(batch.n_seqs) * kv.nkvh;
     if (scratch.partials == nullptr || scratch.counters == nullptr || scratch.error_flag == nullptr ||
-        scratch.partials_floats < (size_t(grid) + n_pairs) * group * kPartStride || scratch.counters_len < n_pairs) {
+        scratch.partials_floats < (size_t(grid) * (1 + kMergeWarps) + n_pairs) * group * kPartStride ||
+        scratch.counters_len < n_pairs) {
         reason = "split-KV scratch missing or too small for this batch";
         return -1;
     }
@@ -880,13 +933,16 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
         memcpy(ix.v + batch.n_seqs, batch.host_kv_lens, size_t(batch.n_seqs) * sizeof(int32_t));
     }
     const bool xchg = out.peers != nullptr;
-    if (bf16) {
-        xchg ? launch<true, true>(s, tmap, ix, p, grid, smem, kv.overlap_launch)
-             : launch<true, false>(s, tmap, ix, p, grid, smem, kv.overlap_launch);
-    } else {
-        xchg ? launch<false, true>(s, tmap, ix, p, grid, smem, kv.overlap_launch)
-             : launch<false, false>(s, tmap, ix, p, grid, smem, kv.overlap_launch);
-    }
+    // pairs can be in kSharedMergeFrom pieces or more only where the grid has that many CTAs per pair
+    const bool share = size_t(grid) >= n_pairs * size_t(kSharedMergeFrom - 1);
+    auto go = [&](auto bf, auto xc, auto sh) {
+        launch<decltype(bf)::value, decltype(xc)::value, decltype(sh)::value>(s, tmap, ix, p, grid, smem, kv.overlap_launch);
+    };
+    auto pick_share = [&](auto bf, auto xc) {
+        share ? go(bf, xc, std::true_type{}) : go(bf, xc, std::false_type{});
+    };
+    auto pick_xchg = [&](auto bf) { xchg ? pick_share(bf, std::true_type{}) : pick_share(bf, std::false_type{}); };
+    bf16 ? pick_xchg(std::true_type{}) : pick_xchg(std::false_type{});
     check_launch("paged_decode_tma");
     return 0;
 }

@@ -105,42 +105,65 @@ __device__ __forceinline__ void combine_partials(const float *first, int expecte
 // a microsecond, so a round keeps kParts parts x kHeads heads of 16-byte loads in flight per lane (the common cut,
 // 2-4 pieces per pair, merges in ONE round trip); the (m, l) scalars of a round are loaded one per lane and
 // broadcast with shuffles instead of occupying kParts * kHeads more registers.
-template <bool kBf16, int kHeads, int kParts>
-__device__ __forceinline__ void warp_combine_impl(const float *first, int expected, int group, int lane, void *out,
-                                                  float *part, long long out_row0) {
-    constexpr int kD = 128, kStride = kD + 4, kOutStride = kD + 2;
-    static_assert(kHeads * kParts <= 32, "one (m, l) pair per lane per round");
-    float m_run[kHeads], l_run[kHeads];
-    float4 o_run[kHeads];
+// The running state of a merge: per head the max m (log2 units), the sum l and this lane's four output dimensions.
+template <int kHeads>
+struct MergeState {
+    float m[kHeads], l[kHeads];
+    float4 o[kHeads];
+    __device__ __forceinline__ void clear() {
 #pragma unroll
-    for (int h = 0; h < kHeads; ++h) {
-        m_run[h] = -INFINITY;
-        l_run[h] = 0.f;
-        o_run[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int h = 0; h < kHeads; ++h) {
+            m[h] = -INFINITY;
+            l[h] = 0.f;
+            o[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
-    for (int i0 = 0; i0 < expected; i0 += kParts) {
+};
+
+// Folds parts begin, begin + step, ... (< expected) into `st`. kShared: the parts lie in shared memory (plain loads)
+// instead of global memory (L2 loads).
+template <int kHeads, int kParts, bool kShared>
+__device__ __forceinline__ void warp_merge_parts(MergeState<kHeads> &st, const float *first, int expected, int begin,
+                                                 int step, int group, int lane) {
+    constexpr int kD = 128, kStride = kD + 4;
+    static_assert(kHeads * kParts <= 32, "one (m, l) pair per lane per round");
+    auto load4 = [](const float *p) {
+        if constexpr (kShared) {
+            return *reinterpret_cast<const float4 *>(p);
+        } else {
+            return __ldcg(reinterpret_cast<const float4 *>(p));
+        }
+    };
+    auto load2 = [](const float *p) {
+        if constexpr (kShared) {
+            return *reinterpret_cast<const float2 *>(p);
+        } else {
+            return __ldcg(reinterpret_cast<const float2 *>(p));
+        }
+    };
+    for (int i0 = begin; i0 < expected; i0 += kParts * step) {
         float4 v[kParts][kHeads];
 #pragma unroll
         for (int u = 0; u < kParts; ++u) {
 #pragma unroll
             for (int h = 0; h < kHeads; ++h) {
-                v[u][h] = (i0 + u < expected && h < group)
-                              ? __ldcg(reinterpret_cast<const float4 *>(first + (long long)((i0 + u) * group + h) * kStride) + lane)
+                v[u][h] = (i0 + u * step < expected && h < group)
+                              ? load4(first + (long long)((i0 + u * step) * group + h) * kStride + lane * 4)
                               : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
-        // lane u * kHeads + h fetches (m, l) of part i0 + u, head h
+        // lane u * kHeads + h fetches (m, l) of part i0 + u * step, head h
         float2 ml = make_float2(-INFINITY, 0.f);
         {
             const int u = lane / kHeads, h = lane - u * kHeads;
-            if (u < kParts && i0 + u < expected && h < group) {
-                ml = __ldcg(reinterpret_cast<const float2 *>(first + (long long)((i0 + u) * group + h) * kStride + kD));
+            if (u < kParts && i0 + u * step < expected && h < group) {
+                ml = load2(first + (long long)((i0 + u * step) * group + h) * kStride + kD);
             }
         }
 #pragma unroll
         for (int h = 0; h < kHeads; ++h) {
             float mi[kParts], li[kParts];
-            float nm = m_run[h];
+            float nm = st.m[h];
 #pragma unroll
             for (int u = 0; u < kParts; ++u) {
                 mi[u] = __shfl_sync(0xffffffffu, ml.x, u * kHeads + h);
@@ -148,39 +171,46 @@ __device__ __forceinline__ void warp_combine_impl(const float *first, int expect
                 nm = fmaxf(nm, mi[u]);
             }
             const float ref = nm == -INFINITY ? 0.f : nm;
-            const float sc = fast_exp2(m_run[h] - ref); // 2^(-inf) = 0 on the first round
-            l_run[h] *= sc;
-            o_run[h].x *= sc;
-            o_run[h].y *= sc;
-            o_run[h].z *= sc;
-            o_run[h].w *= sc;
+            const float sc = fast_exp2(st.m[h] - ref); // 2^(-inf) = 0 on the first round
+            st.l[h] *= sc;
+            st.o[h].x *= sc;
+            st.o[h].y *= sc;
+            st.o[h].z *= sc;
+            st.o[h].w *= sc;
 #pragma unroll
             for (int u = 0; u < kParts; ++u) {
                 const float w = fast_exp2(mi[u] - ref);
-                l_run[h] = fmaf(li[u], w, l_run[h]);
-                o_run[h].x = fmaf(v[u][h].x, w, o_run[h].x);
-                o_run[h].y = fmaf(v[u][h].y, w, o_run[h].y);
-                o_run[h].z = fmaf(v[u][h].z, w, o_run[h].z);
-                o_run[h].w = fmaf(v[u][h].w, w, o_run[h].w);
+                st.l[h] = fmaf(li[u], w, st.l[h]);
+                st.o[h].x = fmaf(v[u][h].x, w, st.o[h].x);
+                st.o[h].y = fmaf(v[u][h].y, w, st.o[h].y);
+                st.o[h].z = fmaf(v[u][h].z, w, st.o[h].z);
+                st.o[h].w = fmaf(v[u][h].w, w, st.o[h].w);
             }
-            m_run[h] = nm;
+            st.m[h] = nm;
         }
     }
-    __syncwarp(); // every lane has consumed its loads: `part` may lie over the partials just read
+}
+
+// Normalises a finished merge and stores it: rows of the K/V dtype into `out`, or (part != nullptr) rows of d + 2
+// floats (o, m in natural-log units, l).
+template <bool kBf16, int kHeads>
+__device__ __forceinline__ void warp_merge_store(const MergeState<kHeads> &st, int group, int lane, void *out, float *part,
+                                                 long long out_row0) {
+    constexpr int kD = 128, kOutStride = kD + 2;
 #pragma unroll
     for (int h = 0; h < kHeads; ++h) {
         if (h < group) {
             const long long row = out_row0 + h;
-            const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
-            const float r[4] = {o_run[h].x * inv, o_run[h].y * inv, o_run[h].z * inv, o_run[h].w * inv};
+            const float inv = st.l[h] > 0.f ? 1.f / st.l[h] : 0.f;
+            const float r[4] = {st.o[h].x * inv, st.o[h].y * inv, st.o[h].z * inv, st.o[h].w * inv};
             if (part != nullptr) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     part[row * kOutStride + lane * 4 + e] = r[e];
                 }
                 if (lane == 0) {
-                    part[row * kOutStride + kD] = m_run[h] * 0.6931471805599453f; // log2 units -> natural log
-                    part[row * kOutStride + kD + 1] = l_run[h];
+                    part[row * kOutStride + kD] = st.m[h] * 0.6931471805599453f; // log2 units -> natural log
+                    part[row * kOutStride + kD + 1] = st.l[h];
                 }
             } else {
 #pragma unroll
@@ -192,6 +222,33 @@ __device__ __forceinline__ void warp_combine_impl(const float *first, int expect
     }
 }
 
+// Leaves an unfinished merge as one more "part" (same layout as a partial result: o[128], m, l per head, rows of 132
+// floats) at `dst`, shared or global memory: for merges that several warps share.
+template <int kHeads>
+__device__ __forceinline__ void warp_merge_stash(const MergeState<kHeads> &st, int group, int lane, float *dst) {
+    constexpr int kD = 128, kStride = kD + 4;
+#pragma unroll
+    for (int h = 0; h < kHeads; ++h) {
+        if (h < group) {
+            *reinterpret_cast<float4 *>(dst + h * kStride + lane * 4) = st.o[h];
+            if (lane == 0) {
+                dst[h * kStride + kD] = st.m[h];
+                dst[h * kStride + kD + 1] = st.l[h];
+            }
+        }
+    }
+}
+
+template <bool kBf16, int kHeads, int kParts>
+__device__ __forceinline__ void warp_combine_impl(const float *first, int expected, int group, int lane, void *out,
+                                                  float *part, long long out_row0) {
+    MergeState<kHeads> st;
+    st.clear();
+    warp_merge_parts<kHeads, kParts, false>(st, first, expected, 0, 1, group, lane);
+    __syncwarp(); // every lane has consumed its loads: `part` may lie over the partials just read
+    warp_merge_store<kBf16, kHeads>(st, group, lane, out, part, out_row0);
+}
+
 template <bool kBf16>
 __device__ __forceinline__ void warp_combine_partials(const float *first, int expected, int group, int lane, void *out,
                                                       float *part, long long out_row0) {
@@ -201,6 +258,55 @@ __device__ __forceinline__ void warp_combine_partials(const float *first, int ex
         warp_combine_impl<kBf16, 6, 4>(first, expected, group, lane, out, part, out_row0);
     } else {
         warp_combine_impl<kBf16, 8, 2>(first, expected, group, lane, out, part, out_row0);
+    }
+}
+
+// A merge shared by n_warps warps of one CTA (for pairs cut into many pieces: one long sequence on a whole GPU leaves
+// dozens of partials per pair, and one warp merges them four per round trip). Warp w folds parts w, w + n_warps, ...
+// and leaves its unfinished state as part w of `stash` (global memory of the CTA's own, n_warps x group x 132 floats);
+// after a barrier over the warps, one of them folds the n_warps stashed states and stores the result. Which warp takes which parts is
+// fixed, so the bits do not depend on timing.
+template <bool kBf16>
+__device__ __forceinline__ void warp_merge_share(const float *first, int expected, int w, int n_warps, int group, int lane,
+                                                 float *stash) {
+    constexpr int kStride = 132;
+    float *dst = stash + (long long)w * group * kStride;
+    if (group <= 4) {
+        MergeState<4> st;
+        st.clear();
+        warp_merge_parts<4, 4, false>(st, first, expected, w, n_warps, group, lane);
+        warp_merge_stash<4>(st, group, lane, dst);
+    } else if (group <= 6) {
+        MergeState<6> st;
+        st.clear();
+        warp_merge_parts<6, 4, false>(st, first, expected, w, n_warps, group, lane);
+        warp_merge_stash<6>(st, group, lane, dst);
+    } else {
+        MergeState<8> st;
+        st.clear();
+        warp_merge_parts<8, 2, false>(st, first, expected, w, n_warps, group, lane);
+        warp_merge_stash<8>(st, group, lane, dst);
+    }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ void warp_merge_finish(const float *stash, int n_warps, int group, int lane, void *out, float *part,
+                                                  long long out_row0) {
+    if (group <= 4) {
+        MergeState<4> st;
+        st.clear();
+        warp_merge_parts<4, 4, false>(st, stash, n_warps, 0, 1, group, lane);
+        warp_merge_store<kBf16, 4>(st, group, lane, out, part, out_row0);
+    } else if (group <= 6) {
+        MergeState<6> st;
+        st.clear();
+        warp_merge_parts<6, 4, false>(st, stash, n_warps, 0, 1, group, lane);
+        warp_merge_store<kBf16, 6>(st, group, lane, out, part, out_row0);
+    } else {
+        MergeState<8> st;
+        st.clear();
+        warp_merge_parts<8, 2, false>(st, stash, n_warps, 0, 1, group, lane);
+        warp_merge_store<kBf16, 8>(st, group, lane, out, part, out_row0);
     }
 }
 
