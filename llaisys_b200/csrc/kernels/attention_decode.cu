@@ -510,10 +510,12 @@ int decode_grid_size(int32_t n_seqs, int32_t nkvh, int32_t max_kv_len) {
     const long long by_work = (pages_bound + kPagesPerStage - 1) / kPagesPerStage; // at least one stage per CTA
     // Few (sequence, kv-head) pairs: every CTA that cuts a pair adds a partial result, and the pair's last CTA merges
     // them four per dependent round trip (about a microsecond each). With P pairs and H page-heads of 8 KiB, n CTAs
-    // stream for about H * 8 KiB / (n * 22 GB/s) and merge for about n / (4 P) us: least at n = sqrt(1.5 P H).
+    // stream for about H * 8 KiB / (n * 22 GB/s) and merge for about n / (4 P) us: least near n = sqrt(1.5 P H); swept on
+    // one to four sequences of 4096 to 131072 tokens, sqrt(P H) measured best (17 / 29 / 44 us for one sequence of 16384 /
+    // 65536 / 131072 tokens).
     // Measured on one 16384-token sequence: 47.8 us with the full grid, 19.4 us with 64 CTAs. Batches with many pairs
     // reach the cap as before.
-    const double balanced = std::sqrt(1.5 * double(n_seqs) * double(nkvh) * double(pages_bound));
+    const double balanced = std::sqrt(1.0 * double(n_seqs) * double(nkvh) * double(pages_bound));
     const long long by_merge = (long long)std::ceil(balanced);
     const long long cap = (long long)kCtasPerSm * sm_count();
     const long long want = by_work < by_merge ? by_work : by_merge;
