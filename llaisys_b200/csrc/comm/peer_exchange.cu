@@ -84,12 +84,19 @@ __global__ void peer_merge_kernel(T *__restrict__ out, unsigned char *local_base
     if (row < n_rows) {
         const uint2 *parts = reinterpret_cast<const uint2 *>(local_base) + size_t(step & 1u) * world * slot_floats;
         const uint2 *base = parts + size_t(row) * (d + 2);
+        // Every word a lane needs in one batch (4 dims x 8 ranks) is REQUESTED before any of them is looked at, and a
+        // batch with a word still missing is asked for again as a whole: a word that has arrived costs one round trip to
+        // L2 whether it is asked for alone or with thirty others, and taking them one after the other made the merge of
+        // eight ranks' rows cost thirty-four such trips in a row.
         // (m, l) of every rank: lane p fetches rank p's pair, the warp shares them
         float m_mine = -INFINITY, l_mine = 0.f;
         if (lane < world) {
-            m_mine = wait_word(base + size_t(lane) * slot_floats + d, step, spin_limit, gave_up, error_word);
-            l_mine = wait_word(base + size_t(lane) * slot_floats + d + 1, step, spin_limit, gave_up, error_word);
+            const uint2 *at = base + size_t(lane) * slot_floats + d;
+            const uint2 wm = load_word(at), wl = load_word(at + 1);
+            m_mine = wm.y == step ? __uint_as_float(wm.x) : wait_word(at, step, spin_limit, gave_up, error_word);
+            l_mine = wl.y == step ? __uint_as_float(wl.x) : wait_word(at + 1, step, spin_limit, gave_up, error_word);
         }
+        __syncwarp();
         float m_all = -INFINITY;
         for (int p = 0; p < world; ++p) {
             const float l = __shfl_sync(0xffffffffu, l_mine, p), m = __shfl_sync(0xffffffffu, m_mine, p);
@@ -105,18 +112,69 @@ __global__ void peer_merge_kernel(T *__restrict__ out, unsigned char *local_base
             }
         }
         const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-        for (int dim0 = 0; dim0 < d; dim0 += 32) { // uniform trip count: the shuffles below need the whole warp
-            const int dim = dim0 + lane;
-            float o = 0.f;
-            for (int p = 0; p < world; ++p) {
-                const float l = __shfl_sync(0xffffffffu, l_mine, p), m = __shfl_sync(0xffffffffu, m_mine, p);
-                if (l > 0.f && dim < d) {
-                    const float v = wait_word(base + size_t(p) * slot_floats + dim, step, spin_limit, gave_up, error_word);
-                    o = fmaf(l * expf(m - m_all), v, o);
+        constexpr int kDimsAtOnce = 4, kRanksAtOnce = 8;
+        for (int dim_first = 0; dim_first < d; dim_first += kDimsAtOnce * 32) { // uniform trip counts: shuffles inside
+            float o[kDimsAtOnce];
+#pragma unroll
+            for (int a = 0; a < kDimsAtOnce; ++a) {
+                o[a] = 0.f;
+            }
+            for (int p_first = 0; p_first < world; p_first += kRanksAtOnce) {
+                float weight[kRanksAtOnce]; // 0 for a rank that saw no key (its words are not waited for) and past the last rank
+#pragma unroll
+                for (int b = 0; b < kRanksAtOnce; ++b) {
+                    const int p = min(p_first + b, world - 1);
+                    const float l = __shfl_sync(0xffffffffu, l_mine, p), m = __shfl_sync(0xffffffffu, m_mine, p);
+                    weight[b] = (p_first + b < world && l > 0.f) ? l * expf(m - m_all) : 0.f;
+                }
+                uint2 w[kDimsAtOnce][kRanksAtOnce];
+                for (uint32_t spins = 0;;) {
+                    bool missing = false;
+#pragma unroll
+                    for (int a = 0; a < kDimsAtOnce; ++a) {
+#pragma unroll
+                        for (int b = 0; b < kRanksAtOnce; ++b) {
+                            const int dim = dim_first + a * 32 + lane;
+                            w[a][b] = make_uint2(0u, step);
+                            if (dim < d && weight[b] != 0.f) {
+                                w[a][b] = load_word(base + size_t(p_first + b) * slot_floats + dim);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int a = 0; a < kDimsAtOnce; ++a) {
+#pragma unroll
+                        for (int b = 0; b < kRanksAtOnce; ++b) {
+                            missing = missing || w[a][b].y != step;
+                        }
+                    }
+                    if (!missing || gave_up) {
+                        break;
+                    }
+                    if (++spins > spin_limit) {
+                        gave_up = true;
+                        atomicOr(error_word, kErrPeerTimeout);
+                        break;
+                    }
+                    __nanosleep(100);
+                }
+                // ranks in their order, one chain per dim: the sums are those of the library's LSE merge
+#pragma unroll
+                for (int b = 0; b < kRanksAtOnce; ++b) {
+#pragma unroll
+                    for (int a = 0; a < kDimsAtOnce; ++a) {
+                        if (weight[b] != 0.f) {
+                            o[a] = fmaf(weight[b], __uint_as_float(w[a][b].x), o[a]);
+                        }
+                    }
                 }
             }
-            if (dim < d) {
-                out[size_t(row) * d + dim] = kernels::from_f32<T>(o * inv);
+#pragma unroll
+            for (int a = 0; a < kDimsAtOnce; ++a) {
+                const int dim = dim_first + a * 32 + lane;
+                if (dim < d) {
+                    out[size_t(row) * d + dim] = kernels::from_f32<T>(o[a] * inv);
+                }
             }
         }
     }
@@ -146,7 +204,8 @@ PeerExchange::PeerExchange(int rank, int world, size_t slot_floats) : _rank(rank
     const size_t slots_bytes = 2 * size_t(world) * slot_floats * sizeof(uint2); // a word per float: value and step
     _epoch_offset = align_up(slots_bytes, 256);
     _error_offset = _epoch_offset + 256;
-    _bytes = _error_offset + 256;
+    _table_offset = _error_offset + 256; // every rank's buffer as THIS rank maps it (read by the decode kernel)
+    _bytes = _table_offset + align_up(size_t(kMaxPeers) * sizeof(void *), 256);
     cuda_ok(cudaMalloc(&_base, _bytes), "peer exchange: cudaMalloc");
     cuda_ok(cudaMemset(_base, 0, _bytes), "peer exchange: cudaMemset");
     cuda_ok(cudaMalloc(&_local_part, slot_floats * sizeof(float)), "peer exchange: cudaMalloc");
@@ -155,6 +214,9 @@ PeerExchange::PeerExchange(int rank, int world, size_t slot_floats) : _rank(rank
     _peer.assign(size_t(world), nullptr);
     _peer[size_t(rank)] = _base;
     _connected = world == 1;
+    if (_connected) {
+        writeTable();
+    }
 }
 
 void PeerExchange::disconnect() {
@@ -203,7 +265,13 @@ void PeerExchange::connect(const void *handles) {
         cuda_ok(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess), "peer exchange: cudaIpcOpenMemHandle");
         _peer[size_t(p)] = static_cast<unsigned char *>(mapped);
     }
+    writeTable();
     _connected = true;
+}
+
+void PeerExchange::writeTable() {
+    cuda_ok(cudaMemcpy(_base + _table_offset, _peer.data(), size_t(_world) * sizeof(unsigned char *), cudaMemcpyHostToDevice),
+            "peer exchange: cudaMemcpy");
 }
 
 kernels::PeerSink PeerExchange::sink() const {
@@ -211,9 +279,9 @@ kernels::PeerSink PeerExchange::sink() const {
         fail(LLAISYS_E_INVALID, "peer exchange: connect() has not been called");
     }
     kernels::PeerSink k;
-    for (int p = 0; p < _world; ++p) {
-        k.base[p] = _peer[size_t(p)];
-    }
+    k.table = reinterpret_cast<unsigned char *const *>(_base + _table_offset);
+    k.own = _base;
+    k.rows = _local_part;
     k.world = _world;
     k.rank = _rank;
     k.slot_floats = _slot_floats;

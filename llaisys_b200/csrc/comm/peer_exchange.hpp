@@ -69,7 +69,8 @@ private:
     unsigned char *_base = nullptr;      // this rank's allocation
     float *_local_part = nullptr;        // separate allocation: the decode kernel's output
     std::vector<unsigned char *> _peer;  // mapped bases, [_rank] = _base
-    size_t _epoch_offset = 0, _error_offset = 0, _bytes = 0;
+    size_t _epoch_offset = 0, _error_offset = 0, _table_offset = 0, _bytes = 0;
+    void writeTable();
     uint32_t _spin_limit = 2u << 20;
 };
 

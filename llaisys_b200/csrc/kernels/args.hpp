@@ -65,13 +65,16 @@ struct AttnOut {
     const struct PeerSink *peers = nullptr; // decode over a page pool only: partial rows go to exchange slots instead
 };
 
-// Exchange buffers of a KV-range split across the GPUs of a node, as rank `rank` sees them: base[r] is rank r's buffer
-// (peer memory for r != rank). A buffer holds 2 (step parity) x world slots of slot_floats 8-byte words -- slot s of
-// parity p is written by rank s; a word is a float and, beside it, the number of the step it belongs to, so that a
-// reader can tell a current value from a stale one without any flag or fence -- then, at epoch_offset bytes, the step
-// counter (merges completed).
+// Exchange buffers of a KV-range split across the GPUs of a node, as rank `rank` sees them: table[r] (an array in
+// device memory) is rank r's buffer, peer memory for r != rank, and `own` is table[rank]. A buffer holds 2 (step
+// parity) x world slots of slot_floats 8-byte words -- slot s of parity p is written by rank s; a word is a float and,
+// beside it, the number of the step it belongs to, so that a reader can tell a current value from a stale one without
+// any flag or fence -- then, at epoch_offset bytes, the step counter (merges completed). `rows` is local memory for
+// this rank's rows [n_rows][d + 2] on their way out: the kernel completes a row there and copies it to every rank.
 struct PeerSink {
-    unsigned char *base[16] = {};
+    unsigned char *const *table = nullptr;
+    unsigned char *own = nullptr;
+    float *rows = nullptr;
     int32_t world = 0, rank = 0;
     size_t slot_floats = 0, epoch_offset = 0;
 };

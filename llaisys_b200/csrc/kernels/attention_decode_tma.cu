@@ -93,27 +93,54 @@ struct TmaDecodeParams {
     PeerSink xchg;
 };
 
-constexpr int kMaxXchg = int(sizeof(PeerSink::base) / sizeof(PeerSink::base[0]));
+constexpr int kMaxXchg = 16; // ranks of one exchange
 
 // The device-side step counter of the exchange: the number of merges completed so far. This launch belongs to the next.
 __device__ __forceinline__ uint32_t xchg_step(const TmaDecodeParams &p) {
-    return __ldcg(reinterpret_cast<const uint32_t *>(p.xchg.base[p.xchg.rank] + p.xchg.epoch_offset)) + 1u;
+    return __ldcg(reinterpret_cast<const uint32_t *>(p.xchg.own + p.xchg.epoch_offset)) + 1u;
 }
 
-// One float of a partial row: into the plain array, or -- with the step beside it -- into this rank's slot of every
-// rank's buffer (an aligned 8-byte store is one transaction: value and step arrive together).
-template <bool kXchg>
-__device__ __forceinline__ void put_part(const TmaDecodeParams &p, uint32_t step, long long idx, float v) {
-    if constexpr (!kXchg) {
-        p.part[idx] = v;
-        return;
+// Exchange mode: n floats of this rank's finished rows, rows[first .. first + n), go -- each with the step beside it, as
+// one aligned 8-byte store: value and step arrive together -- into this rank's slot of EVERY rank's buffer. Called by one
+// whole warp. Functions of their own on purpose: written into the kernel, the loop over the ranks and its volatile
+// stores changed the code of the consumer warps around them, and the exchange instantiation streamed pages 1.8 times
+// slower than the ordinary one. Sixteen values are fetched before the first is sent: no load passes a volatile store,
+// and one trip to L2 per value would make this the longest step of a short launch.
+__device__ __noinline__ void xchg_send_rows(unsigned char *const *table, int world, long long slot_at, const float *rows,
+                                            long long first, int n, uint32_t step, int lane) {
+    constexpr int kAtOnce = 16;
+    for (int i0 = 0; i0 < n; i0 += kAtOnce * 32) {
+        float vals[kAtOnce];
+#pragma unroll
+        for (int u = 0; u < kAtOnce; ++u) {
+            const int i = i0 + u * 32 + lane;
+            vals[u] = i < n ? __ldcg(rows + first + i) : 0.f;
+        }
+        for (int pe = 0; pe < world; ++pe) {
+            uint2 *dst = reinterpret_cast<uint2 *>(__ldg(reinterpret_cast<const unsigned long long *>(table) + pe)) + slot_at + first;
+#pragma unroll
+            for (int u = 0; u < kAtOnce; ++u) {
+                const int i = i0 + u * 32 + lane;
+                if (i < n) {
+                    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};\n" ::"l"(dst + i), "r"(__float_as_uint(vals[u])),
+                                 "r"(step)
+                                 : "memory");
+                }
+            }
+        }
     }
-    const long long at = ((long long)(step & 1u) * p.xchg.world + p.xchg.rank) * (long long)p.xchg.slot_floats + idx;
-    for (int pe = 0; pe < p.xchg.world; ++pe) {
-        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};\n" ::"l"(reinterpret_cast<uint2 *>(p.xchg.base[pe]) + at),
+}
+// One value (the rows of a sequence without tokens, written by whichever thread owns the dimension).
+__device__ __noinline__ void xchg_send_one(unsigned char *const *table, int world, long long at, float v, uint32_t step) {
+    for (int pe = 0; pe < world; ++pe) {
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};\n" ::"l"(reinterpret_cast<uint2 *>(__ldg(reinterpret_cast<const unsigned long long *>(table) + pe)) + at),
                      "r"(__float_as_uint(v)), "r"(step)
                      : "memory");
     }
+}
+// Word index of this rank's slot (of the step's parity) in every rank's buffer.
+__device__ __forceinline__ long long xchg_slot_at(const TmaDecodeParams &p, uint32_t step) {
+    return ((long long)(step & 1u) * p.xchg.world + p.xchg.rank) * (long long)p.xchg.slot_floats;
 }
 
 struct Cursor {
@@ -196,7 +223,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const uint32_t stage_u32 = (smem_u32(rows + p.n_seqs) + 15u) & ~15u;
     __shared__ int s_abort;
     __shared__ int s_verdict; // shared merge: 1 = this CTA arrived last at its final pair and every warp takes a share
-    __shared__ uint32_t s_step; // exchange mode: the step this launch belongs to (written by consumer thread 0)
     const uint32_t bars_u32 = smem_u32(bars);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -252,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     const long long x0 = (long long)blockIdx.x * span;
     const long long x1 = min(total, x0 + span);
 
-    const bool partial = kXchg || p.part != nullptr;
+    const bool partial = p.part != nullptr; // (exchange mode: the rows on their way out, PeerSink::rows)
     // -- sequences without any token: the output row is zero (partial: o = 0, m = -inf, l = 0). Called by threads
     //    0..127 at least, after their grid_dependency_wait.
     auto write_empty_pairs = [&]() {
@@ -267,11 +293,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             }
             for (int h = 0; h < p.group; ++h) {
                 const long long row = (long long)s * p.nh + kvh * p.group + h;
-                if (partial) {
-                    put_part<kXchg>(p, step, row * (kD + 2) + tid, 0.f);
+                if constexpr (kXchg) {
+                    const long long at = xchg_slot_at(p, step) + row * (kD + 2);
+                    xchg_send_one(p.xchg.table, p.xchg.world, at + tid, 0.f, step);
                     if (tid == 0) {
-                        put_part<kXchg>(p, step, row * (kD + 2) + kD, -INFINITY);
-                        put_part<kXchg>(p, step, row * (kD + 2) + kD + 1, 0.f);
+                        xchg_send_one(p.xchg.table, p.xchg.world, at + kD, -INFINITY, step);
+                        xchg_send_one(p.xchg.table, p.xchg.world, at + kD + 1, 0.f, step);
+                    }
+                } else if (partial) {
+                    p.part[row * (kD + 2) + tid] = 0.f;
+                    if (tid == 0) {
+                        p.part[row * (kD + 2) + kD] = -INFINITY;
+                        p.part[row * (kD + 2) + kD + 1] = 0.f;
                     }
                 } else {
                     store_out<kBf16>(p.out, row * kD + tid, 0.f);
@@ -392,7 +425,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             const long long pair_off = (long long)cum[sg.s] * p.nkvh + (long long)sg.kvh * pair_np;
             const int c_first = int(pair_off / span), c_last = int((pair_off + pair_np - 1) / span);
             const int expected = c_last - c_first + 1;
-            if (expected == 1) {
+            if (expected == 1 && !kXchg) {
                 continue; // the consumers wrote the final output themselves
             }
             if (!wait_or_abort(epi_ready, uint32_t(k) & 1u, &s_abort)) {
@@ -401,6 +434,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                     atomicOr(p.error_flag, kErrTimeout);
                 }
                 break;
+            }
+            const long long row0 = (long long)sg.s * p.nh + sg.kvh * p.group;
+            if (kXchg && expected == 1) { // the consumers have completed the pair's rows: off they go
+                xchg_send_rows(p.xchg.table, p.xchg.world, xchg_slot_at(p, step), p.part, row0 * (kD + 2), p.group * (kD + 2),
+                               step, lane);
+                if (lane == 0) {
+                    mbar_arrive(epi_done);
+                }
+                ++k;
+                continue;
             }
             int last = 0;
             if (lane == 0) {
@@ -425,8 +468,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             }
             if (last) {
                 const float *first = p.partials + (long long)(c_first + pair) * p.group * kPartStride;
-                const long long row0 = (long long)sg.s * p.nh + sg.kvh * p.group;
-                float *staged = p.partials + (long long)(c_first + pair) * p.group * kPartStride; // exchange mode only
                 if constexpr (kShare) {
                   if (shared_merge) {
                     if (helpers) {
@@ -438,27 +479,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                         }
                         __syncwarp();
                     }
-                    if constexpr (kXchg) {
-                        warp_merge_finish<kBf16>(stash, kMergeWarps, p.group, lane, nullptr, staged - row0 * (kD + 2), row0);
-                    } else {
-                        warp_merge_finish<kBf16>(stash, kMergeWarps, p.group, lane, p.out, p.part, row0);
-                    }
+                    warp_merge_finish<kBf16>(stash, kMergeWarps, p.group, lane, p.out, p.part, row0);
                   }
                 }
-                if (shared_merge) {
-                    // done above
-                } else if constexpr (kXchg) {
-                    // merged rows first into the pair's own first partial slot (every piece has been read by then; a
-                    // slot holds group x 132 floats, the rows need group x 130), then from there to every rank
-                    warp_combine_partials_call<kBf16>(first, expected, p.group, lane, nullptr, staged - row0 * (kD + 2), row0);
-                } else {
+                if (!shared_merge) {
                     warp_combine_partials<kBf16>(first, expected, p.group, lane, p.out, p.part, row0);
                 }
                 if constexpr (kXchg) {
-                    __syncwarp();
-                    for (int i = lane; i < p.group * (kD + 2); i += 32) {
-                        put_part<true>(p, step, row0 * (kD + 2) + i, __ldcg(staged + i));
-                    }
+                    __syncwarp(); // the lanes' stores of the merged rows come before the loads that send them
+                    xchg_send_rows(p.xchg.table, p.xchg.world, xchg_slot_at(p, step), p.part, row0 * (kD + 2),
+                                   p.group * (kD + 2), step, lane);
                 }
                 if (lane == 0) {
                     p.counters[pair] = 0; // ready for the next launch
@@ -488,9 +518,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
     // Only now may the successor on the stream be scheduled: whatever starts early behind this grid can then rely on
     // everything BEFORE this grid's predecessor being complete (see the overlap contract in paged_kv.h).
     grid_launch_dependents();
-    if (kXchg && tid == 0) {
-        s_step = xchg_step(p); // read by the others after the first barrier of the consumer warps
-    }
     write_empty_pairs();
     float m2[2], l[2], o_acc[8][4];
     uint32_t qf[8][2];
@@ -705,11 +732,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 const long long row = row0 + h;
                 const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
                 if (partial) {
-                    const uint32_t step = kXchg ? s_step : 0u;
-                    put_part<kXchg>(p, step, row * (kD + 2) + dim, o * inv);
+                    p.part[row * (kD + 2) + dim] = o * inv;
                     if (dim == 0) {
-                        put_part<kXchg>(p, step, row * (kD + 2) + kD, m_all * 0.6931471805599453f); // log2 units -> natural log
-                        put_part<kXchg>(p, step, row * (kD + 2) + kD + 1, l_all);
+                        p.part[row * (kD + 2) + kD] = m_all * 0.6931471805599453f; // log2 units -> natural log
+                        p.part[row * (kD + 2) + kD + 1] = l_all;
                     }
                 } else {
                     store_out<kBf16>(p.out, row * kD + dim, o * inv);
@@ -723,8 +749,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
             }
         }
 
-        if (expected > 1) {
-            // Hand the pair to the epilogue warp and carry on with the next pages. It must have finished the
+        if (expected > 1 || kXchg) {
+            // Hand the pair to the epilogue warp and carry on with the next pages (exchange mode: whole pairs too --
+            // that warp sends their rows to the other ranks). It must have finished the
             // previous cut pair first (the two barriers advance one phase per pair); that wait is normally over
             // long before, since a merge takes microseconds and a segment tens of them.
             if (n_cut > 0 && !dead && !wait_or_abort(epi_done, uint32_t(n_cut - 1) & 1u, &s_abort)) {
@@ -883,7 +910,7 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
     }
     if (out.peers != nullptr) {
         const PeerSink &x = *out.peers;
-        if (out.out != nullptr || out.part != nullptr || x.world < 1 || x.world > kMaxXchg || x.rank < 0 || x.rank >= x.world ||
+        if (out.out != nullptr || out.part != nullptr || x.table == nullptr || x.own == nullptr || x.rows == nullptr || x.world < 1 || x.world > kMaxXchg || x.rank < 0 || x.rank >= x.world ||
             size_t(batch.n_seqs) * batch.nh * (kD + 2) > x.slot_floats) {
             reason = "exchange slots: bad rank / world size, rows do not fit a slot, or another output was given too";
             return -1;
@@ -906,7 +933,7 @@ int attention_decode_tma(stream_t stream, llaisysDataType_t dtype, const KVView 
     p.nh = batch.nh;
     p.q = q;
     p.out = out.out;
-    p.part = out.part;
+    p.part = out.peers != nullptr ? out.peers->rows : out.part;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.partials = scratch.partials;
     p.counters = scratch.counters;
