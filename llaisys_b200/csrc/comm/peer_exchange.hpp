@@ -5,11 +5,13 @@
 // count of finished rows (system-scope fences cost this GPU about 20 us apiece).
 //
 // One step on rank r (all on the caller's stream, capturable in a CUDA graph):
-//   push    done by the TMA decode kernel itself (attention_decode_tma.cu, PeerSink): whichever thread finishes a value
-//           of a partial row stores its word into slot r of EVERY rank's buffer (plain peer stores). Pools the TMA kernel
+//   push    done by the TMA decode kernel itself (attention_decode_tma.cu, PeerSink): the CTA that completes a pair's
+//           rows -- alone, or as the last of the CTAs that share the pair -- stores their words into slot r of EVERY
+//           rank's buffer (plain peer stores, one warp, while the CTA's other warps stream on). Pools the TMA kernel
 //           does not serve write the partial locally and a push kernel (one CTA per destination) forwards it;
-//   merge   takes each value as soon as its word carries the step (bounded wait), log-sum-exp merges the slots; the last
-//           CTA to finish moves the device-side step counter on.
+//   merge   starts under the decode kernel (programmatic launch), asks for a row's words of all ranks at once and again
+//           until each carries the step (bounded), log-sum-exp merges the slots; the last CTA to finish moves the
+//           device-side step counter on.
 // Slots are double-buffered by the step's parity: a rank can run at most one step ahead of the slowest (its next merge
 // needs that rank's next values), so a writer never overwrites a slot that is still being merged, and a word left from
 // two steps ago carries the wrong step. No kernel waits without a limit: a wait that runs out sets the error word and

@@ -85,11 +85,12 @@ struct TmaDecodeParams {
     char *pool_k;                           // K tile of (page 0, kv-head 0) of this layer
     long long page_stride_b, head_stride_b; // bytes between pages / kv-heads
     long long v_offset_b;                   // V tile - K tile of the same (page, kv-head)
-    // KV-range split across GPUs (exchange instantiation; out and part null): every value of a partial row (o, m, l) is
-    // stored, together with the step number, as one 8-byte word into slot `rank` of EVERY rank's exchange buffer (plain
-    // stores into peer memory). The word is its own flag: the reader takes a value once the step beside it is the
-    // current one, so no fence, no flag and no count of finished pairs is needed (a system-scope fence costs this
-    // GPU about 20 us: two per launch doubled the single-sequence kernel's time).
+    // KV-range split across GPUs (exchange instantiation; out null, part = PeerSink::rows): a pair's finished rows
+    // (o, m, l) are written locally like any partial output, and the epilogue warp of the CTA that finished them then
+    // stores every value, together with the step number, as one 8-byte word into slot `rank` of EVERY rank's exchange
+    // buffer (plain stores into peer memory). The word is its own flag: the reader takes a value once the step beside
+    // it is the current one, so no fence, no flag and no count of finished pairs is needed (a system-scope fence costs
+    // this GPU about 20 us: two per launch doubled the single-sequence kernel's time).
     PeerSink xchg;
 };
 
@@ -200,8 +201,9 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
 }
 
 // kXchg: the exchange mode of a KV-range split (PeerSink) -- a separate instantiation, so that the ordinary decode
-// kernel carries none of its code (with a run-time switch the system-scope fences and peer stores, although never
-// executed, cost the ordinary kernel 2 us of 47).
+// kernel carries none of its code (with a run-time switch the peer stores, although never executed, cost the ordinary
+// kernel 2 us of 47). The two differ in the epilogue warp only: in exchange mode it is handed every pair, whole ones
+// too, and sends the rows out (xchg_send_rows); the consumer warps run the same code in both.
 // kShare: launches with few pairs for their grid, whose pairs can be in many pieces, carry the shared merge (all five
 // warps of the last-arriving CTA); the others do not even contain its code -- this kernel's timing moves by a
 // microsecond with what is compiled around its hot loop.
