@@ -34,7 +34,8 @@ struct KVView {
     // written before that previous kernel started (K/V rows, q and outputs are only touched after it completed).
     bool overlap_launch = false;
     const void *tma_desc = nullptr;      // box = K and V of a page, 64 dims (decode)
-    const void *tma_tile_desc = nullptr; // box = one half-tile: 16 slots x 64 dims (prefill)
+    const void *tma_tile_desc = nullptr; // prefill, two maps of 128 bytes: box = one half-tile, 16 slots x 64 dims (K); box = a
+                                         // tile as its two halves, 16 slots x 64 dims x 2 (V)
     int64_t tma_page0 = 0;
 };
 

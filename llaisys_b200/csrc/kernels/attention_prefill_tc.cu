@@ -446,16 +446,27 @@ __global__ void __launch_bounds__(kThreads, 2)
                         mbar_arrive_expect_tx(bar(full), uint32_t(n_pg) * 2 * 2048);
                     }
                     __syncwarp();
-                    if (lane < n_pg) {
-                        const uint32_t lo = dst + is_v * kKvOperandBytes, hi = lo + kKvHalfBytes; // dims 0-63, dims 64-127
+                    if (lane < n_pg && is_v) {
+                        // V: ONE box per page -- 64 dims x 16 tokens x the 2 halves of the row -- lands as
+                        // [half][16 tokens][128 B], which is what the MN-major B operand of P.V reads 16 keys at a time
+                        // (tokens past the end of a contiguous tensor read as 0)
+                        const uint32_t at = kv_u32 + st * kStageBytes + kKvOperandBytes + lane * (2 * 2048);
                         if (p.contiguous) {
-                            // [tokens][kv-heads][128] tensors: box = 64 dims x 1 head x 16 tokens; tokens past the end read as 0
-                            const CUtensorMap *m = is_v ? &tmap_v : &tmap;
-                            tma_load_3d(lo, m, 0, kvh, page * kPage, bar(full));
-                            tma_load_3d(hi, m, 64, kvh, page * kPage, bar(full));
+                            tma_load_4d(at, &tmap_v, 0, page * kPage, 0, kvh, bar(full));
                         } else {
-                            tma_load_4d(lo, &tmap, 0, 0, kvh, c3 + is_v, bar(full));
-                            tma_load_4d(hi, &tmap, 64, 0, kvh, c3 + is_v, bar(full));
+                            tma_load_5d(at, &tmap_v, 0, 0, 0, kvh, c3 + 1, bar(full));
+                        }
+                    } else if (lane < n_pg) {
+                        // K: the K-major B operand of Q.K^T wants the 64 keys of a block side by side in each 64-dim half,
+                        // so a page is two boxes of 64 dims x 16 tokens
+                        const uint32_t lo = dst, hi = lo + kKvHalfBytes; // dims 0-63, dims 64-127
+                        if (p.contiguous) {
+                            // [tokens][kv-heads][128] tensor: box = 64 dims x 1 head x 16 tokens; tokens past the end read as 0
+                            tma_load_3d(lo, &tmap, 0, kvh, page * kPage, bar(full));
+                            tma_load_3d(hi, &tmap, 64, kvh, page * kPage, bar(full));
+                        } else {
+                            tma_load_4d(lo, &tmap, 0, 0, kvh, c3, bar(full));
+                            tma_load_4d(hi, &tmap, 64, 0, kvh, c3, bar(full));
                         }
                     }
                 }
@@ -479,10 +490,10 @@ __global__ void __launch_bounds__(kThreads, 2)
                 const uint32_t v_u32 = kv_u32 + (gj & 1) * kStageBytes + kKvOperandBytes;
 #pragma unroll
                 for (int kk = 0; kk < kBlockN / 16; ++kk) {
-                    // B = 16 keys x 128 dims of V, MN-major: 8-key groups 1 KiB apart, the two 64-dim halves one
-                    // half-operand apart. A = P rows x 16 keys from tensor memory: 8 columns of packed pairs per
-                    // step, in S buffer gj & 1
-                    const uint64_t b = smem_desc_sw128(v_u32 + kk * 2048, kKvHalfBytes, 1024);
+                    // B = 16 keys (one page) x 128 dims of V, MN-major: 8-key groups 1 KiB apart, the page's two
+                    // 64-dim halves 2 KiB apart, pages 4 KiB apart. A = P rows x 16 keys from tensor memory: 8 columns
+                    // of packed pairs per step, in S buffer gj & 1
+                    const uint64_t b = smem_desc_sw128(v_u32 + kk * (2 * 2048), 2048, 1024);
                     umma_f16_ts(tmem_o, tmem_base + kColS + (gj & 1) * kBlockN + kk * 8, b, idesc_pv,
                                 (!first_of_fragment || kk > 0) ? 1u : 0u);
                 }
@@ -944,7 +955,7 @@ void attention_prefill_tc_scratch(size_t *floats, size_t *counters) {
     *counters = slots;
 }
 
-int make_kv_tile_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, uint32_t nkvh,
+int make_kv_tile_tensor_map(void *out_256_bytes, void *pool_base, uint64_t total_rows, uint32_t nkvh,
                             llaisysDataType_t dtype) {
     if (dtype != LLAISYS_DTYPE_BF16 && dtype != LLAISYS_DTYPE_F16) {
         return -1;
@@ -971,7 +982,23 @@ int make_kv_tile_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total
     if (rc != CUDA_SUCCESS) {
         return -1;
     }
-    memcpy(out_128_bytes, &map, sizeof(map));
+    // The second map is for V: a 5-D view [page-and-K|V][kv-head][half of the row][slot][64 elements] whose box is a whole
+    // tile as two 64-dim halves, 64 x 16 x 2 (4 KiB): one copy per page instead of two.
+    const cuuint64_t dims5[5] = {64, cuuint64_t(kPage), 2, cuuint64_t(nkvh), cuuint64_t(total_rows / (kPage * nkvh))};
+    const cuuint64_t strides5[4] = {cuuint64_t(kD * 2), 128, cuuint64_t(kPage * kD * 2), cuuint64_t(kPage * kD * 2) * nkvh};
+    const cuuint32_t box5[5] = {64, cuuint32_t(kPage), 2, 1, 1};
+    const cuuint32_t elem_strides5[5] = {1, 1, 1, 1, 1};
+    CUtensorMap map_v;
+    const CUresult rc_v =
+        encode(&map_v, dtype == LLAISYS_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+               pool_base, dims5, strides5, box5, elem_strides5, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc_v != CUDA_SUCCESS) {
+        return -1;
+    }
+    static_assert(sizeof(CUtensorMap) == 128, "two maps in 256 bytes");
+    memcpy(out_256_bytes, &map, sizeof(map));
+    memcpy(static_cast<unsigned char *>(out_256_bytes) + sizeof(map), &map_v, sizeof(map_v));
     return 0;
 }
 
@@ -989,6 +1016,21 @@ bool contiguous_kv_map(CUtensorMap *out, const void *base, const KVView &kv, uin
     const cuuint32_t box[3] = {64, 1, cuuint32_t(kPage)};
     const cuuint32_t elem_strides[3] = {1, 1, 1};
     return encode(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base),
+                  dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The same tensor for V: 4-D (64 dims, tokens, half of the row, kv-head) with a box of 64 x 16 x 2 x 1, one copy per 16 tokens.
+bool contiguous_v_map(CUtensorMap *out, const void *base, const KVView &kv, uint64_t tokens, bool bf16) {
+    EncodeTiledFn encode = prefill_encode_fn();
+    if (encode == nullptr || tokens == 0 || tokens >= (uint64_t(1) << 31)) {
+        return false;
+    }
+    const cuuint64_t dims[4] = {64, cuuint64_t(tokens), 2, cuuint64_t(kv.nkvh)};
+    const cuuint64_t strides[3] = {cuuint64_t(kv.token_stride) * 2, 128, cuuint64_t(kv.head_stride) * 2};
+    const cuuint32_t box[4] = {64, cuuint32_t(kPage), 2, 1};
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    return encode(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void *>(base),
                   dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -1049,9 +1091,9 @@ int attention_prefill_tc(stream_t stream, llaisysDataType_t dtype, const KVView 
     CUtensorMap tmap, tmap_v;
     if (paged) {
         memcpy(&tmap, kv.tma_tile_desc, sizeof(tmap));
-        tmap_v = tmap;
+        memcpy(&tmap_v, static_cast<const unsigned char *>(kv.tma_tile_desc) + sizeof(tmap), sizeof(tmap_v));
     } else if (!contiguous_kv_map(&tmap, kv.k_base, kv, uint64_t(batch.const_kv_len), bf16) ||
-               !contiguous_kv_map(&tmap_v, kv.v_base, kv, uint64_t(batch.const_kv_len), bf16)) {
+               !contiguous_v_map(&tmap_v, kv.v_base, kv, uint64_t(batch.const_kv_len), bf16)) {
         return -1;
     }
     auto s = static_cast<cudaStream_t>(stream);

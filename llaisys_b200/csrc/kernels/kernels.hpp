@@ -122,7 +122,8 @@ int make_kv_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows
 int attention_prefill_tc(stream_t stream, llaisysDataType_t dtype, const KVView &kv, const AttnBatch &batch,
                          const void *q, float scale, const AttnOut &out, const AttnScratch &scratch);
 void attention_prefill_tc_scratch(size_t *floats, size_t *counters);
-int make_kv_tile_tensor_map(void *out_128_bytes, void *pool_base, uint64_t total_rows, uint32_t nkvh,
+// Two maps, 128 bytes each: the half-tile map (K) and the whole-tile-as-two-halves map (V).
+int make_kv_tile_tensor_map(void *out_256_bytes, void *pool_base, uint64_t total_rows, uint32_t nkvh,
                             llaisysDataType_t dtype);
 
 // K3: out[r, :] = sum_p w_p o_p[r, :] / sum_p w_p, w_p = l_p exp(m_p - max_p m_p), over n_parts partials laid out

@@ -181,7 +181,7 @@ private:
 
     // TMA view of the pool (NVIDIA, 16-bit, head_dim 128, page 16 only); _has_tma is false otherwise
     alignas(64) unsigned char _tma_desc[128] = {};      // decode: box = K and V of a page
-    alignas(64) unsigned char _tma_tile_desc[128] = {}; // prefill: box = one half-tile
+    alignas(64) unsigned char _tma_tile_desc[256] = {}; // prefill, two maps: box = one half-tile (K); box = one tile as two halves (V)
     bool _has_tma = false, _has_tma_tile = false;
     bool _overlap = false; // launch append / decode with programmatic stream serialisation
     int _last_kernel = 0;
