@@ -55,7 +55,7 @@ METRIC = "decode tokens/s (paged KV append + flash-decoding attention, one layer
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the step kernel (mean of two captured launches), from
 # `ncu --set full -k regex:paged_decode_tma -s 4 -c 2` over `bench.py --quick --steps 3 --warmup 3 --layers 2
 # [--workload config2]`: a profiler reading, taken once per kernel change, not measured by this run.
-NCU_TRAFFIC_BYTES = {"north_star": 274_092_928, "config2": 72_993_920}
+NCU_TRAFFIC_BYTES = {"north_star": 273_638_912, "config2": 73_196_160}
 MIN_REPEATS = 30
 
 
