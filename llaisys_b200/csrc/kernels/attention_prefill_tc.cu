@@ -87,6 +87,10 @@ constexpr int kPartialFloats = kBlockM * kD + 2 * kBlockM;
 // Merging one partial costs its reader about as much as kMergeCostBlocks blocks (64 KiB from L2 by one CTA);
 // pieces shorter than sqrt(kMergeCostBlocks * longest tile) blocks would spend more on merging than they save.
 constexpr float kMergeCostBlocks = 2.7f;
+// What a tile costs besides its blocks -- loading its Q rows, draining the pipeline, normalising and storing (or parking)
+// its rows -- in units of one block's time. The line that is cut into equal pieces counts every tile as its blocks plus
+// this many units, so a CTA whose piece is made of many short tiles gets fewer blocks than one inside a long tile.
+constexpr int kTileCost = 5;
 
 // barrier indices
 enum : int {
@@ -152,10 +156,11 @@ __device__ __forceinline__ SeqGeom seq_geom(const PrefillParams &p, int a) {
 __device__ __forceinline__ int tile_kv_hi(const SeqGeom &g, int qb) { return min(g.kv_len, qb * kBlockM + kBlockM + g.off); }
 __device__ __forceinline__ int tile_blocks(const SeqGeom &g, int qb) { return (tile_kv_hi(g, qb) + kBlockN - 1) / kBlockN; }
 
+// units of the line that a sequence takes: per tile its blocks, then kTileCost units that stand for no block
 __device__ __forceinline__ int seq_blocks(const PrefillParams &p, const SeqGeom &g) {
     int per_head = 0;
     for (int qb = 0; qb < g.n_qb; ++qb) {
-        per_head += tile_blocks(g, qb);
+        per_head += tile_blocks(g, qb) + kTileCost;
     }
     return per_head * p.nh;
 }
@@ -175,29 +180,42 @@ struct Fragment {
     int tile_begin; // index on the line of the tile's block 0
 };
 
-__device__ __forceinline__ Fragment locate(const PrefillParams &p, Walker &w, int pos, int piece_end) {
-    while (pos >= w.seq_begin + w.n_blocks && w.a + 1 < p.n_seqs) {
-        w.seq_begin += w.n_blocks;
-        ++w.a;
-        w.g = seq_geom(p, w.a);
-        w.n_blocks = seq_blocks(p, w.g);
+// The fragment that starts at or after unit `pos` of the line and before piece_end: `pos` moves on to its first block
+// (over the units at a tile's end that stand for no block). False when the piece holds no further block.
+__device__ __forceinline__ bool locate(const PrefillParams &p, Walker &w, int &pos, int piece_end, Fragment &f) {
+    while (pos < piece_end) {
+        while (pos >= w.seq_begin + w.n_blocks && w.a + 1 < p.n_seqs) {
+            w.seq_begin += w.n_blocks;
+            ++w.a;
+            w.g = seq_geom(p, w.a);
+            w.n_blocks = seq_blocks(p, w.g);
+        }
+        int x = pos - w.seq_begin;
+        int qb = 0, nb = tile_blocks(w.g, 0);
+        while (x >= (nb + kTileCost) * p.nh && qb + 1 < w.g.n_qb) {
+            x -= (nb + kTileCost) * p.nh;
+            ++qb;
+            nb = tile_blocks(w.g, qb);
+        }
+        const int h = min(x / (nb + kTileCost), p.nh - 1);
+        const int b0 = x - h * (nb + kTileCost);
+        if (b0 >= nb + kTileCost) {
+            return false; // (past the end of the line: no caller asks)
+        }
+        if (b0 >= nb) { // behind the tile's last block: on to the next tile
+            pos += nb + kTileCost - b0;
+            continue;
+        }
+        f.a = w.a;
+        f.qb = qb;
+        f.h = h;
+        f.b0 = b0;
+        f.tile_nblk = nb;
+        f.b1 = min(nb, b0 + (piece_end - pos));
+        f.tile_begin = pos - b0;
+        return true;
     }
-    Fragment f;
-    f.a = w.a;
-    int x = pos - w.seq_begin;
-    int qb = 0, nb = tile_blocks(w.g, 0);
-    while (x >= nb * p.nh && qb + 1 < w.g.n_qb) {
-        x -= nb * p.nh;
-        ++qb;
-        nb = tile_blocks(w.g, qb);
-    }
-    f.qb = qb;
-    f.h = min(x / nb, p.nh - 1);
-    f.b0 = x - f.h * nb;
-    f.tile_nblk = nb;
-    f.b1 = min(nb, f.b0 + (piece_end - pos));
-    f.tile_begin = pos - f.b0;
-    return f;
+    return false;
 }
 
 // Blackwell's wider scalar arithmetic for the softmax rows: a three-input maximum and two-wide f32 multiply-add / add
@@ -281,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     const int n_slots = int(gridDim.x);
     const int min_piece = int(ceilf(sqrtf(kMergeCostBlocks * float(longest_tile))));
-    const int piece = max((line_blocks + n_slots - 1) / n_slots, max(min_piece, 1)); // blocks per CTA
+    const int piece = max((line_blocks + n_slots - 1) / n_slots, max(min_piece, kTileCost + 1)); // units per CTA
     const int slot = int(blockIdx.x);
     const int piece_begin = slot * piece;
     if (piece_begin >= line_blocks) {
@@ -327,6 +345,14 @@ __global__ void __launch_bounds__(kThreads, 2)
     walker.seq_begin = s_sched[13];
     walker.g = seq_geom(p, walker.a);
     walker.n_blocks = seq_blocks(p, walker.g);
+    Fragment first_fragment;
+    Walker first_walker = walker;
+    {
+        int pos0 = piece_begin;
+        if (!locate(p, first_walker, pos0, piece_end, first_fragment)) {
+            return; // the piece holds no block (the line's last units): uniform over the CTA, nothing set up yet
+        }
+    }
 
     auto load_q = [&](const Fragment &f, const SeqGeom &g, int first, int stride) {
         // Q rows of the tile, 16 bytes per store, into the K-major 128-byte-swizzled layout
@@ -373,9 +399,7 @@ __global__ void __launch_bounds__(kThreads, 2)
         tmem_relinquish();
     }
     {
-        Walker w0 = walker;
-        const Fragment f0 = locate(p, w0, piece_begin, piece_end);
-        load_q(f0, w0.g, tid, kThreads);
+        load_q(first_fragment, first_walker.g, tid, kThreads);
         // A block shorter than kBlockN keys leaves ring rows unwritten; they are masked out of S, but V rows enter
         // the PV product with weight 0, so they must at least be finite: start from zeros.
         for (int idx = tid; idx < kStages * kStageBytes / 16; idx += kThreads) {
@@ -398,8 +422,11 @@ __global__ void __launch_bounds__(kThreads, 2)
         // ================================ producer: TMA tiles of K and V =========================================
         bool alive = true;
         int done = 0; // blocks of earlier fragments: ring stage and parity run on across fragments
-        for (int pos = piece_begin; pos < piece_end && alive;) {
-            const Fragment f = locate(p, walker, pos, piece_end);
+        for (int pos = piece_begin; alive;) {
+            Fragment f;
+            if (!locate(p, walker, pos, piece_end, f)) {
+                break;
+            }
             const int n = f.b1 - f.b0;
             const int n_pages = (tile_kv_hi(walker.g, f.qb) + kPage - 1) / kPage;
             const int kvh = f.h / p.group;
@@ -501,8 +528,11 @@ __global__ void __launch_bounds__(kThreads, 2)
                 return true;
             };
             int done = 0, frag_no = 0;
-            for (int pos = piece_begin; pos < piece_end && ok; ++frag_no) {
-                const Fragment f = locate(p, walker, pos, piece_end);
+            for (int pos = piece_begin; ok; ++frag_no) {
+                Fragment f;
+                if (!locate(p, walker, pos, piece_end, f)) {
+                    break;
+                }
                 const int n = f.b1 - f.b0;
                 if (frag_no > 0) { // the softmax threads have stored this fragment's Q rows
                     ok = wait_or_abort(bar(kBarQFull), uint32_t(frag_no - 1) & 1u, s_abort);
@@ -545,8 +575,11 @@ __global__ void __launch_bounds__(kThreads, 2)
         // the arrival counts below see all 128 threads every time.
         bool dead = false;
         int done = 0;
-        for (int pos = piece_begin; pos < piece_end;) {
-            const Fragment f = locate(p, walker, pos, piece_end);
+        for (int pos = piece_begin;;) {
+            Fragment f;
+            if (!locate(p, walker, pos, piece_end, f)) {
+                break;
+            }
             const SeqGeom g = walker.g;
             const int n = f.b1 - f.b0;
             const int t = f.qb * kBlockM + row;        // query index inside the chunk
@@ -695,12 +728,17 @@ __global__ void __launch_bounds__(kThreads, 2)
                 mbar_arrive(bar(kBarPFull));
             }
             // ---- Q rows of the next fragment: every QK^T of this one has finished (its last S was read above) -------
-            if (pos + n < piece_end && !dead) {
+            bool more; // another fragment follows in this CTA (uniform over the CTA)
+            {
                 Walker wn = walker;
-                const Fragment fn = locate(p, wn, pos + n, piece_end);
-                load_q(fn, wn.g, tid, kSoftmaxThreads);
-                fence_proxy_async_smem();
-                mbar_arrive(bar(kBarQFull));
+                Fragment fn;
+                int pos_n = pos + n;
+                more = locate(p, wn, pos_n, piece_end, fn);
+                if (more && !dead) {
+                    load_q(fn, wn.g, tid, kSoftmaxThreads);
+                    fence_proxy_async_smem();
+                    mbar_arrive(bar(kBarQFull));
+                }
             }
             // ---- epilogue of the fragment ---------------------------------------------------------------------------
             if (!dead && !wait_or_abort(bar(kBarPVDone + ((done + n - 1) & 1)), uint32_t((done + n - 1) >> 1) & 1u, s_abort)) {
@@ -710,8 +748,11 @@ __global__ void __launch_bounds__(kThreads, 2)
             const bool whole = f.b0 == 0 && f.b1 == f.tile_nblk;
             char *out_row = static_cast<char *>(p.out) + ((long long)(g.q_start + t) * p.nh + f.h) * (kD * 2);
             bool store_rows = whole, staged = false;
-            float w_own = 1.f, w_other = 0.f, l_all = l, m_all = m_used;
+            float w_own = 1.f, l_all = l, m_all = m_used;
+            float w_oth[4] = {0.f, 0.f, 0.f, 0.f}; // staged merge: weights of the other fragments, in the order of their CTAs
             const int first_slot = f.tile_begin / piece, last_slot = (f.tile_begin + f.tile_nblk - 1) / piece;
+            const int n_others = last_slot - first_slot, own_at = slot - first_slot; // fragments besides this one; those before it
+            int chunks_per_trip = 4; // staged merge: 32-column chunks of every other fragment fetched per trip (4 / n_others)
             if (!whole) {
                 // unnormalised accumulator + (max, sum) of the rows into this CTA's workspace slot: slot 1 for the
                 // fragment that begins its tile (and continues in the next CTA), slot 0 for one that began earlier
@@ -743,37 +784,68 @@ __global__ void __launch_bounds__(kThreads, 2)
                 }
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");
                 store_rows = s_sched[14] != 0;
-                // The usual merge: the CTA's last fragment begins a tile that the next CTA finished long ago. The
-                // operands and Q are no longer needed, so the other half (64 KiB + maxima and sums) is fetched into
-                // their place by five bulk copies and combined from shared memory: one trip to L2 instead of six
-                // dependent ones. Same arithmetic, in the same order, as the general path below.
-                staged = store_rows && last_slot == first_slot + 1 && slot == first_slot && pos + n == piece_end;
+                // The usual merge: the CTA's last fragment begins a tile that the next CTA finished long ago (or, for a
+                // tile longer than a piece, that the next CTAs are spread over). The operands and Q are no longer
+                // needed, so the other fragments (64 KiB each + maxima and sums) are fetched into their place by bulk
+                // copies and combined from shared memory: one trip to L2 for one other fragment, two for two, four
+                // for three or four (the K/V ring holds 64 KiB) instead of six dependent ones. Same arithmetic, in the
+                // same order, as the general path below.
+                staged = store_rows && !more && n_others <= 4;
                 if (staged) {
-                    const float *other = p.partials + (long long)((slot + 1) * 2) * kPartialFloats;
+                    chunks_per_trip = 4 / n_others; // 4, 2, 1, 1
                     if (tid == 0) {
                         __threadfence();
                         asm volatile("fence.proxy.async;\n" ::: "memory"); // generic-proxy writes of another SM -> bulk read
-                        mbar_arrive_expect_tx(bar(kBarMerge), uint32_t(kPartialFloats * sizeof(float)));
-                        for (int j = 0; j < 4; ++j) {
+                        mbar_arrive_expect_tx(bar(kBarMerge), uint32_t(n_others) * uint32_t(chunks_per_trip * 16384 + 2 * kBlockM * 4));
+                        int j = 0;
+                        for (int s2 = first_slot; s2 <= last_slot; ++s2) {
+                            if (s2 == slot) {
+                                continue;
+                            }
+                            const float *other =
+                                p.partials + (long long)(s2 * 2 + (s2 * piece <= f.tile_begin ? 1 : 0)) * kPartialFloats;
+                            for (int u = 0; u < chunks_per_trip; ++u) {
+                                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                                                 kv_u32 + (j * chunks_per_trip + u) * 16384),
+                                             "l"(other + u * 4096), "r"(16384), "r"(bar(kBarMerge))
+                                             : "memory");
+                            }
                             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                                             kv_u32 + j * 16384),
-                                         "l"(other + j * 4096), "r"(16384), "r"(bar(kBarMerge))
+                                             q_u32 + j * (2 * kBlockM * 4)),
+                                         "l"(other + kBlockM * kD), "r"(2 * kBlockM * 4), "r"(bar(kBarMerge))
                                          : "memory");
+                            ++j;
                         }
-                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(q_u32),
-                                     "l"(other + kBlockM * kD), "r"(2 * kBlockM * 4), "r"(bar(kBarMerge))
-                                     : "memory");
                     }
                     if (!dead && !wait_or_abort(bar(kBarMerge), 0u, s_abort)) {
                         dead = true;
                     }
-                    float m2, l2;
-                    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(m2) : "r"(q_u32 + row * 4) : "memory");
-                    asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(l2) : "r"(q_u32 + (kBlockM + row) * 4) : "memory");
-                    m_all = fmaxf(m_used, m2);
+                    float m_oth[4], l_oth[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        m_oth[j] = -INFINITY;
+                        l_oth[j] = 0.f;
+                        if (j < n_others) {
+                            asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(m_oth[j]) : "r"(q_u32 + j * (2 * kBlockM * 4) + row * 4) : "memory");
+                            asm volatile("ld.shared.f32 %0, [%1];\n"
+                                         : "=f"(l_oth[j])
+                                         : "r"(q_u32 + j * (2 * kBlockM * 4) + (kBlockM + row) * 4)
+                                         : "memory");
+                        }
+                        m_all = fmaxf(m_all, m_oth[j]);
+                    }
                     w_own = m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_all);
-                    w_other = m2 == -INFINITY ? 0.f : fast_exp2(m2 - m_all);
-                    l_all = fmaf(l2, w_other, fmaf(l, w_own, 0.f));
+                    l_all = 0.f;
+#pragma unroll
+                    for (int j = 0; j <= 4; ++j) { // the others in the order of their CTAs, this fragment in its place
+                        if (j == own_at) {
+                            l_all = fmaf(l, w_own, l_all);
+                        }
+                        if (j < 4 && j < n_others) {
+                            w_oth[j] = m_oth[j] == -INFINITY ? 0.f : fast_exp2(m_oth[j] - m_all);
+                            l_all = fmaf(l_oth[j], w_oth[j], l_all);
+                        }
+                    }
                 } else if (store_rows && !dead) {
                     __threadfence();
                     // merge the other fragments' rows into this one's: weights 2^(m_i - m) in the log2 domain
@@ -801,24 +873,72 @@ __global__ void __launch_bounds__(kThreads, 2)
                     }
                 }
             }
-            if (store_rows && !dead) {
+            if (store_rows && (staged || !dead)) {
                 const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) {
+                    if (staged && c4 > 0 && c4 % chunks_per_trip == 0) {
+                        // next trip: everybody has read the chunks in shared memory (all 128 threads meet here, also
+                        // those that have given up), then one thread asks for the next ones
+                        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                        if (tid == 0) {
+                            asm volatile("fence.proxy.async;\n" ::: "memory"); // reads above -> the copies' writes
+                            mbar_arrive_expect_tx(bar(kBarMerge), uint32_t(n_others) * uint32_t(chunks_per_trip * 16384));
+                            int j = 0;
+                            for (int s2 = first_slot; s2 <= last_slot; ++s2) {
+                                if (s2 == slot) {
+                                    continue;
+                                }
+                                const float *other =
+                                    p.partials + (long long)(s2 * 2 + (s2 * piece <= f.tile_begin ? 1 : 0)) * kPartialFloats;
+                                for (int u = 0; u < chunks_per_trip; ++u) {
+                                    asm volatile(
+                                        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                                            kv_u32 + (j * chunks_per_trip + u) * 16384),
+                                        "l"(other + (c4 + u) * 4096), "r"(16384), "r"(bar(kBarMerge))
+                                        : "memory");
+                                }
+                                ++j;
+                            }
+                        }
+                        if (!dead && !wait_or_abort(bar(kBarMerge), uint32_t(c4 / chunks_per_trip) & 1u, s_abort)) {
+                            dead = true;
+                        }
+                    }
+                    if (dead) {
+                        continue;
+                    }
                     float v[32];
                     tmem_ld32(tmem_o + c4 * 32, v);
                     if (staged) {
+                        const uint32_t chunk_u32 = kv_u32 + uint32_t(c4 % chunks_per_trip) * 16384u + uint32_t(row) * 16u;
 #pragma unroll
                         for (int q8 = 0; q8 < 8; ++q8) {
-                            float4 o;
-                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n"
-                                         : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w)
-                                         : "r"(kv_u32 + ((c4 * 8 + q8) * kBlockM + row) * 16)
-                                         : "memory");
-                            v[q8 * 4] = fmaf(o.x, w_other, fmaf(v[q8 * 4], w_own, 0.f));
-                            v[q8 * 4 + 1] = fmaf(o.y, w_other, fmaf(v[q8 * 4 + 1], w_own, 0.f));
-                            v[q8 * 4 + 2] = fmaf(o.z, w_other, fmaf(v[q8 * 4 + 2], w_own, 0.f));
-                            v[q8 * 4 + 3] = fmaf(o.w, w_other, fmaf(v[q8 * 4 + 3], w_own, 0.f));
+                            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int j = 0; j <= 4; ++j) {
+                                if (j == own_at) {
+                                    acc.x = fmaf(v[q8 * 4], w_own, acc.x);
+                                    acc.y = fmaf(v[q8 * 4 + 1], w_own, acc.y);
+                                    acc.z = fmaf(v[q8 * 4 + 2], w_own, acc.z);
+                                    acc.w = fmaf(v[q8 * 4 + 3], w_own, acc.w);
+                                }
+                                if (j < 4 && j < n_others) {
+                                    float4 o;
+                                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n"
+                                                 : "=f"(o.x), "=f"(o.y), "=f"(o.z), "=f"(o.w)
+                                                 : "r"(chunk_u32 + uint32_t(j * chunks_per_trip) * 16384u + uint32_t(q8 * kBlockM) * 16u)
+                                                 : "memory");
+                                    acc.x = fmaf(o.x, w_oth[j], acc.x);
+                                    acc.y = fmaf(o.y, w_oth[j], acc.y);
+                                    acc.z = fmaf(o.z, w_oth[j], acc.z);
+                                    acc.w = fmaf(o.w, w_oth[j], acc.w);
+                                }
+                            }
+                            v[q8 * 4] = acc.x;
+                            v[q8 * 4 + 1] = acc.y;
+                            v[q8 * 4 + 2] = acc.z;
+                            v[q8 * 4 + 3] = acc.w;
                         }
                     } else if (!whole) {
                         float own[32];
