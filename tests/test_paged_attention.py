@@ -591,6 +591,46 @@ def test_prefill_one_long_sequence_split_over_ctas_nvidia(cuda_device, nh, nkvh,
 
 
 @pytest.mark.gpu
+def test_prefill_tiles_of_very_different_lengths_in_one_batch_nvidia(cuda_device):
+    """Contexts from 100 to 10500 tokens in one batch of 256-row chunks: the kernel cuts the line of all tiles' blocks
+    into equal pieces, so the long tiles run over two to five CTAs each (their partial results are merged from shared
+    memory, one, two or four trips for the other fragments) while one CTA takes half a dozen short tiles. Every row
+    must match the oracle and, the merge order being fixed, be the same bits on every launch."""
+    g = torch.Generator().manual_seed(77)
+    ctxs = [10500, 700, 3000, 100, 5200, 1500, 8000, 6100]
+    chunk = 256
+    kv_lens = [c + chunk for c in ctxs]
+    pages = sum((l + 15) // 16 for l in kv_lens) + 8
+    cache = llaisys.PagedKVCache(pages, 2, 128, dtype=llaisys.DataType.BF16, device=NVIDIA, max_seqs=len(ctxs),
+                                 max_pages_per_seq=max((l + 15) // 16 for l in kv_lens))
+    seqs, ks, vs, qs = [], [], [], []
+    for kl in kv_lens:
+        s = cache.add_seq()
+        cache.reserve(s, kl)
+        seqs.append(s)
+        ks.append(workloads.randn((kl, 2, 128), torch.bfloat16, g))
+        vs.append(workloads.randn((kl, 2, 128), torch.bfloat16, g))
+        qs.append(workloads.randn((chunk, 12, 128), torch.bfloat16, g))
+    helpers.append_all(cache, 0, seqs, ks, vs, NVIDIA)
+    q = torch.cat(qs).cuda()
+    q_lens = [chunk] * len(ctxs)
+    out = torch.full_like(q, float("nan"))
+    cache.prefill(0, out, q, seqs, q_lens, kv_lens, 12, 128 ** -0.5)
+    cache.check()
+    assert cache.last_kernel() == llaisys.Kernel.PREFILL_TC
+    for _ in range(5):
+        again = torch.full_like(q, float("nan"))
+        cache.prefill(0, again, q, seqs, q_lens, kv_lens, 12, 128 ** -0.5)
+        cache.check()
+        assert torch.equal(helpers.tensor_words(again.cpu()), helpers.tensor_words(out.cpu()))
+    out = out.cpu()
+    assert not out.float().isnan().any()
+    for i in range(len(ctxs)):
+        expect = attention.self_attention(qs[i], ks[i], vs[i], 128 ** -0.5)
+        assert helpers.max_abs(out[i * chunk:(i + 1) * chunk], expect) <= helpers.MAX_ABS["bf16"], (i, ctxs[i])
+
+
+@pytest.mark.gpu
 def test_prefill_many_short_sequences_and_one_long_chunk_nvidia(cuda_device):
     """More sequences than the kernel has threads per CTA (its prologue sums and scans the sequences' block counts in
     rounds of one sequence per thread), most with a chunk of one to three rows, some with none, and one whole prompt
