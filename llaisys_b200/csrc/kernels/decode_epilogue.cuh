@@ -310,14 +310,4 @@ __device__ __forceinline__ void warp_merge_finish(const float *stash, int n_warp
     }
 }
 
-// The same merge as a function of its own, for kernels in which the inlined loop does not come out well: it keeps up
-// to 96 registers of loads in flight, and inlined into the exchange instantiation of the TMA decode kernel (whose other
-// warps sit at the register limit) it ran 2.3 times slower than in the ordinary one. Compiled by itself it does not
-// depend on its surroundings; the call costs about a microsecond, which is why the ordinary kernel keeps the inlined one.
-template <bool kBf16>
-__device__ __noinline__ void warp_combine_partials_call(const float *first, int expected, int group, int lane, void *out,
-                                                        float *part, long long out_row0) {
-    warp_combine_partials<kBf16>(first, expected, group, lane, out, part, out_row0);
-}
-
 } // namespace llaisys::kernels
