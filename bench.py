@@ -588,19 +588,25 @@ def measure_prefill(env, args, *, repeats: int) -> dict:
         cache.close()
         return {"workload": "config3", "quick": True, "launches": {"paged_prefill_tc_kernel": max(3, args.warmup) + steps}}
 
-    def capture(body):
+    overlap = not args.no_overlap
+
+    def capture(body, with_overlap):
+        cache.set_launch_overlap(with_overlap)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             for i in range(steps):
                 body(i)
+        cache.set_launch_overlap(False)
         return graph
 
-    g_step, g_att, g_app = capture(do_step), capture(do_attend), capture(do_append)
+    g_step, g_att, g_app = capture(do_step, overlap), capture(do_attend, overlap), capture(do_append, overlap)
+    g_att_plain = capture(do_attend, False)
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
     step_ms = replay_times(torch, stream, g_step, repeats)
     attend_ms = replay_times(torch, stream, g_att, repeats)
+    attend_plain_ms = replay_times(torch, stream, g_att_plain, repeats)
     append_ms = replay_times(torch, stream, g_app, repeats)
     cache.check()
 
@@ -639,7 +645,7 @@ def measure_prefill(env, args, *, repeats: int) -> dict:
                "d2h_bytes_per_step": out_h.numel() * 2, "steps": n_e2e,
                "matches_device_path": bool(torch.equal(out_h.view(torch.int16), out.cpu().view(torch.int16)))}
 
-    med = reduce_max(torch, dist, [statistics.median(x) for x in (step_ms, attend_ms, append_ms)])
+    med = reduce_max(torch, dist, [statistics.median(x) for x in (step_ms, attend_ms, append_ms, attend_plain_ms)])
     _, burst, sustained, kind = _peaks()
     flops = sum(4 * NH * D * (chunk * c + chunk * (chunk + 1) // 2) for c in context)
     kernel_ms = med[1] / steps
@@ -652,17 +658,21 @@ def measure_prefill(env, args, *, repeats: int) -> dict:
         "config": {"workload": "config3", "batch_per_gpu": B, "context": context, "chunk": chunk,
                    "heads": "12q/2kv", "head_dim": D, "page_size": PAGE, "pool_pages": POOL_PAGES,
                    "parallelism": f"sequences sharded over {world} GPU(s), no collective",
-                   "l2": f"layer pool rotates over {layers} x {cache.layer_bytes() >> 20} MiB between steps"},
+                   "l2": f"layer pool rotates over {layers} x {cache.layer_bytes() >> 20} MiB between steps",
+                   "launch": ("programmatic dependent launch: a kernel's set-up overlaps the previous kernel's tail" if overlap
+                              else "plain launches")},
         "roofline": {"bound": "tensor", "kernel": "paged_prefill_tc_kernel", "achieved": achieved,
                      "peak": burst, "peak_kind": f"burst bf16 (a kernel timed alone), of {kind}", "unit": "TFLOP/s",
                      "frac": achieved / burst, "frac_of_sustained": achieved / sustained, "peak_sustained": sustained,
                      "frac_of_nominal_2250": achieved / 2250.0, "traffic": None,
                      "algorithmic_flops_per_launch": flops, "kernel_ms": kernel_ms,
-                     "kernel_ms_spread": spread(attend_ms, steps), "append_kernel_ms": med[2] / steps},
+                     "kernel_ms_spread": spread(attend_ms, steps), "append_kernel_ms": med[2] / steps,
+                     "kernel_ms_without_launch_overlap": med[3] / steps,
+                     "frac_without_launch_overlap": flops / (med[3] / steps * 1e-3) / 1e12 / burst},
         "e2e": e2e, "gpu_launches": 2 * steps * repeats,
         "timing": f"CUDA graphs of {steps} steps, {repeats} replays, event pair per replay, median",
     }
-    del g_step, g_att, g_app
+    del g_step, g_att, g_app, g_att_plain
     cache.close()
     return record
 

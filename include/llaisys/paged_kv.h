@@ -132,7 +132,9 @@ LLAISYS_API int llaisysPagedKVFlush(llaisysPagedKV_t kv);
  *     sequence append and for the one-launch decode step of the token before; after a multi-page append (a prefill
  *     chunk) put any non-overlapping kernel, a copy or a synchronisation before the first decode call;
  *   - index arrays and block-table rows passed to a call were written before that directly preceding kernel started
- *     (true for host-array calls, whose staging copies break the chain, and for device arrays prepared per batch). */
+ *     (true for host-array calls, whose staging copies break the chain, and for device arrays prepared per batch).
+ * The chunked-prefill kernel takes part too: it reads its index arrays, sums the work and sets up its on-chip state
+ * before waiting, and touches q, K/V, workspace and outputs only after the kernel directly before it has completed. */
 LLAISYS_API int llaisysPagedKVSetLaunchOverlap(llaisysPagedKV_t kv, int enable);
 /* LLAISYS_KERNEL_* of this cache's most recent attention call (-1 for a null handle). */
 LLAISYS_API int llaisysPagedKVLastKernel(llaisysPagedKV_t kv);

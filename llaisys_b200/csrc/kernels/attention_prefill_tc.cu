@@ -399,6 +399,11 @@ __global__ void __launch_bounds__(kThreads, 2)
         tmem_relinquish();
     }
     {
+        // Everything above read only the launch's index arrays and set up on-chip state; q, the K/V rows of the chunk,
+        // the workspace and the outputs belong to the stream's order: with launch overlap on, wait here for the kernel
+        // directly before this one, and only then let the one behind this one start.
+        grid_dependency_wait();
+        grid_launch_dependents();
         load_q(first_fragment, first_walker.g, tid, kThreads);
         // A block shorter than kBlockN keys leaves ring rows unwritten; they are masked out of S, but V rows enter
         // the PV product with weight 0, so they must at least be finite: start from zeros.
@@ -1056,7 +1061,7 @@ int prefill_slots() {
 }
 
 template <bool kBf16>
-void launch(cudaStream_t s, const CUtensorMap &tmap, const CUtensorMap &tmap_v, const PrefillParams &p, int grid) {
+void launch(cudaStream_t s, const CUtensorMap &tmap, const CUtensorMap &tmap_v, const PrefillParams &p, int grid, bool overlap) {
     static std::once_flag once[64];
     int dev = 0;
     LLAISYS_CUDA_CHECK(cudaGetDevice(&dev));
@@ -1064,7 +1069,17 @@ void launch(cudaStream_t s, const CUtensorMap &tmap, const CUtensorMap &tmap_v, 
         LLAISYS_CUDA_CHECK(cudaFuncSetAttribute(paged_prefill_tc_kernel<kBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 int(kSmemBytes)));
     });
-    paged_prefill_tc_kernel<kBf16><<<grid, kThreads, kSmemBytes, s>>>(tmap, tmap_v, p);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(grid));
+    cfg.blockDim = dim3(unsigned(kThreads));
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, paged_prefill_tc_kernel<kBf16>, tmap, tmap_v, p));
 }
 
 } // namespace
@@ -1218,9 +1233,9 @@ int attention_prefill_tc(stream_t stream, llaisysDataType_t dtype, const KVView 
     }
     auto s = static_cast<cudaStream_t>(stream);
     if (bf16) {
-        launch<true>(s, tmap, tmap_v, p, grid);
+        launch<true>(s, tmap, tmap_v, p, grid, kv.overlap_launch);
     } else {
-        launch<false>(s, tmap, tmap_v, p, grid);
+        launch<false>(s, tmap, tmap_v, p, grid, kv.overlap_launch);
     }
     check_launch("paged_prefill_tc");
     return 0;

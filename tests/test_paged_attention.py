@@ -703,6 +703,56 @@ def test_back_to_back_steps_with_launch_overlap_nvidia(cuda_device):
 
 
 @pytest.mark.gpu
+def test_back_to_back_prefill_chunks_with_launch_overlap_nvidia(cuda_device):
+    """Six rounds of "append a chunk per sequence, attend over the grown context" on ONE layer, queued without any host
+    synchronisation and with programmatic dependent launch on: the chunk kernel may do its set-up under the append
+    before it, the next append may be scheduled under the chunk kernel, and yet every round must match the oracle."""
+    rounds, chunk, nseq = 6, 150, 3
+    g = torch.Generator().manual_seed(71)
+    start = [700, 0, 2300]
+    total = [s + rounds * chunk for s in start]
+    ks = [workloads.randn((n, 2, 128), torch.bfloat16, g) for n in total]
+    vs = [workloads.randn((n, 2, 128), torch.bfloat16, g) for n in total]
+    cache = llaisys.PagedKVCache(sum((n + 15) // 16 for n in total) + 4, 2, 128, dtype=llaisys.DataType.BF16, device=NVIDIA,
+                                 max_seqs=nseq, max_pages_per_seq=max((n + 15) // 16 for n in total))
+    seqs = []
+    for n in total:
+        s = cache.add_seq()
+        cache.reserve(s, n)
+        seqs.append(s)
+    helpers.append_all(cache, 0, seqs, ks, vs, NVIDIA, hi=start)
+    cache.flush()
+    stream = llaisys.context_stream()
+    ids = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    starts = torch.tensor([i * chunk for i in range(nseq + 1)], dtype=torch.int32, device="cuda")
+    qs = [workloads.randn((nseq * chunk, 12, 128), torch.bfloat16, g) for _ in range(rounds)]
+    # everything the kernels index with is prepared before the first launch
+    row_seq = torch.repeat_interleave(ids, chunk)
+    row_pos, lens, k_new, v_new = [], [], [], []
+    for r in range(rounds):
+        row_pos.append(torch.cat([torch.arange(st + r * chunk, st + (r + 1) * chunk, dtype=torch.int32) for st in start]).cuda())
+        lens.append(torch.tensor([st + (r + 1) * chunk for st in start], dtype=torch.int32, device="cuda"))
+        k_new.append(torch.cat([ks[i][start[i] + r * chunk:start[i] + (r + 1) * chunk] for i in range(nseq)]).cuda())
+        v_new.append(torch.cat([vs[i][start[i] + r * chunk:start[i] + (r + 1) * chunk] for i in range(nseq)]).cuda())
+    q_dev = [q.cuda() for q in qs]
+    outs = [torch.full((nseq * chunk, 12, 128), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(rounds)]
+    torch.cuda.synchronize()
+    cache.set_launch_overlap(True)
+    for r in range(rounds):
+        cache.append_dev(0, k_new[r], v_new[r], row_seq, row_pos[r], nseq * chunk, stream)
+        cache.prefill_dev(0, outs[r], q_dev[r], ids, starts, lens[r], nseq, nseq * chunk, chunk, max(total), 12, 128 ** -0.5,
+                          stream)
+    cache.check()
+    assert cache.last_kernel() == llaisys.Kernel.PREFILL_TC
+    for r in range(rounds):
+        got = outs[r].cpu()
+        for i in range(nseq):
+            n = start[i] + (r + 1) * chunk
+            expect = attention.self_attention(qs[r][i * chunk:(i + 1) * chunk], ks[i][:n], vs[i][:n], 128 ** -0.5)
+            assert helpers.max_abs(got[i * chunk:(i + 1) * chunk], expect) <= helpers.MAX_ABS["bf16"], (r, i)
+
+
+@pytest.mark.gpu
 def test_kernel_flags_bad_metadata_instead_of_faulting_nvidia(cuda_device):
     """Device-array entry points do no host validation; a position past the block table is skipped and reported
     by check(), and the cache stays usable."""
