@@ -894,8 +894,12 @@ def run_copy_workload(args) -> None:
         stream.synchronize()
         return e0.elapsed_time(e1) / reps
 
+    overlap = not args.no_overlap
     with ClockSampler(local_rank) as clocks:
+        append_plain_ms = timed(lambda i: cache.append_dev(i % layers, k_rows, v_rows, seq_of_row, pos_of_row, rows, cs))
+        cache.set_launch_overlap(overlap)  # programmatic launches: the next append is scheduled under this one's tail
         append_ms = timed(lambda i: cache.append_dev(i % layers, k_rows, v_rows, seq_of_row, pos_of_row, rows, cs))
+        cache.set_launch_overlap(False)
     fused_ms = timed(lambda i: cache.rope_append_dev(i % layers, q_out, qkv, bias, seq_of_row, pos_of_row, rows, NH, 10000.0, cs))
     # A plain device-to-device copy that moves the same bytes as the append (K and V rows read once, written once), timed
     # the same way: what a copy of THIS size reaches (the measured peak is taken on a 4 GB copy). Four destinations rotate.
@@ -933,11 +937,14 @@ def run_copy_workload(args) -> None:
             "ms_per_step": append_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "copy", "rows": rows, "heads": "12q/2kv", "head_dim": D, "page_size": PAGE,
-                       "pool_pages": POOL_PAGES, "l2": f"layer pool rotates over {layers} x 256 MiB between launches"},
+                       "pool_pages": POOL_PAGES, "l2": f"layer pool rotates over {layers} x 256 MiB between launches",
+                       "launch": "programmatic dependent launch" if overlap else "plain launches"},
             "roofline": {"bound": "hbm", "kernel": "paged_append_kernel", "achieved": append_bytes / (append_ms * 1e-3) / 1e9,
                          "peak": hbm_peak, "peak_kind": f"of {kind}", "unit": "GB/s",
                          "frac": append_bytes / (append_ms * 1e-3) / 1e9 / hbm_peak, "traffic": None,
                          "algorithmic_bytes_per_launch": append_bytes, "kernel_ms_mean": append_ms,
+                         "kernel_ms_without_launch_overlap": append_plain_ms,
+                         "frac_without_launch_overlap": append_bytes / (append_plain_ms * 1e-3) / 1e9 / hbm_peak,
                          "plain_copy_of_the_same_bytes": {"ms": plain_copy_ms, "GB/s": 2 * rows * row_kv / (plain_copy_ms * 1e-3) / 1e9,
                                                           "append_vs_copy": plain_copy_ms / append_ms}},
             "rope_append": {"kernel": "paged_rope_append_kernel", "ms": fused_ms, "algorithmic_bytes_per_launch": fused_bytes,
