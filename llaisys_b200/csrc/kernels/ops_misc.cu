@@ -3,10 +3,29 @@
 // f32 arithmetic with one rounding to the tensor dtype.
 #include "device_utils.cuh"
 #include "kernels.hpp"
+#include "mma_utils.cuh"
+
+#include <utility>
 
 namespace llaisys::kernels {
 
 namespace {
+
+// A launch with programmatic stream serialisation, for kernels that wait for their predecessor (griddepcontrol.wait)
+// before they touch anything: safe behind any kernel, and behind a long one it hides the launch.
+template <typename... KArgs, typename... Args>
+void launch_programmatic(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t s, Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(block);
+    cfg.stream = s;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    LLAISYS_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...));
+}
 
 // ---- argmax: one CTA per row, (value, index) pairs reduced with shuffles then through shared memory ----------------
 template <typename T>
@@ -86,6 +105,10 @@ __global__ void embedding_kernel(unsigned char *__restrict__ out, const int64_t 
 // ---- rms_norm: one CTA per row; 16-byte loads when the row allows, the row kept in registers between the passes --
 template <typename T, int VEC, int PER_THREAD>
 __global__ void rms_norm_vec_kernel(T *__restrict__ out, const T *__restrict__ in, const T *__restrict__ w, float eps, size_t d) {
+    // launched programmatically: the grid may be scheduled under the tail of the kernel before it, touches nothing
+    // until that kernel has completed, and lets its own successor be scheduled the same way
+    grid_launch_dependents();
+    grid_dependency_wait();
     struct alignas(sizeof(T) * VEC) P {
         T v[VEC];
     };
@@ -206,6 +229,8 @@ __global__ void bias_add_kernel(T *__restrict__ out, const T *__restrict__ bias,
 
 template <typename T, int VEC>
 __global__ void swiglu_packed_kernel(T *__restrict__ out, const T *__restrict__ gu, size_t rows, size_t di) {
+    grid_launch_dependents(); // (programmatic launch, as rms_norm_vec_kernel)
+    grid_dependency_wait();
     struct alignas(sizeof(T) * VEC) P {
         T v[VEC];
     };
@@ -337,8 +362,8 @@ void rms_norm(stream_t stream, llaisysDataType_t dtype, void *out, const void *i
         if (ptrs_ok && d % kVec == 0 && n_vec <= size_t(1024) * kPerThread) {
             const size_t want = (n_vec + kPerThread - 1) / kPerThread;
             const unsigned block = unsigned(want <= 64 ? 64 : (want + 31) / 32 * 32);
-            rms_norm_vec_kernel<T, kVec, kPerThread><<<unsigned(rows), block, 0, s>>>(
-                static_cast<T *>(out), static_cast<const T *>(in), static_cast<const T *>(weight), eps, d);
+            launch_programmatic(rms_norm_vec_kernel<T, kVec, kPerThread>, unsigned(rows), block, s, static_cast<T *>(out),
+                                static_cast<const T *>(in), static_cast<const T *>(weight), eps, d);
         } else {
             rms_norm_kernel<T><<<unsigned(rows), 256, 0, s>>>(static_cast<T *>(out), static_cast<const T *>(in),
                                                                static_cast<const T *>(weight), eps, d);
@@ -379,11 +404,11 @@ void swiglu_packed(stream_t stream, llaisysDataType_t dtype, void *out, const vo
     LLAISYS_CUDA_DISPATCH_FLOAT(dtype, {
         constexpr int kVec = 16 / int(sizeof(T));
         if (ptrs_ok && di % kVec == 0) {
-            swiglu_packed_kernel<T, kVec><<<grid_for(rows * di / kVec, 256), 256, 0, s>>>(
-                static_cast<T *>(out), static_cast<const T *>(gate_up), rows, di);
+            launch_programmatic(swiglu_packed_kernel<T, kVec>, unsigned(grid_for(rows * di / kVec, 256)), 256u, s,
+                                static_cast<T *>(out), static_cast<const T *>(gate_up), rows, di);
         } else {
-            swiglu_packed_kernel<T, 1><<<grid_for(rows * di, 256), 256, 0, s>>>(static_cast<T *>(out),
-                                                                                static_cast<const T *>(gate_up), rows, di);
+            launch_programmatic(swiglu_packed_kernel<T, 1>, unsigned(grid_for(rows * di, 256)), 256u, s, static_cast<T *>(out),
+                                static_cast<const T *>(gate_up), rows, di);
         }
     });
     check_launch("swiglu_packed");
