@@ -1095,6 +1095,16 @@ def measure_kv_split(env, args, *, steps: int, one_gpu_reference: bool) -> dict:
     expect = out.clone()
     peer_ms = timed(graphed(peer_batched), n_rep)
     peer.check(cs)
+    # consecutive tokens: four steps per graph, so that a step's launch and set-up overlap the merge of the step before it
+    # (programmatic launches), as they do in the per-layer mode and in the headline's graphs of many steps
+    steps_per_graph = 4
+
+    def peer_batched_run():
+        for _ in range(steps_per_graph):
+            peer_batched()
+
+    peer_run_ms = [t / steps_per_graph for t in timed(graphed(peer_batched_run), n_rep)]
+    peer.check(cs)
     assert cache.last_kernel() == llaisys.Kernel.DECODE_TMA, "the partial decode did not run on the TMA decode kernel"
     peer_same = bool(torch.equal(out_p.view(torch.int16), expect.view(torch.int16)))  # same partials, same merge order
     peer_layer_ms = timed(graphed(peer_per_layer), max(10, n_rep // 5))
@@ -1159,7 +1169,7 @@ def measure_kv_split(env, args, *, steps: int, one_gpu_reference: bool) -> dict:
         sync_all()
 
     med = reduce_max(torch, dist, [statistics.median(x) for x in
-                                   (peer_ms, peer_layer_ms, nccl_ms, nccl_layer_ms, decode_ms, decode_layer_ms)])
+                                   (peer_ms, peer_layer_ms, nccl_ms, nccl_layer_ms, decode_ms, decode_layer_ms, peer_run_ms)])
     hbm, _, _, kind = _peaks()
     bytes_per_launch = n_layers * local * (2 * NKVH * D * 2) + 2 * n_layers * NH * D * 2 + 4 * n_layers * pages_per
     achieved = bytes_per_launch / (med[4] * 1e-3) / 1e9
@@ -1168,6 +1178,7 @@ def measure_kv_split(env, args, *, steps: int, one_gpu_reference: bool) -> dict:
         "metric": "decode tokens/s (one 131072-token sequence, attention of 28 layers, KV range split across GPUs)",
         "value": 1e3 / med[0], "unit": "tokens/s", "n_gpus": world,
         "ms_per_step": med[0], "ms_per_step_spread": spread(peer_ms),
+        "ms_per_step_in_a_run": med[6], "steps_per_graph_in_a_run": steps_per_graph,
         "per_layer_ms": med[1], "per_layer_round_ms": med[1] / n_layers,
         "nccl_ms": med[2], "nccl_per_layer_ms": med[3],
         "speedup_vs_1gpu": (one_gpu_ms / med[0]) if one_gpu_ms else None, "one_gpu_ms": one_gpu_ms,
@@ -1210,6 +1221,7 @@ def run_longctx_workload(args) -> None:
                 "per_layer": {"ms_per_step": rec["per_layer_ms"], "ms_per_round": rec["per_layer_round_ms"],
                               "note": "28 dependent rounds of partial decode (+ exchange in the kernel) + merge",
                               "decode_kernel_ms_one_layer_host_driven": rec["decode_kernel_ms_one_layer_host_driven"]},
+                "in_a_run": {"ms_per_step": rec["ms_per_step_in_a_run"], "steps_per_graph": rec["steps_per_graph_in_a_run"]},
                 "nccl_all_gather": {"ms_per_step": rec["nccl_ms"], "per_layer_ms_per_step": rec["nccl_per_layer_ms"],
                                     "peer_path_matches": rec["peer_path_matches_nccl_path"]},
                 "max_abs_vs_oracle": rec["max_abs_vs_oracle"], "e2e": None, "gpu_launches": rec["gpu_launches"],
@@ -1304,6 +1316,7 @@ def main() -> None:
         else:
             kv = measure_kv_split(env, args, steps=repeats, one_gpu_reference=True)
             subs["kv_split"] = {k: kv[k] for k in ("metric", "value", "unit", "n_gpus", "ms_per_step", "ms_per_step_spread",
+                                                   "ms_per_step_in_a_run", "steps_per_graph_in_a_run",
                                                    "per_layer_ms", "per_layer_round_ms", "speedup_vs_1gpu", "one_gpu_ms",
                                                    "max_abs_vs_oracle", "nccl_ms", "nccl_per_layer_ms",
                                                    "peer_path_matches_nccl_path", "decode_kernel_ms", "config", "oracle",
