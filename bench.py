@@ -579,7 +579,7 @@ def measure_prefill(env, args, *, repeats: int) -> dict:
     stream.synchronize()
     cache.check()
     assert cache.last_kernel() == llaisys.Kernel.PREFILL_TC, "the chunk attention did not run on the tcgen05 kernel"
-    steps = layers
+    steps = 2 * layers  # per graph: a run of launches over the rotating layer pools
     if args.quick:  # profiler runs: eager launches only
         for i in range(steps):
             do_step(i)
