@@ -362,8 +362,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm)
                 // on one slot would wait for consecutive phases of the same barrier, and a parity wait cannot tell
                 // phase k + 1 from phase k - 1.
                 if (!waited && sg.j0 + min(base + kIssueLanes, sg.n) > guard_page) {
-                    grid_dependency_wait(); // this round reaches the sequence's newest rows: they may come from the
-                    waited = true;          // previous kernel on the stream (everything before it was there long ago)
+                    // these copies reach the sequence's newest rows, which may come from the previous kernel on the
+                    // stream (everything before it was there long ago)
+                    grid_dependency_wait();
+                    waited = true;
                 }
                 const bool active = lane < kIssueLanes && base + lane < sg.n;
                 int ok = 1;

@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     {
         // the sequence that holds block piece_begin, by a block-wide scan over kThreads sequences at a time
         __syncthreads();
-        int before = 0; // blocks of the sequences in front of this round's
+        int before = 0; // blocks of the sequences in front of this pass's
         for (int a0 = 0; a0 < p.n_seqs; a0 += kThreads) {
             const int a = a0 + tid;
             const int w_a = a < p.n_seqs ? seq_blocks(p, seq_geom(p, a)) : 0;
