@@ -106,9 +106,10 @@ __global__ void embedding_kernel(unsigned char *__restrict__ out, const int64_t 
 template <typename T, int VEC, int PER_THREAD>
 __global__ void rms_norm_vec_kernel(T *__restrict__ out, const T *__restrict__ in, const T *__restrict__ w, float eps, size_t d) {
     // launched programmatically: the grid may be scheduled under the tail of the kernel before it, touches nothing
-    // until that kernel has completed, and lets its own successor be scheduled the same way
-    grid_launch_dependents();
+    // until that kernel has completed, and only then lets its own successor be scheduled the same way (so whatever
+    // starts early behind this grid can rely on everything before this grid's predecessor being complete)
     grid_dependency_wait();
+    grid_launch_dependents();
     struct alignas(sizeof(T) * VEC) P {
         T v[VEC];
     };
@@ -229,8 +230,8 @@ __global__ void bias_add_kernel(T *__restrict__ out, const T *__restrict__ bias,
 
 template <typename T, int VEC>
 __global__ void swiglu_packed_kernel(T *__restrict__ out, const T *__restrict__ gu, size_t rows, size_t di) {
-    grid_launch_dependents(); // (programmatic launch, as rms_norm_vec_kernel)
-    grid_dependency_wait();
+    grid_dependency_wait(); // (programmatic launch, as rms_norm_vec_kernel)
+    grid_launch_dependents();
     struct alignas(sizeof(T) * VEC) P {
         T v[VEC];
     };
