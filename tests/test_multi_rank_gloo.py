@@ -94,3 +94,68 @@ def test_two_ranks_sequence_sharding_and_kv_range_split():
         assert all(worst <= 2e-2 for _, worst in gathered)
         assert r0[1] == r1[0] and r0[0] == 0
         assert err0 <= 8e-3 and err1 <= 8e-3  # one bf16 ulp of the merged output
+
+
+def _worker_missing_rank(rank: int, world: int, ports, results, rank0_gave_up):
+    """Step 1 normal; in step 2 rank 1 leaves its collective out (a host-side failure: nothing faults, nobody exits);
+    rank 0's all-gather ends with an error after the group's short timeout; both ranks then tear the group down, build a
+    new one and step 3 is normal again."""
+    import datetime
+
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(78)
+    total = 16 * 21 + 3
+    qq = workloads.randn((1, 12, 128), torch.bfloat16, g)
+    kk = workloads.randn((total, 2, 128), torch.bfloat16, g)
+    vv = workloads.randn((total, 2, 128), torch.bfloat16, g)
+    lo, hi = sharding.kv_range(total, world, rank)
+    cache = llaisys.PagedKVCache(64, 2, 128, dtype=llaisys.DataType.BF16, max_seqs=1)
+    s = cache.add_seq()
+    cache.reserve(s, hi - lo)
+    helpers.append_all(cache, 0, [s], [kk[lo:hi]], [vv[lo:hi]], CPU)
+    full = attention.self_attention_f64(qq, kk, vv, 0.09)
+
+    def step():
+        merged = torch.empty_like(qq)
+        sharding.split_decode(cache, 0, merged, qq, [s], [hi - lo], 12, 0.09)
+        return helpers.max_abs(merged, full)
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(ports[0]))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    first = step()
+    failed = None
+    if rank == 0:
+        try:
+            step()  # rank 1 never joins this one
+        except Exception as e:  # the process group's timeout (the kind of exception is the backend's)
+            failed = type(e).__name__
+        rank0_gave_up.set()
+    else:
+        rank0_gave_up.wait(timeout=60)  # learns on the host that the step is lost, between steps
+    try:
+        dist.destroy_process_group()
+    except Exception:
+        pass  # a group whose collective timed out may refuse an orderly shutdown
+    os.environ["MASTER_PORT"] = str(ports[1])
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
+    try:
+        third = step()
+    finally:
+        dist.destroy_process_group()
+    results[rank] = (first, failed, third)
+
+
+@pytest.mark.timeout(300)
+def test_a_rank_that_leaves_a_step_out_ends_the_others_collective_with_an_error():
+    """Failure detection on the collective path, without a GPU: the process group's timeout is the bounded wait."""
+    world = 2
+    with mp.Manager() as manager:
+        results = manager.dict()
+        gave_up = manager.Event()
+        mp.spawn(_worker_missing_rank, args=(world, (free_port(), free_port()), results, gave_up), nprocs=world, join=True)
+        assert set(results.keys()) == {0, 1}
+        for rank in (0, 1):
+            first, _, third = results[rank]
+            assert first <= 8e-3 and third <= 8e-3, (rank, first, third)
+        assert results[0][1] is not None, "rank 0's collective should have ended with an error"
+        assert results[1][1] is None
