@@ -21,7 +21,7 @@ def free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, results):
+def _worker(rank: int, world: int, port: int, results, total: int = 16 * 150 + 5, n_layers: int = 3):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
     import llaisys_b200 as llaisys
@@ -37,15 +37,14 @@ def _worker(rank: int, world: int, port: int, results):
         stream = llaisys.context_stream()
         ext = torch.cuda.ExternalStream(stream)
         g = torch.Generator().manual_seed(91)
-        n_layers, nh, nkvh, d = 3, 12, 2, 128
-        total = 16 * 150 + 5  # the last rank's slice ends inside a page
+        nh, nkvh, d = 12, 2, 128  # (default total: the last rank's slice ends inside a page)
         lo, hi = sharding.kv_range(total, world, rank)
         local = hi - lo
         ks = [workloads.randn((total, nkvh, d), torch.bfloat16, g) for _ in range(n_layers)]
         vs = [workloads.randn((total, nkvh, d), torch.bfloat16, g) for _ in range(n_layers)]
         # each "layer" is a sequence of one cache layer, as the long-context benchmark lays them out
-        cache = llaisys.PagedKVCache(1024, nkvh, d, dtype=llaisys.DataType.BF16, device=nvidia, device_id=rank,
-                                     max_seqs=n_layers, max_pages_per_seq=-(-local // 16) + 1)
+        cache = llaisys.PagedKVCache(max(1024, n_layers * (-(-local // 16) + 1)), nkvh, d, dtype=llaisys.DataType.BF16,
+                                     device=nvidia, device_id=rank, max_seqs=n_layers, max_pages_per_seq=-(-local // 16) + 1)
         seqs = []
         for layer in range(n_layers):
             s = cache.add_seq()
@@ -66,7 +65,12 @@ def _worker(rank: int, world: int, port: int, results):
             ex.check(stream)
             cache.check()
             for layer in range(n_layers):
-                full = attention.self_attention_f64(q[layer:layer + 1], ks[layer], vs[layer], 0.09)
+                if total > 20000:  # a full-length layer: the chunked float64 oracle, on the first and the last step only
+                    if step not in (0, 4):
+                        continue
+                    full = attention.decode_attention_f64_chunked(q[layer:layer + 1], ks[layer], vs[layer], 0.09)
+                else:
+                    full = attention.self_attention_f64(q[layer:layer + 1], ks[layer], vs[layer], 0.09)
                 worst = max(worst, helpers.max_abs(out[layer:layer + 1].cpu(), full))
             outs.append(out.cpu())
         # the same step as a CUDA graph, replayed: the step number lives on the device, so replays keep alternating
@@ -103,6 +107,24 @@ def test_split_decode_through_peer_memory():
     with mp.Manager() as manager:
         results = manager.dict()
         mp.spawn(_worker, args=(world, free_port(), results), nprocs=world, join=True)
+        assert len(results) == world
+        for rank in range(world):
+            worst, same, _ = results[rank]
+            assert worst <= 8e-3, (rank, worst)
+            assert same, f"rank {rank}: a graph replay differs from the eager step"
+
+
+@pytest.mark.gpu
+@pytest.mark.timeout(900)
+def test_split_decode_of_one_full_131072_token_layer_through_peer_memory():
+    """One layer of the long-context configuration at its full length, split over the GPUs of the box (up to 4): the
+    merged rows against the float64 oracle over all 131072 tokens, and graph replays bit for bit."""
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs two GPUs")
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_worker, args=(world, free_port(), results, 131072, 1), nprocs=world, join=True)
         assert len(results) == world
         for rank in range(world):
             worst, same, _ = results[rank]
