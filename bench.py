@@ -452,6 +452,28 @@ def measure_decode(env, workload: str, args, *, steps: int, repeats: int, with_e
         sampler.__exit__()
     cache.check()
 
+    # ---- the no-allocation entry point (the caller's pool, static scratch, the cp.async decode kernel): decode only, plain
+    #      launches queued back to back, one event pair around the lot (no claim is made for it about graph capture) -------
+    no_alloc_ms = None
+    if B * NKVH <= 512:
+        n_na = max(20, min(steps, 100))
+
+        def no_alloc(i):
+            llaisys.decode_no_alloc(out, q, cache.pool_ptr(i % layers), cache.block_table_ptr(), cache.max_pages_per_seq,
+                                    POOL_PAGES, seq_ids_dev, kv_lens_dev, B, max_kv, NH, NKVH, scale, device_id=local_rank,
+                                    stream=cs)
+
+        for i in range(3):
+            no_alloc(i)
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(n_na):
+            no_alloc(i)
+        e1.record(stream)
+        stream.synchronize()
+        no_alloc_ms = e0.elapsed_time(e1) / n_na
+
     # ---- end to end through the host-buffer call: host buffers, copies inside the timed region ---------------------
     e2e = None
     if with_e2e:
@@ -506,7 +528,8 @@ def measure_decode(env, workload: str, args, *, steps: int, repeats: int, with_e
                      "kernel_ms_without_launch_overlap": med[1] / steps,
                      "frac_without_launch_overlap": bytes_step / (med[1] / steps * 1e-3) / 1e9 / hbm,
                      "decode_only_kernel_ms": med[2] / steps, "append_only_kernel_ms": med[3] / steps,
-                     "two_launch_step_ms": med[4] / steps},
+                     "two_launch_step_ms": med[4] / steps,
+                     "no_alloc_entry_decode_only_ms": no_alloc_ms},  # llaisysPagedAttentionDecodeNoAlloc, plain launches
         "e2e": e2e,
         "gpu_launches": steps * repeats,
         "timing": f"CUDA graph of {steps} steps, {repeats} replays, event pair per replay, median (min/max beside it)",
